@@ -1,0 +1,443 @@
+/*
+ * schedforge_b200 — C ABI of the B200 (sm_100a) decoder-layer executor.
+ *
+ * Two groups of entry points live in libschedforge_b200.so:
+ *
+ *   1. Kernel entry points (`sfb_k_*`): one call = one (or a fixed short chain of) CUDA
+ *      kernel launch(es) on the caller's stream.  All pointers are DEVICE pointers, shapes
+ *      are int32 (the reference uses `int`), nothing is allocated, nothing synchronises.
+ *      Each replaces one CPU function of the reference's decoder hot path; the reference
+ *      location is cited beside each declaration (paths are relative to the reference
+ *      repository root).
+ *
+ *   2. Plan entry points (`sfb_decoder_*`, `sfb_attention_*`, `sfb_paged_*`, `sfb_moe_*`,
+ *      `sfb_import_*`): the reference's public C++ API for this path restated as a C ABI
+ *      with HOST buffers (float32, the reference's `std::vector<float>` contents).  They
+ *      are thin wrappers around the C++20 host runtime in this library, which owns device
+ *      memory, builds the plan once and runs the kernels of group 1.
+ *
+ * Every function returns an `sfb_status`.  SFB_INVALID_ARGUMENT corresponds to the
+ * reference throwing std::invalid_argument for the same condition, SFB_RUNTIME_ERROR to
+ * std::runtime_error.  `sfb_last_error()` returns the message of the calling thread's
+ * last failure.  The library has no CPU fallback: without a CUDA device every compute
+ * entry point fails with SFB_CUDA_ERROR.
+ *
+ * The only C ABIs in the reference are its JIT/AOT matmul symbol
+ * `schedforge_matmul_v1(A, B, bias, residual, C, M, N, K)` (src/llvm_backend.cpp:39-40,
+ * src/aot_runtime.cpp:23-24) and `schedforge_fused_attention(q, k, v, out, row_begin,
+ * row_end)` (src/attention_llvm_backend.cpp:36-37): raw pointers plus integer extents.
+ * This header keeps that convention and adds a status return.
+ */
+#ifndef SCHEDFORGE_B200_H
+#define SCHEDFORGE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum sfb_status {
+    SFB_OK = 0,
+    SFB_INVALID_ARGUMENT = -1, /* reference: std::invalid_argument */
+    SFB_RUNTIME_ERROR = -2,    /* reference: std::runtime_error    */
+    SFB_CUDA_ERROR = -3,       /* a CUDA runtime/driver call failed, or no device */
+    SFB_UNSUPPORTED = -4,      /* shape/dtype outside what the kernels cover */
+    SFB_DEVICE_TIMEOUT = -5    /* a bounded device-side wait gave up (status word set) */
+} sfb_status;
+
+typedef enum sfb_dtype { SFB_F32 = 0, SFB_BF16 = 1 } sfb_dtype;
+
+typedef void* sfb_stream; /* cudaStream_t */
+
+const char* sfb_last_error(void);
+const char* sfb_version(void);
+/* Number of kernels this library has launched in this process (for launch accounting). */
+uint64_t sfb_launch_count(void);
+/* Reads and clears the device status word that bounded waits set when they give up.
+ * 0 = no device-side wait timed out since the last call. */
+sfb_status sfb_device_status(uint32_t* status_word);
+
+/* ======================================================================================
+ * 1. Kernel entry points (device pointers)
+ * ====================================================================================== */
+
+/* y[r,:] = x[r,:] * (1/sqrt(mean(x[r,:]^2) + eps)) * weight[:].
+ * f32: sum of squares in double, (x*inv)*w order.  weight is always float32.
+ * Replaces rms_norm, src/decoder_compiler.cpp:41-62. */
+sfb_status sfb_k_rms_norm(const void* x, const float* weight, void* y, int rows, int width,
+                          float epsilon, sfb_dtype dtype, sfb_stream stream);
+
+/* Elementwise z = x + y.  Replaces add, src/decoder_compiler.cpp:176-181. */
+sfb_status sfb_k_add(const void* x, const void* y, void* z, int64_t count, sfb_dtype dtype,
+                     sfb_stream stream);
+
+/* out[r,j] = silu(gate_up[r,j]) * gate_up[r, I+j], gate = first I columns.
+ * Replaces swiglu, src/decoder_compiler.cpp:183-194. */
+sfb_status sfb_k_swiglu(const void* gate_up, void* out, int rows, int intermediate,
+                        sfb_dtype dtype, sfb_stream stream);
+
+/* float32 <-> bfloat16 (round to nearest even, as convert_to_bf16, src/compiler.cpp:34-43). */
+sfb_status sfb_k_convert(const void* src, sfb_dtype src_dtype, void* dst, sfb_dtype dst_dtype,
+                         int64_t count, sfb_stream stream);
+
+/* C[m,n] = A[m,k] . B[k,n], float32 row-major, one FMA chain per output over ascending k:
+ * the rounding sequence of the reference's native GEMM (execute -> register_kernel_16/8,
+ * src/runtime.cpp:581-626, 278-370), so results are bit-identical to it. */
+sfb_status sfb_k_gemm_f32(const float* a, const float* b, float* c, int m, int n, int k,
+                          sfb_stream stream);
+
+typedef enum sfb_gemm_epilogue {
+    SFB_EPI_STORE = 0,      /* out[m,n] = acc                                              */
+    SFB_EPI_RESIDUAL = 1,   /* out[m,n] = acc + residual[m,n]                               */
+    SFB_EPI_SWIGLU = 2,     /* out[m,n/2]: weight rows come in blocks of 2*swiglu_block:    */
+                            /* swiglu_block gate rows then swiglu_block up rows;            */
+                            /* out = silu(gate) * up                                        */
+    SFB_EPI_ROPE_SPLIT = 3  /* n = hidden + 2*kv: rotary on Q,K and scatter to head-major   */
+} sfb_gemm_epilogue;
+
+typedef enum sfb_gemm_backend {
+    SFB_GEMM_AUTO = 0,
+    SFB_GEMM_SIMT = 1,     /* CUDA-core tiles, any shape                                   */
+    SFB_GEMM_TCGEN05 = 2   /* tcgen05.mma + TMEM + TMA, needs k % 8 == 0                   */
+} sfb_gemm_backend;
+
+/* bf16 GEMM with fp32 accumulation.  A is [m,k] row-major bf16.  The weight is passed
+ * TRANSPOSED: bt is [n,k] row-major bf16 (k contiguous), i.e. y = x . W with W = bt^T.
+ * Grouped mode (group_offsets != NULL): rows [group_offsets[g], group_offsets[g+1]) of A
+ * use weight slab g (bt + g*n*k); groups = number of slabs.  Replaces the four decoder
+ * GEMMs (execute calls at src/decoder_compiler.cpp:230,252,272,276) and the variable-M
+ * expert GEMMs (execute_loop_kernel / compute_task, src/moe_compiler.cpp:64-155). */
+typedef struct sfb_gemm_args {
+    const void* a;
+    const void* bt;
+    void* out;              /* bf16 unless out_f32 != 0                                    */
+    int m, n, k;
+    int epilogue;           /* sfb_gemm_epilogue                                           */
+    int backend;            /* sfb_gemm_backend                                            */
+    int out_f32;
+    const void* residual;   /* SFB_EPI_RESIDUAL: [m,n] bf16                                */
+    int swiglu_block;       /* SFB_EPI_SWIGLU: gate/up interleave block in weight rows     */
+    /* SFB_EPI_ROPE_SPLIT */
+    void* q;                /* [batch, q_heads, seq, head_dim] bf16                        */
+    void* key;              /* [batch, kv_heads, seq, head_dim]                            */
+    void* value;            /* [batch, kv_heads, seq, head_dim]                            */
+    const float* rope_cos;  /* [seq, head_dim/2]                                           */
+    const float* rope_sin;
+    int batch, seq, q_heads, kv_heads, head_dim;
+    /* grouped mode */
+    const int* group_offsets; /* device int32[groups+1], NULL for a dense GEMM             */
+    int groups;
+    void* tile_table;       /* grouped tcgen05: device scratch, int32[4*(m/128 + groups + 1)] */
+} sfb_gemm_args;
+
+sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
+
+/* cos/sin tables for interleaved-pair rotary embedding, computed on the HOST with the
+ * same powf/cosf/sinf calls as apply_rope, src/decoder_compiler.cpp:96-114:
+ * freq = powf(theta, -float(d)/float(dim)), angle = float(t)*freq for even d.
+ * cos_out/sin_out are HOST float32 [seq, dim/2]. */
+sfb_status sfb_rope_table(int seq, int head_dim, float theta, float* cos_out, float* sin_out);
+
+/* fused[T, hidden+2*kv] -> Q [B,Hq,S,D], K,V [B,Hkv,S,D] with rotary on Q and K; token
+ * positions restart at 0 for every batch element.  Replaces split_qkv + apply_rope,
+ * src/decoder_compiler.cpp:96-148. */
+sfb_status sfb_k_rope_split(const void* fused, void* q, void* key, void* value,
+                            const float* rope_cos, const float* rope_sin, int batch, int seq,
+                            int q_heads, int kv_heads, int head_dim, sfb_dtype dtype,
+                            sfb_stream stream);
+
+/* Exact causal/non-causal GQA softmax attention, online softmax over KV tiles.
+ * q [B,Hq,Sq,D], key [B,Hkv,Sk,D], value [B,Hkv,Sk,Dv].  Key j is visible to query i iff
+ * !causal or j <= Sk - Sq + i; kv_head = head*Hkv/Hq; scale 0 means 1/sqrt(D).
+ * out is [B,Hq,Sq,Dv] (token_major == 0) or [B*Sq, Hq*Dv] (token_major != 0, the layout
+ * merge_attention produces, src/decoder_compiler.cpp:150-174).
+ * Replaces execute_attention -> execute_streaming (IO-aware branch),
+ * src/attention_compiler.cpp:879-885, 286-376. */
+typedef struct sfb_attention_args {
+    const void* q;
+    const void* key;
+    const void* value;
+    void* out;
+    int batch, q_heads, kv_heads, seq_q, seq_kv, head_dim, head_dim_value;
+    int causal;
+    float scale;
+    int token_major;
+    int dtype;    /* sfb_dtype of q/key/value/out */
+    int backend;  /* 0 auto, 1 SIMT, 2 tcgen05 */
+} sfb_attention_args;
+
+sfb_status sfb_k_attention_prefill(const sfb_attention_args* args, sfb_stream stream);
+
+/* Split-KV decode over a paged KV cache, one new query token per sequence.
+ * Pool layout: k_pool/v_pool [num_blocks][kv_heads][block_tokens][dim] (the reference's
+ * [page][batch][kv_head][page_tokens][dim], src/next_milestones.cpp:29-33, with the
+ * per-sequence caches of a batch folded into one pool: batch == 1 per page).
+ * block_table[b*max_blocks + i] = physical block of logical block i of sequence b;
+ * context_len[b] = live tokens.  Each (sequence, kv head, split) block writes a partial
+ * (max, sum, numerator) into `partials`; a second kernel merges the splits with the
+ * log-sum-exp rule (merge_online, src/attention_compiler.cpp:132-145; empty splits are
+ * skipped).  Replaces execute_decode_attention / execute_paged_decode_attention,
+ * src/attention_compiler.cpp:968-1007, src/next_milestones.cpp:583-609, 137-184.
+ * `partials` needs sfb_attention_decode_workspace() bytes.  splits <= 0 picks a value. */
+typedef struct sfb_decode_args {
+    const void* q;          /* [batch, q_heads, head_dim]                                  */
+    const void* k_pool;
+    const void* v_pool;
+    const int* block_table; /* int32 [batch, max_blocks]                                   */
+    const int* context_len; /* int32 [batch]                                               */
+    void* out;              /* [batch, q_heads, head_dim_value]                            */
+    void* partials;
+    int batch, q_heads, kv_heads, head_dim, head_dim_value;
+    int block_tokens, max_blocks, num_blocks;
+    int max_context;        /* upper bound of context_len, sizes the split count           */
+    int splits;
+    float scale;
+    int dtype;
+} sfb_decode_args;
+
+size_t sfb_attention_decode_workspace(int batch, int q_heads, int head_dim_value, int splits);
+int sfb_attention_decode_default_splits(int batch, int kv_heads, int max_context);
+sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* args, sfb_stream stream);
+
+/* Writes `tokens` new tokens per sequence into the paged pool.  new_k/new_v are
+ * [batch, kv_heads, tokens, dim]; the token at logical position start_len[b] + t goes to
+ * block block_table[b][pos / block_tokens], slot pos % block_tokens.
+ * Replaces the copy loop of append_paged_kv, src/next_milestones.cpp:502-522. */
+sfb_status sfb_k_paged_kv_append(const void* new_k, const void* new_v, void* k_pool, void* v_pool,
+                                 const int* block_table, const int* start_len, int batch,
+                                 int kv_heads, int tokens, int head_dim, int head_dim_value,
+                                 int block_tokens, int max_blocks, sfb_dtype dtype,
+                                 sfb_stream stream);
+
+/* Paged pool -> contiguous [batch, kv_heads, length, dim] (all sequences `length` long).
+ * Replaces gather_paged_kv, src/next_milestones.cpp:552-581. */
+sfb_status sfb_k_paged_kv_gather(const void* k_pool, const void* v_pool, void* keys, void* values,
+                                 const int* block_table, int batch, int kv_heads, int length,
+                                 int head_dim, int head_dim_value, int block_tokens,
+                                 int max_blocks, sfb_dtype dtype, sfb_stream stream);
+
+/* Router: logits[t,e] = sum_f x[t,f]*router[f,e] accumulated sequentially in float32
+ * (multiply rounded, then add rounded, f ascending) + optional bias[e]; softmax
+ * numerators p = exp(logit - max); top-k by descending p (ties: lower expert id);
+ * weights (p/den)/sum_selected(p/den); per-expert histogram.  router is float32 [H,E].
+ * counts must be zeroed by the caller's stream before the call (the entry point does it).
+ * Replaces route_topk, src/moe_compiler.cpp:412-455.  Limits: experts <= 64, top_k <= 8. */
+sfb_status sfb_k_moe_route(const void* x, sfb_dtype x_dtype, const float* router,
+                           const float* bias, int tokens, int hidden, int experts, int top_k,
+                           int* expert_ids, float* expert_weights, int* counts,
+                           sfb_stream stream);
+
+/* Exclusive prefix sum of counts -> offsets[E+1], then the stable counting-sort scatter in
+ * (token, slot) order: dest = offsets[e] + rank of the assignment among earlier
+ * assignments to e.  Writes values[dest,:] = x[token,:], token_ids, route_slots,
+ * routing_weights, and dest_of[token*k+slot] = dest.  Deterministic (no atomics).
+ * Replaces the prefix loop and dispatch_tokens, src/moe_compiler.cpp:496-528.
+ * scratch: device int32[(ceil(tokens*top_k/1024) + 1) * experts]. */
+sfb_status sfb_k_moe_dispatch(const void* x, sfb_dtype dtype, const int* expert_ids,
+                              const float* expert_weights, const int* counts, int tokens,
+                              int hidden, int experts, int top_k, void* values, int* offsets,
+                              int* token_ids, int* route_slots, float* routing_weights,
+                              int* dest_of, int* scratch, sfb_stream stream);
+size_t sfb_moe_dispatch_scratch_bytes(int tokens, int experts, int top_k);
+
+/* out[t,:] = (residual ? residual[t,:] : 0) + sum over the token's assignments, in
+ * ascending dispatched position (= the reference's expert-major accumulation order), of
+ * routing_weights[pos] * y[pos,:].
+ * Replaces the weighted combine, src/moe_compiler.cpp:219-226 (+ the FFN residual add,
+ * src/decoder_compiler.cpp:285). */
+sfb_status sfb_k_moe_combine(const void* y, const int* dest_of, const float* routing_weights,
+                             const void* residual, void* out, int tokens, int hidden, int top_k,
+                             sfb_dtype dtype, sfb_stream stream);
+
+/* ======================================================================================
+ * 2. Plan entry points (host float32 buffers; mirror of the reference's C++ API)
+ * ====================================================================================== */
+
+/* DecoderConfig, include/schedforge/decoder_compiler.h:17-32. */
+typedef struct sfb_decoder_config {
+    int batch, sequence, hidden, intermediate, query_heads, kv_heads, head_dim;
+    float rms_epsilon, rope_theta;
+    int causal;
+    int ffn_moe;           /* DecoderFFNKind: 0 Dense, 1 MoE */
+    int experts, top_k;
+    int context_sequence;  /* > 0: decode over cached K/V of this length */
+} sfb_decoder_config;
+
+/* DecoderData, include/schedforge/decoder_compiler.h:34-49 (+ MoeData, moe_compiler.h:79-85).
+ * All weights are [in, out] row-major float32, y = x . W.  Unused members may be NULL.
+ * router_bias has no counterpart in the reference (its router has no bias term). */
+typedef struct sfb_decoder_data {
+    const float* rms1_weight;
+    const float* query_weight;
+    const float* key_weight;
+    const float* value_weight;
+    const float* output_weight;
+    const float* rms2_weight;
+    const float* gate_weight;
+    const float* up_weight;
+    const float* down_weight;
+    const float* router_weight; /* [H, E]   */
+    const float* router_bias;   /* [E]      */
+    const float* w1;            /* [E, H, I] */
+    const float* w3;            /* [E, H, I] */
+    const float* w2;            /* [E, I, H] */
+    const float* cached_key;    /* [B, Hkv, context, D] */
+    const float* cached_value;
+} sfb_decoder_data;
+
+/* DecoderCompileOptions + DecoderPlanPolicy, include/schedforge/decoder_compiler.h:55-65,132-138,
+ * reduced to what applies to a GPU plan, plus the sharding this build adds. */
+typedef struct sfb_compile_options {
+    int dtype;            /* sfb_dtype: SFB_F32 = exact-order fp32 path, SFB_BF16 = tensor cores */
+    int token_major_attention; /* DecoderIntermediateLayout::TokenMajor (1) or HeadMajor (0) */
+    int fuse_epilogues;   /* bf16: RoPE/residual/SwiGLU inside the GEMM epilogues (1) or as
+                             separate kernels (0, the "materialize" policy) */
+    int gemm_backend;     /* sfb_gemm_backend */
+    int attention_backend;
+    int page_tokens;      /* decode: KV block size of the paged cache (0 -> 16) */
+    int tp_rank, tp_size; /* tensor parallel shard of this plan (heads / FFN columns) */
+    int seed_block_table; /* decode: != 0 permutes the physical block order with this seed */
+} sfb_compile_options;
+
+/* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */
+typedef struct sfb_decoder_result {
+    double milliseconds;
+    double attention_milliseconds;
+    double projection_milliseconds;
+    double norm_rope_milliseconds;
+    double ffn_milliseconds;
+    double residual_milliseconds;
+    double h2d_milliseconds;
+    double d2h_milliseconds;
+    double tokens_per_second;
+    uint64_t kernel_launches;
+} sfb_decoder_result;
+
+/* StableHLOImporter::importText + DecoderFusionPass::run, src/graph_compiler.cpp:1129-1198,
+ * src/decoder_compiler.cpp:380-410. */
+typedef struct sfb_graph_summary {
+    int operations, values, inputs, matmuls;
+    int fused_qkv, fused_gate_up, fused_rope;
+} sfb_graph_summary;
+
+sfb_status sfb_import_stablehlo(const char* text, sfb_graph_summary* summary);
+/* graph dump ("graph @model { ... }") of the imported text into buffer. */
+sfb_status sfb_import_stablehlo_dump(const char* text, char* buffer, size_t capacity);
+
+typedef struct sfb_decoder_plan sfb_decoder_plan;
+
+/* DecoderCompiler::compile, src/decoder_compiler.cpp:518-620: validates the configuration,
+ * runs the fusion pass on the imported graph (NULL/empty text = the canonical graph) and
+ * fails with SFB_INVALID_ARGUMENT ("decoder graph is missing required fusion patterns") when
+ * a pattern is missing, packs Wq|Wk|Wv and Wgate|Wup, uploads every weight once and lays
+ * all activations out in one device workspace. */
+sfb_status sfb_decoder_compile(const sfb_decoder_config* config, const sfb_decoder_data* data,
+                               const char* stablehlo_text, const sfb_compile_options* options,
+                               sfb_decoder_plan** plan);
+void sfb_decoder_destroy(sfb_decoder_plan* plan);
+
+/* execute_decoder_layer, src/decoder_compiler.cpp:675-692, one repetition: copies
+ * input [T,H] float32 from host, runs the layer, copies output [T,H] float32 back.
+ * routing trace (optional, MoE): expert_ids/expert_weights [T*k] and counts [E] replace the
+ * router, like DecoderData::routing_trace (include/schedforge/decoder_compiler.h:48). */
+sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float* output,
+                               const int* trace_expert_ids, const float* trace_expert_weights,
+                               const int* trace_counts, sfb_decoder_result* result);
+
+/* The same layer with the input already resident (last sfb_decoder_execute /
+ * sfb_decoder_upload_input) and the output left on the device: kernels only. */
+sfb_status sfb_decoder_upload_input(sfb_decoder_plan* plan, const float* input);
+sfb_status sfb_decoder_execute_resident(sfb_decoder_plan* plan, sfb_stream stream);
+sfb_status sfb_decoder_download_output(sfb_decoder_plan* plan, float* output);
+
+/* Tensor-parallel hook: called on the plan's stream after the O projection and after the
+ * Down projection partial sums are in `buffer` (`count` elements of `dtype`); the callee
+ * must all-reduce (sum) in place on `stream`.  NULL = single shard. */
+typedef void (*sfb_allreduce_fn)(void* user, void* buffer, int64_t count, int dtype,
+                                 sfb_stream stream);
+sfb_status sfb_decoder_set_allreduce(sfb_decoder_plan* plan, sfb_allreduce_fn fn, void* user);
+
+/* Introspection: text dump in the reference's `sfe.decoder_executable` layout
+ * (DecoderExecutablePlan::dump, src/decoder_compiler.cpp:694-717), workspace bytes, the
+ * device pointer of a named intermediate ("normalized2", "attention_residual", "output",
+ * ...) and its element count, for tests that feed the oracle the very same tensor. */
+sfb_status sfb_decoder_dump(const sfb_decoder_plan* plan, char* buffer, size_t capacity);
+size_t sfb_decoder_workspace_bytes(const sfb_decoder_plan* plan);
+sfb_status sfb_decoder_read_tensor(sfb_decoder_plan* plan, const char* name, float* host_out,
+                                   int64_t capacity, int64_t* count);
+sfb_stream sfb_decoder_stream(sfb_decoder_plan* plan);
+
+/* AttentionConfig, include/schedforge/attention_compiler.h:23-33. */
+typedef struct sfb_attention_config {
+    int batch, query_heads, kv_heads, sequence_query, sequence_kv, head_dim, head_dim_value;
+    int causal;
+    float scale;
+} sfb_attention_config;
+
+/* execute_attention, src/attention_compiler.cpp:879-885 (host q/k/v/out, float32). */
+sfb_status sfb_attention_execute(const sfb_attention_config* config, const float* q,
+                                 const float* key, const float* value, float* out, int dtype,
+                                 int backend, double* milliseconds);
+
+/* make_kv_cache + append_kv + execute_decode_attention (contiguous cache),
+ * src/attention_compiler.cpp:923-1007: keys/values [B,Hkv,length,D]; guard
+ * 0 < length <= config.sequence_kv else SFB_INVALID_ARGUMENT. */
+sfb_status sfb_attention_decode(const sfb_attention_config* config, const float* q,
+                                const float* keys, const float* values, int length, float* out,
+                                int dtype, double* milliseconds);
+
+/* PagedKVCache, include/schedforge/next_milestones.h:15-43, kept on the device.  One page
+ * table and one length for the whole batch, pages handed out from the BACK of the free
+ * list, like the reference. */
+typedef struct sfb_paged_kv sfb_paged_kv;
+sfb_status sfb_paged_create(int batch, int kv_heads, int head_dim, int head_dim_value,
+                            int page_tokens, int capacity, int dtype, sfb_paged_kv** cache);
+void sfb_paged_destroy(sfb_paged_kv* cache);
+sfb_status sfb_paged_set_free_pages(sfb_paged_kv* cache, const int* pages, int count);
+sfb_status sfb_paged_append(sfb_paged_kv* cache, const float* keys, const float* values, int tokens);
+sfb_status sfb_paged_truncate(sfb_paged_kv* cache, int new_length);
+sfb_status sfb_paged_release(sfb_paged_kv* cache, const int* pages, int count);
+/* info[0..3] = length, pages in table, free pages, total pages. */
+sfb_status sfb_paged_info(const sfb_paged_kv* cache, int* info, int* page_table, int table_capacity,
+                          int* free_pages, int free_capacity);
+sfb_status sfb_paged_gather(sfb_paged_kv* cache, float* keys, float* values);
+/* execute_paged_decode_attention, src/next_milestones.cpp:583-609 (guards :98-120). */
+sfb_status sfb_paged_decode(sfb_paged_kv* cache, const sfb_attention_config* config,
+                            const float* q, float* out, double* milliseconds);
+
+/* MoeConfig, include/schedforge/moe_compiler.h:71-77. */
+typedef struct sfb_moe_config {
+    int tokens, hidden, intermediate, experts, top_k;
+} sfb_moe_config;
+
+/* route_topk, src/moe_compiler.cpp:412-455 (host buffers; input dtype selects whether the
+ * activations are rounded to bf16 before routing). */
+sfb_status sfb_moe_route_topk(const sfb_moe_config* config, const float* input, int tokens,
+                              const float* router_weight, const float* router_bias, int dtype,
+                              int* expert_ids, float* expert_weights, int* counts);
+/* dispatch_tokens, src/moe_compiler.cpp:496-528. values may be NULL. */
+sfb_status sfb_moe_dispatch_tokens(const sfb_moe_config* config, const float* input, int tokens,
+                                   const int* expert_ids, const float* expert_weights,
+                                   const int* counts, int dtype, float* values, int* offsets,
+                                   int* token_ids, int* route_slots, float* routing_weights);
+/* execute_moe with a routing trace, src/moe_compiler.cpp:691-718 (guard: tokens <=
+ * config.tokens).  Weights w1,w3 [E,H,I], w2 [E,I,H]. */
+sfb_status sfb_moe_execute(const sfb_moe_config* config, const float* input, int tokens,
+                           const float* w1, const float* w3, const float* w2,
+                           const int* expert_ids, const float* expert_weights, const int* counts,
+                           int dtype, int gemm_backend, float* out, double* milliseconds);
+/* plan_moe_tasks, src/moe_compiler.cpp:530-558: rows (expert, begin, end, bucket). */
+sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, int split_threshold,
+                              int* tasks, int capacity, int* task_count);
+
+/* Column shard of a [rows, cols] row-major host matrix / row shard, used by the
+ * tensor-parallel plan build and exposed for tests: copies shard `rank` of `size`. */
+sfb_status sfb_shard_columns(const float* src, int rows, int cols, int rank, int size, float* dst);
+sfb_status sfb_shard_rows(const float* src, int rows, int cols, int rank, int size, float* dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCHEDFORGE_B200_H */

@@ -1,0 +1,158 @@
+"""ctypes view of libschedforge_b200.so: the structs and prototypes of
+include/schedforge_b200.h.  Loading never needs a GPU; the first compute call does."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libschedforge_b200.so")
+
+SFB_OK, SFB_INVALID_ARGUMENT, SFB_RUNTIME_ERROR, SFB_CUDA_ERROR, SFB_UNSUPPORTED, SFB_DEVICE_TIMEOUT = 0, -1, -2, -3, -4, -5
+F32, BF16 = 0, 1
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_ROPE_SPLIT = 0, 1, 2, 3
+GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
+
+vp = C.c_void_p
+f32p = C.POINTER(C.c_float)
+i32p = C.POINTER(C.c_int)
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [("a", vp), ("bt", vp), ("out", vp),
+                ("m", C.c_int), ("n", C.c_int), ("k", C.c_int),
+                ("epilogue", C.c_int), ("backend", C.c_int), ("out_f32", C.c_int),
+                ("residual", vp), ("swiglu_block", C.c_int),
+                ("q", vp), ("key", vp), ("value", vp), ("rope_cos", vp), ("rope_sin", vp),
+                ("batch", C.c_int), ("seq", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int),
+                ("head_dim", C.c_int),
+                ("group_offsets", vp), ("groups", C.c_int), ("tile_table", vp)]
+
+
+class AttentionArgs(C.Structure):
+    _fields_ = [("q", vp), ("key", vp), ("value", vp), ("out", vp)] + \
+               [(n, C.c_int) for n in ("batch", "q_heads", "kv_heads", "seq_q", "seq_kv", "head_dim",
+                                       "head_dim_value", "causal")] + \
+               [("scale", C.c_float), ("token_major", C.c_int), ("dtype", C.c_int), ("backend", C.c_int)]
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [("q", vp), ("k_pool", vp), ("v_pool", vp), ("block_table", vp), ("context_len", vp),
+                ("out", vp), ("partials", vp)] + \
+               [(n, C.c_int) for n in ("batch", "q_heads", "kv_heads", "head_dim", "head_dim_value",
+                                       "block_tokens", "max_blocks", "num_blocks", "max_context", "splits")] + \
+               [("scale", C.c_float), ("dtype", C.c_int)]
+
+
+class DecoderConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("batch", "sequence", "hidden", "intermediate", "query_heads",
+                                       "kv_heads", "head_dim")] + \
+               [("rms_epsilon", C.c_float), ("rope_theta", C.c_float)] + \
+               [(n, C.c_int) for n in ("causal", "ffn_moe", "experts", "top_k", "context_sequence")]
+
+
+DATA_FIELDS = ("rms1_weight", "query_weight", "key_weight", "value_weight", "output_weight",
+               "rms2_weight", "gate_weight", "up_weight", "down_weight", "router_weight",
+               "router_bias", "w1", "w3", "w2", "cached_key", "cached_value")
+
+
+class DecoderData(C.Structure):
+    _fields_ = [(n, f32p) for n in DATA_FIELDS]
+
+
+class CompileOptions(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("dtype", "token_major_attention", "fuse_epilogues",
+                                       "gemm_backend", "attention_backend", "page_tokens", "tp_rank",
+                                       "tp_size", "seed_block_table")]
+
+
+class DecoderResult(C.Structure):
+    _fields_ = [(n, C.c_double) for n in ("milliseconds", "attention_milliseconds",
+                                          "projection_milliseconds", "norm_rope_milliseconds",
+                                          "ffn_milliseconds", "residual_milliseconds",
+                                          "h2d_milliseconds", "d2h_milliseconds", "tokens_per_second")] + \
+               [("kernel_launches", C.c_uint64)]
+
+
+class GraphSummary(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("operations", "values", "inputs", "matmuls", "fused_qkv",
+                                       "fused_gate_up", "fused_rope")]
+
+
+class AttentionConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("batch", "query_heads", "kv_heads", "sequence_query",
+                                       "sequence_kv", "head_dim", "head_dim_value", "causal")] + \
+               [("scale", C.c_float)]
+
+
+class MoeConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("tokens", "hidden", "intermediate", "experts", "top_k")]
+
+
+ALLREDUCE_FN = C.CFUNCTYPE(None, vp, vp, C.c_int64, C.c_int, vp)
+
+# Every symbol include/schedforge_b200.h declares (checked by tests/test_abi.py).
+EXPORTS = (
+    "sfb_last_error sfb_version sfb_launch_count sfb_device_status "
+    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 "
+    "sfb_rope_table sfb_k_rope_split sfb_k_attention_prefill "
+    "sfb_attention_decode_workspace sfb_attention_decode_default_splits sfb_k_attention_decode_paged "
+    "sfb_k_paged_kv_append sfb_k_paged_kv_gather "
+    "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_combine "
+    "sfb_import_stablehlo sfb_import_stablehlo_dump "
+    "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_upload_input "
+    "sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce "
+    "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
+    "sfb_attention_execute sfb_attention_decode "
+    "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "
+    "sfb_paged_release sfb_paged_info sfb_paged_gather sfb_paged_decode "
+    "sfb_moe_route_topk sfb_moe_dispatch_tokens sfb_moe_execute sfb_moe_plan_tasks "
+    "sfb_shard_columns sfb_shard_rows"
+).split()
+
+
+class SfbError(RuntimeError):
+    """Raised for a non-zero sfb_status; `.status` holds the code."""
+
+    def __init__(self, status, message):
+        super().__init__(f"sfb status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class InvalidArgument(SfbError, ValueError):
+    """SFB_INVALID_ARGUMENT — where the reference throws std::invalid_argument."""
+
+
+_lib = None
+
+
+def load():
+    """Loads the library (building it first when the .so is missing and nvcc exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        from . import build
+        build.build()
+    lib = C.CDLL(LIB_PATH)
+    lib.sfb_last_error.restype = C.c_char_p
+    lib.sfb_version.restype = C.c_char_p
+    lib.sfb_launch_count.restype = C.c_uint64
+    for name in ("sfb_attention_decode_workspace", "sfb_moe_dispatch_scratch_bytes",
+                 "sfb_decoder_workspace_bytes"):
+        if hasattr(lib, name):
+            getattr(lib, name).restype = C.c_size_t
+    if hasattr(lib, "sfb_decoder_stream"):
+        lib.sfb_decoder_stream.restype = vp
+    _lib = lib
+    return lib
+
+
+def check(status):
+    if status == SFB_OK:
+        return
+    message = load().sfb_last_error().decode(errors="replace")
+    if status == SFB_INVALID_ARGUMENT:
+        raise InvalidArgument(status, message)
+    raise SfbError(status, message)

@@ -1,0 +1,172 @@
+"""GEMM parity: the fp32 exact-order kernel, the CUDA-core bf16 kernel and the tcgen05
+tensor-core kernel against the oracle, through sfb_k_gemm_f32 / sfb_k_gemm_bf16."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2  # max-abs relative, bf16 outputs with fp32 accumulation
+
+
+def gemm_bf16(sfb, dev, a, bt, epilogue=0, backend=0, out_f32=False, residual=None, swiglu_block=0,
+              rope=None, offsets=None, groups=0, n=None):
+    torch = dev.torch
+    m, k = a.shape
+    n = n if n is not None else bt.shape[-2]
+    g = sfb.GemmArgs()
+    g.a, g.bt = a.data_ptr(), bt.data_ptr()
+    g.m, g.n, g.k = m, n, k
+    g.epilogue, g.backend, g.out_f32 = epilogue, backend, int(out_f32)
+    out = None
+    keep = []
+    if epilogue == sfb.EPI_ROPE_SPLIT:
+        batch, seq, hq, hkv, d, cos, sin = rope
+        q = dev.zeros((batch, hq, seq, d), torch.bfloat16)
+        key = dev.zeros((batch, hkv, seq, d), torch.bfloat16)
+        val = dev.zeros((batch, hkv, seq, d), torch.bfloat16)
+        g.q, g.key, g.value = q.data_ptr(), key.data_ptr(), val.data_ptr()
+        g.rope_cos, g.rope_sin = cos.data_ptr(), sin.data_ptr()
+        g.batch, g.seq, g.q_heads, g.kv_heads, g.head_dim = batch, seq, hq, hkv, d
+        out = (q, key, val)
+    else:
+        width = n // 2 if epilogue == sfb.EPI_SWIGLU else n
+        out = dev.zeros((m, width), torch.float32 if out_f32 else torch.bfloat16)
+        g.out = out.data_ptr()
+    if residual is not None:
+        g.residual = residual.data_ptr()
+    g.swiglu_block = swiglu_block
+    if offsets is not None:
+        g.group_offsets, g.groups = offsets.data_ptr(), groups
+        table = dev.zeros((4 * (m // 128 + groups + 2),), torch.int32)
+        keep.append(table)
+        g.tile_table = table.data_ptr()
+    sfb.check(sfb.load().sfb_k_gemm_bf16(C.byref(g), C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    word = C.c_uint32(0)
+    sfb.check(sfb.load().sfb_device_status(C.byref(word)))
+    assert word.value == 0, f"device wait timed out, status word {word.value:#x}"
+    return out
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 384, 256), (7, 33, 19), (130, 70, 1000)])
+def test_gemm_f32_bit_exact(sfb, dev, port, m, n, k):
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+    da, db = dev.f32(a), dev.f32(b)
+    dc = dev.zeros((m, n), dev.torch.float32)
+    sfb.check(sfb.load().sfb_k_gemm_f32(C.c_void_p(da.data_ptr()), C.c_void_p(db.data_ptr()),
+                                        C.c_void_p(dc.data_ptr()), m, n, k, C.c_void_p(dev.stream())))
+    want = port.matmul(a, b, fma=True)  # FMA chain of the reference's native GEMM
+    assert np.array_equal(dev.np(dc), want)
+    # and within fp32 round-off of the scalar (multiply-then-add) layer reference
+    assert rel_err(dev.np(dc), port.matmul(a, b, fma=False)) < 1e-5
+
+
+def _inputs(port, m, n, k, seed=0, scale=0.05):
+    rng = np.random.default_rng(seed)
+    a = port.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    w = port.round_bf16((rng.standard_normal((k, n)) * scale).astype(np.float32))  # [k, n], y = x.W
+    return a, w
+
+
+BACKENDS = [1, 2]  # SIMT, tcgen05
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 256), (300, 264, 136), (1, 256, 128),
+                                   (520, 1024, 320)])
+def test_gemm_bf16_store(sfb, dev, port, backend, m, n, k):
+    a, w = _inputs(port, m, n, k)
+    want = port.matmul(a, w, fma=True)
+    got = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), backend=backend)
+    assert rel_err(dev.np(got), want) < BF16_TOL
+    got32 = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), backend=backend, out_f32=True)
+    assert rel_err(dev.np(got32), want) < 1e-4  # fp32 accumulation of exact bf16 products
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_gemm_bf16_residual(sfb, dev, port, backend):
+    m, n, k = 260, 384, 192
+    a, w = _inputs(port, m, n, k, seed=2)
+    res = port.round_bf16(np.random.default_rng(3).standard_normal((m, n)).astype(np.float32))
+    want = port.matmul(a, w, fma=True) + res
+    got = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), epilogue=sfb.EPI_RESIDUAL,
+                    backend=backend, residual=dev.bf16(res))
+    assert rel_err(dev.np(got), want) < BF16_TOL
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("block", [64, 128])
+def test_gemm_bf16_swiglu(sfb, dev, port, backend, block):
+    m, inter, k = 200, 384, 128
+    rng = np.random.default_rng(4)
+    a = port.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    wg = port.round_bf16((rng.standard_normal((k, inter)) * 0.1).astype(np.float32))
+    wu = port.round_bf16((rng.standard_normal((k, inter)) * 0.1).astype(np.float32))
+    gate_up = port.matmul(a, np.concatenate([wg, wu], axis=1), fma=True)
+    want = port.swiglu(gate_up, inter)
+    # weight rows: blocks of `block` gate rows followed by `block` up rows
+    bt = np.concatenate([np.concatenate([wg.T[i:i + block], wu.T[i:i + block]]) for i in range(0, inter, block)])
+    got = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(bt), epilogue=sfb.EPI_SWIGLU, backend=backend,
+                    swiglu_block=block)
+    assert rel_err(dev.np(got), want) < BF16_TOL
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_gemm_bf16_rope_split(sfb, dev, port, backend):
+    from oracle import binding as ob
+    batch, seq, hq, hkv, d = 2, 96, 4, 2, 64
+    hidden = hq * d
+    c = ob.decoder_config(batch, seq, hidden, 64, hq, hkv, d, rope_theta=10000.0)
+    n, k, m = hidden + 2 * hkv * d, hidden, batch * seq
+    a, w = _inputs(port, m, n, k, seed=5)
+    fused = port.matmul(a, w, fma=True)
+    wq, wk, wv = port.split_qkv_rope(c, fused)
+    cos = np.zeros((seq, d // 2), np.float32)
+    sin = np.zeros((seq, d // 2), np.float32)
+    sfb.check(sfb.load().sfb_rope_table(seq, d, C.c_float(10000.0), cos.ctypes.data_as(sfb.f32p),
+                                        sin.ctypes.data_as(sfb.f32p)))
+    q, key, val = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), epilogue=sfb.EPI_ROPE_SPLIT,
+                            backend=backend, rope=(batch, seq, hq, hkv, d, dev.f32(cos), dev.f32(sin)))
+    assert rel_err(dev.np(q), wq) < BF16_TOL
+    assert rel_err(dev.np(key), wk) < BF16_TOL
+    assert rel_err(dev.np(val), wv) < BF16_TOL
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_gemm_bf16_grouped(sfb, dev, port, backend):
+    """Variable-M expert GEMM: empty, tiny, ragged and >128-row segments."""
+    groups, n, k = 5, 256, 128
+    offsets = np.array([0, 5, 5, 200, 456, 460], np.int32)
+    m = int(offsets[-1])
+    rng = np.random.default_rng(6)
+    a = port.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    w = port.round_bf16((rng.standard_normal((groups, k, n)) * 0.1).astype(np.float32))
+    want = np.zeros((m, n), np.float32)
+    for g in range(groups):
+        lo, hi = offsets[g], offsets[g + 1]
+        if hi > lo:
+            want[lo:hi] = port.matmul(a[lo:hi], w[g], fma=True)
+    bt = np.ascontiguousarray(w.transpose(0, 2, 1))
+    got = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(bt), backend=backend, offsets=dev.i32(offsets),
+                    groups=groups, n=n)
+    assert rel_err(dev.np(got), want) < BF16_TOL
+
+
+def test_gemm_tcgen05_llama_shape_sampled_rows(sfb, dev, port):
+    """Full-size projection (T=8192, 4096x4096): oracle on 24 sampled rows."""
+    m, n, k = 8192, 4096, 4096
+    torch = dev.torch
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+    bt = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    got = gemm_bf16(sfb, dev, a, bt, backend=2)
+    rows = np.random.default_rng(0).choice(m, 24, replace=False)
+    a_rows = a[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+    want = port.matmul(a_rows, bt.float().cpu().numpy().T.copy(), fma=True)
+    assert rel_err(dev.np(got)[rows], want) < BF16_TOL
