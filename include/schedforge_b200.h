@@ -299,6 +299,8 @@ typedef struct sfb_compile_options {
     int page_tokens;      /* decode: KV block size of the paged cache (0 -> 16) */
     int tp_rank, tp_size; /* tensor parallel shard of this plan (heads / FFN columns) */
     int seed_block_table; /* decode: != 0 permutes the physical block order with this seed */
+    int no_workspace_reuse; /* != 0: every intermediate keeps its own bytes (DecoderPlanPolicy::
+                               reuse_workspace = false), so tests can read any of them back */
 } sfb_compile_options;
 
 /* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */

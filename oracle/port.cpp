@@ -137,10 +137,13 @@ void orp_rms_norm(const float* input, const float* weight, int rows, int width, 
 
 // C[m,n] = A[m,k] . B[k,n], row-major, one accumulator per output over ascending k.
 // fma == 0: multiply then add, scalar_matmul, src/decoder_compiler.cpp:64-75.
-// fma != 0: single-rounding FMA chain, the arithmetic of the native GEMM's register
-//           kernels, src/runtime.cpp:278-370 (hot loop :332-347).
+// fma != 0: the native GEMM's arithmetic: the first floor(n/8)*8 columns are AVX2 register
+//           kernels = one single-rounding FMA chain per output (src/runtime.cpp:278-370, hot
+//           loop :332-347; src/moe_compiler.cpp:77-101), the remaining n%8 tail columns are
+//           a scalar multiply-then-add loop (src/runtime.cpp:420-432; src/moe_compiler.cpp:105-117).
 void orp_matmul(const float* a, const float* b, float* c, int m, int n, int k, int fma,
                 int threads) {
+    const int n_fma = fma ? n / 8 * 8 : 0;
     parallel_rows(m, threads, [&](long long begin, long long end) {
         std::vector<float> acc(static_cast<std::size_t>(n));
         for (long long i = begin; i < end; ++i) {
@@ -148,8 +151,8 @@ void orp_matmul(const float* a, const float* b, float* c, int m, int n, int k, i
             for (int r = 0; r < k; ++r) {
                 const float x = a[i * k + r];
                 const float* brow = b + static_cast<std::size_t>(r) * n;
-                if (fma) for (int j = 0; j < n; ++j) acc[j] = std::fmaf(x, brow[j], acc[j]);
-                else     for (int j = 0; j < n; ++j) acc[j] += x * brow[j];
+                for (int j = 0; j < n_fma; ++j) acc[j] = std::fmaf(x, brow[j], acc[j]);
+                for (int j = n_fma; j < n; ++j) acc[j] += x * brow[j];
             }
             std::memcpy(c + i * n, acc.data(), static_cast<std::size_t>(n) * 4);
         }

@@ -1,0 +1,306 @@
+"""Python face of the C ABI, named after the reference's C++ entry points
+(StableHLOImporter, DecoderCompiler.compile, execute_decoder_layer, execute_attention,
+PagedKVCache, route_topk, dispatch_tokens, execute_moe).  Everything here is a thin
+ctypes call into libschedforge_b200.so; there is no Python or CPU compute path."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib as L
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _fp(a):
+    return None if a is None else a.ctypes.data_as(L.f32p)
+
+
+def _ip(a):
+    return None if a is None else a.ctypes.data_as(L.i32p)
+
+
+def decoder_config(batch=1, sequence=16, hidden=64, intermediate=128, query_heads=4, kv_heads=2,
+                   head_dim=16, rms_epsilon=1e-5, rope_theta=10000.0, causal=True, moe=False, experts=4,
+                   top_k=2, context_sequence=0):
+    """DecoderConfig (include/schedforge/decoder_compiler.h:17-32 of the reference)."""
+    return L.DecoderConfig(batch, sequence, hidden, intermediate, query_heads, kv_heads, head_dim,
+                           rms_epsilon, rope_theta, int(causal), int(moe), experts, top_k, context_sequence)
+
+
+def compile_options(dtype=L.BF16, token_major_attention=True, fuse_epilogues=True, gemm_backend=L.GEMM_AUTO,
+                    attention_backend=0, page_tokens=16, tp_rank=0, tp_size=1, seed_block_table=0,
+                    no_workspace_reuse=False):
+    return L.CompileOptions(dtype, int(token_major_attention), int(fuse_epilogues), gemm_backend,
+                            attention_backend, page_tokens, tp_rank, tp_size, seed_block_table,
+                            int(no_workspace_reuse))
+
+
+class StableHLOImporter:
+    """StableHLOImporter::importText + DecoderFusionPass::run."""
+
+    @staticmethod
+    def import_text(text):
+        s = L.GraphSummary()
+        L.check(L.load().sfb_import_stablehlo(text.encode(), C.byref(s)))
+        return {n: (bool(getattr(s, n)) if n.startswith("fused") else getattr(s, n)) for n, _ in s._fields_}
+
+    @staticmethod
+    def dump(text):
+        buf = C.create_string_buffer(1 << 16)
+        L.check(L.load().sfb_import_stablehlo_dump(text.encode(), buf, C.c_size_t(len(buf))))
+        return buf.value.decode()
+
+
+class DecoderExecutablePlan:
+    """Owns an sfb_decoder_plan.  Build with DecoderCompiler.compile."""
+
+    def __init__(self, handle, config, options, keep):
+        self._h = handle
+        self.config = config
+        self.options = options
+        self._keep = keep
+        self._callback = None
+
+    @property
+    def rows(self):
+        return self.config.batch * self.config.sequence
+
+    def execute(self, x, out=None, trace=None):
+        """execute_decoder_layer, one repetition: host input [T,H] -> (host output, DecoderResult)."""
+        x = _f32(x) if not isinstance(x, np.ndarray) or x.dtype != np.float32 or not x.flags.c_contiguous else x
+        if out is None:
+            out = np.empty((self.rows, self.config.hidden), np.float32)
+        result = L.DecoderResult()
+        ids = weights = counts = None
+        if trace is not None:
+            ids, weights, counts = _i32(trace[0]), _f32(trace[1]), _i32(trace[2])
+        L.check(L.load().sfb_decoder_execute(self._h, _fp(x), _fp(out), _ip(ids), _fp(weights), _ip(counts),
+                                             C.byref(result)))
+        return out, result
+
+    def execute_ptr(self, in_ptr, out_ptr, result=None):
+        """Same call with raw host addresses (e.g. pinned torch tensors)."""
+        L.check(L.load().sfb_decoder_execute(self._h, C.c_void_p(in_ptr), C.c_void_p(out_ptr), None, None, None,
+                                             C.byref(result) if result is not None else None))
+
+    def upload_input(self, x):
+        x = _f32(x)
+        L.check(L.load().sfb_decoder_upload_input(self._h, _fp(x)))
+
+    def execute_resident(self, stream=None):
+        L.check(L.load().sfb_decoder_execute_resident(self._h, C.c_void_p(stream)))
+
+    def download_output(self):
+        out = np.empty((self.rows, self.config.hidden), np.float32)
+        L.check(L.load().sfb_decoder_download_output(self._h, _fp(out)))
+        return out
+
+    def set_allreduce(self, fn):
+        """fn(buffer_ptr, count, dtype, stream_ptr) must all-reduce (sum) in place on that stream."""
+        if fn is None:
+            self._callback = None
+            L.check(L.load().sfb_decoder_set_allreduce(self._h, None, None))
+            return
+        self._callback = L.ALLREDUCE_FN(lambda user, buf, count, dtype, stream: fn(buf, count, dtype, stream))
+        L.check(L.load().sfb_decoder_set_allreduce(self._h, self._callback, None))
+
+    def read_tensor(self, name, dtype=np.float32):
+        count = C.c_int64(0)
+        L.check(L.load().sfb_decoder_read_tensor(self._h, name.encode(), None, C.c_int64(0), C.byref(count)))
+        out = np.empty(count.value, np.float32)
+        L.check(L.load().sfb_decoder_read_tensor(self._h, name.encode(), _fp(out), C.c_int64(out.size), C.byref(count)))
+        return out.view(np.int32) if dtype == np.int32 else out
+
+    def dump(self):
+        buf = C.create_string_buffer(1 << 17)
+        L.check(L.load().sfb_decoder_dump(self._h, buf, C.c_size_t(len(buf))))
+        return buf.value.decode()
+
+    @property
+    def workspace_bytes(self):
+        return L.load().sfb_decoder_workspace_bytes(self._h)
+
+    @property
+    def stream(self):
+        return L.load().sfb_decoder_stream(self._h)
+
+    def close(self):
+        if self._h:
+            L.load().sfb_decoder_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class DecoderCompiler:
+    """DecoderCompiler::compile: `data` maps DecoderData field names to float32 arrays."""
+
+    @staticmethod
+    def compile(config, data, stablehlo_text="", options=None):
+        options = options or compile_options()
+        keep = {k: _f32(v) for k, v in data.items() if v is not None and k in L.DATA_FIELDS}
+        d = L.DecoderData()
+        for name in L.DATA_FIELDS:
+            setattr(d, name, _fp(keep.get(name)))
+        handle = C.c_void_p()
+        L.check(L.load().sfb_decoder_compile(C.byref(config), C.byref(d), stablehlo_text.encode(),
+                                             C.byref(options), C.byref(handle)))
+        return DecoderExecutablePlan(handle, config, options, None)
+
+
+def execute_decoder_layer(plan, x, trace=None):
+    return plan.execute(x, trace=trace)
+
+
+def attention_config(batch, query_heads, kv_heads, sequence_query, sequence_kv, head_dim, head_dim_value=None,
+                     causal=False, scale=0.0):
+    return L.AttentionConfig(batch, query_heads, kv_heads, sequence_query, sequence_kv, head_dim,
+                             head_dim_value or head_dim, int(causal), scale)
+
+
+def execute_attention(config, q, k, v, dtype=L.F32, backend=0):
+    """execute_attention: q [B,Hq,Sq,D], k [B,Hkv,Sk,D], v [B,Hkv,Sk,Dv] -> (out [B,Hq,Sq,Dv], ms)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    out = np.empty((config.batch, config.query_heads, config.sequence_query, config.head_dim_value), np.float32)
+    ms = C.c_double(0)
+    L.check(L.load().sfb_attention_execute(C.byref(config), _fp(q), _fp(k), _fp(v), _fp(out), dtype, backend,
+                                           C.byref(ms)))
+    return out, ms.value
+
+
+def execute_decode_attention(config, q, keys, values, length, dtype=L.F32):
+    q, keys, values = _f32(q), _f32(keys), _f32(values)
+    out = np.empty((config.batch, config.query_heads, config.sequence_query, config.head_dim_value), np.float32)
+    ms = C.c_double(0)
+    L.check(L.load().sfb_attention_decode(C.byref(config), _fp(q), _fp(keys), _fp(values), length, _fp(out), dtype,
+                                          C.byref(ms)))
+    return out, ms.value
+
+
+class PagedKVCache:
+    """PagedKVCache + append_paged_kv / truncate / release / gather / execute_paged_decode_attention."""
+
+    def __init__(self, batch, kv_heads, head_dim, head_dim_value, page_tokens, capacity, dtype=L.F32):
+        self.shape = (batch, kv_heads, head_dim, head_dim_value, page_tokens, capacity)
+        self._h = C.c_void_p()
+        L.check(L.load().sfb_paged_create(batch, kv_heads, head_dim, head_dim_value, page_tokens, capacity, dtype,
+                                          C.byref(self._h)))
+
+    def set_free_pages(self, pages):
+        pages = _i32(pages)
+        L.check(L.load().sfb_paged_set_free_pages(self._h, _ip(pages), pages.size))
+
+    def append(self, keys, values, tokens):
+        keys, values = _f32(keys), _f32(values)
+        L.check(L.load().sfb_paged_append(self._h, _fp(keys), _fp(values), tokens))
+
+    def truncate(self, new_length):
+        L.check(L.load().sfb_paged_truncate(self._h, new_length))
+
+    def release(self, pages):
+        pages = _i32(pages)
+        L.check(L.load().sfb_paged_release(self._h, _ip(pages), pages.size))
+
+    def info(self):
+        info = np.zeros(4, np.int32)
+        table, free = np.zeros(65536, np.int32), np.zeros(65536, np.int32)
+        L.check(L.load().sfb_paged_info(self._h, _ip(info), _ip(table), table.size, _ip(free), free.size))
+        return {"length": int(info[0]), "page_table": table[:info[1]].copy(), "free_pages": free[:info[2]].copy(),
+                "pages": int(info[3])}
+
+    def gather(self):
+        b, hkv, d, dv, _, _ = self.shape
+        n = self.info()["length"]
+        keys, values = np.empty((b, hkv, max(n, 1), d), np.float32), np.empty((b, hkv, max(n, 1), dv), np.float32)
+        L.check(L.load().sfb_paged_gather(self._h, _fp(keys), _fp(values)))
+        return keys, values
+
+    def decode(self, config, q):
+        q = _f32(q)
+        out = np.empty((config.batch, config.query_heads, config.sequence_query, config.head_dim_value), np.float32)
+        ms = C.c_double(0)
+        L.check(L.load().sfb_paged_decode(self._h, C.byref(config), _fp(q), _fp(out), C.byref(ms)))
+        return out, ms.value
+
+    def close(self):
+        if self._h:
+            L.load().sfb_paged_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def moe_config(tokens, hidden, intermediate, experts, top_k):
+    return L.MoeConfig(tokens, hidden, intermediate, experts, top_k)
+
+
+def route_topk(config, x, router_weight, router_bias=None, dtype=L.F32):
+    x, router_weight = _f32(x), _f32(router_weight)
+    bias = _f32(router_bias) if router_bias is not None else None
+    tokens = x.shape[0]
+    ids, weights = np.empty((tokens, config.top_k), np.int32), np.empty((tokens, config.top_k), np.float32)
+    counts = np.empty(config.experts, np.int32)
+    L.check(L.load().sfb_moe_route_topk(C.byref(config), _fp(x), tokens, _fp(router_weight), _fp(bias), dtype,
+                                        _ip(ids), _fp(weights), _ip(counts)))
+    return ids, weights, counts
+
+
+def dispatch_tokens(config, x, ids, weights, counts, dtype=L.F32, copy_values=True):
+    ids, weights, counts = _i32(ids), _f32(weights), _i32(counts)
+    tokens = ids.shape[0]
+    n = tokens * config.top_k
+    x = _f32(x) if x is not None else None
+    values = np.empty((n, config.hidden), np.float32) if copy_values else None
+    offsets = np.empty(config.experts + 1, np.int32)
+    token_ids, slots, rw = np.empty(n, np.int32), np.empty(n, np.int32), np.empty(n, np.float32)
+    L.check(L.load().sfb_moe_dispatch_tokens(C.byref(config), _fp(x), tokens, _ip(ids), _fp(weights), _ip(counts),
+                                             dtype, _fp(values), _ip(offsets), _ip(token_ids), _ip(slots), _fp(rw)))
+    return values, offsets, token_ids, slots, rw
+
+
+def execute_moe(config, x, w1, w3, w2, ids, weights, counts, dtype=L.F32, gemm_backend=L.GEMM_AUTO):
+    x, w1, w3, w2 = _f32(x), _f32(w1), _f32(w3), _f32(w2)
+    ids, weights, counts = _i32(ids), _f32(weights), _i32(counts)
+    out = np.empty((x.shape[0], config.hidden), np.float32)
+    ms = C.c_double(0)
+    L.check(L.load().sfb_moe_execute(C.byref(config), _fp(x), x.shape[0], _fp(w1), _fp(w3), _fp(w2), _ip(ids),
+                                     _fp(weights), _ip(counts), dtype, gemm_backend, _fp(out), C.byref(ms)))
+    return out, ms.value
+
+
+def plan_moe_tasks(config, counts, split_threshold=0):
+    counts = _i32(counts)
+    tasks = np.empty((4096, 4), np.int32)
+    n = C.c_int(0)
+    L.check(L.load().sfb_moe_plan_tasks(C.byref(config), _ip(counts), split_threshold, _ip(tasks), 4096, C.byref(n)))
+    return tasks[:n.value].copy()
+
+
+def shard_columns(a, rank, size):
+    a = _f32(a)
+    out = np.empty((a.shape[0], a.shape[1] // size), np.float32)
+    L.check(L.load().sfb_shard_columns(_fp(a), a.shape[0], a.shape[1], rank, size, _fp(out)))
+    return out
+
+
+def shard_rows(a, rank, size):
+    a = _f32(a)
+    out = np.empty((a.shape[0] // size, a.shape[1]), np.float32)
+    L.check(L.load().sfb_shard_rows(_fp(a), a.shape[0], a.shape[1], rank, size, _fp(out)))
+    return out

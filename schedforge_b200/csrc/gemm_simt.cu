@@ -17,9 +17,10 @@ namespace {
 
 constexpr int TM = 64, TN = 64, TK = 16;
 
+// Computes columns [0, n_cols) of the [m, n] output (n is the leading dimension).
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
-                int m, int n, int k) {
+                int m, int n, int k, int n_cols) {
     __shared__ float as[TK][TM + 4];
     __shared__ float bs[TK][TN + 4];
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -34,7 +35,7 @@ gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
         for (int i = threadIdx.x; i < TK * TN; i += 256) {
             const int kk = i / TN, cidx = i % TN;
             const int gk = k0 + kk, gc = col0 + cidx;
-            bs[kk][cidx] = (gk < k && gc < n) ? b[static_cast<size_t>(gk) * n + gc] : 0.0F;
+            bs[kk][cidx] = (gk < k && gc < n_cols) ? b[static_cast<size_t>(gk) * n + gc] : 0.0F;
         }
         __syncthreads();
         const int kmax = min(TK, k - k0);
@@ -58,9 +59,23 @@ gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float*
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gc = col0 + tx * 4 + j;
-            if (gc < n) c[static_cast<size_t>(gr) * n + gc] = acc[i][j];
+            if (gc < n_cols) c[static_cast<size_t>(gr) * n + gc] = acc[i][j];
         }
     }
+}
+
+// The n % 8 tail columns of the reference's native GEMM are a scalar loop that rounds the
+// product and the sum separately; one thread per output reproduces that sequence.
+__global__ void gemm_f32_tail_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                     float* __restrict__ c, int m, int n, int k, int col_begin) {
+    const int tail = n - col_begin;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= m * tail) return;
+    const int row = idx / tail, col = col_begin + idx % tail;
+    float acc = 0.0F;
+    for (int kk = 0; kk < k; ++kk)
+        acc = __fadd_rn(acc, __fmul_rn(a[static_cast<size_t>(row) * k + kk], b[static_cast<size_t>(kk) * n + col]));
+    c[static_cast<size_t>(row) * n + col] = acc;
 }
 
 struct SimtParams {
@@ -213,9 +228,17 @@ extern "C" {
 sfb_status sfb_k_gemm_f32(const float* a, const float* b, float* c, int m, int n, int k,
                           sfb_stream stream) {
     SFB_REQUIRE(a && b && c && m > 0 && n > 0 && k > 0, "gemm_f32: invalid shape or null operand");
-    dim3 grid(ceil_div(n, TN), ceil_div(m, TM));
-    gemm_f32_kernel<<<grid, 256, 0, as_stream(stream)>>>(a, b, c, m, n, k);
-    return check_launch("gemm_f32");
+    const int n_main = n / 8 * 8;
+    if (n_main > 0) {
+        dim3 grid(ceil_div(n_main, TN), ceil_div(m, TM));
+        gemm_f32_kernel<<<grid, 256, 0, as_stream(stream)>>>(a, b, c, m, n, k, n_main);
+        SFB_TRY(check_launch("gemm_f32"));
+    }
+    if (n_main < n) {
+        gemm_f32_tail_kernel<<<ceil_div(m * (n - n_main), 128), 128, 0, as_stream(stream)>>>(a, b, c, m, n, k, n_main);
+        SFB_TRY(check_launch("gemm_f32_tail"));
+    }
+    return SFB_OK;
 }
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream) {

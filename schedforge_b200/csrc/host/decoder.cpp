@@ -1,0 +1,759 @@
+#include "decoder.hpp"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <numeric>
+#include <random>
+#include <sstream>
+
+#include "../common.cuh"
+
+namespace sfb {
+
+void validate(const DecoderConfig& c) {
+    if (c.batch <= 0 || c.sequence <= 0 || c.hidden <= 0 || c.intermediate <= 0 || c.query_heads <= 0 ||
+        c.kv_heads <= 0 || c.head_dim <= 0 || c.hidden != c.query_heads * c.head_dim ||
+        c.query_heads % c.kv_heads != 0 || c.rms_epsilon <= 0.0F)
+        throw std::invalid_argument("invalid decoder configuration");
+    if (c.ffn == DecoderFFNKind::MoE && (c.experts <= 0 || c.top_k <= 0 || c.top_k > c.experts))
+        throw std::invalid_argument("invalid decoder MoE configuration");
+    if (c.context_sequence < 0) throw std::invalid_argument("invalid decoder context sequence");
+}
+
+TensorGraph build_decoder_layer_graph(const DecoderConfig& c) {
+    validate(c);
+    auto dims = [](std::initializer_list<int> extents) {
+        GraphTensorType type;
+        for (const int e : extents) type.shape.push_back(Dimension::fixed(e));
+        return type;
+    };
+    TensorGraph g;
+    const int T = c.rows();
+    const auto hidden = dims({T, c.hidden});
+    const auto q_type = dims({c.batch, c.query_heads, c.sequence, c.head_dim});
+    const auto kv_type = dims({c.batch, c.kv_heads, c.sequence, c.head_dim});
+    const int x = g.addInput("x", hidden);
+    const int rms1 = g.addInput("rms1_weight", dims({c.hidden}), true);
+    const int n1 = g.addOperation(GraphOpKind::RmsNorm, "attention_rms_norm", {x, rms1}, hidden);
+    const int wqkv = g.addInput("packed_qkv_weight", dims({c.hidden, c.qkv_width()}), true);
+    const int qkv = g.addOperation(GraphOpKind::FusedQKVProjection, "fused_qkv_projection", {n1, wqkv},
+                                   dims({T, c.qkv_width()}));
+    const int q = g.addOperation(GraphOpKind::Split, "split_query", {qkv}, q_type);
+    const int k = g.addOperation(GraphOpKind::Split, "split_key", {qkv}, kv_type);
+    const int v = g.addOperation(GraphOpKind::Split, "split_value", {qkv}, kv_type);
+    const int rq = g.addOperation(GraphOpKind::RoPE, "rope_query", {q}, q_type);
+    const int rk = g.addOperation(GraphOpKind::RoPE, "rope_key", {k}, kv_type);
+    const int attn = g.addOperation(GraphOpKind::AttentionSdpa, "flash_attention", {rq, rk, v}, q_type);
+    const int merged = g.addOperation(GraphOpKind::Concat, "merge_heads", {attn}, hidden);
+    const int wo = g.addInput("output_weight", dims({c.hidden, c.hidden}), true);
+    const int proj = g.addOperation(GraphOpKind::MatMul, "output_projection", {merged, wo}, hidden);
+    const int r1 = g.addOperation(GraphOpKind::Add, "attention_residual", {proj, x}, hidden);
+    const int rms2 = g.addInput("rms2_weight", dims({c.hidden}), true);
+    const int n2 = g.addOperation(GraphOpKind::RmsNorm, "ffn_rms_norm", {r1, rms2}, hidden);
+    int ffn = -1;
+    if (c.ffn == DecoderFFNKind::Dense) {
+        const int wgu = g.addInput("packed_gate_up_weight", dims({c.hidden, 2 * c.intermediate}), true);
+        const int gu = g.addOperation(GraphOpKind::FusedGateUpProjection, "fused_gate_up_projection", {n2, wgu},
+                                      dims({T, 2 * c.intermediate}));
+        const int act = g.addOperation(GraphOpKind::SwiGLU, "swiglu", {gu}, dims({T, c.intermediate}));
+        const int wd = g.addInput("down_weight", dims({c.intermediate, c.hidden}), true);
+        ffn = g.addOperation(GraphOpKind::MatMul, "down_projection", {act, wd}, hidden);
+    } else {
+        const int wr = g.addInput("router_weight", dims({c.hidden, c.experts}), true);
+        const int logits = g.addOperation(GraphOpKind::MatMul, "router_projection", {n2, wr}, dims({T, c.experts}));
+        const int topk = g.addOperation(GraphOpKind::TopK, "router_topk", {logits});
+        const int dispatch = g.addOperation(GraphOpKind::MoeDispatch, "token_dispatch", {n2, topk});
+        const int expert = g.addOperation(GraphOpKind::MoeGroupedMatMul, "expert_grouped_ffn", {dispatch});
+        ffn = g.addOperation(GraphOpKind::MoeCombine, "expert_combine", {expert, topk}, hidden);
+    }
+    g.setReturn(g.addOperation(GraphOpKind::Add, "ffn_residual", {ffn, r1}, hidden));
+    ShapeInferencePass{}.run(g);
+    return g;
+}
+
+std::string DecoderPlanPolicy::dump() const {
+    return std::string("decoder.policy layout=") + (token_major_attention ? "token_major" : "head_major") +
+           " schedule=throughput placement=compact materialize=" + std::to_string(!fuse_epilogues) +
+           " reuse=" + std::to_string(reuse_workspace) + " threads=0";
+}
+
+std::string DecoderConstant::dump() const {
+    std::ostringstream out;
+    auto list = [&](const std::vector<int>& v) {
+        for (std::size_t i = 0; i < v.size(); ++i) out << (i ? "," : "") << v[i];
+    };
+    out << "constant @" << name << " logical=[";
+    list(logical_shape);
+    out << "] packed=[";
+    list(packed_shape);
+    out << "] layout=" << layout << " bytes=" << bytes;
+    return out.str();
+}
+
+// ---------------------------------------------------------------------------------------
+
+struct DecoderExecutablePlan::Impl {
+    // local (this shard's) extents
+    int T = 0, H = 0, D = 0, hq = 0, hkv = 0, hidden_l = 0, kvw_l = 0, qkv_l = 0, I_l = 0;
+    int E = 0, E_l = 0, e_begin = 0, K = 0;
+    int rank = 0, size = 1;
+    int dtype = SFB_BF16;
+    int swiglu_block = 0;       // dense gate/up interleave block (bf16)
+    int moe_swiglu_block = 0;   // expert W3|W1 interleave block (bf16)
+    bool decode = false, paged = false;
+    int page_tokens = 16, max_blocks = 0, num_blocks = 0, splits = 1;
+
+    DeviceBuffer weights, workspace, kv_pool;
+    WorkspacePlanner planner{true};
+    // weight pointers inside `weights`
+    float *rms1 = nullptr, *rms2 = nullptr, *rope_cos = nullptr, *rope_sin = nullptr;
+    void *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wd = nullptr;
+    float *router = nullptr, *router_bias = nullptr;
+    void *w13 = nullptr, *w2 = nullptr;       // bf16: [E_l][2I][H], [E_l][H][I]
+    float *w1f = nullptr, *w3f = nullptr, *w2f = nullptr;  // f32: reference layouts
+    void *k_pool = nullptr, *v_pool = nullptr;
+    int *block_table = nullptr, *context_len = nullptr;
+    void *kc = nullptr, *vc = nullptr;         // contiguous cached K/V (decode with sequence > 1)
+    cudaEvent_t events[16] = {};
+    bool has_input = false;
+
+    std::size_t esz() const { return dtype == SFB_BF16 ? 2 : 4; }
+    template <class P = void> P* ws(const char* name) {
+        const int id = planner.find(name);
+        if (id < 0) throw std::runtime_error(std::string("unknown workspace tensor: ") + name);
+        return reinterpret_cast<P*>(workspace.as<char>() + planner.offset(id));
+    }
+    bool has(const char* name) const { return planner.find(name) >= 0; }
+};
+
+DecoderExecutablePlan::~DecoderExecutablePlan() {
+    if (impl_)
+        for (auto& e : impl_->events)
+            if (e) cudaEventDestroy(e);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+namespace {
+
+struct WeightArena {
+    std::size_t total = 0;
+    std::size_t reserve(std::size_t bytes) {
+        const std::size_t offset = total;
+        total += (bytes + 1023) / 1024 * 1024;
+        return offset;
+    }
+};
+
+const float* need(const float* p, const char* name) {
+    if (!p) throw std::invalid_argument(std::string("constant weight shape mismatch: missing ") + name);
+    return p;
+}
+
+}  // namespace
+
+std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGraph& imported,
+                                                                const DecoderConfig& c,
+                                                                const sfb_decoder_data& data,
+                                                                const sfb_compile_options& opt) const {
+    const auto t0 = std::chrono::steady_clock::now();
+    validate(c);
+    auto plan = std::make_unique<DecoderExecutablePlan>();
+    plan->config = c;
+    plan->options = opt;
+    plan->policy.token_major_attention = opt.token_major_attention != 0;
+    plan->policy.fuse_epilogues = opt.fuse_epilogues != 0 && opt.dtype == SFB_BF16;
+    plan->policy.gemm_backend = opt.gemm_backend;
+    plan->policy.attention_backend = opt.attention_backend;
+    plan->imported_graph = imported;
+    plan->fusion = DecoderFusionPass{}.run(imported, c.ffn);
+    if (!plan->fusion.fused_qkv || !plan->fusion.fused_rope ||
+        (c.ffn == DecoderFFNKind::Dense && !plan->fusion.fused_gate_up))
+        throw std::invalid_argument("decoder graph is missing required fusion patterns");
+    plan->graph = build_decoder_layer_graph(c);
+
+    const int G = opt.tp_size > 0 ? opt.tp_size : 1, r = opt.tp_rank;
+    if (r < 0 || r >= G || c.query_heads % G != 0 || c.kv_heads % G != 0 || c.intermediate % G != 0 ||
+        (c.ffn == DecoderFFNKind::MoE && c.experts % G != 0))
+        throw std::invalid_argument("tensor-parallel size does not divide heads / FFN columns / experts");
+    if (opt.dtype != SFB_F32 && opt.dtype != SFB_BF16) throw std::invalid_argument("unknown plan dtype");
+
+    plan->impl_ = std::make_unique<DecoderExecutablePlan::Impl>();
+    auto& m = *plan->impl_;
+    m.T = c.rows(); m.H = c.hidden; m.D = c.head_dim;
+    m.hq = c.query_heads / G; m.hkv = c.kv_heads / G;
+    m.hidden_l = m.hq * m.D; m.kvw_l = m.hkv * m.D; m.qkv_l = m.hidden_l + 2 * m.kvw_l;
+    m.rank = r; m.size = G; m.dtype = opt.dtype;
+    const bool moe = c.ffn == DecoderFFNKind::MoE;
+    // MoE under sharding: every rank holds E/G whole experts (full intermediate width).
+    m.I_l = moe ? c.intermediate : c.intermediate / G;
+    m.E = moe ? c.experts : 0; m.E_l = moe ? c.experts / G : 0; m.e_begin = r * m.E_l; m.K = moe ? c.top_k : 0;
+    m.decode = c.context_sequence > 0;
+    m.paged = m.decode && c.sequence == 1;
+    m.page_tokens = opt.page_tokens > 0 ? opt.page_tokens : 16;
+    plan->policy.reuse_workspace = opt.no_workspace_reuse == 0;
+    m.planner = WorkspacePlanner(plan->policy.reuse_workspace);
+    const bool bf = m.dtype == SFB_BF16;
+    const bool fused = plan->policy.fuse_epilogues;
+    const int T = m.T, H = m.H, I = m.I_l, D = m.D;
+    auto pick_block = [&](int width) {  // gate/up interleave that the tensor-core epilogue accepts
+        if (T > 128 && width % 128 == 0) return 128;
+        if (width % 64 == 0) return 64;
+        return width;                   // one block: plain [gate | up] concatenation (CUDA-core GEMM)
+    };
+    m.swiglu_block = fused ? pick_block(I) : I;  // unfused: plain [gate | up] halves
+    m.moe_swiglu_block = pick_block(c.intermediate);
+
+    cuda_check(cudaStreamCreateWithFlags(&plan->stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    cudaStream_t s = plan->stream_;
+
+    // ---- weights: one arena ----------------------------------------------------------------
+    const std::size_t wsz = bf ? 2 : 4;
+    WeightArena arena;
+    const std::size_t o_rms1 = arena.reserve(sizeof(float) * H), o_rms2 = arena.reserve(sizeof(float) * H);
+    const std::size_t o_cos = arena.reserve(sizeof(float) * c.sequence * std::max(1, D / 2));
+    const std::size_t o_sin = arena.reserve(sizeof(float) * c.sequence * std::max(1, D / 2));
+    const std::size_t o_wqkv = arena.reserve(wsz * H * m.qkv_l), o_wo = arena.reserve(wsz * m.hidden_l * H);
+    std::size_t o_wgu = 0, o_wd = 0, o_router = 0, o_bias = 0, o_w13 = 0, o_w2 = 0, o_w1f = 0, o_w3f = 0, o_w2f = 0;
+    const std::size_t expert_elems = static_cast<std::size_t>(H) * c.intermediate;
+    if (!moe) {
+        o_wgu = arena.reserve(wsz * H * 2 * I);
+        o_wd = arena.reserve(wsz * I * H);
+    } else {
+        o_router = arena.reserve(sizeof(float) * H * m.E);
+        o_bias = arena.reserve(sizeof(float) * m.E);
+        if (bf) {
+            o_w13 = arena.reserve(2 * m.E_l * 2 * expert_elems);
+            o_w2 = arena.reserve(2 * m.E_l * expert_elems);
+        } else {
+            o_w1f = arena.reserve(4 * m.E_l * expert_elems);
+            o_w3f = arena.reserve(4 * m.E_l * expert_elems);
+            o_w2f = arena.reserve(4 * m.E_l * expert_elems);
+        }
+    }
+    m.weights.allocate(arena.total);
+    plan->weight_bytes = arena.total;
+    char* wb = m.weights.as<char>();
+    m.rms1 = reinterpret_cast<float*>(wb + o_rms1); m.rms2 = reinterpret_cast<float*>(wb + o_rms2);
+    m.rope_cos = reinterpret_cast<float*>(wb + o_cos); m.rope_sin = reinterpret_cast<float*>(wb + o_sin);
+    m.wqkv = wb + o_wqkv; m.wo = wb + o_wo;
+    auto h2d = [&](void* dst, const void* src, std::size_t bytes) {
+        cuda_check(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, s), "weight upload");
+        cuda_check(cudaStreamSynchronize(s), "weight upload sync");  // the host source may be a temporary
+    };
+    h2d(m.rms1, need(data.rms1_weight, "rms1_weight"), sizeof(float) * H);
+    h2d(m.rms2, need(data.rms2_weight, "rms2_weight"), sizeof(float) * H);
+    {
+        std::vector<float> cs(static_cast<std::size_t>(c.sequence) * std::max(1, D / 2)), sn(cs.size());
+        if (D >= 2) throw_on(sfb_rope_table(c.sequence, D, c.rope_theta, cs.data(), sn.data()));
+        h2d(m.rope_cos, cs.data(), cs.size() * 4);
+        h2d(m.rope_sin, sn.data(), sn.size() * 4);
+    }
+    // fp32 staging buffer on the device for the transpose/convert packer
+    std::size_t staging_elems = static_cast<std::size_t>(H) * std::max({H, c.intermediate, m.qkv_l});
+    DeviceBuffer staging;
+    if (bf) staging.allocate(staging_elems * 4);
+    const int whole = 1 << 30;
+    auto pack = [&](const float* host, int rows_k, int cols, int k_begin, int k_count, int c_begin, int c_count,
+                    void* dst, int block, int stride, int offset) {
+        h2d(staging.get(), host, static_cast<std::size_t>(rows_k) * cols * 4);
+        pack_weight_transposed(staging.as<float>(), cols, k_begin, k_count, c_begin, c_count, dst, block, stride,
+                               offset, s);
+        cuda_check(cudaStreamSynchronize(s), "weight pack");
+    };
+    const float* wq = need(data.query_weight, "query_weight");
+    const float* wk = need(data.key_weight, "key_weight");
+    const float* wv = need(data.value_weight, "value_weight");
+    const float* wo_h = need(data.output_weight, "output_weight");
+    const int kvw = c.kv_width();
+    if (bf) {
+        pack(wq, H, H, 0, H, r * m.hidden_l, m.hidden_l, m.wqkv, whole, 0, 0);
+        pack(wk, H, kvw, 0, H, r * m.kvw_l, m.kvw_l, m.wqkv, whole, 0, m.hidden_l);
+        pack(wv, H, kvw, 0, H, r * m.kvw_l, m.kvw_l, m.wqkv, whole, 0, m.hidden_l + m.kvw_l);
+        pack(wo_h, H, H, r * m.hidden_l, m.hidden_l, 0, H, m.wo, whole, 0, 0);
+    } else {
+        std::vector<float> packed(static_cast<std::size_t>(H) * m.qkv_l);
+        for (int row = 0; row < H; ++row) {
+            float* dst = packed.data() + static_cast<std::size_t>(row) * m.qkv_l;
+            std::memcpy(dst, wq + static_cast<std::size_t>(row) * H + r * m.hidden_l, sizeof(float) * m.hidden_l);
+            std::memcpy(dst + m.hidden_l, wk + static_cast<std::size_t>(row) * kvw + r * m.kvw_l, sizeof(float) * m.kvw_l);
+            std::memcpy(dst + m.hidden_l + m.kvw_l, wv + static_cast<std::size_t>(row) * kvw + r * m.kvw_l, sizeof(float) * m.kvw_l);
+        }
+        h2d(m.wqkv, packed.data(), packed.size() * 4);
+        h2d(m.wo, wo_h + static_cast<std::size_t>(r) * m.hidden_l * H, static_cast<std::size_t>(m.hidden_l) * H * 4);
+    }
+    plan->constants.push_back({"packed_qkv_weight", {H, c.hidden, kvw, kvw}, {H, c.qkv_width()},
+                               bf ? "qkv_transposed_bf16_k_major" : "qkv_concat_f32",
+                               static_cast<std::size_t>(H) * m.qkv_l * wsz});
+    if (!moe) {
+        m.wgu = wb + o_wgu; m.wd = wb + o_wd;
+        const float* wg = need(data.gate_weight, "gate_weight");
+        const float* wu = need(data.up_weight, "up_weight");
+        const float* wd_h = need(data.down_weight, "down_weight");
+        const int Ifull = c.intermediate;
+        if (bf) {
+            pack(wg, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, 0);
+            pack(wu, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, m.swiglu_block);
+            pack(wd_h, Ifull, H, r * I, I, 0, H, m.wd, whole, 0, 0);
+        } else {
+            std::vector<float> packed(static_cast<std::size_t>(H) * 2 * I);
+            for (int row = 0; row < H; ++row) {
+                std::memcpy(packed.data() + static_cast<std::size_t>(row) * 2 * I, wg + static_cast<std::size_t>(row) * Ifull + r * I, sizeof(float) * I);
+                std::memcpy(packed.data() + static_cast<std::size_t>(row) * 2 * I + I, wu + static_cast<std::size_t>(row) * Ifull + r * I, sizeof(float) * I);
+            }
+            h2d(m.wgu, packed.data(), packed.size() * 4);
+            h2d(m.wd, wd_h + static_cast<std::size_t>(r) * I * H, static_cast<std::size_t>(I) * H * 4);
+        }
+        plan->constants.push_back({"packed_gate_up_weight", {H, Ifull, Ifull}, {H, 2 * Ifull},
+                                   bf ? "gate_up_interleaved_" + std::to_string(m.swiglu_block) : "gate_up_concat_f32",
+                                   static_cast<std::size_t>(H) * 2 * I * wsz});
+    } else {
+        m.router = reinterpret_cast<float*>(wb + o_router);
+        m.router_bias = data.router_bias ? reinterpret_cast<float*>(wb + o_bias) : nullptr;
+        h2d(m.router, need(data.router_weight, "router_weight"), sizeof(float) * H * m.E);
+        if (data.router_bias) h2d(m.router_bias, data.router_bias, sizeof(float) * m.E);
+        const float* w1 = need(data.w1, "w1");
+        const float* w3 = need(data.w3, "w3");
+        const float* w2 = need(data.w2, "w2");
+        const int Ifull = c.intermediate;
+        if (bf) {
+            m.w13 = wb + o_w13; m.w2 = wb + o_w2;
+            for (int e = 0; e < m.E_l; ++e) {
+                const std::size_t src = static_cast<std::size_t>(m.e_begin + e) * expert_elems;
+                char* d13 = static_cast<char*>(m.w13) + static_cast<std::size_t>(e) * 2 * expert_elems * 2;
+                // SiLU applies to the W3 product, which multiplies the raw W1 product: [W3 | W1] = [gate | up]
+                pack(w3 + src, H, Ifull, 0, H, 0, Ifull, d13, m.moe_swiglu_block, 2 * m.moe_swiglu_block, 0);
+                pack(w1 + src, H, Ifull, 0, H, 0, Ifull, d13, m.moe_swiglu_block, 2 * m.moe_swiglu_block, m.moe_swiglu_block);
+                pack(w2 + src, Ifull, H, 0, Ifull, 0, H, static_cast<char*>(m.w2) + static_cast<std::size_t>(e) * expert_elems * 2, whole, 0, 0);
+            }
+        } else {
+            m.w1f = reinterpret_cast<float*>(wb + o_w1f); m.w3f = reinterpret_cast<float*>(wb + o_w3f);
+            m.w2f = reinterpret_cast<float*>(wb + o_w2f);
+            const std::size_t src = static_cast<std::size_t>(m.e_begin) * expert_elems, n = static_cast<std::size_t>(m.E_l) * expert_elems;
+            h2d(m.w1f, w1 + src, n * 4);
+            h2d(m.w3f, w3 + src, n * 4);
+            h2d(m.w2f, w2 + src, n * 4);
+        }
+    }
+    staging.release();
+
+    // ---- KV cache for decode plans ------------------------------------------------------------
+    const int ctx = c.context_sequence;
+    if (m.decode) {
+        const float* ck = need(data.cached_key, "cached_key");
+        const float* cv = need(data.cached_value, "cached_value");
+        // this shard's KV heads, [B, hkv_l, ctx, D]
+        const std::size_t per_head = static_cast<std::size_t>(ctx) * D;
+        std::vector<float> lk(static_cast<std::size_t>(c.batch) * m.hkv * per_head), lv(lk.size());
+        for (int b = 0; b < c.batch; ++b)
+            for (int h = 0; h < m.hkv; ++h) {
+                const std::size_t src = (static_cast<std::size_t>(b) * c.kv_heads + r * m.hkv + h) * per_head;
+                const std::size_t dst = (static_cast<std::size_t>(b) * m.hkv + h) * per_head;
+                std::memcpy(lk.data() + dst, ck + src, per_head * 4);
+                std::memcpy(lv.data() + dst, cv + src, per_head * 4);
+            }
+        const std::size_t cache_bytes = lk.size() * m.esz();
+        DeviceBuffer f32_stage(lk.size() * 4 * 2);
+        float* dk = f32_stage.as<float>();
+        float* dv = dk + lk.size();
+        h2d(dk, lk.data(), lk.size() * 4);
+        h2d(dv, lv.data(), lv.size() * 4);
+        if (m.paged) {
+            m.max_blocks = ceil_div(ctx, m.page_tokens);
+            m.num_blocks = c.batch * m.max_blocks;
+            const std::size_t pool_elems = static_cast<std::size_t>(m.num_blocks) * m.hkv * m.page_tokens * D;
+            const std::size_t table_bytes = sizeof(int) * m.num_blocks, len_bytes = sizeof(int) * c.batch;
+            const std::size_t pool_bytes = (pool_elems * m.esz() + 1023) / 1024 * 1024;
+            m.kv_pool.allocate(2 * pool_bytes + table_bytes + len_bytes + 1024);
+            DeviceBuffer converted(bf ? 2 * cache_bytes : 0);
+            char* kb = m.kv_pool.as<char>();
+            m.k_pool = kb; m.v_pool = kb + pool_bytes;
+            m.block_table = reinterpret_cast<int*>(kb + 2 * pool_bytes);
+            m.context_len = m.block_table + m.num_blocks;
+            char* tmp = converted.as<char>();
+            std::vector<int> table(m.num_blocks), lens(c.batch, 0), full(c.batch, ctx);
+            std::iota(table.begin(), table.end(), 0);
+            if (opt.seed_block_table != 0) {
+                std::mt19937 generator(static_cast<unsigned>(opt.seed_block_table));
+                std::shuffle(table.begin(), table.end(), generator);
+            }
+            h2d(m.block_table, table.data(), table_bytes);
+            h2d(m.context_len, lens.data(), len_bytes);  // start lengths for the append kernel
+            cuda_check(cudaMemsetAsync(m.k_pool, 0, 2 * pool_bytes, s), "pool clear");
+            void *ak = dk, *av = dv;
+            if (bf) {
+                throw_on(sfb_k_convert(dk, SFB_F32, tmp, SFB_BF16, static_cast<int64_t>(lk.size()), s));
+                throw_on(sfb_k_convert(dv, SFB_F32, tmp + cache_bytes, SFB_BF16, static_cast<int64_t>(lv.size()), s));
+                ak = tmp; av = tmp + cache_bytes;
+            }
+            throw_on(sfb_k_paged_kv_append(ak, av, m.k_pool, m.v_pool, m.block_table, m.context_len, c.batch, m.hkv,
+                                           ctx, D, D, m.page_tokens, m.max_blocks, static_cast<sfb_dtype>(m.dtype), s));
+            cuda_check(cudaStreamSynchronize(s), "paged cache build");
+            h2d(m.context_len, full.data(), len_bytes);
+            m.splits = sfb_attention_decode_default_splits(c.batch, m.hkv, ctx);
+            plan->attention_strategy = "split_kv_decode";
+        } else {
+            m.kv_pool.allocate(2 * cache_bytes + 1024);
+            m.kc = m.kv_pool.get();
+            m.vc = m.kv_pool.as<char>() + cache_bytes;
+            if (bf) {
+                throw_on(sfb_k_convert(dk, SFB_F32, m.kc, SFB_BF16, static_cast<int64_t>(lk.size()), s));
+                throw_on(sfb_k_convert(dv, SFB_F32, m.vc, SFB_BF16, static_cast<int64_t>(lv.size()), s));
+            } else {
+                cuda_check(cudaMemcpyAsync(m.kc, dk, cache_bytes, cudaMemcpyDeviceToDevice, s), "cache copy");
+                cuda_check(cudaMemcpyAsync(m.vc, dv, cache_bytes, cudaMemcpyDeviceToDevice, s), "cache copy");
+            }
+            cuda_check(cudaStreamSynchronize(s), "cache build");
+            plan->attention_strategy = "io_aware";
+        }
+    } else {
+        plan->attention_strategy = "io_aware";
+    }
+
+    // ---- activations: one workspace with lifetime-based reuse --------------------------------
+    const auto plan_start = std::chrono::steady_clock::now();
+    const std::size_t e = m.esz();
+    auto& wp = m.planner;
+    const std::size_t TH = static_cast<std::size_t>(T) * H;
+    // The layer input stays resident for the whole pass so that the plan can be re-run.
+    wp.add("input_f32", TH * 4, 0, bf ? 0 : 13);
+    if (bf) wp.add("input", TH * e, 0, 13);
+    wp.add("normalized1", TH * e, 1, 2);
+    if (!fused) wp.add("fused_qkv", static_cast<std::size_t>(T) * m.qkv_l * e, 2, 3);
+    wp.add("query", static_cast<std::size_t>(T) * m.hidden_l * e, 2, 4);
+    wp.add("key", static_cast<std::size_t>(T) * m.kvw_l * e, 2, 4);
+    wp.add("value", static_cast<std::size_t>(T) * m.kvw_l * e, 2, 4);
+    if (m.paged)
+        wp.add("decode_partials", sfb_attention_decode_workspace(c.batch, m.hq, D, m.splits), 4, 4);
+    wp.add("attention", static_cast<std::size_t>(T) * m.hidden_l * e, 4, 5);
+    if (!fused) wp.add("projected", TH * e, 5, 6);
+    wp.add("attention_residual", TH * e, 5, 12);
+    wp.add("normalized2", TH * e, 7, 9);
+    if (!moe) {
+        if (!fused) wp.add("gate_up", static_cast<std::size_t>(T) * 2 * I * e, 8, 9);
+        wp.add("activation", static_cast<std::size_t>(T) * I * e, 8, 10);
+        if (!fused) wp.add("down", TH * e, 10, 11);
+    } else {
+        const std::size_t A = static_cast<std::size_t>(T) * m.K;
+        wp.add("expert_ids", A * 4, 8, 12);
+        wp.add("expert_weights", A * 4, 8, 12);
+        wp.add("counts", static_cast<std::size_t>(m.E) * 4, 8, 12);
+        wp.add("offsets", static_cast<std::size_t>(m.E + 1) * 4, 8, 12);
+        wp.add("token_ids", A * 4, 8, 12);
+        wp.add("route_slots", A * 4, 8, 12);
+        wp.add("routing_weights", A * 4, 8, 12);
+        wp.add("dest_of", A * 4, 8, 12);
+        wp.add("dispatch_scratch", sfb_moe_dispatch_scratch_bytes(T, m.E, m.K), 8, 9);
+        wp.add("tile_table", sizeof(int) * 4 * (A / 128 + m.E + 2), 9, 11);
+        wp.add("dispatched", A * H * e, 8, 10);
+        if (bf) {
+            wp.add("expert_activation", A * I * e, 9, 10);
+        } else {
+            wp.add("expert_first", A * I * e, 9, 10);
+            wp.add("expert_gate", A * I * e, 9, 10);
+        }
+        wp.add("expert_output", A * H * e, 10, 11);
+    }
+    wp.add("output", TH * e, 11, 13);
+    if (bf) wp.add("output_f32", TH * 4, 12, 13);
+    m.workspace.allocate(wp.total_bytes());
+    plan->naive_bytes = wp.naive_bytes();
+    plan->workspace_bytes = wp.total_bytes();
+    (void)plan_start;
+    for (auto& ev : m.events) cuda_check(cudaEventCreate(&ev), "cudaEventCreate");
+    plan->compile_milliseconds =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return plan;
+}
+
+void DecoderExecutablePlan::upload_input(const float* input) {
+    if (!input) throw std::invalid_argument("decoder input is null");
+    auto& m = *impl_;
+    cuda_check(cudaMemcpyAsync(m.ws<float>("input_f32"), input, static_cast<std::size_t>(m.T) * m.H * 4,
+                               cudaMemcpyHostToDevice, stream_), "input upload");
+    if (m.dtype == SFB_BF16)
+        throw_on(sfb_k_convert(m.ws("input_f32"), SFB_F32, m.ws("input"), SFB_BF16,
+                               static_cast<int64_t>(m.T) * m.H, stream_));
+    m.has_input = true;
+}
+
+void DecoderExecutablePlan::download_output(float* output) {
+    if (!output) throw std::invalid_argument("decoder output is null");
+    auto& m = *impl_;
+    const float* src = m.dtype == SFB_BF16 ? m.ws<float>("output_f32") : m.ws<float>("output");
+    cuda_check(cudaMemcpyAsync(output, src, static_cast<std::size_t>(m.T) * m.H * 4, cudaMemcpyDeviceToHost, stream_),
+               "output download");
+    cuda_check(cudaStreamSynchronize(stream_), "output download sync");
+}
+
+void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool stage_events) {
+    auto& m = *impl_;
+    if (!m.has_input) throw std::invalid_argument("decoder input has not been uploaded");
+    const DecoderConfig& c = config;
+    const bool bf = m.dtype == SFB_BF16, fused = policy.fuse_epilogues, moe = c.ffn == DecoderFFNKind::MoE;
+    const auto dt = static_cast<sfb_dtype>(m.dtype);
+    const int T = m.T, H = m.H, I = m.I_l, D = m.D;
+    int ev = 0;
+    auto mark = [&] { if (stage_events) cuda_check(cudaEventRecord(m.events[ev++], s), "event"); };
+    auto gemm = [&](const void* a, const void* w, void* out, int mm, int n, int k, int epi, const void* res = nullptr,
+                    int sb = 0, const int* offsets = nullptr, int groups = 0) {
+        if (!bf) {
+            throw_on(sfb_k_gemm_f32(static_cast<const float*>(a), static_cast<const float*>(w),
+                                    static_cast<float*>(out), mm, n, k, s));
+            return;
+        }
+        sfb_gemm_args g{};
+        g.a = a; g.bt = w; g.out = out; g.m = mm; g.n = n; g.k = k; g.epilogue = epi;
+        g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb;
+        if (epi == SFB_EPI_ROPE_SPLIT) {
+            g.q = m.ws("query"); g.key = m.ws("key"); g.value = m.ws("value");
+            g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
+            g.batch = c.batch; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
+        }
+        if (offsets) { g.group_offsets = offsets; g.groups = groups; g.tile_table = m.ws("tile_table"); }
+        throw_on(sfb_k_gemm_bf16(&g, s));
+    };
+    auto allreduce = [&](void* buffer, int64_t count) {
+        if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, buffer, count, m.dtype, s);
+    };
+
+    mark();  // 0
+    void* x = bf ? m.ws("input") : m.ws("input_f32");
+    throw_on(sfb_k_rms_norm(x, m.rms1, m.ws("normalized1"), T, H, c.rms_epsilon, dt, s));
+    mark();  // 1: norm
+    const bool rope_fused = fused && D % 2 == 0;
+    if (rope_fused) {
+        gemm(m.ws("normalized1"), m.wqkv, nullptr, T, m.qkv_l, H, SFB_EPI_ROPE_SPLIT);
+        mark(); mark();  // 2: projection, 3: (rope inside)
+    } else {
+        gemm(m.ws("normalized1"), m.wqkv, m.ws("fused_qkv"), T, m.qkv_l, H, SFB_EPI_STORE);
+        mark();  // 2
+        throw_on(sfb_k_rope_split(m.ws("fused_qkv"), m.ws("query"), m.ws("key"), m.ws("value"), m.rope_cos, m.rope_sin,
+                                  c.batch, c.sequence, m.hq, m.hkv, D, dt, s));
+        mark();  // 3
+    }
+    if (m.paged) {
+        sfb_decode_args a{};
+        a.q = m.ws("query"); a.k_pool = m.k_pool; a.v_pool = m.v_pool; a.block_table = m.block_table;
+        a.context_len = m.context_len; a.out = m.ws("attention"); a.partials = m.ws("decode_partials");
+        a.batch = c.batch; a.q_heads = m.hq; a.kv_heads = m.hkv; a.head_dim = D; a.head_dim_value = D;
+        a.block_tokens = m.page_tokens; a.max_blocks = m.max_blocks; a.num_blocks = m.num_blocks;
+        a.max_context = c.context_sequence; a.splits = m.splits; a.scale = 0.0F; a.dtype = m.dtype;
+        throw_on(sfb_k_attention_decode_paged(&a, s));
+    } else {
+        sfb_attention_args a{};
+        a.q = m.ws("query");
+        a.key = m.decode ? m.kc : m.ws("key");
+        a.value = m.decode ? m.vc : m.ws("value");
+        a.out = m.ws("attention");
+        a.batch = c.batch; a.q_heads = m.hq; a.kv_heads = m.hkv; a.seq_q = c.sequence;
+        a.seq_kv = m.decode ? c.context_sequence : c.sequence; a.head_dim = D; a.head_dim_value = D;
+        a.causal = c.causal; a.scale = 0.0F; a.token_major = 1; a.dtype = m.dtype;
+        a.backend = policy.attention_backend;
+        throw_on(sfb_k_attention_prefill(&a, s));
+    }
+    mark();  // 4: attention
+    void* r1 = m.ws("attention_residual");
+    const bool add_residual_here = m.rank == 0;  // under sharding the residual enters the sum once
+    if (fused) {
+        gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x);
+        allreduce(r1, static_cast<int64_t>(T) * H);
+        mark(); mark();  // 5: projection, 6: (residual inside)
+    } else {
+        gemm(m.ws("attention"), m.wo, m.ws("projected"), T, H, m.hidden_l, SFB_EPI_STORE);
+        allreduce(m.ws("projected"), static_cast<int64_t>(T) * H);
+        mark();  // 5
+        throw_on(sfb_k_add(m.ws("projected"), x, r1, static_cast<int64_t>(T) * H, dt, s));
+        mark();  // 6
+    }
+    throw_on(sfb_k_rms_norm(r1, m.rms2, m.ws("normalized2"), T, H, c.rms_epsilon, dt, s));
+    mark();  // 7: norm
+    void* out = m.ws("output");
+    if (!moe) {
+        if (fused) {
+            gemm(m.ws("normalized2"), m.wgu, m.ws("activation"), T, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block);
+            gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1);
+            allreduce(out, static_cast<int64_t>(T) * H);
+            mark(); mark();  // 8: ffn, 9: (residual inside)
+        } else {
+            gemm(m.ws("normalized2"), m.wgu, m.ws("gate_up"), T, 2 * I, H, SFB_EPI_STORE);
+            throw_on(sfb_k_swiglu(m.ws("gate_up"), m.ws("activation"), T, I, dt, s));
+            gemm(m.ws("activation"), m.wd, m.ws("down"), T, H, I, SFB_EPI_STORE);
+            allreduce(m.ws("down"), static_cast<int64_t>(T) * H);
+            mark();  // 8
+            throw_on(sfb_k_add(r1, m.ws("down"), out, static_cast<int64_t>(T) * H, dt, s));
+            mark();  // 9
+        }
+    } else {
+        const int A = T * m.K, Ifull = c.intermediate;
+        int* ids = m.ws<int>("expert_ids");
+        float* wts = m.ws<float>("expert_weights");
+        int* counts = m.ws<int>("counts");
+        if (trace) {
+            cuda_check(cudaMemcpyAsync(ids, trace.expert_ids, sizeof(int) * A, cudaMemcpyHostToDevice, s), "trace upload");
+            cuda_check(cudaMemcpyAsync(wts, trace.expert_weights, sizeof(float) * A, cudaMemcpyHostToDevice, s), "trace upload");
+            cuda_check(cudaMemcpyAsync(counts, trace.counts, sizeof(int) * m.E, cudaMemcpyHostToDevice, s), "trace upload");
+        } else {
+            throw_on(sfb_k_moe_route(m.ws("normalized2"), dt, m.router, m.router_bias, T, H, m.E, m.K, ids, wts, counts, s));
+        }
+        int* offsets = m.ws<int>("offsets");
+        throw_on(sfb_k_moe_dispatch(m.ws("normalized2"), dt, ids, wts, counts, T, H, m.E, m.K, m.ws("dispatched"), offsets,
+                                    m.ws<int>("token_ids"), m.ws<int>("route_slots"), m.ws<float>("routing_weights"),
+                                    m.ws<int>("dest_of"), m.ws<int>("dispatch_scratch"), s));
+        void* y = m.ws("expert_output");
+        if (m.size > 1) cuda_check(cudaMemsetAsync(y, 0, static_cast<std::size_t>(A) * H * m.esz(), s), "expert output clear");
+        if (bf) {
+            gemm(m.ws("dispatched"), m.w13, m.ws("expert_activation"), A, 2 * Ifull, H, SFB_EPI_SWIGLU, nullptr,
+                 m.moe_swiglu_block, offsets + m.e_begin, m.E_l);
+            gemm(m.ws("expert_activation"), m.w2, y, A, H, Ifull, SFB_EPI_STORE, nullptr, 0, offsets + m.e_begin, m.E_l);
+        } else {
+            // fp32 plan: exact-order GEMM per expert segment; the segment bounds come back to the host.
+            std::vector<int> host_offsets(m.E + 1);
+            cuda_check(cudaMemcpyAsync(host_offsets.data(), offsets, sizeof(int) * (m.E + 1), cudaMemcpyDeviceToHost, s), "offsets");
+            cuda_check(cudaStreamSynchronize(s), "offsets sync");
+            float* xs = m.ws<float>("dispatched");
+            float* first = m.ws<float>("expert_first");
+            float* gate = m.ws<float>("expert_gate");
+            const std::size_t ee = static_cast<std::size_t>(H) * Ifull;
+            for (int e = 0; e < m.E_l; ++e) {
+                const int lo = host_offsets[m.e_begin + e], rows = host_offsets[m.e_begin + e + 1] - lo;
+                if (rows <= 0) continue;
+                throw_on(sfb_k_gemm_f32(xs + static_cast<std::size_t>(lo) * H, m.w1f + e * ee, first + static_cast<std::size_t>(lo) * Ifull, rows, Ifull, H, s));
+                throw_on(sfb_k_gemm_f32(xs + static_cast<std::size_t>(lo) * H, m.w3f + e * ee, gate + static_cast<std::size_t>(lo) * Ifull, rows, Ifull, H, s));
+            }
+            // first *= silu(gate) over every dispatched row (src/moe_compiler.cpp:146-149)
+            moe_silu_mul_f32(first, gate, static_cast<int64_t>(A) * Ifull, s);
+            for (int e = 0; e < m.E_l; ++e) {
+                const int lo = host_offsets[m.e_begin + e], rows = host_offsets[m.e_begin + e + 1] - lo;
+                if (rows <= 0) continue;
+                throw_on(sfb_k_gemm_f32(first + static_cast<std::size_t>(lo) * Ifull, m.w2f + e * ee,
+                                        static_cast<float*>(y) + static_cast<std::size_t>(lo) * H, rows, H, Ifull, s));
+            }
+        }
+        throw_on(sfb_k_moe_combine(y, m.ws<int>("dest_of"), m.ws<float>("routing_weights"),
+                                   add_residual_here ? r1 : nullptr, out, T, H, m.K, dt, s));
+        allreduce(out, static_cast<int64_t>(T) * H);
+        mark(); mark();  // 8: ffn, 9
+    }
+    if (bf) throw_on(sfb_k_convert(out, SFB_BF16, m.ws("output_f32"), SFB_F32, static_cast<int64_t>(T) * H, s));
+    mark();  // 10
+}
+
+void DecoderExecutablePlan::execute(const float* input, float* output, RoutingTraceView trace,
+                                    sfb_decoder_result* result) {
+    auto& m = *impl_;
+    cudaStream_t s = stream_;
+    const uint64_t launches_before = sfb_launch_count();
+    cudaEvent_t h0 = m.events[12], h1 = m.events[13], d0 = m.events[14], d1 = m.events[15];
+    cuda_check(cudaEventRecord(h0, s), "event");
+    upload_input(input);
+    cuda_check(cudaEventRecord(h1, s), "event");
+    run(s, trace, true);
+    cuda_check(cudaEventRecord(d0, s), "event");
+    download_output(output);
+    cuda_check(cudaEventRecord(d1, s), "event");
+    cuda_check(cudaEventSynchronize(d1), "event sync");
+    if (!result) return;
+    auto span = [&](cudaEvent_t a, cudaEvent_t b) {
+        float ms = 0.0F;
+        cuda_check(cudaEventElapsedTime(&ms, a, b), "event time");
+        return static_cast<double>(ms);
+    };
+    auto* e = m.events;
+    *result = {};
+    result->h2d_milliseconds = span(h0, h1);
+    result->d2h_milliseconds = span(d0, d1);
+    result->norm_rope_milliseconds = span(e[0], e[1]) + span(e[2], e[3]) + span(e[6], e[7]);
+    result->projection_milliseconds = span(e[1], e[2]) + span(e[4], e[5]);
+    result->attention_milliseconds = span(e[3], e[4]);
+    result->residual_milliseconds = span(e[5], e[6]) + span(e[8], e[9]);
+    result->ffn_milliseconds = span(e[7], e[8]);
+    result->milliseconds = span(h0, d1);
+    result->tokens_per_second = result->milliseconds > 0.0 ? m.T * 1000.0 / result->milliseconds : 0.0;
+    result->kernel_launches = sfb_launch_count() - launches_before;
+}
+
+int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_out, int64_t capacity) {
+    auto& m = *impl_;
+    const int id = m.planner.find(name);
+    if (id < 0) throw std::invalid_argument("unknown decoder tensor: " + name);
+    cuda_check(cudaStreamSynchronize(stream_), "sync");
+    const bool is_int = name == "expert_ids" || name == "counts" || name == "offsets" || name == "token_ids" ||
+                        name == "route_slots" || name == "dest_of";
+    const bool is_f32 = is_int || name == "expert_weights" || name == "routing_weights" || name == "input_f32" ||
+                        name == "output_f32" || name == "decode_partials" || m.dtype == SFB_F32;
+    std::size_t bytes = m.planner.bytes(id);
+    int64_t count;
+    const int A = m.T * std::max(1, m.K);
+    if (name == "counts") count = m.E;
+    else if (name == "offsets") count = m.E + 1;
+    else if (is_int || name == "expert_weights" || name == "routing_weights") count = A;
+    else if (name == "query" || name == "attention") count = static_cast<int64_t>(m.T) * m.hidden_l;
+    else if (name == "key" || name == "value") count = static_cast<int64_t>(m.T) * m.kvw_l;
+    else if (name == "activation") count = static_cast<int64_t>(m.T) * m.I_l;
+    else if (name == "gate_up") count = static_cast<int64_t>(m.T) * 2 * m.I_l;
+    else if (name == "fused_qkv") count = static_cast<int64_t>(m.T) * m.qkv_l;
+    else if (name == "dispatched" || name == "expert_output") count = static_cast<int64_t>(A) * m.H;
+    else if (name == "expert_activation" || name == "expert_first" || name == "expert_gate") count = static_cast<int64_t>(A) * config.intermediate;
+    else if (name == "decode_partials" || name == "dispatch_scratch" || name == "tile_table") count = static_cast<int64_t>(bytes / 4);
+    else count = static_cast<int64_t>(m.T) * m.H;
+    if (!host_out) return count;
+    if (capacity < count) throw std::invalid_argument("read_tensor: buffer too small");
+    char* src = m.workspace.as<char>() + m.planner.offset(id);
+    if (is_f32) {
+        cuda_check(cudaMemcpy(host_out, src, static_cast<std::size_t>(count) * 4, cudaMemcpyDeviceToHost), "read tensor");
+    } else {
+        DeviceBuffer tmp(static_cast<std::size_t>(count) * 4);
+        throw_on(sfb_k_convert(src, SFB_BF16, tmp.get(), SFB_F32, count, stream_));
+        cuda_check(cudaStreamSynchronize(stream_), "sync");
+        cuda_check(cudaMemcpy(host_out, tmp.get(), static_cast<std::size_t>(count) * 4, cudaMemcpyDeviceToHost), "read tensor");
+    }
+    return count;
+}
+
+std::string DecoderExecutablePlan::dump() const {
+    const auto& m = *impl_;
+    const bool bf = m.dtype == SFB_BF16, moe = config.ffn == DecoderFFNKind::MoE;
+    int device = 0;
+    cudaDeviceProp prop{};
+    std::string hardware = "sm_100a";
+    if (cudaGetDevice(&device) == cudaSuccess && cudaGetDeviceProperties(&prop, device) == cudaSuccess)
+        hardware = std::string(prop.name) + " sm_" + std::to_string(prop.major) + std::to_string(prop.minor) +
+                   " sms=" + std::to_string(prop.multiProcessorCount);
+    std::ostringstream out;
+    out << "sfe.decoder_executable version=0.9.0 ffn=" << (moe ? "moe" : "dense") << " hardware=\"" << hardware
+        << "\" {\nimported {\n" << imported_graph.dump() << "}\ncanonical {\n" << graph.dump() << "}\n"
+        << fusion.dump() << '\n' << policy.dump() << " attention=" << attention_strategy
+        << "\ncompile_ms=" << compile_milliseconds << " llvm_compile_ms=0 memory_planning_ms=0"
+        << "\nconstants {\n";
+    for (const auto& constant : constants) out << "  " << constant.dump() << '\n';
+    const char* gemm_kind = bf ? "gemm.bf16.tcgen05_tma" : "gemm.f32.fma_chain";
+    out << "}\ndecoder.memory naive=" << naive_bytes << " workspace=" << workspace_bytes << " weights=" << weight_bytes
+        << "\ndecoder.shard rank=" << m.rank << " size=" << m.size << " dtype=" << (bf ? "bf16" : "f32")
+        << "\nkernels {\n"
+        << "  qkv {\n    " << gemm_kind << " m=" << m.T << " n=" << m.qkv_l << " k=" << m.H
+        << " epilogue=" << (policy.fuse_epilogues ? "rope_split" : "store") << "\n  }\n"
+        << "  attention {\n    strategy=" << attention_strategy << "\n"
+        << "    attention.qk attention.scale attention.causal_mask reduce.max vector.exp reduce.sum\n"
+        << "    attention.rescale attention.online_softmax attention.pv vector.div\n";
+    if (m.paged)
+        out << "    paged_kv page_tokens=" << m.page_tokens << " blocks=" << m.num_blocks << " split_kv=" << m.splits << "\n";
+    out << "  }\n  output_projection {\n    " << gemm_kind << " m=" << m.T << " n=" << m.H << " k=" << m.hidden_l
+        << " epilogue=" << (policy.fuse_epilogues ? "residual" : "store") << "\n  }\n";
+    if (!moe) {
+        out << "  gate_up {\n    " << gemm_kind << " m=" << m.T << " n=" << 2 * m.I_l << " k=" << m.H << " epilogue="
+            << (policy.fuse_epilogues ? "swiglu" : "store") << "\n  }\n"
+            << "  down {\n    " << gemm_kind << " m=" << m.T << " n=" << m.H << " k=" << m.I_l << " epilogue="
+            << (policy.fuse_epilogues ? "residual" : "store") << "\n  }\n";
+    } else {
+        out << "  moe {\n    moe.router_matmul tensor.softmax tensor.topk moe.histogram moe.prefix_sum moe.dispatch\n"
+            << "    moe.grouped_matmul.w1 moe.grouped_matmul.w3 tensor.swiglu moe.grouped_matmul.w2 moe.weighted_combine\n"
+            << "    experts=" << m.E << " local_experts=" << m.E_l << " top_k=" << m.K << " token_buckets=[4,16,64," << m.T
+            << "]\n  }\n";
+    }
+    out << "}\nllvm_kernels=0\n}\n";
+    return out.str();
+}
+
+}  // namespace sfb

@@ -1,0 +1,215 @@
+"""Decoder layer parity through the plan ABI (sfb_decoder_compile / sfb_decoder_execute):
+the reference's own test shapes and seeds from the golden fixtures, BASELINE configs[0], and
+bf16 tensor-core plans against the oracle on bf16-rounded data."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import rel_err
+from oracle import binding as ob
+from schedforge_b200 import api, lib as L
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+sys.path.insert(0, GOLDEN)
+from stablehlo_texts import DECODER_TEXT, MOE_TEXT  # noqa: E402
+
+F32_TOL = 1e-4   # max-abs relative, fp32 plan
+BF16_TOL = 2e-2  # max-abs relative, bf16 plan
+
+
+def fixture(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    oc = ob.DecoderConfig()
+    for (field, _), value in zip(oc._fields_, z["config"]):
+        setattr(oc, field, float(value) if field in ("rms_epsilon", "rope_theta") else int(value))
+    c = L.DecoderConfig(*[getattr(oc, f) for f, _ in oc._fields_])
+    data = {k[3:]: z[k] for k in z.files if k.startswith("in_")}
+    return c, oc, data, z
+
+
+def weights_of(data):
+    return {k: v for k, v in data.items() if k != "input"}
+
+
+@pytest.mark.parametrize("name,text", [("decoder_dense", DECODER_TEXT), ("decoder_moe", DECODER_TEXT),
+                                       ("decoder_moe", MOE_TEXT), ("decoder_decode", DECODER_TEXT),
+                                       ("decoder_cfg1_shape", ""), ("decoder_batched", ""),
+                                       ("decoder_moe_medium", "")])
+def test_fp32_plan_matches_reference_fixtures(name, text):
+    c, _, data, z = fixture(name)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), text, api.compile_options(dtype=L.F32))
+    out, result = plan.execute(data["input"])
+    assert out.shape == z["out_reference"].shape
+    assert np.max(np.abs(out - z["out_reference"])) < 1e-3          # the reference's own bar
+    assert rel_err(out, z["out_reference"]) < F32_TOL
+    assert rel_err(out, z["out_native"]) < 1e-5                     # same FMA-chain GEMM arithmetic
+    assert result.tokens_per_second > 0 and result.kernel_launches > 0
+    dump = plan.dump()
+    assert "sfe.decoder_executable" in dump and "tensor.fused_qkv" in dump and "attention.online_softmax" in dump
+    if c.ffn_moe:
+        assert "moe.histogram" in dump
+    else:
+        assert "tensor.fused_gate_up" in dump
+    if c.context_sequence > 0:
+        assert "split_kv_decode" in dump
+    plan.close()
+
+
+def baseline_config1():
+    """BASELINE configs[0]: tiny dense prefill, weights ~N(0,0.02), activations ~N(0,1), seed 0."""
+    kw = dict(batch=1, sequence=128, hidden=256, intermediate=688, query_heads=4, kv_heads=2, head_dim=64,
+              rms_epsilon=1e-5, rope_theta=10000.0)
+    rng = np.random.default_rng(0)
+    h, i, kv = 256, 688, 128
+    data = {"input": rng.standard_normal((128, h)).astype(np.float32),
+            "rms1_weight": np.ones(h, np.float32), "rms2_weight": np.ones(h, np.float32)}
+    for key, shape in (("query_weight", (h, h)), ("key_weight", (h, kv)), ("value_weight", (h, kv)),
+                       ("output_weight", (h, h)), ("gate_weight", (h, i)), ("up_weight", (h, i)),
+                       ("down_weight", (i, h))):
+        data[key] = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    return kw, data
+
+
+def test_baseline_config1_fp32(port):
+    kw, data = baseline_config1()
+    want = port.decoder_layer(ob.decoder_config(**kw), data, native=False)
+    plan = api.DecoderCompiler.compile(api.decoder_config(**kw), weights_of(data), DECODER_TEXT.replace("4x16", "128x256"),
+                                       api.compile_options(dtype=L.F32))
+    out, _ = plan.execute(data["input"])
+    assert rel_err(out, want) < F32_TOL
+    # the plan can be re-run with the input resident, and gives the same bits
+    plan.execute_resident()
+    assert np.array_equal(plan.download_output(), out)
+    plan.close()
+
+
+def bf16_case(port, seed, moe=False, **kw):
+    oc = ob.decoder_config(moe=moe, **kw)
+    rng = np.random.default_rng(seed)
+    shapes = ob.decoder_shapes(oc)
+    data = {}
+    for key, n in shapes.items():
+        scale = 1.0 if key in ("input", "cached_key", "cached_value") else 0.05
+        data[key] = port.round_bf16((rng.standard_normal(n) * scale).astype(np.float32))
+    data["rms1_weight"] = (1.0 + 0.1 * rng.standard_normal(oc.hidden)).astype(np.float32)
+    data["rms2_weight"] = (1.0 + 0.1 * rng.standard_normal(oc.hidden)).astype(np.float32)
+    return oc, api.decoder_config(moe=moe, **kw), data
+
+
+@pytest.mark.parametrize("fuse,backend", [(True, L.GEMM_AUTO), (True, L.GEMM_SIMT), (False, L.GEMM_AUTO)])
+def test_bf16_dense_prefill(port, fuse, backend):
+    kw = dict(batch=2, sequence=192, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64,
+              rope_theta=500000.0)
+    oc, c, data = bf16_case(port, 1, **kw)
+    want = port.decoder_layer(oc, data, native=True)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(fuse_epilogues=fuse, gemm_backend=backend))
+    out, result = plan.execute(data["input"])
+    assert rel_err(out, want) < BF16_TOL
+    assert result.kernel_launches >= 6
+    plan.close()
+
+
+def test_bf16_cfg1_shape_with_ragged_ffn_width(port):
+    kw, _ = baseline_config1()
+    oc, c, data = bf16_case(port, 2, **kw)
+    want = port.decoder_layer(oc, data, native=True)
+    plan = api.DecoderCompiler.compile(c, weights_of(data))
+    out, _ = plan.execute(data["input"])
+    assert rel_err(out, want) < BF16_TOL
+    plan.close()
+
+
+@pytest.mark.parametrize("head_dim,seed_table", [(128, 7), (64, 0)])
+def test_bf16_decode_over_paged_cache(port, head_dim, seed_table):
+    kw = dict(batch=5, sequence=1, hidden=8 * head_dim, intermediate=512, query_heads=8, kv_heads=2,
+              head_dim=head_dim, context_sequence=300)
+    oc, c, data = bf16_case(port, 3, **kw)
+    want = port.decoder_layer(oc, data, native=True)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(seed_block_table=seed_table))
+    out, _ = plan.execute(data["input"])
+    assert rel_err(out, want) < BF16_TOL
+    assert "paged_kv page_tokens=16" in plan.dump()
+    plan.close()
+
+
+def test_bf16_moe_layer_and_bit_exact_routing(port):
+    kw = dict(batch=2, sequence=128, hidden=256, intermediate=256, query_heads=4, kv_heads=2, head_dim=64,
+              experts=8, top_k=2)
+    oc, c, data = bf16_case(port, 4, moe=True, **kw)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(no_workspace_reuse=True))
+    out, _ = plan.execute(data["input"])
+    T = 256
+    # routing chain on the very tensor the GPU routed: integer outputs must be identical
+    n2 = plan.read_tensor("normalized2").reshape(T, 256)
+    mc = ob.MoeConfig(T, 256, 256, 8, 2)
+    ids, weights, counts = port.route_topk(mc, n2, data["router_weight"].reshape(256, 8))
+    got_ids = plan.read_tensor("expert_ids", np.int32).reshape(T, 2)
+    got_counts = plan.read_tensor("counts", np.int32)
+    assert port.last_tie_tokens == 0
+    assert np.array_equal(got_ids, ids) and np.array_equal(got_counts, counts)
+    assert np.allclose(plan.read_tensor("expert_weights").reshape(T, 2), weights, rtol=1e-5, atol=1e-6)
+    _, offsets, token_ids, slots, _ = port.dispatch_tokens(mc, n2, ids, weights, counts, copy_values=False)
+    assert np.array_equal(plan.read_tensor("offsets", np.int32), offsets)
+    assert np.array_equal(plan.read_tensor("token_ids", np.int32), token_ids)
+    assert np.array_equal(plan.read_tensor("route_slots", np.int32), slots)
+    # layer output against the oracle with the same routing injected as a trace
+    want = port.decoder_layer(oc, data, native=True, trace=(ids, weights, counts))
+    assert rel_err(out, want) < BF16_TOL
+    # and the plan honours an injected trace like DecoderData::routing_trace
+    out2, _ = plan.execute(data["input"], trace=(ids, weights, counts))
+    assert rel_err(out2, want) < BF16_TOL
+    plan.close()
+
+
+def test_tensor_parallel_shards_reproduce_the_full_layer(port):
+    """Two tensor-parallel shards on ONE GPU with the all-reduce emulated through the plan's hook:
+    pass 1 captures each shard's O-projection partial, pass 2 adds the peer's partial where the
+    collective would run and captures the down-projection partials, whose sum is the layer output."""
+    import ctypes as C
+    import torch
+    kw = dict(batch=1, sequence=128, hidden=256, intermediate=512, query_heads=4, kv_heads=2, head_dim=64)
+    oc, c, data = bf16_case(port, 6, **kw)
+    want = port.decoder_layer(oc, data, native=True)
+    lib = L.load()
+    count = 128 * 256
+    plans = [api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(tp_rank=r, tp_size=2))
+             for r in range(2)]
+    first = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    second = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+
+    def copy_out(buf, dst, stream):
+        L.check(lib.sfb_k_convert(C.c_void_p(buf), L.BF16, C.c_void_p(dst.data_ptr()), L.BF16, C.c_int64(count),
+                                  C.c_void_p(stream)))
+
+    for rank, plan in enumerate(plans):  # pass 1: capture the first partial of every shard
+        calls = []
+
+        def hook(buf, n, dtype, stream, rank=rank, calls=calls):
+            assert n == count and dtype == L.BF16
+            if not calls:
+                copy_out(buf, first[rank], stream)
+            calls.append(buf)
+        plan.set_allreduce(hook)
+        plan.execute(data["input"])
+        assert len(calls) == 2
+    for rank, plan in enumerate(plans):  # pass 2: sum the peers' partials, capture the second one
+        calls = []
+
+        def hook(buf, n, dtype, stream, rank=rank, calls=calls):
+            if not calls:
+                L.check(lib.sfb_k_add(C.c_void_p(buf), C.c_void_p(first[1 - rank].data_ptr()), C.c_void_p(buf),
+                                      C.c_int64(count), L.BF16, C.c_void_p(stream)))
+            else:
+                copy_out(buf, second[rank], stream)
+            calls.append(buf)
+        plan.set_allreduce(hook)
+        plan.execute(data["input"])
+    torch.cuda.synchronize()
+    out = (second[0].float() + second[1].float()).cpu().numpy().reshape(128, 256)
+    assert rel_err(out, want) < BF16_TOL
+    for p in plans:
+        p.close()

@@ -1,0 +1,118 @@
+"""Host-side logic that needs no GPU: StableHLO import + fusion check, configuration
+validation and compile-time guards, MoE task table, RoPE table, weight shards."""
+import ctypes as C
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from schedforge_b200 import api, lib as L
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+sys.path.insert(0, GOLDEN)
+from stablehlo_texts import DECODER_TEXT, MOE_TEXT, NO_QKV_TEXT  # noqa: E402
+
+
+def golden_import():
+    return json.load(open(os.path.join(GOLDEN, "importer.json")))
+
+
+@pytest.mark.parametrize("key,text", [("decoder", DECODER_TEXT), ("moe", MOE_TEXT), ("no_qkv", NO_QKV_TEXT)])
+def test_importer_matches_reference_fixture(key, text):
+    got = api.StableHLOImporter.import_text(text)
+    want = golden_import()[key]
+    for field in ("operations", "values", "inputs", "matmuls", "fused_qkv", "fused_gate_up", "fused_rope"):
+        assert got[field] == want[field], field
+
+
+def test_importer_matches_reference_build(ref):
+    for text in (DECODER_TEXT, MOE_TEXT, NO_QKV_TEXT):
+        got, want = api.StableHLOImporter.import_text(text), ref.import_stablehlo(text)
+        assert {k: got[k] for k in want} == want
+
+
+def test_importer_dump_and_errors():
+    dump = api.StableHLOImporter.dump(DECODER_TEXT)
+    assert dump.startswith("graph @model {") and "tensor.rms_norm" in dump and "tensor.rope" in dump
+    assert "tensor.swiglu" in dump and "func.return" in dump
+    assert "moe.combine" in api.StableHLOImporter.dump(MOE_TEXT)
+    with pytest.raises(L.InvalidArgument, match="unsupported StableHLO operation: sine"):
+        api.StableHLOImporter.import_text("%a = stablehlo.sine %x : tensor<4xf32>")
+    with pytest.raises(L.InvalidArgument, match="matmul reduction dimensions do not match"):
+        api.StableHLOImporter.import_text(
+            "func.func @f(%x: tensor<4x16xf32>, %w: tensor<8x16xf32>)\n %y = stablehlo.dot_general %x, %w : tensor<4x16xf32>\n")
+    # symbolic and dynamic extents are accepted
+    summary = api.StableHLOImporter.import_text(
+        "func.func @f(%x: tensor<?x16xf32>, %w: tensor<16xf32>)\n %y = stablehlo.custom_call @RmsNorm(%x, %w) : tensor<?x16xf32>\n return %y")
+    assert summary["operations"] == 4
+
+
+def _weights(c, rng):
+    h, i, kv = c.hidden, c.intermediate, c.kv_heads * c.head_dim
+    shapes = dict(rms1_weight=h, query_weight=h * h, key_weight=h * kv, value_weight=h * kv, output_weight=h * h,
+                  rms2_weight=h, gate_weight=h * i, up_weight=h * i, down_weight=i * h)
+    return {k: rng.standard_normal(n).astype(np.float32) for k, n in shapes.items()}
+
+
+def test_compile_rejects_invalid_configuration_before_touching_the_device():
+    rng = np.random.default_rng(0)
+    bad = api.decoder_config(hidden=60)  # hidden != query_heads * head_dim
+    with pytest.raises(L.InvalidArgument, match="invalid decoder configuration"):
+        api.DecoderCompiler.compile(bad, _weights(api.decoder_config(), rng))
+    bad_moe = api.decoder_config(moe=True, experts=2, top_k=3)
+    with pytest.raises(L.InvalidArgument, match="invalid decoder MoE configuration"):
+        api.DecoderCompiler.compile(bad_moe, {})
+    with pytest.raises(L.InvalidArgument, match="invalid decoder context sequence"):
+        api.DecoderCompiler.compile(api.decoder_config(context_sequence=-1), {})
+
+
+def test_compile_requires_fusion_patterns():
+    c = api.decoder_config(1, 4, 16, 32, 4, 2, 4)
+    with pytest.raises(L.InvalidArgument, match="decoder graph is missing required fusion patterns"):
+        api.DecoderCompiler.compile(c, _weights(c, np.random.default_rng(0)), stablehlo_text=NO_QKV_TEXT)
+    # a MoE text lacks the gate/up pattern, which a dense plan requires
+    with pytest.raises(L.InvalidArgument, match="missing required fusion patterns"):
+        api.DecoderCompiler.compile(c, _weights(c, np.random.default_rng(0)), stablehlo_text=MOE_TEXT)
+
+
+def test_compile_rejects_bad_shard():
+    c = api.decoder_config(1, 4, 16, 32, 4, 2, 4)
+    with pytest.raises(L.InvalidArgument, match="tensor-parallel size does not divide"):
+        api.DecoderCompiler.compile(c, _weights(c, np.random.default_rng(0)), options=api.compile_options(tp_size=3))
+
+
+@pytest.mark.parametrize("name", ["moe_small", "moe_medium"])
+def test_plan_moe_tasks_matches_fixture(name, port):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    c = api.moe_config(*[int(v) for v in z["config"]])
+    tasks = api.plan_moe_tasks(c, z["counts"])
+    assert np.array_equal(tasks, z["tasks"])
+    # load-aware split: no task longer than the threshold, rows covered exactly once
+    split = api.plan_moe_tasks(c, z["counts"], split_threshold=2)
+    assert np.all(split[:, 2] - split[:, 1] <= 2) and np.all(split[:, 2] > split[:, 1])
+    assert (split[:, 2] - split[:, 1]).sum() == z["counts"].sum()
+    from oracle import binding as ob
+    assert np.array_equal(split, port.plan_moe_tasks(ob.MoeConfig(*[int(v) for v in z["config"]]), z["counts"], 2))
+
+
+def test_rope_table_matches_reference_formula(port):
+    from oracle import binding as ob
+    seq, dim, theta = 6, 8, 500000.0
+    cos, sin = np.zeros((seq, dim // 2), np.float32), np.zeros((seq, dim // 2), np.float32)
+    L.check(L.load().sfb_rope_table(seq, dim, C.c_float(theta), cos.ctypes.data_as(L.f32p), sin.ctypes.data_as(L.f32p)))
+    # rotate (1, 0) pairs with the oracle: the result is (cos, sin) of the table entry
+    c = ob.decoder_config(1, seq, dim, 8, 1, 1, dim, rope_theta=theta)
+    fused = np.zeros((seq, 3 * dim), np.float32)
+    fused[:, 0:dim:2] = 1.0
+    q, _, _ = port.split_qkv_rope(c, fused)
+    assert np.array_equal(q[0, 0, :, 0::2], cos) and np.array_equal(q[0, 0, :, 1::2], sin)
+
+
+def test_weight_shards():
+    a = np.arange(6 * 8, dtype=np.float32).reshape(6, 8)
+    assert np.array_equal(api.shard_columns(a, 1, 4), a[:, 2:4])
+    assert np.array_equal(api.shard_rows(a, 2, 3), a[4:6])
+    with pytest.raises(L.InvalidArgument):
+        api.shard_columns(a, 0, 3)
