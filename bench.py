@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Decoder-layer benchmark (one JSON line on stdout).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload prefill|decode]
+
+Workload (default): the Llama-3-8B-shaped dense decoder layer in bf16, prefill batch 4 x
+sequence 2048 (8192 tokens per step), tensor parallel over the N GPUs of one node with an NCCL
+all-reduce after the O and Down projections.  A "step" is one pass of the layer.
+
+  value   whole-job tokens/s with the layer input already resident in HBM (kernels + collectives)
+  e2e     the same metric through the host-buffer plan call (sfb_decoder_execute): pinned host
+          input -> device, layer, device -> pinned host output, every step
+  roofline   the dominant kernel (fused gate/up tcgen05 GEMM) timed live with CUDA events
+  cpu_baseline  the reference's own native CPU path (or the oracle port when the reference build
+          is absent) on a bounded sample of the same layer, rank 0, N == 1 only
+
+`--impl reference` times the reference's CPU implementation instead (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA = dict(hidden=4096, intermediate=14336, query_heads=32, kv_heads=8, head_dim=128, rms_epsilon=1e-5,
+             rope_theta=500000.0)
+PREFILL = dict(batch=4, sequence=2048)
+DECODE = dict(batch=128, sequence=1, context_sequence=2048)
+CPU_SAMPLE = dict(batch=1, sequence=384)  # bounded sample of the prefill workload for the CPU arms
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def make_weights(seed, cfg, with_cache=False):
+    """Synthetic weights ~N(0, 0.02), RMSNorm weights 1, cached K/V ~N(0,1); seeded, on the host."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    h, i = cfg["hidden"], cfg["intermediate"]
+    kv = cfg["kv_heads"] * cfg["head_dim"]
+    shapes = dict(query_weight=(h, h), key_weight=(h, kv), value_weight=(h, kv), output_weight=(h, h),
+                  gate_weight=(h, i), up_weight=(h, i), down_weight=(i, h))
+    data = {k: (torch.randn(s, generator=g) * 0.02).numpy() for k, s in shapes.items()}
+    data["rms1_weight"] = np.ones(h, np.float32)
+    data["rms2_weight"] = np.ones(h, np.float32)
+    if with_cache:
+        n = (cfg["batch"], cfg["kv_heads"], cfg["context_sequence"], cfg["head_dim"])
+        data["cached_key"] = torch.randn(n, generator=g).numpy()
+        data["cached_value"] = torch.randn(n, generator=g).numpy()
+    return data
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = sorted(sm)[len(sm) // 2:]  # upper half of the samples = the ones taken under load
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_arm(steps, warmup, cfg_sample):
+    """The reference's own CPU implementation (oracle/_ref) or the oracle port on a bounded sample."""
+    from oracle import binding as ob
+    cfg = dict(LLAMA, **cfg_sample)
+    oc = ob.decoder_config(**cfg)
+    data = make_weights(0, cfg)
+    import torch
+    t = cfg["batch"] * cfg["sequence"]
+    x = torch.randn((t, cfg["hidden"]), generator=torch.Generator().manual_seed(1)).numpy()
+    port = ob.Port()
+    for k in data:
+        data[k] = port.round_bf16(data[k])
+    data["input"] = port.round_bf16(x)
+    times = []
+    if ob.Ref.available():
+        ref = ob.Ref()
+        cores = ref.hardware_threads()
+        dec = ref.decoder_create(oc, data, threads=cores)
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            dec.execute_once()
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+        dec.close()
+        kind = "reference"
+    else:
+        cores = port.hardware_threads()
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            port.decoder_layer(oc, data, native=True, threads=cores)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+        kind = "port"
+    ms = 1000.0 * float(np.mean(times))
+    return {"value": t * 1000.0 / ms, "unit": "tokens/s", "cores": cores, "kind": kind, "ms_per_step": ms,
+            "sample": f"same layer, bf16-rounded weights, fp32 CPU arithmetic, B{cfg['batch']}xS{cfg['sequence']} "
+                      f"= {t} tokens per step ({steps} timed step(s) after {warmup} warm-up)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    shape = PREFILL if args.workload == "prefill" else DECODE
+    cfg = dict(LLAMA, **shape)
+    tokens = cfg["batch"] * cfg["sequence"]
+    workload = ("llama3_8b_decoder_layer_prefill_b4_s2048" if args.workload == "prefill"
+                else "llama3_8b_decoder_layer_decode_b128_ctx2048")
+    config = {"workload": workload, "hidden": 4096, "intermediate": 14336, "q_heads": 32, "kv_heads": 8,
+              "head_dim": 128, "tokens_per_step": tokens, "parallelism": f"tp{world}",
+              "l2": "weights + activations (>0.9 GB per step) exceed the 126 MB L2; no flush between steps"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        base = cpu_arm(max(1, min(args.steps, 3)), min(args.warmup, 1), CPU_SAMPLE)
+        line = {"impl": "reference", "metric": "decoder_layer_tokens_per_s", "value": base["value"], "unit": "tokens/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from schedforge_b200 import api, lib as L
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = L.load()
+
+    data = make_weights(0, cfg, with_cache=args.workload == "decode")
+    x_host = torch.randn((tokens, cfg["hidden"]), generator=torch.Generator().manual_seed(1)).pin_memory()
+    out_host = torch.empty((tokens, cfg["hidden"]), dtype=torch.float32).pin_memory()
+    c = api.decoder_config(**cfg)
+    plan = api.DecoderCompiler.compile(c, data, "", api.compile_options(tp_rank=rank, tp_size=world,
+                                                                         seed_block_table=1 if args.workload == "decode" else 0))
+    del data
+    stream = torch.cuda.ExternalStream(plan.stream)
+    views = {}
+
+    def allreduce(buf, count, dtype, stream_ptr):
+        key = (buf, count)
+        if key not in views:
+            class Raw:  # CUDA array interface over the plan's workspace (int16 view of the bf16 data)
+                __cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (buf, False), "version": 3}
+            views[key] = torch.as_tensor(Raw(), device="cuda").view(torch.bfloat16)
+        with torch.cuda.stream(stream):
+            dist.all_reduce(views[key])
+
+    if world > 1:
+        plan.set_allreduce(allreduce)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: input resident, kernels (+ collectives) only ------------------------------------
+    plan.upload_input(x_host.numpy())
+    for _ in range(args.warmup):
+        plan.execute_resident()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.sfb_launch_count()
+    start.record(stream)
+    for _ in range(args.steps):
+        plan.execute_resident()
+    stop.record(stream)
+    barrier()
+    launches = lib.sfb_launch_count() - launches0
+    ms = start.elapsed_time(stop) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- e2e: host buffers through the plan call ------------------------------------------------
+    for _ in range(min(args.warmup, 3)):
+        plan.execute_ptr(x_host.data_ptr(), out_host.data_ptr())
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        plan.execute_ptr(x_host.data_ptr(), out_host.data_ptr())
+    barrier()
+    e2e_ms = 1000.0 * (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    result = L.DecoderResult()
+    plan.execute_ptr(x_host.data_ptr(), out_host.data_ptr(), result)
+    clocks = sampler.stop() if rank == 0 else None
+    finite = bool(torch.isfinite(out_host).all())
+
+    # ---- roofline of the dominant kernel, timed live on its launching stream --------------------
+    peaks = measured_peaks()
+    roofline = None
+    if args.workload == "prefill":
+        m, k, n = tokens, cfg["hidden"], 2 * cfg["intermediate"] // world
+        a = (torch.randn((m, k), device="cuda") * 0.5).to(torch.bfloat16)
+        bt = (torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16)
+        o = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+        g = L.GemmArgs()
+        g.a, g.bt, g.out, g.m, g.n, g.k = a.data_ptr(), bt.data_ptr(), o.data_ptr(), m, n, k
+        g.epilogue, g.backend, g.swiglu_block = L.EPI_SWIGLU, L.GEMM_TCGEN05, 128
+        cur = torch.cuda.current_stream()
+        for _ in range(3):
+            L.check(lib.sfb_k_gemm_bf16(C.byref(g), C.c_void_p(cur.cuda_stream)))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record(cur)
+        for _ in range(reps):
+            L.check(lib.sfb_k_gemm_bf16(C.byref(g), C.c_void_p(cur.cuda_stream)))
+        e1.record(cur)
+        torch.cuda.synchronize()
+        kernel_ms = e0.elapsed_time(e1) / reps
+        flops = 2.0 * m * n * k
+        achieved = flops / (kernel_ms * 1e-3) / 1e12
+        roofline = {"kernel": "gemm_tcgen05_kernel<256> (gate/up projection, SwiGLU epilogue)", "bound": "tensor",
+                    "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst: kernel timed alone)",
+                    "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops, "traffic": None}
+    else:
+        kv_bytes = cfg["batch"] * cfg["context_sequence"] * (cfg["kv_heads"] // world) * cfg["head_dim"] * 2 * 2
+        roofline = {"kernel": "decode_paged_d128_kernel<4>", "bound": "hbm", "achieved": kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9
+                    if result.attention_milliseconds > 0 else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": (kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9 / peaks["hbm_gbs"])
+                    if result.attention_milliseconds > 0 else None, "peak_source": peaks["source"],
+                    "kernel_ms": result.attention_milliseconds, "algorithmic_bytes_per_launch": kv_bytes, "traffic": None}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "prefill":
+        base = cpu_arm(1, 1, CPU_SAMPLE)
+        cpu = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        line = {"metric": "decoder_layer_tokens_per_s", "value": tokens * 1000.0 / ms, "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": config,
+                "e2e": {"value": tokens * 1000.0 / e2e_ms, "unit": "tokens/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": tokens * cfg["hidden"] * 4, "d2h_bytes_per_step": tokens * cfg["hidden"] * 4},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+                "stages_ms": {"attention": result.attention_milliseconds, "projection": result.projection_milliseconds,
+                              "norm": result.norm_rope_milliseconds, "ffn": result.ffn_milliseconds,
+                              "h2d": result.h2d_milliseconds, "d2h": result.d2h_milliseconds},
+                "output_finite": finite}
+        print(json.dumps(line))
+    plan.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -54,3 +54,11 @@ NO_QKV_TEXT = """func.func @f(%x: tensor<4x16xf32>, %w: tensor<16x16xf32>) -> te
 }
 """
 
+
+
+def dense_decoder_text(rows, hidden, kv_width, intermediate):
+    """The dense layer text above with other extents."""
+    return (DECODER_TEXT.replace("4x16xf32", f"{rows}x{hidden}xf32").replace("16x16xf32", f"{hidden}x{hidden}xf32")
+            .replace("16x8xf32", f"{hidden}x{kv_width}xf32").replace("4x8xf32", f"{rows}x{kv_width}xf32")
+            .replace("16x32xf32", f"{hidden}x{intermediate}xf32").replace("4x32xf32", f"{rows}x{intermediate}xf32")
+            .replace("32x16xf32", f"{intermediate}x{hidden}xf32").replace("tensor<16xf32>", f"tensor<{hidden}xf32>"))

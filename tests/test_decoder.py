@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 sys.path.insert(0, GOLDEN)
-from stablehlo_texts import DECODER_TEXT, MOE_TEXT  # noqa: E402
+from stablehlo_texts import DECODER_TEXT, MOE_TEXT, dense_decoder_text  # noqa: E402
 
 F32_TOL = 1e-4   # max-abs relative, fp32 plan
 BF16_TOL = 2e-2  # max-abs relative, bf16 plan
@@ -77,7 +77,7 @@ def baseline_config1():
 def test_baseline_config1_fp32(port):
     kw, data = baseline_config1()
     want = port.decoder_layer(ob.decoder_config(**kw), data, native=False)
-    plan = api.DecoderCompiler.compile(api.decoder_config(**kw), weights_of(data), DECODER_TEXT.replace("4x16", "128x256"),
+    plan = api.DecoderCompiler.compile(api.decoder_config(**kw), weights_of(data), dense_decoder_text(128, 256, 128, 688),
                                        api.compile_options(dtype=L.F32))
     out, _ = plan.execute(data["input"])
     assert rel_err(out, want) < F32_TOL
