@@ -202,3 +202,61 @@ def test_paged_append_kernel_then_decode_roundtrip(dev, port):
                                       C.c_void_p(gv.data_ptr()), C.c_void_p(dtab.data_ptr()), batch, hkv, tokens, d, d,
                                       block, max_blocks, L.BF16, s))
     assert np.array_equal(dev.np(gk), k) and np.array_equal(dev.np(gv), v)
+
+
+@pytest.mark.parametrize("backend", [1, 2])  # CUDA-core kernel, tcgen05 kernel
+@pytest.mark.parametrize("batch,hq,hkv,sq,sk,causal,qscale,token_major", [
+    (2, 8, 2, 300, 300, True, 1.0, False),     # ragged tiles, causal
+    (1, 4, 4, 256, 256, False, 1.0, True),     # exact tiles, non-causal, token-major output
+    (1, 4, 1, 200, 333, True, 1.0, False),     # Sq < Sk: causal frontier offset
+    (1, 8, 2, 1000, 1000, True, 6.0, True),    # long rows with large scores: running-max growth
+    (3, 2, 2, 70, 70, True, 1.0, False),       # less than one Q tile
+])
+def test_prefill_bf16_head_dim_128(dev, port, backend, batch, hq, hkv, sq, sk, causal, qscale, token_major):
+    rng = np.random.default_rng(sq + sk)
+    q = port.round_bf16((rng.standard_normal((batch, hq, sq, 128)) * qscale).astype(np.float32))
+    k = port.round_bf16(rng.standard_normal((batch, hkv, sk, 128)).astype(np.float32))
+    v = port.round_bf16(rng.standard_normal((batch, hkv, sk, 128)).astype(np.float32))
+    oc = ob.AttentionConfig(batch, hq, hkv, sq, sk, 128, 128, int(causal), 0.0)
+    want = port.attention_reference(oc, q, k, v)
+    dq, dk, dv = dev.bf16(q), dev.bf16(k), dev.bf16(v)
+    out = dev.zeros((batch * sq * hq * 128,), dev.torch.bfloat16)
+    a = L.AttentionArgs(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), out.data_ptr(), batch, hq, hkv, sq, sk, 128, 128,
+                        int(causal), 0.0, int(token_major), L.BF16, backend)
+    L.check(L.load().sfb_k_attention_prefill(C.byref(a), C.c_void_p(dev.stream())))
+    dev.torch.cuda.synchronize()
+    word = C.c_uint32(0)
+    L.check(L.load().sfb_device_status(C.byref(word)))
+    assert word.value == 0, f"device wait timed out, status word {word.value:#x}"
+    got = dev.np(out)
+    got = got.reshape(batch, sq, hq, 128).transpose(0, 2, 1, 3) if token_major else got.reshape(batch, hq, sq, 128)
+    assert rel_err(got, want) < 2e-2
+
+
+def test_prefill_tcgen05_baseline_config2_slices(dev, port):
+    """BASELINE configs[1] shape (B4, Hq32, Hkv8, S4096, D128, causal): full run on the GPU, the
+    oracle on sampled (batch, head) slices and query rows (materialised softmax(QK^T)V)."""
+    torch = dev.torch
+    batch, hq, hkv, s = 4, 32, 8, 4096
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn((batch, hq, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    k = torch.randn((batch, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn((batch, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.zeros((batch, hq, s, 128), dtype=torch.bfloat16, device="cuda")
+    a = L.AttentionArgs(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), batch, hq, hkv, s, s, 128, 128, 1,
+                        0.0, 0, L.BF16, 2)
+    L.check(L.load().sfb_k_attention_prefill(C.byref(a), C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(0)
+    for b, h in ((0, 0), (3, 31), (1, 13)):
+        rows = np.sort(rng.choice(s, 48, replace=False))
+        rows[-1] = s - 1
+        kvh = h * hkv // hq
+        kk, vv = k[b, kvh].float().cpu().numpy(), v[b, kvh].float().cpu().numpy()
+        for row in rows:
+            # one query row against its visible prefix = a non-causal problem of length row+1
+            oc = ob.AttentionConfig(1, 1, 1, 1, int(row) + 1, 128, 128, 0, 0.0)
+            want = port.attention_reference(oc, q[b, h, row].float().cpu().numpy()[None, None, None, :],
+                                            kk[None, None, :row + 1], vv[None, None, :row + 1])[0, 0, 0]
+            got = out[b, h, row].float().cpu().numpy()
+            assert np.max(np.abs(got - want)) < 2e-2 * max(np.max(np.abs(want)), 0.05), (b, h, int(row))
