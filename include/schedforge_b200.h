@@ -242,6 +242,23 @@ sfb_status sfb_k_moe_dispatch(const void* x, sfb_dtype dtype, const int* expert_
                               int* dest_of, int* scratch, sfb_stream stream);
 size_t sfb_moe_dispatch_scratch_bytes(int tokens, int experts, int top_k);
 
+/* Same dispatch for callers that must not allocate device memory (a host process whose memory
+ * pool owns every byte, a plugin under a "no cudaMalloc after start-up" rule, a latency-critical
+ * loop): the scratch is a 66 816-byte array that lives inside the library image on every GPU that
+ * loads it, so the call takes no scratch pointer and never calls cudaMalloc/cudaFree.
+ * This entry point has no counterpart in the reference.
+ *   - limit: tokens * top_k <= 262144 and experts <= 64, else SFB_UNSUPPORTED;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture;
+ *   - all calls on one GPU share the array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no dependency) race on it; issue them on one stream or order them;
+ *   - the array keeps the last call's contents; nothing in it needs clearing between calls. */
+sfb_status sfb_k_moe_dispatch_static(const void* x, sfb_dtype dtype, const int* expert_ids,
+                                     const float* expert_weights, const int* counts, int tokens,
+                                     int hidden, int experts, int top_k, void* values, int* offsets,
+                                     int* token_ids, int* route_slots, float* routing_weights,
+                                     int* dest_of, sfb_stream stream);
+
 /* out[t,:] = (residual ? residual[t,:] : 0) + sum over the token's assignments, in
  * ascending dispatched position (= the reference's expert-major accumulation order), of
  * routing_weights[pos] * y[pos,:].

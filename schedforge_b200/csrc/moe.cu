@@ -6,6 +6,8 @@
 // assignments to the same expert instead of racing on atomics.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace sfb {
 namespace {
 
@@ -209,6 +211,42 @@ void moe_silu_mul_f32(float* first, const float* gate, int64_t count, cudaStream
 
 using namespace sfb;
 
+// ---- scratch for the allocation-free dispatch entry point -------------------------------
+// sfb_k_moe_dispatch_static serves callers that are not allowed to allocate device memory:
+// code running inside a memory-budgeted serving process whose allocator owns every byte, a
+// plugin loaded under a "no cudaMalloc after start-up" rule, or a real-time loop where an
+// allocation could stall.  They still need the per-chunk histogram the dispatch kernels use
+// as scratch, so the library carries one copy per GPU in its own image: the array below.
+// It costs kStaticScratchInts * 4 bytes = 66 816 bytes on every GPU that loads the library,
+// until the process exits.
+constexpr int kStaticMaxAssignments = 262144;  // tokens * top_k the static variant accepts
+constexpr int kStaticScratchInts = (kStaticMaxAssignments / kChunk + 1 + 4) * kMaxExperts;
+static __device__ __align__(256) int g_dispatch_scratch[kStaticScratchInts];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+int* g_scratch_address[kMaxDevices] = {};
+
+// Device address of g_dispatch_scratch on the CURRENT device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address is asked
+// for once per device with cudaGetSymbolAddress and remembered.
+sfb_status static_scratch(int** address) {
+    int device = 0;
+    SFB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail(SFB_UNSUPPORTED, "moe_dispatch_static: device index out of range");
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_address[device]) {
+        void* symbol = nullptr;
+        SFB_CUDA(cudaGetSymbolAddress(&symbol, g_dispatch_scratch));
+        if (!symbol) return fail(SFB_CUDA_ERROR, "moe_dispatch_static: scratch symbol has no device address");
+        g_scratch_address[device] = static_cast<int*>(symbol);
+    }
+    *address = g_scratch_address[device];
+    return SFB_OK;
+}
+}  // namespace
+
 extern "C" {
 
 sfb_status sfb_k_moe_route(const void* x, sfb_dtype x_dtype, const float* router, const float* bias,
@@ -279,6 +317,24 @@ sfb_status sfb_k_moe_dispatch(const void* x, sfb_dtype dtype, const int* expert_
         SFB_TRY(check_launch("moe_dispatch_gather"));
     }
     return SFB_OK;
+}
+
+sfb_status sfb_k_moe_dispatch_static(const void* x, sfb_dtype dtype, const int* expert_ids,
+                                     const float* expert_weights, const int* counts, int tokens, int hidden,
+                                     int experts, int top_k, void* values, int* offsets, int* token_ids,
+                                     int* route_slots, float* routing_weights, int* dest_of,
+                                     sfb_stream stream) {
+    SFB_REQUIRE(tokens > 0 && top_k > 0 && experts > 0, "routing trace does not match MoE configuration");
+    if (static_cast<int64_t>(tokens) * top_k > kStaticMaxAssignments || experts > kMaxExperts)
+        return fail(SFB_UNSUPPORTED,
+                    "moe_dispatch_static: tokens * top_k exceeds 262144 (or experts > 64), the size of the built-in "
+                    "scratch; use sfb_k_moe_dispatch with caller-provided scratch");
+    int* scratch = nullptr;
+    SFB_TRY(static_scratch(&scratch));
+    // Nothing in the scratch has to start at zero: the histogram kernel overwrites every entry the
+    // later kernels read, so whatever the previous call left behind is never observed.
+    return sfb_k_moe_dispatch(x, dtype, expert_ids, expert_weights, counts, tokens, hidden, experts, top_k, values,
+                              offsets, token_ids, route_slots, routing_weights, dest_of, scratch, stream);
 }
 
 sfb_status sfb_k_moe_combine(const void* y, const int* dest_of, const float* routing_weights,

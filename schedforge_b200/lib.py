@@ -98,7 +98,7 @@ EXPORTS = (
     "sfb_rope_table sfb_k_rope_split sfb_k_attention_prefill "
     "sfb_attention_decode_workspace sfb_attention_decode_default_splits sfb_k_attention_decode_paged "
     "sfb_k_paged_kv_append sfb_k_paged_kv_gather "
-    "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_combine "
+    "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_dispatch_static sfb_k_moe_combine "
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
     "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_upload_input "
     "sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce "
