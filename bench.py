@@ -154,6 +154,94 @@ def cpu_arm(steps, warmup, cfg_sample):
                       f"= {t} tokens per step ({steps} timed step(s) after {warmup} warm-up)"}
 
 
+def kernel_case(args):
+    """One kernel of the hot path, timed with CUDA events on its launching stream.
+
+    gemm       the fused gate/up projection (tcgen05, SwiGLU epilogue), Llama-3-8B shape
+               (--small: M=4096, N=16384, K=4096, 224 MB of operands, larger than L2)
+    attention  BASELINE configs[1]: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (--small: B1)
+    decode     BASELINE configs[2]: paged split-KV decode, batch 64, context ~U[512, 8192], 16-token
+               blocks, permuted block table (--small: batch 16)
+    """
+    import torch
+    from schedforge_b200 import lib as L
+    lib = L.load()
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    cur = torch.cuda.current_stream()
+    sp = C.c_void_p(cur.cuda_stream)
+    keep = []
+    if args.kernel == "gemm":
+        m, n, k = (4096, 16384, 4096) if args.small else (8192, 28672, 4096)
+        a = (torch.randn((m, k), generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+        bt = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+        o = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+        g = L.GemmArgs()
+        g.a, g.bt, g.out, g.m, g.n, g.k = a.data_ptr(), bt.data_ptr(), o.data_ptr(), m, n, k
+        g.epilogue, g.backend, g.swiglu_block = L.EPI_SWIGLU, L.GEMM_TCGEN05, 128
+        launch = lambda: L.check(lib.sfb_k_gemm_bf16(C.byref(g), sp))
+        work, unit, peak, bound = 2.0 * m * n * k, "TFLOP/s", peaks["bf16_tflops"], "tensor"
+        name, shape = "gemm_tcgen05_kernel<256>", {"m": m, "n": n, "k": k, "epilogue": "swiglu"}
+    elif args.kernel == "attention":
+        b, hq, hkv, s = (1 if args.small else 4), 32, 8, 4096
+        q = torch.randn((b, hq, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+        kk = torch.randn((b, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+        v = torch.randn((b, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+        o = torch.empty((b, hq, s, 128), dtype=torch.bfloat16, device="cuda")
+        a = L.AttentionArgs(q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(), b, hq, hkv, s, s, 128, 128, 1,
+                            0.0, 0, L.BF16, 2)
+        launch = lambda: L.check(lib.sfb_k_attention_prefill(C.byref(a), sp))
+        pairs = b * hq * s * (s + 1) / 2
+        work, unit, peak, bound = 2.0 * pairs * 256, "TFLOP/s", peaks["bf16_tflops"], "tensor"
+        name, shape = "attention_prefill_tcgen05_kernel", {"batch": b, "q_heads": hq, "kv_heads": hkv, "seq": s, "head_dim": 128, "causal": True}
+    else:
+        batch, hq, hkv, d, block = (16 if args.small else 64), 32, 8, 128, 16
+        ctx = torch.randint(512, 8193, (batch,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+        blocks_per = (ctx + block - 1) // block
+        max_blocks = 8192 // block
+        num_blocks = int(blocks_per.sum()) + 8
+        perm = torch.randperm(num_blocks, generator=torch.Generator().manual_seed(1), dtype=torch.int32)
+        table = torch.zeros((batch, max_blocks), dtype=torch.int32)
+        cursor = 0
+        for i in range(batch):
+            nb = int(blocks_per[i])
+            table[i, :nb] = perm[cursor:cursor + nb]
+            cursor += nb
+        k_pool = torch.randn((num_blocks, hkv, block, d), generator=gen, device="cuda").to(torch.bfloat16)
+        v_pool = torch.randn((num_blocks, hkv, block, d), generator=gen, device="cuda").to(torch.bfloat16)
+        q = torch.randn((batch, hq, d), generator=gen, device="cuda").to(torch.bfloat16)
+        o = torch.empty((batch, hq, d), dtype=torch.bfloat16, device="cuda")
+        dtab, dctx = table.cuda(), ctx.cuda()
+        splits = lib.sfb_attention_decode_default_splits(batch, hkv, 8192)
+        part = torch.empty((lib.sfb_attention_decode_workspace(batch, hq, d, splits) // 4,), dtype=torch.float32, device="cuda")
+        a = L.DecodeArgs(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), dtab.data_ptr(), dctx.data_ptr(), o.data_ptr(),
+                         part.data_ptr(), batch, hq, hkv, d, d, block, max_blocks, num_blocks, 8192, splits, 0.0, L.BF16)
+        keep += [dtab, dctx, part]
+        launch = lambda: L.check(lib.sfb_k_attention_decode_paged(C.byref(a), sp))
+        total_ctx = int(ctx.sum())
+        work = total_ctx * hkv * (2 * d) * 2 + 2 * batch * hq * d * 2 + int(blocks_per.sum()) * 4
+        unit, peak, bound = "GB/s", peaks["hbm_gbs"], "hbm"
+        name = "decode_paged_d128_kernel<4> + decode_combine_kernel"
+        shape = {"batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d, "block_tokens": block,
+                 "total_context": total_ctx, "splits": splits}
+    for _ in range(args.warmup):
+        launch()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(cur)
+    for _ in range(args.steps):
+        launch()
+    e1.record(cur)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    achieved = work / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+    print(json.dumps({"kernel": name, "shape": shape, "steps": args.steps, "warmup": args.warmup, "kernel_ms": ms,
+                      "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                                   "peak_source": peaks["source"], "algorithmic_work_per_launch": work}}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -162,7 +250,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default="", choices=["", "gemm", "attention", "decode"],
+                    help="time ONE kernel through the kernel ABI instead of the layer (also the ncu target)")
+    ap.add_argument("--small", action="store_true", help="--kernel: a case small enough for an ncu --set full capture")
     args = ap.parse_args()
+    if args.kernel:
+        return kernel_case(args)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
