@@ -222,7 +222,7 @@ def kernel_case(args):
         total_ctx = int(ctx.sum())
         work = total_ctx * hkv * (2 * d) * 2 + 2 * batch * hq * d * 2 + int(blocks_per.sum()) * 4
         unit, peak, bound = "GB/s", peaks["hbm_gbs"], "hbm"
-        name = "decode_paged_d128_kernel<4> + decode_combine_kernel"
+        name = "decode_paged_mma_kernel<4> + decode_combine_kernel"
         shape = {"batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d, "block_tokens": block,
                  "total_context": total_ctx, "splits": splits}
     for _ in range(args.warmup):
@@ -391,7 +391,7 @@ def main():
                     "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops, "traffic": None}
     else:
         kv_bytes = cfg["batch"] * cfg["context_sequence"] * (cfg["kv_heads"] // world) * cfg["head_dim"] * 2 * 2
-        roofline = {"kernel": "decode_paged_d128_kernel<4>", "bound": "hbm", "achieved": kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9
+        roofline = {"kernel": "decode_paged_mma_kernel<4> + combine (inside the layer)", "bound": "hbm", "achieved": kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9
                     if result.attention_milliseconds > 0 else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": (kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9 / peaks["hbm_gbs"])
                     if result.attention_milliseconds > 0 else None, "peak_source": peaks["source"],

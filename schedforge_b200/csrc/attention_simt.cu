@@ -6,6 +6,7 @@
 // The bf16 prefill hot path is the tensor-core kernel in attention_tcgen05.cu and the
 // head_dim-128 bf16 decode hot path is decode_paged_d128 below; the generic kernels here
 // cover fp32 plans, odd head sizes and serve as their cross-check.
+#include "attention_decode.cuh"
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -132,26 +133,7 @@ attention_prefill_kernel(PrefillParams p) {
     }
 }
 
-// ---- paged decode ---------------------------------------------------------------------
-// partial record per (batch, q_head, split): [max, sum, numerator[Dv]] as float32.
-struct DecodeParams {
-    const void *q, *k_pool, *v_pool;
-    const int *block_table, *context_len;
-    void* out;
-    float* partials;
-    int batch, q_heads, kv_heads, dim, dim_v, block_tokens, max_blocks, splits;
-    float scale;
-    int chunk_tokens;
-};
-
-// Split s covers tokens [s*chunk, (s+1)*chunk) of every sequence (chunk is a multiple of four KV
-// blocks), so all non-empty splits carry the same amount of work whatever the context length;
-// splits beyond a sequence's length are empty and write a neutral partial.
-__device__ __forceinline__ void split_range(int ctx, int chunk_tokens, int split, int& begin, int& end) {
-    begin = min(ctx, split * chunk_tokens);
-    end = min(ctx, begin + chunk_tokens);
-}
-
+// ---- paged decode (parameters and split rule: attention_decode.cuh) ----------------------
 // Generic: one block of 128 threads per (batch, q_head, split).  Chunks of 128 keys:
 // thread j scores key j (reads the key row through the block table), block max/sum,
 // then thread d accumulates output dimension d over the chunk.
@@ -225,243 +207,6 @@ decode_paged_generic_kernel(DecodeParams p) {
     for (int c = 0; c < 2; ++c) {
         const int d = threadIdx.x + 128 * c;
         if (d < Dv) rec[2 + d] = acc[c];
-    }
-}
-
-// bf16, head_dim = head_dim_value = 128, GROUP = q_heads / kv_heads query heads share every
-// K/V byte.  One block (4 warps) per (batch, kv_head, split).  A KV block of 16 tokens of one kv
-// head is 4 KiB of contiguous pool memory, so thread 0 streams the split's blocks into a
-// 3-stage shared-memory ring with one bulk copy (cp.async.bulk, no multicast) per K block and per
-// V block, four blocks per stage (one per warp), completion counted on an mbarrier: ~96 KiB in
-// flight per CTA keeps HBM busy independently of how many warps are resident.  Each warp then
-// reads its block from shared memory: lane l owns dims [8*(l%8), +8) and [64 + 8*(l%8), +8) of
-// token 4*i + l/8.  Each 8-lane token group keeps its own online-softmax state per query head
-// (base-2 exponentials, the running maximum moves only when a score exceeds it by 2^8); the
-// groups, warps and finally the splits are merged with the log-sum-exp rule.
-constexpr int kDecodeStages = 3;
-constexpr int kDecodePagesPerStage = 4;
-constexpr int kDecodeMaxPages = 4096;  // KV blocks one split may cover (page-id list in shared memory)
-
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
-}
-
-// GROUP query heads share a kv head; each warp serves HPW of them, so a block has
-// 4 * (GROUP / HPW) warps: warp w reads KV block (w / (GROUP/HPW)) of the stage for heads
-// [(w % (GROUP/HPW)) * HPW, +HPW).
-template <int GROUP, int HPW>
-__global__ void __launch_bounds__(128 * (GROUP / HPW), (GROUP / HPW) >= 2 ? 2 : 3)
-decode_paged_d128_kernel(DecodeParams p, uint32_t* status) {
-    constexpr int D = 128;
-    constexpr int kSets = GROUP / HPW;          // warps per KV block
-    constexpr int kThreads = 128 * kSets;
-    constexpr float kLog2e = 1.4426950408889634F;
-    extern __shared__ uint8_t decode_smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(decode_smem_raw) + 127) & ~uintptr_t(127));
-    const int P = p.block_tokens;
-    const uint32_t page_bytes = static_cast<uint32_t>(P) * D * 2;
-    const uint32_t stage_bytes = 2 * kDecodePagesPerStage * page_bytes;  // K pages then V pages
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kDecodeStages * stage_bytes);
-    uint64_t* empty_bar = full_bar + kDecodeStages;
-    volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(empty_bar + kDecodeStages);
-    int* page_ids = reinterpret_cast<int*>(empty_bar + kDecodeStages) + 2;
-
-    const int split = blockIdx.z, kvh = blockIdx.y, b = blockIdx.x;
-    const int ctx = p.context_len[b];
-    int begin, end;
-    split_range(ctx, p.chunk_tokens, split, begin, end);
-    if (begin >= end) {  // nothing of this sequence falls into this split: neutral partial
-        for (int idx = threadIdx.x; idx < GROUP * D; idx += kThreads) {
-            const int h = idx / D, d = idx % D;
-            float* rec = p.partials + ((static_cast<size_t>(b) * p.q_heads + kvh * GROUP + h) * p.splits + split) * (D + 2);
-            if (d == 0) { rec[0] = -INFINITY; rec[1] = 0.0F; }
-            rec[2 + d] = 0.0F;
-        }
-        return;
-    }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int page_slot = warp / kSets, head0 = (warp % kSets) * HPW;
-    const int sub = lane & 7, grp = lane >> 3;
-    const bf16* qbase = static_cast<const bf16*>(p.q) + (static_cast<size_t>(b) * p.q_heads + kvh * GROUP + head0) * D;
-    float qreg[HPW][16];
-#pragma unroll
-    for (int h = 0; h < HPW; ++h) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const uint4 packed = *reinterpret_cast<const uint4*>(qbase + h * D + half * 64 + sub * 8);
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&packed);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(h2[i]);
-                qreg[h][half * 8 + 2 * i] = f.x * p.scale * kLog2e;
-                qreg[h][half * 8 + 2 * i + 1] = f.y * p.scale * kLog2e;
-            }
-        }
-    }
-    float mx[HPW], den[HPW], acc[HPW][16];
-#pragma unroll
-    for (int h = 0; h < HPW; ++h) {
-        mx[h] = -INFINITY;
-        den[h] = 0.0F;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[h][i] = 0.0F;
-    }
-    const int* table = p.block_table + static_cast<size_t>(b) * p.max_blocks;
-    const uint8_t* kpool = static_cast<const uint8_t*>(p.k_pool);
-    const uint8_t* vpool = static_cast<const uint8_t*>(p.v_pool);
-    const int first_block = begin / P, last_block = (end + P - 1) / P;
-    const int n_pages = max(0, last_block - first_block);
-    const int n_stages = (n_pages + kDecodePagesPerStage - 1) / kDecodePagesPerStage;
-    for (int i = threadIdx.x; i < n_pages; i += kThreads) page_ids[i] = table[first_block + i];
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kDecodeStages; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 4 * kSets);
-        }
-        *abort_flag = 0;
-        ptx::fence_barrier_init();
-        ptx::fence_proxy_async();
-    }
-    __syncthreads();
-    auto issue_stage = [&](int it) -> bool {  // thread 0 only
-        const int s = it % kDecodeStages;
-        if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[s]), ((it / kDecodeStages) & 1) ^ 1, abort_flag, status, 0x20))
-            return false;
-        const int np = min(kDecodePagesPerStage, n_pages - it * kDecodePagesPerStage);
-        const uint32_t bar = ptx::smem_u32(&full_bar[s]);
-        ptx::mbar_expect_tx(bar, static_cast<uint32_t>(np) * 2 * page_bytes);
-        uint8_t* stage = smem + s * stage_bytes;
-        for (int w = 0; w < np; ++w) {
-            const size_t src = (static_cast<size_t>(page_ids[it * kDecodePagesPerStage + w]) * p.kv_heads + kvh) * page_bytes;
-            bulk_copy_g2s(ptx::smem_u32(stage + w * page_bytes), kpool + src, page_bytes, bar);
-            bulk_copy_g2s(ptx::smem_u32(stage + (kDecodePagesPerStage + w) * page_bytes), vpool + src, page_bytes, bar);
-        }
-        return true;
-    };
-    if (threadIdx.x == 0)
-        for (int it = 0; it < min(kDecodeStages, n_stages); ++it) issue_stage(it);
-    const int quads = P / 4;
-    for (int it = 0; it < n_stages; ++it) {
-        const int s = it % kDecodeStages;
-        if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[s]), (it / kDecodeStages) & 1, abort_flag, status, 0x40)) break;
-        const int local = it * kDecodePagesPerStage + page_slot;
-        if (local < n_pages) {
-            const uint8_t* kpage = smem + s * stage_bytes + page_slot * page_bytes;
-            const uint8_t* vpage = kpage + kDecodePagesPerStage * page_bytes;
-            const int token0 = (first_block + local) * P;
-#pragma unroll 2
-            for (int quad = 0; quad < quads; ++quad) {
-                const int slot = quad * 4 + grp;
-                const bool live = token0 + slot < end;
-                const uint32_t off = static_cast<uint32_t>(slot) * (D * 2) + sub * 16;
-                const uint4 k0 = *reinterpret_cast<const uint4*>(kpage + off);
-                const uint4 k1 = *reinterpret_cast<const uint4*>(kpage + off + 128);
-                const uint4 v0 = *reinterpret_cast<const uint4*>(vpage + off);
-                const uint4 v1 = *reinterpret_cast<const uint4*>(vpage + off + 128);
-                float kf[16], vf[16];
-                {
-                    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&k0);
-                    const __nv_bfloat162* c = reinterpret_cast<const __nv_bfloat162*>(&k1);
-                    const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v0);
-                    const __nv_bfloat162* g = reinterpret_cast<const __nv_bfloat162*>(&v1);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float2 f = __bfloat1622float2(a[i]); kf[2 * i] = f.x; kf[2 * i + 1] = f.y;
-                        f = __bfloat1622float2(c[i]); kf[8 + 2 * i] = f.x; kf[8 + 2 * i + 1] = f.y;
-                        f = __bfloat1622float2(e[i]); vf[2 * i] = f.x; vf[2 * i + 1] = f.y;
-                        f = __bfloat1622float2(g[i]); vf[8 + 2 * i] = f.x; vf[8 + 2 * i + 1] = f.y;
-                    }
-                }
-                // all partial dot products first (four independent chains per head), then all shuffles
-                float dot[HPW];
-#pragma unroll
-                for (int h = 0; h < HPW; ++h) {
-                    float d0 = 0.0F, d1 = 0.0F, d2 = 0.0F, d3 = 0.0F;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        d0 = fmaf(qreg[h][i], kf[i], d0);
-                        d1 = fmaf(qreg[h][4 + i], kf[4 + i], d1);
-                        d2 = fmaf(qreg[h][8 + i], kf[8 + i], d2);
-                        d3 = fmaf(qreg[h][12 + i], kf[12 + i], d3);
-                    }
-                    dot[h] = (d0 + d1) + (d2 + d3);
-                }
-#pragma unroll
-                for (int o = 1; o <= 4; o <<= 1) {
-#pragma unroll
-                    for (int h = 0; h < HPW; ++h) dot[h] += __shfl_xor_sync(0xffffffffu, dot[h], o);
-                }
-#pragma unroll
-                for (int h = 0; h < HPW; ++h) {
-                    const float score = live ? dot[h] : -INFINITY;
-                    if (score > mx[h] + 8.0F) {  // rare after the first tokens; also the first live token (mx = -inf)
-                        const float alpha = exp2f(mx[h] - score);
-                        den[h] *= alpha;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) acc[h][i] *= alpha;
-                        mx[h] = score;
-                    }
-                    const float prob = live ? exp2f(score - mx[h]) : 0.0F;
-                    den[h] += prob;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) acc[h][i] = fmaf(prob, vf[i], acc[h][i]);
-                }
-            }
-        }
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&empty_bar[s]));
-        if (threadIdx.x == 0 && it + kDecodeStages < n_stages)
-            if (!issue_stage(it + kDecodeStages)) break;
-    }
-    __syncthreads();
-    if (*abort_flag)
-        for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land before the CTA exits
-    // merge the four token groups of the warp (lanes differing in bits 3 and 4)
-#pragma unroll
-    for (int h = 0; h < HPW; ++h) {
-#pragma unroll
-        for (int off = 8; off <= 16; off <<= 1) {
-            const float om = __shfl_xor_sync(0xffffffffu, mx[h], off);
-            const float od = __shfl_xor_sync(0xffffffffu, den[h], off);
-            const float nm = fmaxf(mx[h], om);
-            const float sa = mx[h] == -INFINITY ? 0.0F : exp2f(mx[h] - nm);
-            const float sb = om == -INFINITY ? 0.0F : exp2f(om - nm);
-            den[h] = den[h] * sa + od * sb;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float oa = __shfl_xor_sync(0xffffffffu, acc[h][i], off);
-                acc[h][i] = acc[h][i] * sa + oa * sb;
-            }
-            mx[h] = nm;
-        }
-    }
-    // merge the four page slots through shared memory
-    __shared__ float wm[4][GROUP], wd[4][GROUP], wacc[4][GROUP][D];
-    if (grp == 0) {
-#pragma unroll
-        for (int h = 0; h < HPW; ++h) {
-            if (sub == 0) { wm[page_slot][head0 + h] = mx[h]; wd[page_slot][head0 + h] = den[h]; }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) wacc[page_slot][head0 + h][(i / 8) * 64 + sub * 8 + (i % 8)] = acc[h][i];
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < GROUP * D; idx += kThreads) {
-        const int h = idx / D, d = idx % D;
-        float m = fmaxf(fmaxf(wm[0][h], wm[1][h]), fmaxf(wm[2][h], wm[3][h]));
-        float s = 0.0F, a = 0.0F;
-        if (m != -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float sc = wm[w][h] == -INFINITY ? 0.0F : exp2f(wm[w][h] - m);
-                s += wd[w][h] * sc;
-                a += wacc[w][h][d] * sc;
-            }
-        }
-        float* rec = p.partials + ((static_cast<size_t>(b) * p.q_heads + kvh * GROUP + h) * p.splits + split) * (D + 2);
-        if (d == 0) { rec[0] = m * 0.6931471805599453F; rec[1] = s; }  // maximum back in natural-log units
-        rec[2 + d] = a;
     }
 }
 
@@ -625,28 +370,10 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream str
     const int pages_bound = ceil_div(ceil_div(a->max_context > 0 ? a->max_context : a->max_blocks * a->block_tokens,
                                               a->block_tokens), splits) + 2;
     const bool fast = a->dtype == SFB_BF16 && a->head_dim == 128 && a->head_dim_value == 128 &&
-                      a->block_tokens % 4 == 0 && a->block_tokens <= 32 && pages_bound <= kDecodeMaxPages &&
-                      (group == 1 || group == 2 || group == 4 || group == 8) &&
+                      a->block_tokens == 16 && a->num_blocks > 0 && pages_bound <= kDecodeMaxPages && group <= 8 &&
                       (reinterpret_cast<uintptr_t>(a->k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->v_pool) & 15) == 0;
     if (fast) {
-        dim3 grid(a->batch, a->kv_heads, splits);
-        const size_t page_bytes = static_cast<size_t>(a->block_tokens) * 128 * 2;
-        const int pages_per_split = p.chunk_tokens / a->block_tokens + 2;
-        const size_t smem = kDecodeStages * 2 * kDecodePagesPerStage * page_bytes + 64 + sizeof(int) * (pages_per_split + 2) + 128;
-        uint32_t* status = device_status_word();
-#define SFB_LAUNCH_DECODE(G, HPW)                                                                              \
-        do {                                                                                                   \
-            SFB_CUDA(cudaFuncSetAttribute(decode_paged_d128_kernel<G, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                          static_cast<int>(smem)));                                            \
-            decode_paged_d128_kernel<G, HPW><<<grid, 128 * (G / HPW), smem, s>>>(p, status);                   \
-        } while (0)
-        switch (group) {
-            case 1: SFB_LAUNCH_DECODE(1, 1); break;
-            case 2: SFB_LAUNCH_DECODE(2, 1); break;
-            case 4: SFB_LAUNCH_DECODE(4, 2); break;
-            default: SFB_LAUNCH_DECODE(8, 4); break;
-        }
-#undef SFB_LAUNCH_DECODE
+        SFB_TRY(decode_paged_d128_launch(p, *a, group, s));
     } else {
         if (a->head_dim_value > 256) return fail(SFB_UNSUPPORTED, "paged decode: head_dim_value > 256");
         dim3 grid(a->batch * a->q_heads, splits);
