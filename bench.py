@@ -248,7 +248,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="", choices=["", "gemm", "attention", "decode"],
                     help="time ONE kernel through the kernel ABI instead of the layer (also the ncu target)")
@@ -260,11 +260,14 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    shape = PREFILL if args.workload == "prefill" else DECODE
+    shape = DECODE if args.workload == "decode" else PREFILL
     cfg = dict(LLAMA, **shape)
+    if args.workload == "moe":  # Mixtral-shaped layer: 8 experts, top-2, expert FFN 14336, 8192 tokens
+        cfg.update(moe=True, experts=8, top_k=2)
     tokens = cfg["batch"] * cfg["sequence"]
-    workload = ("llama3_8b_decoder_layer_prefill_b4_s2048" if args.workload == "prefill"
-                else "llama3_8b_decoder_layer_decode_b128_ctx2048")
+    workload = {"prefill": "llama3_8b_decoder_layer_prefill_b4_s2048",
+                "decode": "llama3_8b_decoder_layer_decode_b128_ctx2048",
+                "moe": "mixtral_moe_decoder_layer_8x_top2_t8192"}[args.workload]
     config = {"workload": workload, "hidden": 4096, "intermediate": 14336, "q_heads": 32, "kv_heads": 8,
               "head_dim": 128, "tokens_per_step": tokens, "parallelism": f"tp{world}",
               "l2": "weights + activations (>0.9 GB per step) exceed the 126 MB L2; no flush between steps"}
@@ -294,6 +297,15 @@ def main():
     lib = L.load()
 
     data = make_weights(0, cfg, with_cache=args.workload == "decode")
+    if args.workload == "moe":
+        g = torch.Generator().manual_seed(7)
+        h, i, e = cfg["hidden"], cfg["intermediate"], cfg["experts"]
+        for key in ("gate_weight", "up_weight", "down_weight"):
+            data.pop(key)
+        data["router_weight"] = (torch.randn((h, e), generator=g) * 0.02).numpy()
+        data["router_bias"] = torch.randn(e, generator=g).numpy()  # per-expert bias: skewed expert loads
+        for key, shape_ in (("w1", (e, h, i)), ("w3", (e, h, i)), ("w2", (e, i, h))):
+            data[key] = torch.empty(shape_).normal_(0.0, 0.02, generator=g).numpy()
     x_host = torch.randn((tokens, cfg["hidden"]), generator=torch.Generator().manual_seed(1)).pin_memory()
     out_host = torch.empty((tokens, cfg["hidden"]), dtype=torch.float32).pin_memory()
     c = api.decoder_config(**cfg)
@@ -389,6 +401,15 @@ def main():
                     "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst: kernel timed alone)",
                     "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops, "traffic": None}
+    elif args.workload == "moe":
+        flops = 6.0 * tokens * cfg["top_k"] * cfg["hidden"] * cfg["intermediate"] / world
+        achieved = flops / (result.ffn_milliseconds * 1e-3) / 1e12 if result.ffn_milliseconds > 0 else None
+        roofline = {"kernel": "gemm_tcgen05_kernel<256> grouped mode (experts W3|W1 + SwiGLU, then W2), timed with the "
+                              "routing chain around it (router, dispatch, combine)", "bound": "tensor",
+                    "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops_sustained"] if achieved else None,
+                    "peak_source": peaks["source"] + " (sustained: timed inside the layer step)",
+                    "kernel_ms": result.ffn_milliseconds, "algorithmic_flops_per_launch": flops, "traffic": None}
     else:
         kv_bytes = cfg["batch"] * cfg["context_sequence"] * (cfg["kv_heads"] // world) * cfg["head_dim"] * 2 * 2
         roofline = {"kernel": "decode_paged_mma_kernel<4> + combine (inside the layer)", "bound": "hbm", "achieved": kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9

@@ -6,11 +6,12 @@
 //   warps 4-7   (tile 1)  its 64 scores from tensor memory, masks, takes the row max, and writes
 //               p = 2^(s*c - m) as bf16 into a 128-byte-swizzled shared-memory tile that the next
 //               MMA reads as its A operand.  No cross-thread reduction is ever needed.
-//   warp 8      TMA producer: Q tiles once, then K and V tiles through a 3-stage ring.
+//   warp 8      TMA producer: Q tiles once, then K tiles (4-deep ring) and V tiles (3-deep ring).
 //   warp 9      MMA issuer (one thread): S_t = Q_t.K^T (M128 N64 K128) into tensor memory, then
 //               O_t += P_t.V (M128 N128 K64, V as an MN-major operand) accumulated in tensor
-//               memory.  The two Q tiles alternate, so while one group does exponentials the
-//               tensor pipe works for the other.
+//               memory.  S is double-buffered per Q tile: Q.K^T of KV tile j+2 is issued as soon
+//               as the softmax group has consumed tile j, so a group never waits for the tensor
+//               pipe, and the two Q tiles alternate on it.
 // Running maxima are updated lazily: the accumulator in tensor memory is rescaled (by the
 // owning softmax group, with tcgen05.ld/st) only when a row maximum grows by more than 2^8;
 // the final division by the row sum makes the result exact regardless.
@@ -26,14 +27,16 @@ namespace {
 constexpr int D = 128;          // head_dim == head_dim_value
 constexpr int QT = 128;         // rows per Q tile
 constexpr int KT = 64;          // keys per KV tile
-constexpr int STAGES = 3;
+constexpr int KSTAGES = 4;       // K ring (Q.K^T runs two tiles ahead of P.V)
+constexpr int VSTAGES = 3;       // V ring
 constexpr int kThreads = 320;
 constexpr int kQBytes = QT * D * 2;        // 32 KiB per Q tile (two 16 KiB halves of 64 dims)
 constexpr int kKBytes = KT * D * 2;        // 16 KiB
 constexpr int kVBytes = KT * D * 2;        // 16 KiB
 constexpr int kPBytes = QT * KT * 2;       // 16 KiB per Q tile
-constexpr int kSmemBytes = 2 * kQBytes + STAGES * (kKBytes + kVBytes) + 2 * kPBytes + 512 + 1024;
-constexpr uint32_t kTmemCols = 512;        // S0 [0,64) S1 [64,128) O0 [128,256) O1 [256,384)
+constexpr int kSmemBytes = 2 * kQBytes + KSTAGES * kKBytes + VSTAGES * kVBytes + 2 * kPBytes + 512 + 1024;
+constexpr uint32_t kTmemCols = 512;        // S[t][buf] at (2t+buf)*64 in [0,256); O0 [256,384) O1 [384,512)
+constexpr uint32_t kOCol = 256;
 constexpr uint32_t kCodeAttn = 0x10;
 constexpr float kRescaleThreshold = 8.0F;  // log2 units
 
@@ -57,16 +60,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_smem = smem;                                  // [2][2 halves][128][64]
-    uint8_t* k_smem = q_smem + 2 * kQBytes;                  // [STAGES][2 halves][64][64]
-    uint8_t* v_smem = k_smem + STAGES * kKBytes;             // [STAGES][2 halves][64 keys][64 dv]
-    uint8_t* p_smem = v_smem + STAGES * kVBytes;             // [2][128][64]
+    uint8_t* k_smem = q_smem + 2 * kQBytes;                  // [KSTAGES][2 halves][64][64]
+    uint8_t* v_smem = k_smem + KSTAGES * kKBytes;            // [VSTAGES][2 halves][64 keys][64 dv]
+    uint8_t* p_smem = v_smem + VSTAGES * kVBytes;            // [2][128][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * kPBytes);
     uint64_t* q_full = bars;                 // [2]
-    uint64_t* k_full = bars + 2;             // [STAGES]
-    uint64_t* v_full = k_full + STAGES;      // [STAGES]
-    uint64_t* kv_empty = v_full + STAGES;    // [STAGES]
-    uint64_t* s_full = kv_empty + STAGES;    // [2]
-    uint64_t* p_full = s_full + 2;           // [2]
+    uint64_t* k_full = bars + 2;             // [KSTAGES]
+    uint64_t* k_empty = k_full + KSTAGES;    // [KSTAGES]
+    uint64_t* v_full = k_empty + KSTAGES;    // [VSTAGES]
+    uint64_t* v_empty = v_full + VSTAGES;    // [VSTAGES]
+    uint64_t* s_full = v_empty + VSTAGES;    // [2 tiles][2 buffers]
+    uint64_t* p_full = s_full + 4;           // [2]
     uint64_t* pv_done = p_full + 2;          // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -96,14 +100,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
     if (threadIdx.x == 0) {
         for (int t = 0; t < 2; ++t) {
             ptx::mbar_init(ptx::smem_u32(&q_full[t]), 1);
-            ptx::mbar_init(ptx::smem_u32(&s_full[t]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_full[2 * t]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_full[2 * t + 1]), 1);
             ptx::mbar_init(ptx::smem_u32(&p_full[t]), QT);
             ptx::mbar_init(ptx::smem_u32(&pv_done[t]), 1);
         }
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < KSTAGES; ++s) {
             ptx::mbar_init(ptx::smem_u32(&k_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&k_empty[s]), 1);
+        }
+        for (int s = 0; s < VSTAGES; ++s) {
             ptx::mbar_init(ptx::smem_u32(&v_full[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&kv_empty[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&v_empty[s]), 1);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -132,17 +140,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 ptx::tma_load_2d(ptx::smem_u32(q_smem + t * kQBytes + kQBytes / 2), &tma_q, bar, 64, q_row0 + t * QT);
             }
             for (int j = 0; j < n_max; ++j) {
-                const int s = j % STAGES;
-                const uint32_t ph = (j / STAGES) & 1;
-                if (!ptx::mbar_wait(ptx::smem_u32(&kv_empty[s]), ph ^ 1, abort_flag, p.status, kCodeAttn | 1)) break;
-                const uint32_t kb = ptx::smem_u32(&k_full[s]), vb = ptx::smem_u32(&v_full[s]);
+                const int ks = j % KSTAGES, vs = j % VSTAGES;
                 const int row = kv_row0 + j * KT;
+                if (!ptx::mbar_wait(ptx::smem_u32(&k_empty[ks]), ((j / KSTAGES) & 1) ^ 1, abort_flag, p.status, kCodeAttn | 1)) break;
+                const uint32_t kb = ptx::smem_u32(&k_full[ks]);
                 ptx::mbar_expect_tx(kb, kKBytes);
-                ptx::tma_load_2d(ptx::smem_u32(k_smem + s * kKBytes), &tma_k, kb, 0, row);
-                ptx::tma_load_2d(ptx::smem_u32(k_smem + s * kKBytes + kKBytes / 2), &tma_k, kb, 64, row);
+                ptx::tma_load_2d(ptx::smem_u32(k_smem + ks * kKBytes), &tma_k, kb, 0, row);
+                ptx::tma_load_2d(ptx::smem_u32(k_smem + ks * kKBytes + kKBytes / 2), &tma_k, kb, 64, row);
+                if (!ptx::mbar_wait(ptx::smem_u32(&v_empty[vs]), ((j / VSTAGES) & 1) ^ 1, abort_flag, p.status, kCodeAttn | 1)) break;
+                const uint32_t vb = ptx::smem_u32(&v_full[vs]);
                 ptx::mbar_expect_tx(vb, kVBytes);
-                ptx::tma_load_2d(ptx::smem_u32(v_smem + s * kVBytes), &tma_v, vb, 0, row);
-                ptx::tma_load_2d(ptx::smem_u32(v_smem + s * kVBytes + kVBytes / 2), &tma_v, vb, 64, row);
+                ptx::tma_load_2d(ptx::smem_u32(v_smem + vs * kVBytes), &tma_v, vb, 0, row);
+                ptx::tma_load_2d(ptx::smem_u32(v_smem + vs * kVBytes + kVBytes / 2), &tma_v, vb, 64, row);
             }
         }
     } else if (warp == 9) {
@@ -150,55 +159,61 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
         if (lane == 0) {
             constexpr uint32_t idesc_qk = ptx::umma_idesc_bf16(QT, KT, 0, 0);
             constexpr uint32_t idesc_pv = ptx::umma_idesc_bf16(QT, D, 0, 1);
-            auto issue_qk = [&](int t, int j) {
-                const int s = j % STAGES;
+            auto issue_qk = [&](int t, int j) {  // S_t[j & 1] = Q_t . K_j^T
+                const int s = j % KSTAGES;
                 const uint32_t qa = ptx::smem_u32(q_smem + t * kQBytes), ka = ptx::smem_u32(k_smem + s * kKBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = ptx::umma_desc_k_sw128(qa + (kk / 4) * (kQBytes / 2) + (kk % 4) * 32);
                     const uint64_t db = ptx::umma_desc_k_sw128(ka + (kk / 4) * (kKBytes / 2) + (kk % 4) * 32);
-                    ptx::umma_bf16(tmem_base + t * KT, da, db, idesc_qk, kk != 0);
+                    ptx::umma_bf16(tmem_base + (2 * t + (j & 1)) * KT, da, db, idesc_qk, kk != 0);
                 }
-                ptx::umma_commit(ptx::smem_u32(&s_full[t]));
+                ptx::umma_commit(ptx::smem_u32(&s_full[2 * t + (j & 1)]));
             };
-            auto issue_pv = [&](int t, int j) {
-                const int s = j % STAGES;
+            auto issue_pv = [&](int t, int j) {  // O_t += P_t . V_j
+                const int s = j % VSTAGES;
                 const uint32_t pa = ptx::smem_u32(p_smem + t * kPBytes), va = ptx::smem_u32(v_smem + s * kVBytes);
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
                     const uint64_t da = ptx::umma_desc_k_sw128(pa + kk * 32);
                     const uint64_t db = ptx::umma_desc_mn_sw128(va + kk * 16 * 128, kVBytes / 2, 1024);
-                    ptx::umma_bf16(tmem_base + 128 + t * D, da, db, idesc_pv, (j | kk) != 0);
+                    ptx::umma_bf16(tmem_base + kOCol + t * D, da, db, idesc_pv, (j | kk) != 0);
                 }
                 ptx::umma_commit(ptx::smem_u32(&pv_done[t]));
             };
             bool ok = true;
             for (int t = 0; t < 2 && ok; ++t)
                 if (n_tiles[t] > 0) ok = ptx::mbar_wait(ptx::smem_u32(&q_full[t]), 0, abort_flag, p.status, kCodeAttn | 2);
-            if (ok && n_max > 0) ok = ptx::mbar_wait(ptx::smem_u32(&k_full[0]), 0, abort_flag, p.status, kCodeAttn | 2);
-            if (ok) {
+            // prologue: scores of KV tiles 0 and 1 for both Q tiles
+            for (int j = 0; ok && j < min(2, n_max); ++j) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&k_full[j % KSTAGES]), (j / KSTAGES) & 1, abort_flag, p.status, kCodeAttn | 2);
+                if (!ok) break;
                 ptx::tc_fence_after();
                 for (int t = 0; t < 2; ++t)
-                    if (n_tiles[t] > 0) issue_qk(t, 0);
+                    if (j < n_tiles[t]) issue_qk(t, j);
+                ptx::umma_commit(ptx::smem_u32(&k_empty[j % KSTAGES]));
             }
             for (int j = 0; ok && j < n_max; ++j) {
-                const int s = j % STAGES;
+                const int vs = j % VSTAGES;
                 for (int t = 0; ok && t < 2; ++t) {
                     if (j >= n_tiles[t]) continue;
                     ok = ptx::mbar_wait(ptx::smem_u32(&p_full[t]), j & 1, abort_flag, p.status, kCodeAttn | 2) &&
-                         ptx::mbar_wait(ptx::smem_u32(&v_full[s]), (j / STAGES) & 1, abort_flag, p.status, kCodeAttn | 2);
+                         ptx::mbar_wait(ptx::smem_u32(&v_full[vs]), (j / VSTAGES) & 1, abort_flag, p.status, kCodeAttn | 2);
                     if (!ok) break;
                     ptx::tc_fence_after();
                     issue_pv(t, j);
-                    if (j + 1 < n_tiles[t]) {
-                        ok = ptx::mbar_wait(ptx::smem_u32(&k_full[(j + 1) % STAGES]), ((j + 1) / STAGES) & 1, abort_flag,
+                    if (j + 2 < n_tiles[t]) {  // S_t[j & 1] has been consumed: next scores into it
+                        ok = ptx::mbar_wait(ptx::smem_u32(&k_full[(j + 2) % KSTAGES]), ((j + 2) / KSTAGES) & 1, abort_flag,
                                             p.status, kCodeAttn | 2);
                         if (!ok) break;
                         ptx::tc_fence_after();
-                        issue_qk(t, j + 1);
+                        issue_qk(t, j + 2);
                     }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&kv_empty[s]));
+                if (ok) {
+                    ptx::umma_commit(ptx::smem_u32(&v_empty[vs]));
+                    if (j + 2 < n_max) ptx::umma_commit(ptx::smem_u32(&k_empty[(j + 2) % KSTAGES]));
+                }
             }
         }
     } else {
@@ -208,16 +223,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
         const int r = quarter * 32 + lane;       // row inside the tile == tensor-memory lane
         const int qi = q0 + t * QT + r;          // query index inside the sequence
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_base + t * KT;
-        const uint32_t o_addr = tmem_base + lane_base + 128 + t * D;
+        const uint32_t s_addr0 = tmem_base + lane_base + 2 * t * KT;
+        const uint32_t o_addr = tmem_base + lane_base + kOCol + t * D;
         uint8_t* p_row = p_smem + t * kPBytes + r * 128;
         const int nt = n_tiles[t];
         float m_used = -INFINITY, row_sum = 0.0F;
         bool ok = true;
         for (int j = 0; ok && j < nt; ++j) {
-            ok = ptx::mbar_wait(ptx::smem_u32(&s_full[t]), j & 1, abort_flag, p.status, kCodeAttn | 4);
+            ok = ptx::mbar_wait(ptx::smem_u32(&s_full[2 * t + (j & 1)]), (j >> 1) & 1, abort_flag, p.status, kCodeAttn | 4);
             if (!ok) break;
             ptx::tc_fence_after();
+            const uint32_t s_addr = s_addr0 + (j & 1) * KT;
             uint32_t raw[2][32];
             ptx::tmem_ld_32x32(s_addr, raw[0]);
             ptx::tmem_ld_32x32(s_addr + 32, raw[1]);
