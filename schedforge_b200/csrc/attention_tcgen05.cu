@@ -1,20 +1,24 @@
 // Flash-attention prefill on the 5th-generation tensor cores (bf16, head_dim = 128).
 //
 // One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row Q tiles and walks
-// the keys in tiles of 64.  320 threads in four roles:
-//   warps 0-3   softmax group of Q tile 0: thread r owns query row r.  Per KV tile it reads
-//   warps 4-7   (tile 1)  its 64 scores from tensor memory, masks, takes the row max, and writes
-//               p = 2^(s*c - m) as bf16 into a 128-byte-swizzled shared-memory tile that the next
-//               MMA reads as its A operand.  No cross-thread reduction is ever needed.
-//   warp 8      TMA producer: Q tiles once, then K tiles (4-deep ring) and V tiles (3-deep ring).
-//   warp 9      MMA issuer (one thread): S_t = Q_t.K^T (M128 N64 K128) into tensor memory, then
-//               O_t += P_t.V (M128 N128 K64, V as an MN-major operand) accumulated in tensor
-//               memory.  S is double-buffered per Q tile: Q.K^T of KV tile j+2 is issued as soon
-//               as the softmax group has consumed tile j, so a group never waits for the tensor
-//               pipe, and the two Q tiles alternate on it.
-// Running maxima are updated lazily: the accumulator in tensor memory is rescaled (by the
-// owning softmax group, with tcgen05.ld/st) only when a row maximum grows by more than 2^8;
-// the final division by the row sum makes the result exact regardless.
+// the keys in tiles of 128.  320 threads in four roles:
+//   warps 0-3   softmax group of Q tile 0: thread r owns query row r (= tensor-memory lane r), so
+//   warps 4-7   (tile 1)  no cross-thread reduction is ever needed.  Per KV tile it reads its 128
+//               scores from tensor memory twice (row maximum, then exponentials), and writes
+//               p = 2^(s*c - m) as packed bf16 back into tensor memory OVER the scores it has
+//               consumed; the next MMA reads P from there as its A operand.
+//   warp 8      TMA producer: Q tiles once, then K and V tiles through two 2-deep rings.
+//   warp 9      MMA issuer (one thread): S_t = Q_t.K^T (M128 N128 K128, both operands in shared
+//               memory) and O_t += P_t.V (M128 N128 K128, A = P_t from tensor memory, B = V as an
+//               MN-major shared-memory operand), accumulators in tensor memory
+//               (S0 S1 O0 O1 = 512 columns).  The two Q tiles alternate on the tensor pipe, so
+//               while one group does exponentials the pipe works for the other.
+// Keeping P in tensor memory and using 128-key tiles halves the shared-memory operand traffic per
+// key compared with a 64-key tile and a P tile in shared memory; that traffic, not the MMA rate,
+// bounded the first version of this kernel.
+// Running maxima move lazily: the accumulator is rescaled (by the owning softmax group, with
+// tcgen05.ld/st) only when a row maximum grows by more than 2^8; the final division by the row
+// sum makes the result exact regardless.
 // Causal masking follows the reference: key j is visible to query i iff j <= Sk - Sq + i; KV
 // tiles above the frontier of a Q tile are never loaded or multiplied for it.
 // Every wait is bounded (see ptx_sm100.cuh).
@@ -26,16 +30,15 @@ namespace {
 
 constexpr int D = 128;          // head_dim == head_dim_value
 constexpr int QT = 128;         // rows per Q tile
-constexpr int KT = 64;          // keys per KV tile
-constexpr int KSTAGES = 4;       // K ring (Q.K^T runs two tiles ahead of P.V)
-constexpr int VSTAGES = 3;       // V ring
+constexpr int KT = 128;         // keys per KV tile
+constexpr int KSTAGES = 2;
+constexpr int VSTAGES = 2;
 constexpr int kThreads = 320;
 constexpr int kQBytes = QT * D * 2;        // 32 KiB per Q tile (two 16 KiB halves of 64 dims)
-constexpr int kKBytes = KT * D * 2;        // 16 KiB
-constexpr int kVBytes = KT * D * 2;        // 16 KiB
-constexpr int kPBytes = QT * KT * 2;       // 16 KiB per Q tile
-constexpr int kSmemBytes = 2 * kQBytes + KSTAGES * kKBytes + VSTAGES * kVBytes + 2 * kPBytes + 512 + 1024;
-constexpr uint32_t kTmemCols = 512;        // S[t][buf] at (2t+buf)*64 in [0,256); O0 [256,384) O1 [384,512)
+constexpr int kKBytes = KT * D * 2;        // 32 KiB (two halves of 64 dims)
+constexpr int kVBytes = KT * D * 2;        // 32 KiB (two halves of 64 value dims)
+constexpr int kSmemBytes = 2 * kQBytes + KSTAGES * kKBytes + VSTAGES * kVBytes + 512 + 1024;
+constexpr uint32_t kTmemCols = 512;        // S_t (and P_t over its first 64 columns) at t*128; O_t at 256 + t*128
 constexpr uint32_t kOCol = 256;
 constexpr uint32_t kCodeAttn = 0x10;
 constexpr float kRescaleThreshold = 8.0F;  // log2 units
@@ -60,19 +63,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_smem = smem;                                  // [2][2 halves][128][64]
-    uint8_t* k_smem = q_smem + 2 * kQBytes;                  // [KSTAGES][2 halves][64][64]
-    uint8_t* v_smem = k_smem + KSTAGES * kKBytes;            // [VSTAGES][2 halves][64 keys][64 dv]
-    uint8_t* p_smem = v_smem + VSTAGES * kVBytes;            // [2][128][64]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * kPBytes);
+    uint8_t* k_smem = q_smem + 2 * kQBytes;                  // [KSTAGES][2 halves][128 keys][64 dims]
+    uint8_t* v_smem = k_smem + KSTAGES * kKBytes;            // [VSTAGES][2 halves][128 keys][64 dv]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + VSTAGES * kVBytes);
     uint64_t* q_full = bars;                 // [2]
     uint64_t* k_full = bars + 2;             // [KSTAGES]
     uint64_t* k_empty = k_full + KSTAGES;    // [KSTAGES]
     uint64_t* v_full = k_empty + KSTAGES;    // [VSTAGES]
     uint64_t* v_empty = v_full + VSTAGES;    // [VSTAGES]
-    uint64_t* s_full = v_empty + VSTAGES;    // [2 tiles][2 buffers]
-    uint64_t* p_full = s_full + 4;           // [2]
-    uint64_t* pv_done = p_full + 2;          // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+    uint64_t* s_full = v_empty + VSTAGES;    // [2]
+    uint64_t* p_full = s_full + 2;           // [2]
+    uint64_t* o_full = p_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,10 +102,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
     if (threadIdx.x == 0) {
         for (int t = 0; t < 2; ++t) {
             ptx::mbar_init(ptx::smem_u32(&q_full[t]), 1);
-            ptx::mbar_init(ptx::smem_u32(&s_full[2 * t]), 1);
-            ptx::mbar_init(ptx::smem_u32(&s_full[2 * t + 1]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_full[t]), 1);
             ptx::mbar_init(ptx::smem_u32(&p_full[t]), QT);
-            ptx::mbar_init(ptx::smem_u32(&pv_done[t]), 1);
+            ptx::mbar_init(ptx::smem_u32(&o_full[t]), 1);
         }
         for (int s = 0; s < KSTAGES; ++s) {
             ptx::mbar_init(ptx::smem_u32(&k_full[s]), 1);
@@ -159,39 +160,34 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
         if (lane == 0) {
             constexpr uint32_t idesc_qk = ptx::umma_idesc_bf16(QT, KT, 0, 0);
             constexpr uint32_t idesc_pv = ptx::umma_idesc_bf16(QT, D, 0, 1);
-            auto issue_qk = [&](int t, int j) {  // S_t[j & 1] = Q_t . K_j^T
-                const int s = j % KSTAGES;
-                const uint32_t qa = ptx::smem_u32(q_smem + t * kQBytes), ka = ptx::smem_u32(k_smem + s * kKBytes);
+            auto issue_qk = [&](int t, int j) {  // S_t = Q_t . K_j^T
+                const uint32_t qa = ptx::smem_u32(q_smem + t * kQBytes);
+                const uint32_t ka = ptx::smem_u32(k_smem + (j % KSTAGES) * kKBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = ptx::umma_desc_k_sw128(qa + (kk / 4) * (kQBytes / 2) + (kk % 4) * 32);
                     const uint64_t db = ptx::umma_desc_k_sw128(ka + (kk / 4) * (kKBytes / 2) + (kk % 4) * 32);
-                    ptx::umma_bf16(tmem_base + (2 * t + (j & 1)) * KT, da, db, idesc_qk, kk != 0);
+                    ptx::umma_bf16(tmem_base + t * KT, da, db, idesc_qk, kk != 0);
                 }
-                ptx::umma_commit(ptx::smem_u32(&s_full[2 * t + (j & 1)]));
+                ptx::umma_commit(ptx::smem_u32(&s_full[t]));
             };
-            auto issue_pv = [&](int t, int j) {  // O_t += P_t . V_j
-                const int s = j % VSTAGES;
-                const uint32_t pa = ptx::smem_u32(p_smem + t * kPBytes), va = ptx::smem_u32(v_smem + s * kVBytes);
+            auto issue_pv = [&](int t, int j) {  // O_t += P_t . V_j, P_t read from tensor memory
+                const uint32_t va = ptx::smem_u32(v_smem + (j % VSTAGES) * kVBytes);
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
-                    const uint64_t da = ptx::umma_desc_k_sw128(pa + kk * 32);
                     const uint64_t db = ptx::umma_desc_mn_sw128(va + kk * 16 * 128, kVBytes / 2, 1024);
-                    ptx::umma_bf16(tmem_base + kOCol + t * D, da, db, idesc_pv, (j | kk) != 0);
+                    ptx::umma_bf16_ts(tmem_base + kOCol + t * D, tmem_base + t * KT + kk * 8, db, idesc_pv, (j | kk) != 0);
                 }
-                ptx::umma_commit(ptx::smem_u32(&pv_done[t]));
             };
             bool ok = true;
             for (int t = 0; t < 2 && ok; ++t)
                 if (n_tiles[t] > 0) ok = ptx::mbar_wait(ptx::smem_u32(&q_full[t]), 0, abort_flag, p.status, kCodeAttn | 2);
-            // prologue: scores of KV tiles 0 and 1 for both Q tiles
-            for (int j = 0; ok && j < min(2, n_max); ++j) {
-                ok = ptx::mbar_wait(ptx::smem_u32(&k_full[j % KSTAGES]), (j / KSTAGES) & 1, abort_flag, p.status, kCodeAttn | 2);
-                if (!ok) break;
+            if (ok && n_max > 0) ok = ptx::mbar_wait(ptx::smem_u32(&k_full[0]), 0, abort_flag, p.status, kCodeAttn | 2);
+            if (ok && n_max > 0) {
                 ptx::tc_fence_after();
                 for (int t = 0; t < 2; ++t)
-                    if (j < n_tiles[t]) issue_qk(t, j);
-                ptx::umma_commit(ptx::smem_u32(&k_empty[j % KSTAGES]));
+                    if (n_tiles[t] > 0) issue_qk(t, 0);
+                ptx::umma_commit(ptx::smem_u32(&k_empty[0]));
             }
             for (int j = 0; ok && j < n_max; ++j) {
                 const int vs = j % VSTAGES;
@@ -202,17 +198,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                     if (!ok) break;
                     ptx::tc_fence_after();
                     issue_pv(t, j);
-                    if (j + 2 < n_tiles[t]) {  // S_t[j & 1] has been consumed: next scores into it
-                        ok = ptx::mbar_wait(ptx::smem_u32(&k_full[(j + 2) % KSTAGES]), ((j + 2) / KSTAGES) & 1, abort_flag,
+                    if (j + 1 == n_tiles[t]) ptx::umma_commit(ptx::smem_u32(&o_full[t]));
+                    if (j + 1 < n_tiles[t]) {  // the tensor pipe runs in order: P_t is consumed before S_t is overwritten
+                        ok = ptx::mbar_wait(ptx::smem_u32(&k_full[(j + 1) % KSTAGES]), ((j + 1) / KSTAGES) & 1, abort_flag,
                                             p.status, kCodeAttn | 2);
                         if (!ok) break;
                         ptx::tc_fence_after();
-                        issue_qk(t, j + 2);
+                        issue_qk(t, j + 1);
                     }
                 }
                 if (ok) {
                     ptx::umma_commit(ptx::smem_u32(&v_empty[vs]));
-                    if (j + 2 < n_max) ptx::umma_commit(ptx::smem_u32(&k_empty[(j + 2) % KSTAGES]));
+                    if (j + 1 < n_max) ptx::umma_commit(ptx::smem_u32(&k_empty[(j + 1) % KSTAGES]));
                 }
             }
         }
@@ -223,86 +220,90 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
         const int r = quarter * 32 + lane;       // row inside the tile == tensor-memory lane
         const int qi = q0 + t * QT + r;          // query index inside the sequence
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t s_addr0 = tmem_base + lane_base + 2 * t * KT;
+        const uint32_t s_addr = tmem_base + lane_base + t * KT;   // scores, and P over their first 64 columns
         const uint32_t o_addr = tmem_base + lane_base + kOCol + t * D;
-        uint8_t* p_row = p_smem + t * kPBytes + r * 128;
         const int nt = n_tiles[t];
         float m_used = -INFINITY, row_sum = 0.0F;
         bool ok = true;
         for (int j = 0; ok && j < nt; ++j) {
-            ok = ptx::mbar_wait(ptx::smem_u32(&s_full[2 * t + (j & 1)]), (j >> 1) & 1, abort_flag, p.status, kCodeAttn | 4);
+            ok = ptx::mbar_wait(ptx::smem_u32(&s_full[t]), j & 1, abort_flag, p.status, kCodeAttn | 4);
             if (!ok) break;
             ptx::tc_fence_after();
-            const uint32_t s_addr = s_addr0 + (j & 1) * KT;
-            uint32_t raw[2][32];
-            ptx::tmem_ld_32x32(s_addr, raw[0]);
-            ptx::tmem_ld_32x32(s_addr + 32, raw[1]);
-            ptx::tmem_ld_wait();
-            float x[64];
-#pragma unroll
-            for (int i = 0; i < 64; ++i) x[i] = __uint_as_float(raw[i >> 5][i & 31]) * p.scale_log2;
             const int key0 = j * KT;
             const bool needs_mask = (p.causal && key0 + KT - 1 > offset + q0 + t * QT) || key0 + KT > p.seq_kv;
-            if (needs_mask) {
-                const int limit = p.causal ? min(p.seq_kv - 1, offset + qi) : p.seq_kv - 1;
+            const int limit = p.causal ? min(p.seq_kv - 1, offset + qi) : p.seq_kv - 1;  // last visible key
+            // pass 1: row maximum of the raw scores (scale > 0, so the maximum commutes with scaling)
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (key0 + i > limit) x[i] = -INFINITY;
-            }
-            float tile_max = x[0];
+            for (int c = 0; c < KT / 32; ++c) {
+                uint32_t raw[32];
+                ptx::tmem_ld_32x32(s_addr + c * 32, raw);
+                ptx::tmem_ld_wait();
+                if (needs_mask) {
 #pragma unroll
-            for (int i = 1; i < 64; ++i) tile_max = fmaxf(tile_max, x[i]);
-            // lazy running maximum: move it only when the row maximum outgrows it by 2^8
-            const bool grow = tile_max > m_used + kRescaleThreshold;
-            if (j > 0) {
-                // O_t and the P tile may be touched only after the previous P.V of this tile has finished
-                ok = ptx::mbar_wait(ptx::smem_u32(&pv_done[t]), (j - 1) & 1, abort_flag, p.status, kCodeAttn | 4);
-                if (!ok) break;
-                if (__any_sync(0xffffffffu, grow)) {
-                    const float alpha = grow ? fast_exp2(m_used - tile_max) : 1.0F;  // 2^(-inf) = 0 for a fresh row
-                    ptx::tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        ptx::tmem_ld_32x32(o_addr + c * 32, o);
-                        ptx::tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        ptx::tmem_st_32x32(o_addr + c * 32, o);
-                    }
-                    ptx::tmem_st_wait();
-                    row_sum *= alpha;
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + c * 32 + i > limit) raw[i] = 0xff800000u;  // -inf
                 }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(raw[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
+                }
+            }
+            const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+            // lazy running maximum: move it only when the row maximum outgrows it by 2^8.  S_t(j) is
+            // complete, so every earlier MMA of this tile (including P.V of tile j-1) has finished and
+            // O_t may be touched.
+            const bool grow = tile_max > m_used + kRescaleThreshold;
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? fast_exp2(m_used - tile_max) : 1.0F;  // 2^(-inf) = 0 for a fresh row
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    ptx::tmem_ld_32x32(o_addr + c * 32, o);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    ptx::tmem_st_32x32(o_addr + c * 32, o);
+                }
+                ptx::tmem_st_wait();
+                row_sum *= alpha;
             }
             if (grow) m_used = tile_max;
-            float tile_sum = 0.0F;
-            if (m_used == -INFINITY) {
+            // pass 2: exponentials, row sum, packed bf16 P written over the consumed scores
+            const float neg_m = m_used == -INFINITY ? 0.0F : -m_used;
+            float s0 = 0.0F, s1 = 0.0F, s2 = 0.0F, s3 = 0.0F;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) x[i] = 0.0F;  // nothing visible yet for this row
-            } else {
+            for (int c = 0; c < KT / 32; ++c) {
+                uint32_t raw[32];
+                ptx::tmem_ld_32x32(s_addr + c * 32, raw);
+                ptx::tmem_ld_wait();
+                float x[32];
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    x[i] = fast_exp2(x[i] - m_used);
-                    tile_sum += x[i];
+                for (int i = 0; i < 32; ++i) x[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, neg_m));
+                if (needs_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + c * 32 + i > limit) x[i] = 0.0F;
                 }
-            }
-            row_sum += tile_sum;
-            // P row (64 bf16 = 128 bytes) into the 128-byte-swizzled K-major tile: 16-byte chunk c of
-            // row r lives at chunk position c ^ (r % 8)
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 packed;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+                for (int i = 0; i < 32; i += 4) { s0 += x[i]; s1 += x[i + 1]; s2 += x[i + 2]; s3 += x[i + 3]; }
+                uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(x[8 * c + 2 * i], x[8 * c + 2 * i + 1]);
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
+                for (int i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                ptx::tmem_st_32x16(s_addr + c * 16, packed);
             }
-            ptx::fence_proxy_async();
+            ptx::tmem_st_wait();
+            row_sum += (s0 + s1) + (s2 + s3);
             ptx::tc_fence_before();
             ptx::mbar_arrive(ptx::smem_u32(&p_full[t]));
         }
-        if (ok && nt > 0)
-            ok = ptx::mbar_wait(ptx::smem_u32(&pv_done[t]), (nt - 1) & 1, abort_flag, p.status, kCodeAttn | 4);
+        if (ok && nt > 0) ok = ptx::mbar_wait(ptx::smem_u32(&o_full[t]), 0, abort_flag, p.status, kCodeAttn | 4);
         if (ok && nt > 0) {
             ptx::tc_fence_after();
             const float inv = 1.0F / row_sum;
