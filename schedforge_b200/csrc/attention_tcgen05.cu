@@ -235,21 +235,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
             // pass 1: row maximum of the raw scores (scale > 0, so the maximum commutes with scaling)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < KT / 32; ++c) {
-                uint32_t raw[32];
-                ptx::tmem_ld_32x32(s_addr + c * 32, raw);
+            for (int c = 0; c < KT / 64; ++c) {  // two 32-column loads in flight per wait
+                uint32_t raw[2][32];
+                ptx::tmem_ld_32x32(s_addr + c * 64, raw[0]);
+                ptx::tmem_ld_32x32(s_addr + c * 64 + 32, raw[1]);
                 ptx::tmem_ld_wait();
                 if (needs_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + c * 32 + i > limit) raw[i] = 0xff800000u;  // -inf
+                    for (int i = 0; i < 64; ++i)
+                        if (key0 + c * 64 + i > limit) raw[i >> 5][i & 31] = 0xff800000u;  // -inf
                 }
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(raw[i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
+                for (int i = 0; i < 64; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(raw[i >> 5][i & 31]));
+                    mx1 = fmaxf(mx1, __uint_as_float(raw[(i + 1) >> 5][(i + 1) & 31]));
+                    mx2 = fmaxf(mx2, __uint_as_float(raw[(i + 2) >> 5][(i + 2) & 31]));
+                    mx3 = fmaxf(mx3, __uint_as_float(raw[(i + 3) >> 5][(i + 3) & 31]));
                 }
             }
             const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
@@ -276,27 +277,31 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
             const float neg_m = m_used == -INFINITY ? 0.0F : -m_used;
             float s0 = 0.0F, s1 = 0.0F, s2 = 0.0F, s3 = 0.0F;
 #pragma unroll
-            for (int c = 0; c < KT / 32; ++c) {
-                uint32_t raw[32];
-                ptx::tmem_ld_32x32(s_addr + c * 32, raw);
+            for (int c = 0; c < KT / 64; ++c) {
+                uint32_t raw[2][32];
+                ptx::tmem_ld_32x32(s_addr + c * 64, raw[0]);
+                ptx::tmem_ld_32x32(s_addr + c * 64 + 32, raw[1]);
                 ptx::tmem_ld_wait();
-                float x[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) x[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), p.scale_log2, neg_m));
-                if (needs_mask) {
+                for (int hh = 0; hh < 2; ++hh) {
+                    float x[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + c * 32 + i > limit) x[i] = 0.0F;
+                    for (int i = 0; i < 32; ++i) x[i] = fast_exp2(fmaf(__uint_as_float(raw[hh][i]), p.scale_log2, neg_m));
+                    if (needs_mask) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (key0 + c * 64 + hh * 32 + i > limit) x[i] = 0.0F;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) { s0 += x[i]; s1 += x[i + 1]; s2 += x[i + 2]; s3 += x[i + 3]; }
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    ptx::tmem_st_32x16(s_addr + (2 * c + hh) * 16, packed);
                 }
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) { s0 += x[i]; s1 += x[i + 1]; s2 += x[i + 2]; s3 += x[i + 3]; }
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-                ptx::tmem_st_32x16(s_addr + c * 16, packed);
             }
             ptx::tmem_st_wait();
             row_sum += (s0 + s1) + (s2 + s3);
