@@ -318,6 +318,9 @@ typedef struct sfb_compile_options {
     int seed_block_table; /* decode: != 0 permutes the physical block order with this seed */
     int no_workspace_reuse; /* != 0: every intermediate keeps its own bytes (DecoderPlanPolicy::
                                reuse_workspace = false), so tests can read any of them back */
+    int no_pipeline;      /* != 0: sfb_decoder_execute copies the whole input, runs, copies the whole output;
+                             0: dense bf16 prefill plans overlap the host copies of one group of sequences
+                             with the computation of another */
 } sfb_compile_options;
 
 /* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */

@@ -117,6 +117,9 @@ struct DecoderExecutablePlan::Impl {
     int *block_table = nullptr, *context_len = nullptr;
     void *kc = nullptr, *vc = nullptr;         // contiguous cached K/V (decode with sequence > 1)
     cudaEvent_t events[16] = {};
+    int pipeline_chunks = 1;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
 
     std::size_t esz() const { return dtype == SFB_BF16 ? 2 : 4; }
@@ -129,9 +132,14 @@ struct DecoderExecutablePlan::Impl {
 };
 
 DecoderExecutablePlan::~DecoderExecutablePlan() {
-    if (impl_)
+    if (impl_) {
         for (auto& e : impl_->events)
             if (e) cudaEventDestroy(e);
+        for (auto& e : impl_->chunk_events)
+            if (e) cudaEventDestroy(e);
+        if (impl_->copy_in) cudaStreamDestroy(impl_->copy_in);
+        if (impl_->copy_out) cudaStreamDestroy(impl_->copy_out);
+    }
     if (stream_) cudaStreamDestroy(stream_);
 }
 
@@ -417,7 +425,13 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     auto& wp = m.planner;
     const std::size_t TH = static_cast<std::size_t>(T) * H;
     // The layer input stays resident for the whole pass so that the plan can be re-run.
-    wp.add("input_f32", TH * 4, 0, bf ? 0 : 13);
+    m.pipeline_chunks = 1;
+    if (bf && fused && !moe && !m.decode && c.batch >= 2 && opt.no_pipeline == 0) {
+        m.pipeline_chunks = c.batch;
+        while (m.pipeline_chunks > 8 || c.batch % m.pipeline_chunks != 0) --m.pipeline_chunks;
+    }
+    const bool piped = m.pipeline_chunks > 1;  // host copies overlap compute: I/O staging must not alias anything
+    wp.add("input_f32", TH * 4, 0, (bf && !piped) ? 0 : 13);
     if (bf) wp.add("input", TH * e, 0, 13);
     wp.add("normalized1", TH * e, 1, 2);
     if (!fused) wp.add("fused_qkv", static_cast<std::size_t>(T) * m.qkv_l * e, 2, 3);
@@ -456,12 +470,18 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         wp.add("expert_output", A * H * e, 10, 11);
     }
     wp.add("output", TH * e, 11, 13);
-    if (bf) wp.add("output_f32", TH * 4, 12, 13);
+    if (bf) wp.add("output_f32", TH * 4, piped ? 0 : 12, 13);
     m.workspace.allocate(wp.total_bytes());
     plan->naive_bytes = wp.naive_bytes();
     plan->workspace_bytes = wp.total_bytes();
     (void)plan_start;
     for (auto& ev : m.events) cuda_check(cudaEventCreate(&ev), "cudaEventCreate");
+    if (piped) {
+        cuda_check(cudaStreamCreateWithFlags(&m.copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_check(cudaStreamCreateWithFlags(&m.copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
+        m.chunk_events.resize(static_cast<std::size_t>(m.pipeline_chunks) * 7);
+        for (auto& ev : m.chunk_events) cuda_check(cudaEventCreate(&ev), "cudaEventCreate");
+    }
     plan->compile_milliseconds =
         std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return plan;
@@ -645,6 +665,11 @@ void DecoderExecutablePlan::execute(const float* input, float* output, RoutingTr
     auto& m = *impl_;
     cudaStream_t s = stream_;
     const uint64_t launches_before = sfb_launch_count();
+    if (m.pipeline_chunks > 1 && !trace) {
+        execute_pipelined(input, output, result);
+        if (result) result->kernel_launches = sfb_launch_count() - launches_before;
+        return;
+    }
     cudaEvent_t h0 = m.events[12], h1 = m.events[13], d0 = m.events[14], d1 = m.events[15];
     cuda_check(cudaEventRecord(h0, s), "event");
     upload_input(input);
@@ -672,6 +697,104 @@ void DecoderExecutablePlan::execute(const float* input, float* output, RoutingTr
     result->milliseconds = span(h0, d1);
     result->tokens_per_second = result->milliseconds > 0.0 ? m.T * 1000.0 / result->milliseconds : 0.0;
     result->kernel_launches = sfb_launch_count() - launches_before;
+}
+
+// Dense bf16 prefill with fused epilogues, one chunk of whole sequences at a time: the host->device
+// copy of chunk c+1 and the device->host copy of chunk c-1 run on their own streams while chunk c
+// computes.  Sequences are independent in every stage (row-wise GEMMs and norms, per-sequence
+// attention), so the result equals the unchunked pass.
+void DecoderExecutablePlan::execute_pipelined(const float* input, float* output, sfb_decoder_result* result) {
+    auto& m = *impl_;
+    if (!input || !output) throw std::invalid_argument("decoder input or output is null");
+    const DecoderConfig& c = config;
+    cudaStream_t s = stream_;
+    const int chunks = m.pipeline_chunks, nb = c.batch / chunks, rows = nb * c.sequence;
+    const int H = m.H, I = m.I_l, D = m.D;
+    const std::size_t row_f32 = static_cast<std::size_t>(H) * 4, row_bf = static_cast<std::size_t>(H) * 2;
+    auto at = [](void* base, std::size_t bytes) { return static_cast<void*>(static_cast<char*>(base) + bytes); };
+    auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int b0) {
+        sfb_gemm_args g{};
+        g.a = a; g.bt = w; g.out = out; g.m = rows; g.n = n; g.k = k; g.epilogue = epi;
+        g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb;
+        if (epi == SFB_EPI_ROPE_SPLIT) {
+            g.q = at(m.ws("query"), static_cast<std::size_t>(b0) * m.hq * c.sequence * D * 2);
+            g.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
+            g.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
+            g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
+            g.batch = nb; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
+        }
+        throw_on(sfb_k_gemm_bf16(&g, s));
+    };
+    cudaEvent_t t0 = m.events[12], t1 = m.events[15];
+    cuda_check(cudaEventRecord(t0, s), "event");
+    cuda_check(cudaStreamWaitEvent(m.copy_in, t0, 0), "stream wait");
+    const bool add_residual_here = m.rank == 0;
+    for (int ch = 0; ch < chunks; ++ch) {
+        cudaEvent_t* ev = &m.chunk_events[static_cast<std::size_t>(ch) * 7];
+        const int b0 = ch * nb;
+        const std::size_t r0 = static_cast<std::size_t>(b0) * c.sequence;
+        cuda_check(cudaMemcpyAsync(at(m.ws("input_f32"), r0 * row_f32), input + r0 * H, rows * row_f32,
+                                   cudaMemcpyHostToDevice, m.copy_in), "input upload");
+        cuda_check(cudaEventRecord(ev[0], m.copy_in), "event");
+        cuda_check(cudaStreamWaitEvent(s, ev[0], 0), "stream wait");
+        void* x = at(m.ws("input"), r0 * row_bf);
+        void* n1 = at(m.ws("normalized1"), r0 * row_bf);
+        void* attn = at(m.ws("attention"), r0 * static_cast<std::size_t>(m.hidden_l) * 2);
+        void* r1 = at(m.ws("attention_residual"), r0 * row_bf);
+        void* n2 = at(m.ws("normalized2"), r0 * row_bf);
+        void* act = at(m.ws("activation"), r0 * static_cast<std::size_t>(I) * 2);
+        void* out = at(m.ws("output"), r0 * row_bf);
+        void* out32 = at(m.ws("output_f32"), r0 * row_f32);
+        cuda_check(cudaEventRecord(ev[2], s), "event");
+        throw_on(sfb_k_convert(at(m.ws("input_f32"), r0 * row_f32), SFB_F32, x, SFB_BF16, static_cast<int64_t>(rows) * H, s));
+        throw_on(sfb_k_rms_norm(x, m.rms1, n1, rows, H, c.rms_epsilon, SFB_BF16, s));
+        gemm(n1, m.wqkv, nullptr, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, b0);
+        cuda_check(cudaEventRecord(ev[3], s), "event");
+        sfb_attention_args a{};
+        a.q = at(m.ws("query"), static_cast<std::size_t>(b0) * m.hq * c.sequence * D * 2);
+        a.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
+        a.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
+        a.out = attn;
+        a.batch = nb; a.q_heads = m.hq; a.kv_heads = m.hkv; a.seq_q = c.sequence; a.seq_kv = c.sequence;
+        a.head_dim = D; a.head_dim_value = D; a.causal = c.causal; a.scale = 0.0F; a.token_major = 1;
+        a.dtype = SFB_BF16; a.backend = policy.attention_backend;
+        throw_on(sfb_k_attention_prefill(&a, s));
+        cuda_check(cudaEventRecord(ev[4], s), "event");
+        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, b0);
+        if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, r1, static_cast<int64_t>(rows) * H, m.dtype, s);
+        throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
+        cuda_check(cudaEventRecord(ev[5], s), "event");
+        gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, b0);
+        gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, b0);
+        if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, out, static_cast<int64_t>(rows) * H, m.dtype, s);
+        cuda_check(cudaEventRecord(ev[6], s), "event");
+        throw_on(sfb_k_convert(out, SFB_BF16, out32, SFB_F32, static_cast<int64_t>(rows) * H, s));
+        cuda_check(cudaEventRecord(ev[1], s), "event");
+        cuda_check(cudaStreamWaitEvent(m.copy_out, ev[1], 0), "stream wait");
+        cuda_check(cudaMemcpyAsync(output + r0 * H, out32, rows * row_f32, cudaMemcpyDeviceToHost, m.copy_out), "output download");
+    }
+    cuda_check(cudaEventRecord(m.events[14], m.copy_out), "event");
+    cuda_check(cudaStreamWaitEvent(s, m.events[14], 0), "stream wait");
+    cuda_check(cudaEventRecord(t1, s), "event");
+    cuda_check(cudaEventSynchronize(t1), "event sync");
+    m.has_input = true;  // the whole input is resident (as bf16) for later resident runs
+    if (!result) return;
+    auto span = [&](cudaEvent_t a, cudaEvent_t b) {
+        float ms = 0.0F;
+        cuda_check(cudaEventElapsedTime(&ms, a, b), "event time");
+        return static_cast<double>(ms);
+    };
+    *result = {};
+    for (int ch = 0; ch < chunks; ++ch) {
+        cudaEvent_t* ev = &m.chunk_events[static_cast<std::size_t>(ch) * 7];
+        result->projection_milliseconds += span(ev[2], ev[3]) + span(ev[4], ev[5]);  // incl. the fused norms
+        result->attention_milliseconds += span(ev[3], ev[4]);
+        result->ffn_milliseconds += span(ev[5], ev[6]);
+    }
+    result->h2d_milliseconds = span(t0, m.chunk_events[0]);                       // exposed part: first chunk
+    result->d2h_milliseconds = span(m.chunk_events[static_cast<std::size_t>(chunks - 1) * 7 + 1], t1);  // last chunk
+    result->milliseconds = span(t0, t1);
+    result->tokens_per_second = result->milliseconds > 0.0 ? m.T * 1000.0 / result->milliseconds : 0.0;
 }
 
 int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_out, int64_t capacity) {
