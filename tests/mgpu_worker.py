@@ -1,0 +1,86 @@
+"""Rank program for tests/test_multi_gpu.py (launched with torch.distributed.run, one rank per
+GPU): tensor-parallel dense layer and expert-sharded MoE layer with a real NCCL all-reduce behind
+the plan's hook, checked against the unsharded CPU oracle on rank 0."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from oracle import binding as ob  # noqa: E402
+from schedforge_b200 import api, lib as L  # noqa: E402
+
+
+def make_hook(plan):
+    stream = torch.cuda.ExternalStream(plan.stream)
+    views = {}
+
+    def hook(buf, count, dtype, stream_ptr):
+        key = (buf, count)
+        if key not in views:
+            class Raw:
+                __cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (buf, False), "version": 3}
+            views[key] = torch.as_tensor(Raw(), device="cuda").view(torch.bfloat16)
+        with torch.cuda.stream(stream):
+            dist.all_reduce(views[key])
+    return hook
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    port = ob.Port()
+    failures = []
+    cases = [("dense", dict(batch=2, sequence=128, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64), False),
+             ("dense_decode", dict(batch=3, sequence=1, hidden=1024, intermediate=512, query_heads=8, kv_heads=2,
+                                   head_dim=128, context_sequence=200), False),
+             ("moe", dict(batch=1, sequence=256, hidden=256, intermediate=256, query_heads=4, kv_heads=2, head_dim=64,
+                          experts=8, top_k=2), True)]
+    for name, kw, moe in cases:
+        oc = ob.decoder_config(moe=moe, **kw)
+        rng = np.random.default_rng(11)
+        data = {}
+        for key, n in ob.decoder_shapes(oc).items():
+            scale = 1.0 if key in ("input", "cached_key", "cached_value") else 0.05
+            data[key] = port.round_bf16((rng.standard_normal(n) * scale).astype(np.float32))
+        data["rms1_weight"] = np.ones(oc.hidden, np.float32)
+        data["rms2_weight"] = np.ones(oc.hidden, np.float32)
+        weights = {k: v for k, v in data.items() if k != "input"}
+        plan = api.DecoderCompiler.compile(api.decoder_config(moe=moe, **kw), weights, "",
+                                           api.compile_options(tp_rank=rank, tp_size=world, no_workspace_reuse=True))
+        plan.set_allreduce(make_hook(plan))
+        out, _ = plan.execute(data["input"])
+        trace = None
+        if moe:  # route the oracle exactly as the GPU did (identical on every rank)
+            t = oc.batch * oc.sequence
+            trace = (plan.read_tensor("expert_ids", np.int32).reshape(t, oc.top_k),
+                     plan.read_tensor("expert_weights").reshape(t, oc.top_k), plan.read_tensor("counts", np.int32))
+        if rank == 0:
+            want = port.decoder_layer(oc, data, native=True, trace=trace)
+            err = float(np.max(np.abs(out - want)) / np.max(np.abs(want)))
+            print(f"{name}: rel err {err:.3e}", flush=True)
+            if not err < 2e-2:
+                failures.append(name)
+        # every rank must hold the same replicated output
+        mine = torch.from_numpy(out).cuda()
+        ref = mine.clone()
+        dist.broadcast(ref, 0)
+        if not torch.equal(mine, ref):
+            failures.append(name + ":ranks differ")
+        plan.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if failures:
+        print("FAILED", failures, flush=True)
+        sys.exit(1)
+    if rank == 0:
+        print("MULTI_GPU_OK", flush=True)
+
+
+if __name__ == "__main__":
+    main()
