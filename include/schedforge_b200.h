@@ -130,9 +130,28 @@ typedef struct sfb_gemm_args {
     const int* group_offsets; /* device int32[groups+1], NULL for a dense GEMM             */
     int groups;
     void* tile_table;       /* grouped tcgen05: device scratch, int32[4*(m/128 + groups + 1)] */
+    /* optional scratch for GEMMs with m <= 128 (decode): with it the tcgen05 kernel gives every
+     * SM an equal share of the K blocks and sums partial tiles here.  Device memory, 16-byte
+     * aligned, at least sfb_gemm_stream_workspace_bytes(n) bytes, ZERO-FILLED before its first
+     * use; every call leaves it zero-filled again.  NULL = whole tiles per SM. */
+    void* split_workspace;
+    size_t split_workspace_bytes;
+    /* bt_tiled != 0: bt holds the weight in 64x64 blocks (sfb_k_tile_weight_bf16) so that a
+     * weight-streaming GEMM reads 8 KB contiguous runs; tcgen05 backend, dense mode only */
+    int bt_tiled;
 } sfb_gemm_args;
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
+size_t sfb_gemm_stream_workspace_bytes(int n);
+
+/* Blocked weight layout for decode-shaped (few rows, HBM-bound) GEMMs.  The [n,k] row-major
+ * bf16 weight is cut into 64x64 blocks; block (j, b) = rows [64j, 64j+64) x columns
+ * [64b, 64b+64), zero padded at the edges, stored row-major (64 rows of 128 bytes) at element
+ * offset (j * ceil(k/64) + b) * 4096.  sfb_tiled_weight_elems gives the element count of the
+ * blocked copy.  src and dst must not overlap.  No counterpart in the reference, whose CPU
+ * packing is the plain transpose of pack_transposed (src/decoder_compiler.cpp:57-66). */
+int64_t sfb_tiled_weight_elems(int n, int k);
+sfb_status sfb_k_tile_weight_bf16(const void* bt, void* tiled, int n, int k, sfb_stream stream);
 
 /* cos/sin tables for interleaved-pair rotary embedding, computed on the HOST with the
  * same powf/cosf/sinf calls as apply_rope, src/decoder_compiler.cpp:96-114:

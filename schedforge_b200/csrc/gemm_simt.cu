@@ -6,6 +6,8 @@
 //  * gemm_bf16_simt_kernel: shape-agnostic bf16 GEMM (fp32 accumulate) with the same
 //    epilogues as the tensor-core kernel.  It is the path for shapes the tcgen05 kernel
 //    does not take (k % 8 != 0, tiny head sizes) and the cross-check for it in tests.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace sfb {
@@ -98,6 +100,46 @@ __device__ __forceinline__ void store_out(const SimtParams& p, size_t index, flo
     else static_cast<bf16*>(p.out)[index] = from_float<bf16>(v);
 }
 
+// Writes the outputs of column pair (c0, c1) of `row` according to the epilogue of `p`.
+__device__ __forceinline__ void apply_epilogue(const SimtParams& p, int row, int pair, int c0, int c1, float acc0,
+                                               float acc1) {
+    switch (p.epilogue) {
+        case SFB_EPI_STORE:
+        case SFB_EPI_RESIDUAL: {
+            const size_t i0 = static_cast<size_t>(row) * p.n + c0;
+            const bool res = p.epilogue == SFB_EPI_RESIDUAL;
+            store_out(p, i0, acc0 + (res ? to_float(p.residual[i0]) : 0.0F));
+            if (c1 < p.n) store_out(p, i0 + 1, acc1 + (res ? to_float(p.residual[i0 + 1]) : 0.0F));
+            break;
+        }
+        case SFB_EPI_SWIGLU:
+            store_out(p, static_cast<size_t>(row) * (p.n / 2) + pair, acc0 / (1.0F + __expf(-acc0)) * acc1);
+            break;
+        case SFB_EPI_ROPE_SPLIT: {
+            const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
+            const int b = row / p.seq, t = row % p.seq;
+            bf16* dst;
+            int heads, local;
+            bool rotate = true;
+            if (c0 < hidden) { dst = p.q; heads = p.q_heads; local = c0; }
+            else if (c0 < hidden + kvw) { dst = p.key; heads = p.kv_heads; local = c0 - hidden; }
+            else { dst = p.value; heads = p.kv_heads; local = c0 - hidden - kvw; rotate = false; }
+            const int head = local / p.head_dim, d = local % p.head_dim;
+            const size_t o = ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d;
+            if (rotate) {
+                const float c = p.rope_cos[t * (p.head_dim / 2) + d / 2];
+                const float s = p.rope_sin[t * (p.head_dim / 2) + d / 2];
+                dst[o] = from_float<bf16>(acc0 * c - acc1 * s);
+                dst[o + 1] = from_float<bf16>(acc0 * s + acc1 * c);
+            } else {
+                dst[o] = from_float<bf16>(acc0);
+                dst[o + 1] = from_float<bf16>(acc1);
+            }
+            break;
+        }
+    }
+}
+
 // 16x16 threads; thread (ty, tx) owns row `row0 + ty` and the column PAIR `pair0 + tx`.
 // A pair is two adjacent columns (2j, 2j+1), or for SwiGLU a gate column and its up column.
 __global__ void __launch_bounds__(256)
@@ -154,41 +196,7 @@ gemm_bf16_simt_kernel(SimtParams p) {
     if (row >= row_end || pair >= pairs) return;
     int c0 = 0, c1 = 0;
     columns(pair, c0, c1);
-    switch (p.epilogue) {
-        case SFB_EPI_STORE:
-        case SFB_EPI_RESIDUAL: {
-            const size_t i0 = static_cast<size_t>(row) * p.n + c0;
-            const bool res = p.epilogue == SFB_EPI_RESIDUAL;
-            store_out(p, i0, acc0 + (res ? to_float(p.residual[i0]) : 0.0F));
-            if (c1 < p.n) store_out(p, i0 + 1, acc1 + (res ? to_float(p.residual[i0 + 1]) : 0.0F));
-            break;
-        }
-        case SFB_EPI_SWIGLU:
-            store_out(p, static_cast<size_t>(row) * (p.n / 2) + pair, acc0 / (1.0F + __expf(-acc0)) * acc1);
-            break;
-        case SFB_EPI_ROPE_SPLIT: {
-            const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
-            const int b = row / p.seq, t = row % p.seq;
-            bf16* dst;
-            int heads, local;
-            bool rotate = true;
-            if (c0 < hidden) { dst = p.q; heads = p.q_heads; local = c0; }
-            else if (c0 < hidden + kvw) { dst = p.key; heads = p.kv_heads; local = c0 - hidden; }
-            else { dst = p.value; heads = p.kv_heads; local = c0 - hidden - kvw; rotate = false; }
-            const int head = local / p.head_dim, d = local % p.head_dim;
-            const size_t o = ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d;
-            if (rotate) {
-                const float c = p.rope_cos[t * (p.head_dim / 2) + d / 2];
-                const float s = p.rope_sin[t * (p.head_dim / 2) + d / 2];
-                dst[o] = from_float<bf16>(acc0 * c - acc1 * s);
-                dst[o + 1] = from_float<bf16>(acc0 * s + acc1 * c);
-            } else {
-                dst[o] = from_float<bf16>(acc0);
-                dst[o + 1] = from_float<bf16>(acc1);
-            }
-            break;
-        }
-    }
+    apply_epilogue(p, row, pair, c0, c1, acc0, acc1);
 }
 
 sfb_status validate_gemm(const sfb_gemm_args& g) {
@@ -218,7 +226,27 @@ sfb_status validate_gemm(const sfb_gemm_args& g) {
     return SFB_OK;
 }
 
+// One thread per 16-byte piece (8 elements) of the blocked copy.
+__global__ void tile_weight_kernel(const bf16* __restrict__ bt, bf16* __restrict__ tiled, int n, int k,
+                                   long long pieces) {
+    const int k_blocks = (k + 63) / 64;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < pieces;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long block = i >> 9;               // 512 pieces per 64x64 block
+        const int within = static_cast<int>(i & 511);
+        const int r = within >> 3, c8 = (within & 7) * 8;
+        const int row = static_cast<int>(block / k_blocks) * 64 + r;
+        const int col = static_cast<int>(block % k_blocks) * 64 + c8;
+        bf16 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] = (row < n && col + j < k) ? bt[static_cast<size_t>(row) * k + col + j] : from_float<bf16>(0.0F);
+        *reinterpret_cast<uint4*>(tiled + i * 8) = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
 }  // namespace
+
 }  // namespace sfb
 
 using namespace sfb;
@@ -241,10 +269,28 @@ sfb_status sfb_k_gemm_f32(const float* a, const float* b, float* c, int m, int n
     return SFB_OK;
 }
 
+int64_t sfb_tiled_weight_elems(int n, int k) {
+    if (n <= 0 || k <= 0) return 0;
+    return static_cast<int64_t>(ceil_div(n, 64)) * ceil_div(k, 64) * 4096;
+}
+
+sfb_status sfb_k_tile_weight_bf16(const void* bt, void* tiled, int n, int k, sfb_stream stream) {
+    SFB_REQUIRE(bt && tiled && n > 0 && k > 0, "tile_weight: invalid shape or null operand");
+    SFB_REQUIRE((reinterpret_cast<uintptr_t>(tiled) & 15) == 0, "tile_weight: destination must be 16-byte aligned");
+    const long long pieces = sfb_tiled_weight_elems(n, k) / 8;
+    const int grid = static_cast<int>(std::min<long long>((pieces + 255) / 256, static_cast<long long>(sm_count()) * 16));
+    tile_weight_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const bf16*>(bt), static_cast<bf16*>(tiled), n,
+                                                            k, pieces);
+    return check_launch("tile_weight");
+}
+
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream) {
     SFB_REQUIRE(args, "gemm: null arguments");
     SFB_TRY(validate_gemm(*args));
+    SFB_REQUIRE(!args->bt_tiled || (!args->group_offsets && args->backend != SFB_GEMM_SIMT),
+                "gemm: the blocked weight layout needs the dense tcgen05 kernel");
     int backend = args->backend;
+    if (args->bt_tiled) backend = SFB_GEMM_TCGEN05;
     if (backend == SFB_GEMM_AUTO)
         backend = gemm_bf16_tcgen05_supported(*args) ? SFB_GEMM_TCGEN05 : SFB_GEMM_SIMT;
     if (backend == SFB_GEMM_TCGEN05) {

@@ -1,22 +1,36 @@
 // bf16 GEMM on the 5th-generation tensor cores: out = epilogue(A[m,k] . Bt[n,k]^T).
 //
-// One persistent CTA per SM, 192 threads in three roles:
+// One persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: streams 128x64 A tiles and BNx64 B tiles (128-byte swizzle)
-//               through a ring of shared-memory stages guarded by full/empty mbarriers;
+//               through rings of shared-memory stages guarded by full/empty mbarriers;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) four times per
-//               stage into one of TWO accumulator buffers in tensor memory and commits the
-//               stage back to the producer and the finished tile to the epilogue;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (one row per thread, 32 columns at a
-//               time), apply the fused epilogue and store straight to global memory, while
-//               the MMA warp already works on the next tile in the other buffer.
+//               K block into one of TWO accumulator buffers in tensor memory and commits the
+//               stages back to the producer and the finished work item to the epilogue;
+//   warps 2-9   epilogue: tcgen05.ld the accumulator (one row per thread, 32 columns at a
+//               time; two warps share each 32-row quarter and alternate over the column
+//               chunks), apply the fused epilogue and store to global memory, while the MMA
+//               warp already works on the next item in the other buffer.
 // Epilogues: plain store, + residual, SwiGLU over [gate | up] halves of the tile, and
 // RoPE + scatter into head-major Q/K/V for the fused QKV projection.
 // Grouped mode (MoE experts): a device-built tile table maps every M-tile to a row range
 // of one expert; the weight slab of that expert is addressed through the row coordinate
 // of the B tensor map, rows outside the range are masked in the epilogue.
 //
-// Tiles are visited in bands of 16 M-tiles so that one band's A rows stay in L2 while
-// the CTAs sweep the N direction.
+// Many rows (prefill): a work item is one output tile; tiles are visited in bands of 16
+// M-tiles so that one band's A rows stay in L2 while the CTAs sweep the N direction.
+//
+// One M-tile (decode): every weight byte is read once, the kernel is HBM-bound, and one SM
+// can only keep a bounded number of HBM bytes in flight, so ALL SMs must stream for the whole
+// kernel.  The (tile, K block) pairs are laid end to end and cut into one equal contiguous
+// range per CTA.  A range that covers a whole tile runs the fused epilogue from tensor
+// memory.  Ranges that cover part of a tile add their fp32 partial sums into a zeroed
+// accumulator in global memory (reductions performed at L2) and count the K blocks they
+// contributed; the CTA whose contribution completes the tile reads the sums back, runs the
+// epilogue and restores the zeros.  No CTA ever waits for another.  In this mode the
+// activation tiles (L2 hits) and the weight tiles (HBM) use separate rings, a shallow and a
+// deep one, so that nearly all of shared memory holds HBM bytes in flight.
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -26,18 +40,24 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GROUP_M = 16;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kCodeProducer = 0x1, kCodeMma = 0x2, kCodeEpilogue = 0x4;
 
-template <int BN>
+template <int BN, bool STREAM>
 struct Tile {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStagesB = STREAM ? (192 * 1024 - 4 * kABytes) / kBBytes : (BN == 256 ? 4 : 6);
+    static constexpr int kStagesA = STREAM ? 4 : kStagesB;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kBarrierBytes = 256;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+    static constexpr int kBarrierBytes = 512;
+    static constexpr int kEpilogueStagingBytes = kEpilogueWarps * 32 * 32 * 4;  // per warp 32 rows x 32 fp32 columns
+    static constexpr int kSmemBytes =
+        kStagesA * kABytes + kStagesB * kBBytes + kEpilogueStagingBytes + kBarrierBytes + 1024;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+    static_assert(8 * (2 * kStagesA + 2 * kStagesB + 4) + 16 <= kBarrierBytes, "barrier block too small");
 };
 
 struct TcParams {
@@ -51,6 +71,11 @@ struct TcParams {
     const int* tile_table;  // grouped: [0] = number of M-tiles, entries from [4]
     int dense_m_tiles;
     int n_tiles;
+    int b_tiled;            // weight stored as 64x64 blocks, 8 KB contiguous each
+    // equal K-block ranges per CTA (one M-tile only): fp32 [n_tiles][BM][BN] sums + one counter per tile
+    float* accum;
+    int* tile_counters;
+    int shared_tiles;       // trailing tiles whose K blocks are cut into equal ranges (0 = none)
     uint32_t* status;
 };
 
@@ -58,8 +83,78 @@ struct TileCoord {
     int row_start, row_end, group, n_index;
 };
 
+// One work item: K blocks [kb0, kb1) of one output tile.
+struct Segment {
+    int tile, kb0, kb1;
+};
+
+// The sequence of work items of one CTA.  Every role walks its own copy.
+// Whole tiles go round-robin.  With sum scratch (one M-tile), the tiles left over after the
+// last full round are not handed to a few CTAs: their (tile, K block) pairs are laid end to
+// end and cut into one equal range per CTA.  A CTA works through its range first (the piece
+// at its head, the piece at its tail, then any whole tiles inside it) and through its
+// round-robin tiles afterwards, so that summing and completing shared tiles overlaps streaming.
+struct Walk {
+    long long unit, unit_end;  // this CTA's range of the left-over tiles' K blocks
+    int first_shared;          // tiles [first_shared, total_tiles) are cut into ranges
+    int tile, stride, k_blocks;
+    int phase;                 // 0 = head piece, 1 = tail piece, 2 = whole tiles of the range, 3 = round-robin
+    __device__ bool next(Segment& sg) {
+        if (phase == 0) {
+            phase = 1;
+            const int first = static_cast<int>(unit % k_blocks);
+            if (first != 0 && unit < unit_end) {
+                sg.tile = first_shared + static_cast<int>(unit / k_blocks);
+                sg.kb0 = first;
+                sg.kb1 = static_cast<int>(min(static_cast<long long>(k_blocks), first + (unit_end - unit)));
+                unit += sg.kb1 - sg.kb0;
+                return true;
+            }
+        }
+        if (phase == 1) {  // `unit` is on a tile boundary or the range is used up
+            phase = 2;
+            const int last = static_cast<int>(unit_end % k_blocks);
+            if (last != 0 && unit < unit_end) {
+                sg.tile = first_shared + static_cast<int>(unit_end / k_blocks);
+                sg.kb0 = 0;
+                sg.kb1 = last;
+                unit_end -= last;
+                return true;
+            }
+        }
+        sg.kb0 = 0;
+        sg.kb1 = k_blocks;
+        if (phase == 2) {
+            if (unit < unit_end) {
+                sg.tile = first_shared + static_cast<int>(unit / k_blocks);
+                unit += k_blocks;
+                return true;
+            }
+            phase = 3;
+        }
+        if (tile >= first_shared) return false;
+        sg.tile = tile;
+        tile += stride;
+        return true;
+    }
+};
+
 __device__ __forceinline__ int load_m_tiles(const TcParams& p) {
     return p.tile_table ? p.tile_table[0] : p.dense_m_tiles;
+}
+
+__device__ __forceinline__ Walk make_walk(const TcParams& p, int m_tiles, int k_blocks) {
+    Walk w;
+    const int total_tiles = m_tiles * p.n_tiles;
+    w.k_blocks = k_blocks;
+    w.tile = blockIdx.x;
+    w.stride = gridDim.x;
+    w.first_shared = total_tiles - p.shared_tiles;
+    const long long units = static_cast<long long>(p.shared_tiles) * k_blocks;
+    w.unit = units * blockIdx.x / gridDim.x;
+    w.unit_end = units * (blockIdx.x + 1) / gridDim.x;
+    w.phase = p.shared_tiles > 0 ? 0 : 3;
+    return w;
 }
 
 __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile, int m_tiles) {
@@ -84,79 +179,165 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile, int
     return c;
 }
 
-// 32 consecutive outputs of one row: vector stores when the destination is 16-byte
-// aligned and the chunk is complete, scalar stores otherwise.
-__device__ __forceinline__ void store_chunk(void* out, int out_f32, size_t index, const float (&v)[32],
-                                            int valid) {
+// ---- epilogue --------------------------------------------------------------------------
+// A thread of an epilogue warp reads one accumulator ROW from tensor memory.  Storing rows
+// straight from there would make every store instruction touch 32 different lines, which
+// takes microseconds per tile.  So each warp first parks 32 columns of its 32 rows in shared
+// memory (fp32, 16-byte pieces XOR-swizzled by row so that both phases are conflict-free) and
+// then walks them with 4 adjacent lanes per row: every lane owns 8 adjacent columns, applies
+// the rest of the epilogue and issues 16-byte loads and stores that coalesce per row.
+// SiLU(gate) * up is computed before staging, where a thread has 32 independent values.
+constexpr int kStageFloatsPerWarp = 32 * 32;
+
+// phase 1: lane = row, 32 values = staged columns [0, 32)
+__device__ __forceinline__ void stage_write(float* stage, int lane, const uint32_t (&r)[32]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int piece = j ^ (lane & 7);
+        *reinterpret_cast<uint4*>(stage + lane * 32 + piece * 4) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    }
+}
+// phase 2: 8 staged values of row `r` starting at staged column `first` (a multiple of 8)
+__device__ __forceinline__ void stage_read8(const float* stage, int r, int first, float (&f)[8]) {
+    const int p0 = (first >> 2) ^ (r & 7), p1 = ((first >> 2) + 1) ^ (r & 7);
+    const float4 lo = *reinterpret_cast<const float4*>(stage + r * 32 + p0 * 4);
+    const float4 hi = *reinterpret_cast<const float4*>(stage + r * 32 + p1 * 4);
+    f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w;
+    f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+}
+
+// 8 adjacent outputs: one 16-byte (bf16) or two 16-byte (fp32) stores when complete and aligned
+__device__ __forceinline__ void store8(void* out, int out_f32, size_t index, const float (&f)[8], int valid) {
     if (out_f32) {
         float* dst = static_cast<float*>(out) + index;
-        if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else {
-            for (int i = 0; i < valid; ++i) dst[i] = v[i];
+                if (i < valid) dst[i] = f[i];
         }
     } else {
         bf16* dst = static_cast<bf16*>(out) + index;
-        if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        if (valid >= 8 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            uint4 packed;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 packed;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-                reinterpret_cast<uint4*>(dst)[i] = packed;
-            }
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+            *reinterpret_cast<uint4*>(dst) = packed;
         } else {
-            for (int i = 0; i < valid; ++i) dst[i] = from_float<bf16>(v[i]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (i < valid) dst[i] = from_float<bf16>(f[i]);
         }
     }
 }
 
-__device__ __forceinline__ void load_bf16_chunk(const bf16* src, float (&v)[32], int valid) {
-    if (valid == 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+__device__ __forceinline__ void add_bf16x8(const bf16* src, float (&f)[8], int valid) {
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const uint4 packed = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 packed = reinterpret_cast<const uint4*>(src)[i];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(h[j]);
-                v[8 * i + 2 * j] = f.x;
-                v[8 * i + 2 * j + 1] = f.y;
-            }
+        for (int j = 0; j < 4; ++j) {
+            const float2 x = __bfloat1622float2(h[j]);
+            f[2 * j] += x.x;
+            f[2 * j + 1] += x.y;
         }
     } else {
-        for (int i = 0; i < 32; ++i) v[i] = i < valid ? to_float(src[i]) : 0.0F;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < valid) f[i] += to_float(src[i]);
     }
 }
 
-template <int BN>
+// Epilogue of output columns [col, col + 8) of `row` (not SwiGLU); col is a multiple of 8.
+__device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float (&f)[8]) {
+    if (col >= p.n) return;
+    if (p.epilogue == SFB_EPI_ROPE_SPLIT) {  // head_dim % 32 == 0: the 8 columns lie in one head
+        const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
+        const int b = row / p.seq, t = row - b * p.seq;
+        bf16* dst;
+        int heads, local;
+        bool rotate = true;
+        if (col < hidden) { dst = p.q; heads = p.q_heads; local = col; }
+        else if (col < hidden + kvw) { dst = p.key; heads = p.kv_heads; local = col - hidden; }
+        else { dst = p.value; heads = p.kv_heads; local = col - hidden - kvw; rotate = false; }
+        const int head = local / p.head_dim, d0 = local - head * p.head_dim;
+        if (rotate) {
+            const size_t at = static_cast<size_t>(t) * (p.head_dim / 2) + d0 / 2;
+            const float4 c4 = *reinterpret_cast<const float4*>(p.rope_cos + at);
+            const float4 s4 = *reinterpret_cast<const float4*>(p.rope_sin + at);
+            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float e = f[2 * j], o = f[2 * j + 1];
+                f[2 * j] = e * cc[j] - o * ss[j];
+                f[2 * j + 1] = e * ss[j] + o * cc[j];
+            }
+        }
+        store8(dst, 0, ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d0, f, 8);
+        return;
+    }
+    const size_t index = static_cast<size_t>(row) * p.n + col;
+    const int valid = p.n - col;
+    if (p.epilogue == SFB_EPI_RESIDUAL) add_bf16x8(p.residual + index, f, valid);
+    store8(p.out, p.out_f32, index, f, valid);
+}
+
+// phase 2 for one warp: the staged values are output columns [col0, col0 + 32) of rows
+// [row0, row0 + 32); `plain` = they are final (SwiGLU) and only need storing into [m, width].
+__device__ __forceinline__ void emit_staged(const TcParams& p, const float* stage, int lane, int row0, int row_end,
+                                            int col0, bool plain, int width) {
+#pragma unroll 2
+    for (int i = 0; i < 4; ++i) {
+        const int r = i * 8 + (lane >> 2), first = (lane & 3) * 8;
+        const int row = row0 + r, col = col0 + first;
+        if (row >= row_end || col >= width) continue;
+        float f[8];
+        stage_read8(stage, r, first, f);
+        if (plain) store8(p.out, p.out_f32, static_cast<size_t>(row) * width + col, f, width - col);
+        else emit8(p, row, col, f);
+    }
+}
+
+template <int BN, bool STREAM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ TcParams p) {
-    using T = Tile<BN>;
+    using T = Tile<BN, STREAM>;
+    constexpr int SA = T::kStagesA, SB = T::kStagesB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::kStages * T::kStageBytes);
-    uint64_t* full_bar = bars;
-    uint64_t* empty_bar = bars + T::kStages;
-    uint64_t* tmem_full = bars + 2 * T::kStages;
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + SA * T::kABytes;
+    float* staging = reinterpret_cast<float*>(smem_b + SB * T::kBBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b + SB * T::kBBytes + T::kEpilogueStagingBytes);
+    // shared rings (STREAM = false): full_a/empty_a are unused, full_b/empty_b guard whole stages
+    uint64_t* full_b = bars;
+    uint64_t* empty_b = full_b + SB;
+    uint64_t* full_a = empty_b + SB;
+    uint64_t* empty_a = full_a + SA;
+    uint64_t* tmem_full = empty_a + SA;
     uint64_t* tmem_empty = tmem_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;  // epilogue warps: this CTA completed the tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < T::kStages; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+        for (int s = 0; s < SB; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_b[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_b[s]), 1);
+        }
+        for (int s = 0; s < SA; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_a[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_a[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&tmem_full[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&tmem_empty[b]), 128);
+            ptx::mbar_init(ptx::smem_u32(&tmem_empty[b]), 32 * kEpilogueWarps);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -174,144 +355,244 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     const int m_tiles = load_m_tiles(p);
-    const int total_tiles = m_tiles * p.n_tiles;
     const int k_blocks = (p.k + BK - 1) / BK;
+    Walk walk = make_walk(p, m_tiles, k_blocks);
+
+    // weight tile of K block `kb` for output columns [n_index * BN, +BN) of slab `group`
+    auto load_b = [&](uint8_t* dst, uint32_t bar, int kb, const TileCoord& c) {
+        if (p.b_tiled) {
+            // rows of the map are the 64-row blocks laid end to end, 128 bytes each; a block past
+            // the last weight row lies outside the map and reads as zeros
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) {
+                const int block = (c.n_index * (BN / 64) + j) * k_blocks + kb;
+                ptx::tma_load_2d(ptx::smem_u32(dst + j * 8192), &tma_b, bar, 0, block * 64);
+            }
+        } else {
+            ptx::tma_load_2d(ptx::smem_u32(dst), &tma_b, bar, kb * BK, c.group * p.n + c.n_index * BN);
+        }
+    };
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileCoord c = tile_coord(p, tile, m_tiles);
-                const int b_row = c.group * p.n + c.n_index * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % T::kStages, ph = (it / T::kStages) & 1;
-                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, p.status, kCodeProducer)) {
-                        ok = false;
-                        break;
+            if constexpr (!STREAM) {
+                Segment sg;
+                uint32_t it = 0;
+                bool ok = true;
+                while (ok && walk.next(sg)) {
+                    const TileCoord c = tile_coord(p, sg.tile, m_tiles);
+                    for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                        const uint32_t s = it % SB, ph = (it / SB) & 1;
+                        if (!ptx::mbar_wait(ptx::smem_u32(&empty_b[s]), ph ^ 1, abort_flag, p.status, kCodeProducer)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = ptx::smem_u32(&full_b[s]);
+                        ptx::mbar_expect_tx(full, T::kStageBytes);
+                        ptx::tma_load_2d(ptx::smem_u32(smem_a + s * T::kABytes), &tma_a, full, kb * BK, c.row_start);
+                        load_b(smem_b + s * T::kBBytes, full, kb, c);
                     }
-                    const uint32_t full = ptx::smem_u32(&full_bar[s]);
-                    ptx::mbar_expect_tx(full, T::kStageBytes);
-                    uint8_t* stage = smem + s * T::kStageBytes;
-                    ptx::tma_load_2d(ptx::smem_u32(stage), &tma_a, full, kb * BK, c.row_start);
-                    ptx::tma_load_2d(ptx::smem_u32(stage + T::kABytes), &tma_b, full, kb * BK, b_row);
+                }
+            } else {
+                // Two cursors over the same sequence; whichever ring has a free stage gets its next load.
+                struct Cursor {
+                    Walk walk;
+                    Segment sg;
+                    TileCoord c;
+                    int kb;
+                    uint32_t it;
+                    bool live;
+                };
+                auto open = [&](Cursor& cu) {
+                    cu.live = cu.walk.next(cu.sg);
+                    if (cu.live) {
+                        cu.c = tile_coord(p, cu.sg.tile, m_tiles);
+                        cu.kb = cu.sg.kb0;
+                    }
+                };
+                auto advance = [&](Cursor& cu) {
+                    ++cu.it;
+                    if (++cu.kb == cu.sg.kb1) open(cu);
+                };
+                Cursor ca{walk, {}, {}, 0, 0, false}, cb{walk, {}, {}, 0, 0, false};
+                open(ca);
+                open(cb);
+                long long stall_start = 0;
+                uint32_t idle = 0;
+                while (ca.live || cb.live) {
+                    bool progressed = false;
+                    if (cb.live) {
+                        const uint32_t s = cb.it % SB, ph = (cb.it / SB) & 1;
+                        if (ptx::mbar_try_wait(ptx::smem_u32(&empty_b[s]), ph ^ 1)) {
+                            const uint32_t full = ptx::smem_u32(&full_b[s]);
+                            ptx::mbar_expect_tx(full, T::kBBytes);
+                            load_b(smem_b + s * T::kBBytes, full, cb.kb, cb.c);
+                            advance(cb);
+                            progressed = true;
+                        }
+                    }
+                    if (ca.live) {
+                        const uint32_t s = ca.it % SA, ph = (ca.it / SA) & 1;
+                        if (ptx::mbar_try_wait(ptx::smem_u32(&empty_a[s]), ph ^ 1)) {
+                            const uint32_t full = ptx::smem_u32(&full_a[s]);
+                            ptx::mbar_expect_tx(full, T::kABytes);
+                            ptx::tma_load_2d(ptx::smem_u32(smem_a + s * T::kABytes), &tma_a, full, ca.kb * BK,
+                                             ca.c.row_start);
+                            advance(ca);
+                            progressed = true;
+                        }
+                    }
+                    if (progressed) {
+                        idle = 0;
+                    } else if (idle++ == 0) {
+                        stall_start = clock64();
+                    } else if ((idle & 0x3FFu) == 0) {  // bounded like every other wait
+                        if (*abort_flag) break;
+                        if (clock64() - stall_start > ptx::kWaitCycles) {
+                            *abort_flag = 1;
+                            atomicOr(p.status, kCodeProducer);
+                            break;
+                        }
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
-            uint32_t it = 0, tcount = 0;
+            uint32_t it = 0, count = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tcount) {
-                const uint32_t buf = tcount & 1, tph = (tcount >> 1) & 1;
+            Segment sg;
+            for (; ok && walk.next(sg); ++count) {
+                const uint32_t buf = count & 1, tph = (count >> 1) & 1;
                 if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty[buf]), tph ^ 1, abort_flag, p.status, kCodeMma)) break;
                 ptx::tc_fence_after();
                 const uint32_t acc = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % T::kStages, ph = (it / T::kStages) & 1;
-                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status, kCodeMma)) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                    const uint32_t sb = it % SB, phb = (it / SB) & 1;
+                    const uint32_t sa = STREAM ? it % SA : sb, pha = (it / SA) & 1;
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_b[sb]), phb, abort_flag, p.status, kCodeMma)) {
                         ok = false;
                         break;
                     }
+                    if constexpr (STREAM) {
+                        if (!ptx::mbar_wait(ptx::smem_u32(&full_a[sa]), pha, abort_flag, p.status, kCodeMma)) {
+                            ok = false;
+                            break;
+                        }
+                    }
                     ptx::tc_fence_after();
-                    uint8_t* stage = smem + s * T::kStageBytes;
-                    const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(stage));
-                    const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(stage + T::kABytes));
+                    const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(smem_a + sa * T::kABytes));
+                    const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(smem_b + sb * T::kBBytes));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)
-                        ptx::umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
-                    ptx::umma_commit(ptx::smem_u32(&empty_bar[s]));
+                        ptx::umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb > sg.kb0) || kk != 0);
+                    ptx::umma_commit(ptx::smem_u32(&empty_b[sb]));
+                    if constexpr (STREAM) ptx::umma_commit(ptx::smem_u32(&empty_a[sa]));
                 }
                 if (ok) ptx::umma_commit(ptx::smem_u32(&tmem_full[buf]));
             }
         }
     } else {
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;            // tensor-memory lanes this warp may read
+        const int pass = (warp - 2) >> 2;        // the two warps of a quarter alternate over the chunks
         const int row_in_tile = quarter * 32 + lane;
-        uint32_t tcount = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
-            const TileCoord c = tile_coord(p, tile, m_tiles);
-            const uint32_t buf = tcount & 1, tph = (tcount >> 1) & 1;
+        const bool leader = threadIdx.x == 64;  // first epilogue thread
+        float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
+        constexpr uint32_t kEpilogueThreads = 32 * kEpilogueWarps;
+        uint32_t count = 0;
+        Segment sg;
+        for (; walk.next(sg); ++count) {
+            const TileCoord c = tile_coord(p, sg.tile, m_tiles);
+            const uint32_t buf = count & 1, tph = (count >> 1) & 1;
             if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue)) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            const int row = c.row_start + row_in_tile;
-            const bool row_ok = row < c.row_end;
-            const int n0 = c.n_index * BN;
-            uint32_t r0[32];
-            float v[32];
-            if (p.epilogue == SFB_EPI_SWIGLU) {
-                const int half_n = p.n / 2;
-                uint32_t r1[32];
-                for (int ch = 0; ch < BN / 64; ++ch) {
-                    const int out_col = c.n_index * (BN / 2) + ch * 32;
-                    if (out_col >= half_n) break;
-                    ptx::tmem_ld_32x32(acc + ch * 32, r0);
-                    ptx::tmem_ld_32x32(acc + BN / 2 + ch * 32, r1);
-                    ptx::tmem_ld_wait();
-                    if (row_ok) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float g = __uint_as_float(r0[i]), u = __uint_as_float(r1[i]);
-                            v[i] = g / (1.0F + __expf(-g)) * u;
-                        }
-                        store_chunk(p.out, p.out_f32, static_cast<size_t>(row) * half_n + out_col, v,
-                                    min(32, half_n - out_col));
-                    }
-                }
-            } else {
-                for (int ch = 0; ch < BN / 32; ++ch) {
-                    const int col = n0 + ch * 32;
-                    if (col >= p.n) break;
-                    ptx::tmem_ld_32x32(acc + ch * 32, r0);
+            const int row0 = c.row_start + quarter * 32;
+            const bool row_ok = row0 + lane < c.row_end;
+            const bool swiglu = p.epilogue == SFB_EPI_SWIGLU;
+            // An output chunk is 32 columns: one 32-column group of the accumulator, or for SwiGLU
+            // a gate group and its up group from the other half of the tile.
+            const int chunks = swiglu ? BN / 64 : BN / 32;
+            const int width = swiglu ? p.n / 2 : p.n;
+            const int out0 = swiglu ? c.n_index * (BN / 2) : c.n_index * BN;
+            const bool whole = sg.kb0 == 0 && sg.kb1 == k_blocks;
+            uint32_t r0[32], r1[32];
+            // Sums of a tile: [BN / 4 column groups][BM rows][4], so that a warp touches 512 contiguous bytes.
+            float* sums = p.accum + static_cast<size_t>(sg.tile) * BM * BN + row_in_tile * 4;
+            if (!whole) {
+                // Part of a tile: add the partial sums, then find out whether they completed the tile.
+#pragma unroll 1
+                for (int g = pass; g < BN / 32; g += 2) {
+                    if (c.n_index * BN + g * 32 >= p.n) break;
+                    ptx::tmem_ld_32x32(acc + g * 32, r0);
                     ptx::tmem_ld_wait();
                     if (!row_ok) continue;
-                    const int valid = min(32, p.n - col);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]);
-                    if (p.epilogue == SFB_EPI_ROPE_SPLIT) {
-                        const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
-                        const int b = row / p.seq, t = row - b * p.seq;
-                        bf16* dst;
-                        int heads, local;
-                        bool rotate = true;
-                        if (col < hidden) { dst = p.q; heads = p.q_heads; local = col; }
-                        else if (col < hidden + kvw) { dst = p.key; heads = p.kv_heads; local = col - hidden; }
-                        else { dst = p.value; heads = p.kv_heads; local = col - hidden - kvw; rotate = false; }
-                        const int head = local / p.head_dim, d0 = local - head * p.head_dim;
-                        if (rotate) {
-                            const float* cs = p.rope_cos + static_cast<size_t>(t) * (p.head_dim / 2) + d0 / 2;
-                            const float* sn = p.rope_sin + static_cast<size_t>(t) * (p.head_dim / 2) + d0 / 2;
+                    for (int i = 0; i < 8; ++i)
+                        ptx::red_add_f32x4(sums + (g * 8 + i) * (BM * 4), __uint_as_float(r0[4 * i]),
+                                           __uint_as_float(r0[4 * i + 1]), __uint_as_float(r0[4 * i + 2]),
+                                           __uint_as_float(r0[4 * i + 3]));
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(ptx::smem_u32(&tmem_empty[buf]));
+                __threadfence();
+                ptx::named_barrier(1, kEpilogueThreads);
+                if (leader) {
+                    const int mine = sg.kb1 - sg.kb0;
+                    *last_flag = (atomicAdd(p.tile_counters + sg.tile, mine) + mine == k_blocks) ? 1u : 0u;
+                }
+                ptx::named_barrier(1, kEpilogueThreads);
+                if (*last_flag == 0) continue;
+                // this CTA completed the tile: it reads the sums back (past L1), restores the zeros
+                // and runs the epilogue
+                __threadfence();
+                if (leader) p.tile_counters[sg.tile] = 0;
+            }
+            // 32 accumulator columns starting at `group_col`, from tensor memory or from the sums
+            auto fetch = [&](int group_col, uint32_t (&dst)[32]) {
+                if (whole) {
+                    ptx::tmem_ld_32x32(acc + group_col, dst);
+                    return;
+                }
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float4 c4 = reinterpret_cast<const float4*>(cs)[i];
-                                const float4 s4 = reinterpret_cast<const float4*>(sn)[i];
-                                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+                for (int i = 0; i < 8; ++i) {
+                    float4* src = reinterpret_cast<float4*>(sums + (group_col / 4 + i) * (BM * 4));
+                    float4 f = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+                    if (row_ok) {
+                        f = __ldcg(src);
+                        __stcg(src, make_float4(0.0F, 0.0F, 0.0F, 0.0F));
+                    }
+                    dst[4 * i] = __float_as_uint(f.x); dst[4 * i + 1] = __float_as_uint(f.y);
+                    dst[4 * i + 2] = __float_as_uint(f.z); dst[4 * i + 3] = __float_as_uint(f.w);
+                }
+            };
+#pragma unroll 1
+            for (int ch = pass; ch < chunks; ch += 2) {
+                const int col0 = out0 + ch * 32;
+                const bool live = col0 < width;
+                if (live) {
+                    fetch(ch * 32, r0);
+                    if (swiglu) fetch(BN / 2 + ch * 32, r1);
+                    if (whole) ptx::tmem_ld_wait();
+                }
+                if (whole && ch + 2 >= chunks) {  // this thread has read all it needs: hand the accumulator back
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&tmem_empty[buf]));
+                }
+                if (!live) continue;
+                if (swiglu) {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float e = v[8 * i + 2 * j], o = v[8 * i + 2 * j + 1];
-                                    v[8 * i + 2 * j] = e * cc[j] - o * ss[j];
-                                    v[8 * i + 2 * j + 1] = e * ss[j] + o * cc[j];
-                                }
-                            }
-                        }
-                        const size_t o = ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d0;
-                        store_chunk(dst, 0, o, v, 32);
-                    } else {
-                        const size_t index = static_cast<size_t>(row) * p.n + col;
-                        if (p.epilogue == SFB_EPI_RESIDUAL) {
-                            float res[32];
-                            load_bf16_chunk(p.residual + index, res, valid);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] += res[i];
-                        }
-                        store_chunk(p.out, p.out_f32, index, v, valid);
+                    for (int i = 0; i < 32; ++i) {
+                        const float gate = __uint_as_float(r0[i]);
+                        r0[i] = __float_as_uint(__fdividef(gate, 1.0F + __expf(-gate)) * __uint_as_float(r1[i]));
                     }
                 }
+                stage_write(stage, lane, r0);
+                __syncwarp();
+                emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width);
+                __syncwarp();
             }
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(ptx::smem_u32(&tmem_empty[buf]));
         }
     }
 
@@ -349,12 +630,14 @@ __global__ void build_tile_table_kernel(const int* __restrict__ offsets, int gro
     table[0] = count;
 }
 
-template <int BN>
+bool stream_shape(const sfb_gemm_args& g) { return g.m <= BM && !g.group_offsets; }
+
+template <int BN, bool STREAM>
 sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
-    using T = Tile<BN>;
+    using T = Tile<BN, STREAM>;
     static bool configured = false;
     if (!configured) {
-        SFB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        SFB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STREAM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       T::kSmemBytes));
         configured = true;
     }
@@ -362,9 +645,13 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     CUtensorMap map_a, map_b;
     if (!encode_tensor_map_bf16_2d(&map_a, g.a, static_cast<uint64_t>(g.m), static_cast<uint64_t>(g.k), BM, BK))
         return SFB_CUDA_ERROR;
-    if (!encode_tensor_map_bf16_2d(&map_b, g.bt, static_cast<uint64_t>(groups) * g.n, static_cast<uint64_t>(g.k),
-                                   BN, BK))
+    if (g.bt_tiled) {
+        const uint64_t blocks = static_cast<uint64_t>(ceil_div(g.n, 64)) * ceil_div(g.k, 64);
+        if (!encode_tensor_map_bf16_2d(&map_b, g.bt, blocks * 64, 64, 64, 64)) return SFB_CUDA_ERROR;
+    } else if (!encode_tensor_map_bf16_2d(&map_b, g.bt, static_cast<uint64_t>(groups) * g.n,
+                                          static_cast<uint64_t>(g.k), BN, BK)) {
         return SFB_CUDA_ERROR;
+    }
     TcParams p{};
     p.out = g.out;
     p.m = g.m; p.n = g.n; p.k = g.k;
@@ -378,6 +665,7 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     p.rope_sin = g.rope_sin;
     p.seq = g.seq; p.q_heads = g.q_heads; p.kv_heads = g.kv_heads; p.head_dim = g.head_dim;
     p.n_tiles = ceil_div(g.n, BN);
+    p.b_tiled = g.bt_tiled;
     p.status = device_status_word();
     int max_m_tiles;
     if (g.group_offsets) {
@@ -394,14 +682,27 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
         p.dense_m_tiles = max_m_tiles;
     }
     const long long tiles = static_cast<long long>(max_m_tiles) * p.n_tiles;
-    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    gemm_tcgen05_kernel<BN><<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, p);
+    int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    if (STREAM && stream_shape(g) && g.split_workspace && (reinterpret_cast<uintptr_t>(g.split_workspace) & 15) == 0 &&
+        g.split_workspace_bytes >= sfb_gemm_stream_workspace_bytes(g.n)) {
+        // tiles left over after the last full round; cutting them up pays unless they nearly fill a round
+        const int left = static_cast<int>(tiles % sm_count());
+        if (left != 0 && left <= sm_count() * 7 / 8) {
+            p.shared_tiles = left;
+            p.accum = static_cast<float*>(g.split_workspace);
+            p.tile_counters = reinterpret_cast<int*>(p.accum + static_cast<size_t>(p.n_tiles) * BM * BN);
+            const long long units = static_cast<long long>(left) * ceil_div(g.k, BK);
+            grid = static_cast<int>(tiles >= sm_count() || units >= sm_count() ? sm_count() : units);
+        }
+    }
+    gemm_tcgen05_kernel<BN, STREAM><<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, p);
     return check_launch("gemm_tcgen05");
 }
 
 int pick_bn(const sfb_gemm_args& g) {
     if (g.epilogue == SFB_EPI_SWIGLU) return 2 * g.swiglu_block;
-    // Few rows (decode) or a narrow output: more, smaller tiles keep more SMs streaming weights.
+    if (g.bt_tiled || stream_shape(g)) return 128;
+    // A narrow output or few tiles: more, smaller tiles keep more SMs busy.
     const long long wide_tiles = static_cast<long long>(ceil_div(g.m, BM)) * ceil_div(g.n, 256);
     return (g.n < 256 || wide_tiles < sm_count()) ? 128 : 256;
 }
@@ -412,12 +713,21 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
     if (g.k % 8 != 0) return false;  // TMA row pitch must be a multiple of 16 bytes
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.bt) & 15)) return false;
     if (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64 && g.swiglu_block != 128) return false;
+    if (g.bt_tiled && (g.group_offsets || (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64))) return false;
     if (g.epilogue == SFB_EPI_ROPE_SPLIT && g.head_dim % 32 != 0) return false;
     return true;
 }
 
 sfb_status gemm_bf16_tcgen05(const sfb_gemm_args& g, cudaStream_t stream) {
-    return pick_bn(g) == 256 ? launch<256>(g, stream) : launch<128>(g, stream);
+    if (pick_bn(g) == 256) return launch<256, false>(g, stream);
+    if (stream_shape(g)) return launch<128, true>(g, stream);
+    return launch<128, false>(g, stream);
 }
 
 }  // namespace sfb
+
+extern "C" size_t sfb_gemm_stream_workspace_bytes(int n) {
+    if (n <= 0) return 0;
+    const size_t tiles = static_cast<size_t>(sfb::ceil_div(n, 128));
+    return tiles * (128 * 128 * sizeof(float)) + (tiles * sizeof(int) + 15) / 16 * 16;
+}

@@ -121,6 +121,10 @@ struct DecoderExecutablePlan::Impl {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
+    std::vector<const void*> blocked_weights;  // weights re-laid in 64x64 blocks (decode-shaped plans)
+    bool blocked(const void* w) const {
+        return std::find(blocked_weights.begin(), blocked_weights.end(), w) != blocked_weights.end();
+    }
 
     std::size_t esz() const { return dtype == SFB_BF16 ? 2 : 4; }
     template <class P = void> P* ws(const char* name) {
@@ -345,6 +349,29 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         }
     }
     staging.release();
+    // Plans with few rows stream every weight once per pass: store the dense weights in 64x64
+    // blocks so that the GEMM reads 8 KB contiguous runs instead of 128-byte row pieces.
+    if (bf && T <= 128 && plan->policy.gemm_backend != SFB_GEMM_SIMT) {
+        auto reblock = [&](void* w, int n, int k) {
+            if (!w || n % 64 != 0 || k % 64 != 0) return;
+            const std::size_t bytes = static_cast<std::size_t>(n) * k * 2;
+            DeviceBuffer blocked(bytes);
+            throw_on(sfb_k_tile_weight_bf16(w, blocked.get(), n, k, s));
+            cuda_check(cudaMemcpyAsync(w, blocked.get(), bytes, cudaMemcpyDeviceToDevice, s), "weight reblock");
+            cuda_check(cudaStreamSynchronize(s), "weight reblock");
+            m.blocked_weights.push_back(w);
+        };
+        reblock(m.wqkv, m.qkv_l, H);
+        reblock(m.wo, H, m.hidden_l);
+        if (!moe) {
+            reblock(m.wgu, 2 * I, H);
+            reblock(m.wd, H, I);
+        }
+        for (auto& constant : plan->constants)
+            if ((constant.name == "packed_qkv_weight" && m.blocked(m.wqkv)) ||
+                (constant.name == "packed_gate_up_weight" && m.blocked(m.wgu)))
+                constant.layout += "_blocked64";
+    }
 
     // ---- KV cache for decode plans ------------------------------------------------------------
     const int ctx = c.context_sequence;
@@ -469,9 +496,13 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         }
         wp.add("expert_output", A * H * e, 10, 11);
     }
+    if (bf && T <= 128)  // partial tile sums of the weight-streaming GEMMs; zero between kernels
+        wp.add("gemm_partials", sfb_gemm_stream_workspace_bytes(std::max({m.qkv_l, H, 2 * I})), 0, 13);
     wp.add("output", TH * e, 11, 13);
     if (bf) wp.add("output_f32", TH * 4, piped ? 0 : 12, 13);
     m.workspace.allocate(wp.total_bytes());
+    if (m.has("gemm_partials"))
+        cuda_check(cudaMemsetAsync(m.ws("gemm_partials"), 0, wp.bytes(wp.find("gemm_partials")), s), "scratch clear");
     plan->naive_bytes = wp.naive_bytes();
     plan->workspace_bytes = wp.total_bytes();
     (void)plan_start;
@@ -532,6 +563,11 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             g.batch = c.batch; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
         }
         if (offsets) { g.group_offsets = offsets; g.groups = groups; g.tile_table = m.ws("tile_table"); }
+        if (m.has("gemm_partials")) {
+            g.split_workspace = m.ws("gemm_partials");
+            g.split_workspace_bytes = m.planner.bytes(m.planner.find("gemm_partials"));
+        }
+        g.bt_tiled = m.blocked(w) ? 1 : 0;
         throw_on(sfb_k_gemm_bf16(&g, s));
     };
     auto allreduce = [&](void* buffer, int64_t count) {
@@ -723,6 +759,7 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
             g.batch = nb; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
         }
+        g.bt_tiled = m.blocked(w) ? 1 : 0;
         throw_on(sfb_k_gemm_bf16(&g, s));
     };
     cudaEvent_t t0 = m.events[12], t1 = m.events[15];
@@ -819,7 +856,7 @@ int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_
     else if (name == "fused_qkv") count = static_cast<int64_t>(m.T) * m.qkv_l;
     else if (name == "dispatched" || name == "expert_output") count = static_cast<int64_t>(A) * m.H;
     else if (name == "expert_activation" || name == "expert_first" || name == "expert_gate") count = static_cast<int64_t>(A) * config.intermediate;
-    else if (name == "decode_partials" || name == "dispatch_scratch" || name == "tile_table") count = static_cast<int64_t>(bytes / 4);
+    else if (name == "decode_partials" || name == "dispatch_scratch" || name == "tile_table" || name == "gemm_partials") count = static_cast<int64_t>(bytes / 4);
     else count = static_cast<int64_t>(m.T) * m.H;
     if (!host_out) return count;
     if (capacity < count) throw std::invalid_argument("read_tensor: buffer too small");

@@ -51,6 +51,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
+// Barrier among `threads` threads of the CTA (a multiple of 32) on hardware barrier `id` (1..15).
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// fp32 x4 reduction into global memory (performed at L2, no return value).
+__device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
 // Bounded wait.  `abort_flag` (shared memory) is polled so that once one role has given
 // up the others leave quickly too.  Returns false on timeout/abort.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,

@@ -26,7 +26,8 @@ class GemmArgs(C.Structure):
                 ("q", vp), ("key", vp), ("value", vp), ("rope_cos", vp), ("rope_sin", vp),
                 ("batch", C.c_int), ("seq", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int),
                 ("head_dim", C.c_int),
-                ("group_offsets", vp), ("groups", C.c_int), ("tile_table", vp)]
+                ("group_offsets", vp), ("groups", C.c_int), ("tile_table", vp),
+                ("split_workspace", vp), ("split_workspace_bytes", C.c_size_t), ("bt_tiled", C.c_int)]
 
 
 class AttentionArgs(C.Structure):
@@ -94,7 +95,7 @@ ALLREDUCE_FN = C.CFUNCTYPE(None, vp, vp, C.c_int64, C.c_int, vp)
 # Every symbol include/schedforge_b200.h declares (checked by tests/test_abi.py).
 EXPORTS = (
     "sfb_last_error sfb_version sfb_launch_count sfb_device_status "
-    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 "
+    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 sfb_tiled_weight_elems sfb_k_tile_weight_bf16 sfb_gemm_stream_workspace_bytes "
     "sfb_rope_table sfb_k_rope_split sfb_k_attention_prefill "
     "sfb_attention_decode_workspace sfb_attention_decode_default_splits sfb_k_attention_decode_paged "
     "sfb_k_paged_kv_append sfb_k_paged_kv_gather "
@@ -139,8 +140,9 @@ def load():
     lib.sfb_last_error.restype = C.c_char_p
     lib.sfb_version.restype = C.c_char_p
     lib.sfb_launch_count.restype = C.c_uint64
+    lib.sfb_tiled_weight_elems.restype = C.c_int64
     for name in ("sfb_attention_decode_workspace", "sfb_moe_dispatch_scratch_bytes",
-                 "sfb_decoder_workspace_bytes"):
+                 "sfb_decoder_workspace_bytes", "sfb_gemm_stream_workspace_bytes"):
         if hasattr(lib, name):
             getattr(lib, name).restype = C.c_size_t
     if hasattr(lib, "sfb_decoder_stream"):

@@ -13,16 +13,23 @@ BF16_TOL = 2e-2  # max-abs relative, bf16 outputs with fp32 accumulation
 
 
 def gemm_bf16(sfb, dev, a, bt, epilogue=0, backend=0, out_f32=False, residual=None, swiglu_block=0,
-              rope=None, offsets=None, groups=0, n=None):
+              rope=None, offsets=None, groups=0, n=None, scratch=None, blocked=False):
     torch = dev.torch
     m, k = a.shape
     n = n if n is not None else bt.shape[-2]
     g = sfb.GemmArgs()
     g.a, g.bt = a.data_ptr(), bt.data_ptr()
     g.m, g.n, g.k = m, n, k
+    keep = []
+    if blocked:  # re-lay the [n,k] weight in 64x64 blocks first
+        lib = sfb.load()
+        tiled = dev.zeros((lib.sfb_tiled_weight_elems(n, k),), torch.bfloat16)
+        sfb.check(lib.sfb_k_tile_weight_bf16(C.c_void_p(bt.data_ptr()), C.c_void_p(tiled.data_ptr()), n, k,
+                                             C.c_void_p(dev.stream())))
+        keep.append(tiled)
+        g.bt, g.bt_tiled = tiled.data_ptr(), 1
     g.epilogue, g.backend, g.out_f32 = epilogue, backend, int(out_f32)
     out = None
-    keep = []
     if epilogue == sfb.EPI_ROPE_SPLIT:
         batch, seq, hq, hkv, d, cos, sin = rope
         q = dev.zeros((batch, hq, seq, d), torch.bfloat16)
@@ -44,6 +51,8 @@ def gemm_bf16(sfb, dev, a, bt, epilogue=0, backend=0, out_f32=False, residual=No
         table = dev.zeros((4 * (m // 128 + groups + 2),), torch.int32)
         keep.append(table)
         g.tile_table = table.data_ptr()
+    if scratch is not None:
+        g.split_workspace, g.split_workspace_bytes = scratch[0].data_ptr(), scratch[1]
     sfb.check(sfb.load().sfb_k_gemm_bf16(C.byref(g), C.c_void_p(dev.stream())))
     torch.cuda.synchronize()
     word = C.c_uint32(0)
@@ -136,6 +145,84 @@ def test_gemm_bf16_rope_split(sfb, dev, port, backend):
     assert rel_err(dev.np(q), wq) < BF16_TOL
     assert rel_err(dev.np(key), wk) < BF16_TOL
     assert rel_err(dev.np(val), wv) < BF16_TOL
+
+
+# Few rows (decode).  Given zeroed scratch the tcgen05 kernel cuts the (tile, K block) sequence
+# into one equal range per SM, sums partial tiles in the scratch and leaves it zeroed again.
+def _scratch(sfb, dev, n):
+    nbytes = sfb.load().sfb_gemm_stream_workspace_bytes(n)
+    return dev.zeros((nbytes // 4,), dev.torch.float32), nbytes
+
+
+@pytest.mark.parametrize("blocked", [False, True])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 4096), (17, 200, 2048), (1, 512, 8200), (64, 320, 1000),
+                                   (128, 128, 512), (100, 6144, 1024)])
+def test_gemm_tcgen05_few_rows_equal_ranges(sfb, dev, port, m, n, k, blocked):
+    a, w = _inputs(port, m, n, k, seed=11, scale=0.02)
+    res = port.round_bf16(np.random.default_rng(12).standard_normal((m, n)).astype(np.float32))
+    want = port.matmul(a, w, fma=True)
+    da, dw = dev.bf16(a), dev.bf16(w.T.copy())
+    scratch = _scratch(sfb, dev, n)
+    got32 = gemm_bf16(sfb, dev, da, dw, backend=2, out_f32=True, scratch=scratch, blocked=blocked)
+    assert rel_err(dev.np(got32), want) < 1e-4
+    assert not dev.np(scratch[0]).any()  # the kernel put the zeros back
+    got = gemm_bf16(sfb, dev, da, dw, backend=0, epilogue=sfb.EPI_RESIDUAL, residual=dev.bf16(res),
+                    scratch=scratch, blocked=blocked)
+    assert rel_err(dev.np(got), want + res) < BF16_TOL
+    assert not dev.np(scratch[0]).any()
+
+
+def test_gemm_tcgen05_few_rows_rope_split(sfb, dev, port):
+    from oracle import binding as ob
+    batch, seq, hq, hkv, d = 24, 1, 8, 2, 64
+    hidden = hq * d
+    c = ob.decoder_config(batch, seq, hidden, 64, hq, hkv, d, rope_theta=10000.0)
+    n, k, m = hidden + 2 * hkv * d, 2048, batch * seq
+    a, w = _inputs(port, m, n, k, seed=13, scale=0.02)
+    wq, wk, wv = port.split_qkv_rope(c, port.matmul(a, w, fma=True))
+    cos = np.zeros((seq, d // 2), np.float32)
+    sin = np.zeros((seq, d // 2), np.float32)
+    sfb.check(sfb.load().sfb_rope_table(seq, d, C.c_float(10000.0), cos.ctypes.data_as(sfb.f32p),
+                                        sin.ctypes.data_as(sfb.f32p)))
+    scratch = _scratch(sfb, dev, n)
+    for _ in range(2):  # the second call runs on the scratch the first one left behind
+        q, key, val = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), epilogue=sfb.EPI_ROPE_SPLIT,
+                                backend=2, rope=(batch, seq, hq, hkv, d, dev.f32(cos), dev.f32(sin)),
+                                scratch=scratch, blocked=True)
+        assert rel_err(dev.np(q), wq) < BF16_TOL
+        assert rel_err(dev.np(key), wk) < BF16_TOL
+        assert rel_err(dev.np(val), wv) < BF16_TOL
+
+
+def test_gemm_blocked_weight_many_rows(sfb, dev, port):
+    m, n, k = 300, 384, 512
+    a, w = _inputs(port, m, n, k, seed=15, scale=0.02)
+    got32 = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), backend=2, out_f32=True, blocked=True)
+    assert rel_err(dev.np(got32), port.matmul(a, w, fma=True)) < 1e-4
+
+
+def test_gemm_blocked_weight_rejected_by_simt(sfb, dev, port):
+    a, w = _inputs(port, 8, 64, 64)
+    with pytest.raises(sfb.SfbError):
+        gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(w.T.copy()), backend=1, blocked=True)
+
+
+@pytest.mark.parametrize("blocked", [False, True])
+@pytest.mark.parametrize("m", [1, 100, 128])
+def test_gemm_tcgen05_swiglu_few_rows(sfb, dev, port, m, blocked):
+    inter, k, block = 320, 1024, 64
+    rng = np.random.default_rng(14)
+    a = port.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    wg = port.round_bf16((rng.standard_normal((k, inter)) * 0.1).astype(np.float32))
+    wu = port.round_bf16((rng.standard_normal((k, inter)) * 0.1).astype(np.float32))
+    want = port.swiglu(port.matmul(a, np.concatenate([wg, wu], axis=1), fma=True), inter)
+    bt = np.concatenate([np.concatenate([wg.T[i:i + block], wu.T[i:i + block]]) for i in range(0, inter, block)])
+    scratch = _scratch(sfb, dev, 2 * inter)
+    for _ in range(2):
+        got = gemm_bf16(sfb, dev, dev.bf16(a), dev.bf16(bt), epilogue=sfb.EPI_SWIGLU, backend=2,
+                        swiglu_block=block, scratch=scratch, blocked=blocked)
+        assert rel_err(dev.np(got), want) < BF16_TOL
+    assert not dev.np(scratch[0]).any()
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
