@@ -236,6 +236,36 @@ __global__ void decode_combine_kernel(const float* __restrict__ partials, T* __r
     }
 }
 
+// The same merge for at most 32 splits: lane s holds the record header of split s, the weights
+// exp(max_s - max) / denominator are computed once per row and broadcast by shuffles, and the
+// loads of all splits are independent.
+template <class T>
+__global__ void decode_combine_warp_kernel(const float* __restrict__ partials, T* __restrict__ out, int rows,
+                                           int splits, int dim_v) {
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const size_t record = static_cast<size_t>(dim_v) + 2;
+    const float* rec = partials + static_cast<size_t>(row) * splits * record;
+    float ms = -INFINITY, ls = 0.0F;
+    if (lane < splits) {
+        ms = rec[lane * record];
+        ls = rec[lane * record + 1];
+    }
+    const float m = warp_max(ms);
+    float w = ms == -INFINITY ? 0.0F : expf(ms - m);
+    float den = 0.0F;
+    for (int s = 0; s < splits; ++s) den += __shfl_sync(0xffffffffu, ls * w, s);  // split order, as the serial merge
+    for (int d = lane; d < dim_v; d += 32) {
+        float a = 0.0F;
+        for (int s = 0; s < splits; ++s) {
+            const float ws = __shfl_sync(0xffffffffu, w, s);
+            if (ws != 0.0F) a += rec[s * record + 2 + d] * ws;
+        }
+        out[static_cast<size_t>(row) * dim_v + d] = from_float<T>(a / den);
+    }
+}
+
 template <class T>
 __global__ void paged_append_kernel(const T* __restrict__ new_k, const T* __restrict__ new_v, T* __restrict__ k_pool,
                                     T* __restrict__ v_pool, const int* __restrict__ table,
@@ -383,7 +413,12 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream str
     }
     SFB_TRY(check_launch("attention_decode_paged"));
     const int rows = a->batch * a->q_heads;
-    if (a->dtype == SFB_F32)
+    if (splits <= 32 && a->head_dim_value % 32 == 0) {
+        if (a->dtype == SFB_F32)
+            decode_combine_warp_kernel<float><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<float*>(a->out), rows, splits, a->head_dim_value);
+        else
+            decode_combine_warp_kernel<bf16><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<bf16*>(a->out), rows, splits, a->head_dim_value);
+    } else if (a->dtype == SFB_F32)
         decode_combine_kernel<float><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<float*>(a->out), rows, splits, a->head_dim_value);
     else
         decode_combine_kernel<bf16><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<bf16*>(a->out), rows, splits, a->head_dim_value);

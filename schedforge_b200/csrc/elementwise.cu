@@ -64,6 +64,43 @@ __global__ void rms_norm_kernel(const T* __restrict__ x, const float* __restrict
     }
 }
 
+// bf16, few rows (decode): one 256-thread block per row, so that a row is read by 256 threads
+// at once instead of 32 threads sixteen times over.  width % 8 == 0.
+__global__ void __launch_bounds__(256)
+rms_norm_row_block_kernel(const bf16* __restrict__ x, const float* __restrict__ weight, bf16* __restrict__ y,
+                          int width, float epsilon) {
+    __shared__ float partial[8];
+    const uint4* row4 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(blockIdx.x) * width);
+    uint4* out4 = reinterpret_cast<uint4*>(y + static_cast<size_t>(blockIdx.x) * width);
+    const int pieces = width / 8;
+    float ss = 0.0F;
+    for (int c = threadIdx.x; c < pieces; c += 256) {
+        const uint4 packed = row4[c];
+        const bf16* v = reinterpret_cast<const bf16*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float f = to_float(v[i]); ss += f * f; }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.0F;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += partial[i];
+    const float inv = 1.0F / sqrtf(total / static_cast<float>(width) + epsilon);
+    for (int c = threadIdx.x; c < pieces; c += 256) {
+        const uint4 packed = row4[c];
+        const bf16* v = reinterpret_cast<const bf16*>(&packed);
+        const float4 w0 = reinterpret_cast<const float4*>(weight)[2 * c];
+        const float4 w1 = reinterpret_cast<const float4*>(weight)[2 * c + 1];
+        const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        uint4 result;
+        bf16* r = reinterpret_cast<bf16*>(&result);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = from_float<bf16>(to_float(v[i]) * inv * w[i]);
+        out4[c] = result;
+    }
+}
+
 template <class T>
 __global__ void add_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ z,
                            int64_t count) {
@@ -146,6 +183,13 @@ sfb_status sfb_k_rms_norm(const void* x, const float* weight, void* y, int rows,
                           float epsilon, sfb_dtype dtype, sfb_stream stream) {
     SFB_REQUIRE(x && weight && y && rows > 0 && width > 0, "RMSNorm shape mismatch");
     const int block = 256, grid = ceil_div(rows, block / 32);
+    if (dtype == SFB_BF16 && rows <= 2048 && width % 8 == 0 && width >= 2048 &&
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(weight) & 15) == 0) {
+        rms_norm_row_block_kernel<<<rows, 256, 0, as_stream(stream)>>>(static_cast<const bf16*>(x), weight,
+                                                                       static_cast<bf16*>(y), width, epsilon);
+        return check_launch("rms_norm");
+    }
     if (dtype == SFB_F32)
         rms_norm_kernel<float><<<grid, block, 0, as_stream(stream)>>>(
             static_cast<const float*>(x), weight, static_cast<float*>(y), rows, width, epsilon);

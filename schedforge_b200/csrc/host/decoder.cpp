@@ -121,6 +121,8 @@ struct DecoderExecutablePlan::Impl {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
+    // dense fused bf16 plan on one rank: the last GEMM writes the fp32 result itself, "output" is skipped
+    bool direct_f32_output = false;
     std::vector<const void*> blocked_weights;  // weights re-laid in 64x64 blocks (decode-shaped plans)
     bool blocked(const void* w) const {
         return std::find(blocked_weights.begin(), blocked_weights.end(), w) != blocked_weights.end();
@@ -457,6 +459,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         m.pipeline_chunks = c.batch;
         while (m.pipeline_chunks > 8 || c.batch % m.pipeline_chunks != 0) --m.pipeline_chunks;
     }
+    m.direct_f32_output = bf && fused && !moe && m.size == 1;
     const bool piped = m.pipeline_chunks > 1;  // host copies overlap compute: I/O staging must not alias anything
     wp.add("input_f32", TH * 4, 0, (bf && !piped) ? 0 : 13);
     if (bf) wp.add("input", TH * e, 0, 13);
@@ -499,7 +502,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     if (bf && T <= 128)  // partial tile sums of the weight-streaming GEMMs; zero between kernels
         wp.add("gemm_partials", sfb_gemm_stream_workspace_bytes(std::max({m.qkv_l, H, 2 * I})), 0, 13);
     wp.add("output", TH * e, 11, 13);
-    if (bf) wp.add("output_f32", TH * 4, piped ? 0 : 12, 13);
+    if (bf) wp.add("output_f32", TH * 4, piped ? 0 : (m.direct_f32_output ? 10 : 12), 13);  // written by the last GEMM when direct
     m.workspace.allocate(wp.total_bytes());
     if (m.has("gemm_partials"))
         cuda_check(cudaMemsetAsync(m.ws("gemm_partials"), 0, wp.bytes(wp.find("gemm_partials")), s), "scratch clear");
@@ -548,7 +551,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     int ev = 0;
     auto mark = [&] { if (stage_events) cuda_check(cudaEventRecord(m.events[ev++], s), "event"); };
     auto gemm = [&](const void* a, const void* w, void* out, int mm, int n, int k, int epi, const void* res = nullptr,
-                    int sb = 0, const int* offsets = nullptr, int groups = 0) {
+                    int sb = 0, const int* offsets = nullptr, int groups = 0, bool f32_out = false) {
         if (!bf) {
             throw_on(sfb_k_gemm_f32(static_cast<const float*>(a), static_cast<const float*>(w),
                                     static_cast<float*>(out), mm, n, k, s));
@@ -556,7 +559,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         }
         sfb_gemm_args g{};
         g.a = a; g.bt = w; g.out = out; g.m = mm; g.n = n; g.k = k; g.epilogue = epi;
-        g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb;
+        g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb; g.out_f32 = f32_out ? 1 : 0;
         if (epi == SFB_EPI_ROPE_SPLIT) {
             g.q = m.ws("query"); g.key = m.ws("key"); g.value = m.ws("value");
             g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
@@ -629,8 +632,12 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     if (!moe) {
         if (fused) {
             gemm(m.ws("normalized2"), m.wgu, m.ws("activation"), T, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block);
-            gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1);
-            allreduce(out, static_cast<int64_t>(T) * H);
+            if (m.direct_f32_output) {
+                gemm(m.ws("activation"), m.wd, m.ws("output_f32"), T, H, I, SFB_EPI_RESIDUAL, r1, 0, nullptr, 0, true);
+            } else {
+                gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1);
+                allreduce(out, static_cast<int64_t>(T) * H);
+            }
             mark(); mark();  // 8: ffn, 9: (residual inside)
         } else {
             gemm(m.ws("normalized2"), m.wgu, m.ws("gate_up"), T, 2 * I, H, SFB_EPI_STORE);
@@ -692,7 +699,8 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         allreduce(out, static_cast<int64_t>(T) * H);
         mark(); mark();  // 8: ffn, 9
     }
-    if (bf) throw_on(sfb_k_convert(out, SFB_BF16, m.ws("output_f32"), SFB_F32, static_cast<int64_t>(T) * H, s));
+    if (bf && !m.direct_f32_output)
+        throw_on(sfb_k_convert(out, SFB_BF16, m.ws("output_f32"), SFB_F32, static_cast<int64_t>(T) * H, s));
     mark();  // 10
 }
 
@@ -748,10 +756,11 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     const int H = m.H, I = m.I_l, D = m.D;
     const std::size_t row_f32 = static_cast<std::size_t>(H) * 4, row_bf = static_cast<std::size_t>(H) * 2;
     auto at = [](void* base, std::size_t bytes) { return static_cast<void*>(static_cast<char*>(base) + bytes); };
-    auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int b0) {
+    auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int b0,
+                    bool f32_out = false) {
         sfb_gemm_args g{};
         g.a = a; g.bt = w; g.out = out; g.m = rows; g.n = n; g.k = k; g.epilogue = epi;
-        g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb;
+        g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb; g.out_f32 = f32_out ? 1 : 0;
         if (epi == SFB_EPI_ROPE_SPLIT) {
             g.q = at(m.ws("query"), static_cast<std::size_t>(b0) * m.hq * c.sequence * D * 2);
             g.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
@@ -802,10 +811,15 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
         cuda_check(cudaEventRecord(ev[5], s), "event");
         gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, b0);
-        gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, b0);
-        if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, out, static_cast<int64_t>(rows) * H, m.dtype, s);
-        cuda_check(cudaEventRecord(ev[6], s), "event");
-        throw_on(sfb_k_convert(out, SFB_BF16, out32, SFB_F32, static_cast<int64_t>(rows) * H, s));
+        if (m.direct_f32_output) {
+            gemm(act, m.wd, out32, H, I, SFB_EPI_RESIDUAL, r1, 0, b0, true);
+            cuda_check(cudaEventRecord(ev[6], s), "event");
+        } else {
+            gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, b0);
+            if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, out, static_cast<int64_t>(rows) * H, m.dtype, s);
+            cuda_check(cudaEventRecord(ev[6], s), "event");
+            throw_on(sfb_k_convert(out, SFB_BF16, out32, SFB_F32, static_cast<int64_t>(rows) * H, s));
+        }
         cuda_check(cudaEventRecord(ev[1], s), "event");
         cuda_check(cudaStreamWaitEvent(m.copy_out, ev[1], 0), "stream wait");
         cuda_check(cudaMemcpyAsync(output + r0 * H, out32, rows * row_f32, cudaMemcpyDeviceToHost, m.copy_out), "output download");
@@ -836,6 +850,7 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
 
 int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_out, int64_t capacity) {
     auto& m = *impl_;
+    if (name == "output" && m.direct_f32_output) return read_tensor("output_f32", host_out, capacity);
     const int id = m.planner.find(name);
     if (id < 0) throw std::invalid_argument("unknown decoder tensor: " + name);
     cuda_check(cudaStreamSynchronize(stream_), "sync");
