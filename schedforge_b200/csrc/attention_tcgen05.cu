@@ -1,12 +1,12 @@
 // Flash-attention prefill on the 5th-generation tensor cores (bf16, head_dim = 128).
 //
 // One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row Q tiles and walks
-// the keys in tiles of 128.  320 threads in four roles:
+// the keys in tiles of 128.  384 threads, 320 of them in four roles:
 //   warps 0-3   softmax group of Q tile 0: thread r owns query row r (= tensor-memory lane r), so
 //   warps 4-7   (tile 1)  no cross-thread reduction is ever needed.  Per KV tile it reads its 128
-//               scores from tensor memory twice (row maximum, then exponentials), and writes
-//               p = 2^(s*c - m) as packed bf16 back into tensor memory OVER the scores it has
-//               consumed; the next MMA reads P from there as its A operand.
+//               scores from tensor memory once into registers (row maximum, then exponentials),
+//               and writes p = 2^(s*c - m) as packed bf16 back into tensor memory OVER the
+//               scores; the next MMA reads P from there as its A operand.
 //   warp 8      TMA producer: Q tiles once, then K and V tiles through two 2-deep rings.
 //   warp 9      MMA issuer (one thread): S_t = Q_t.K^T (M128 N128 K128, both operands in shared
 //               memory) and O_t += P_t.V (M128 N128 K128, A = P_t from tensor memory, B = V as an
@@ -33,7 +33,7 @@ constexpr int QT = 128;         // rows per Q tile
 constexpr int KT = 128;         // keys per KV tile
 constexpr int KSTAGES = 2;
 constexpr int VSTAGES = 2;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;         // three warpgroups; warps 10 and 11 only take part in the register hand-over
 constexpr int kQBytes = QT * D * 2;        // 32 KiB per Q tile (two 16 KiB halves of 64 dims)
 constexpr int kKBytes = KT * D * 2;        // 32 KiB (two halves of 64 dims)
 constexpr int kVBytes = KT * D * 2;        // 32 KiB (two halves of 64 value dims)
@@ -130,6 +130,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // The softmax threads keep a whole 128-score row in registers; the third warpgroup (copy and
+    // MMA issue, one thread each) hands its share of the register file over to them.
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
@@ -213,7 +217,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 }
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         // ---------------------------------------------------------------- softmax groups
         const int t = warp >> 2;                 // Q tile of this group
         const int quarter = warp & 3;
@@ -232,27 +238,32 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
             const int key0 = j * KT;
             const bool needs_mask = (p.causal && key0 + KT - 1 > offset + q0 + t * QT) || key0 + KT > p.seq_kv;
             const int limit = p.causal ? min(p.seq_kv - 1, offset + qi) : p.seq_kv - 1;  // last visible key
-            // pass 1: row maximum of the raw scores (scale > 0, so the maximum commutes with scaling)
+            // The 128 scores of the row are read from tensor memory ONCE and stay in registers: the
+            // second half is in flight while the maximum of the first half is taken.
+            uint32_t raw[KT / 32][32];
+            ptx::tmem_ld_32x32(s_addr, raw[0]);
+            ptx::tmem_ld_32x32(s_addr + 32, raw[1]);
+            ptx::tmem_ld_wait();
+            ptx::tmem_ld_32x32(s_addr + 64, raw[2]);
+            ptx::tmem_ld_32x32(s_addr + 96, raw[3]);
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < KT / 64; ++c) {  // two 32-column loads in flight per wait
-                uint32_t raw[2][32];
-                ptx::tmem_ld_32x32(s_addr + c * 64, raw[0]);
-                ptx::tmem_ld_32x32(s_addr + c * 64 + 32, raw[1]);
-                ptx::tmem_ld_wait();
+            for (int c = 0; c < KT / 64; ++c) {
+                if (c == 1) ptx::tmem_ld_wait();
                 if (needs_mask) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i)
-                        if (key0 + c * 64 + i > limit) raw[i >> 5][i & 31] = 0xff800000u;  // -inf
+                        if (key0 + c * 64 + i > limit) raw[2 * c + (i >> 5)][i & 31] = 0xff800000u;  // -inf, and 2^-inf = 0 below
                 }
 #pragma unroll
                 for (int i = 0; i < 64; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(raw[i >> 5][i & 31]));
-                    mx1 = fmaxf(mx1, __uint_as_float(raw[(i + 1) >> 5][(i + 1) & 31]));
-                    mx2 = fmaxf(mx2, __uint_as_float(raw[(i + 2) >> 5][(i + 2) & 31]));
-                    mx3 = fmaxf(mx3, __uint_as_float(raw[(i + 3) >> 5][(i + 3) & 31]));
+                    mx0 = fmaxf(mx0, __uint_as_float(raw[2 * c + (i >> 5)][i & 31]));
+                    mx1 = fmaxf(mx1, __uint_as_float(raw[2 * c + ((i + 1) >> 5)][(i + 1) & 31]));
+                    mx2 = fmaxf(mx2, __uint_as_float(raw[2 * c + ((i + 2) >> 5)][(i + 2) & 31]));
+                    mx3 = fmaxf(mx3, __uint_as_float(raw[2 * c + ((i + 3) >> 5)][(i + 3) & 31]));
                 }
             }
+            // (scale > 0, so the maximum commutes with scaling)
             const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // lazy running maximum: move it only when the row maximum outgrows it by 2^8.  S_t(j) is
             // complete, so every earlier MMA of this tile (including P.V of tile j-1) has finished and
@@ -260,7 +271,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
             const bool grow = tile_max > m_used + kRescaleThreshold;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
                 const float alpha = grow ? fast_exp2(m_used - tile_max) : 1.0F;  // 2^(-inf) = 0 for a fresh row
-#pragma unroll
+#pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
                     ptx::tmem_ld_32x32(o_addr + c * 32, o);
@@ -273,35 +284,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 row_sum *= alpha;
             }
             if (grow) m_used = tile_max;
-            // pass 2: exponentials, row sum, packed bf16 P written over the consumed scores
+            // exponentials, row sum, packed bf16 P written over the consumed scores
             const float neg_m = m_used == -INFINITY ? 0.0F : -m_used;
             float s0 = 0.0F, s1 = 0.0F, s2 = 0.0F, s3 = 0.0F;
 #pragma unroll
-            for (int c = 0; c < KT / 64; ++c) {
-                uint32_t raw[2][32];
-                ptx::tmem_ld_32x32(s_addr + c * 64, raw[0]);
-                ptx::tmem_ld_32x32(s_addr + c * 64 + 32, raw[1]);
-                ptx::tmem_ld_wait();
+            for (int c = 0; c < KT / 32; ++c) {
+                uint32_t packed[16];
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    float x[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) x[i] = fast_exp2(fmaf(__uint_as_float(raw[hh][i]), p.scale_log2, neg_m));
-                    if (needs_mask) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (key0 + c * 64 + hh * 32 + i > limit) x[i] = 0.0F;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) { s0 += x[i]; s1 += x[i + 1]; s2 += x[i + 2]; s3 += x[i + 3]; }
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-                        packed[i] = *reinterpret_cast<const uint32_t*>(&h);
-                    }
-                    ptx::tmem_st_32x16(s_addr + (2 * c + hh) * 16, packed);
+                for (int i = 0; i < 32; i += 4) {
+                    const float x0 = fast_exp2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2, neg_m));
+                    const float x1 = fast_exp2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2, neg_m));
+                    const float x2 = fast_exp2(fmaf(__uint_as_float(raw[c][i + 2]), p.scale_log2, neg_m));
+                    const float x3 = fast_exp2(fmaf(__uint_as_float(raw[c][i + 3]), p.scale_log2, neg_m));
+                    s0 += x0; s1 += x1; s2 += x2; s3 += x3;
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(x0, x1), hi = __floats2bfloat162_rn(x2, x3);
+                    packed[i / 2] = *reinterpret_cast<const uint32_t*>(&lo);
+                    packed[i / 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
                 }
+                ptx::tmem_st_32x16(s_addr + c * 16, packed);
             }
             ptx::tmem_st_wait();
             row_sum += (s0 + s1) + (s2 + s3);
