@@ -25,7 +25,7 @@ LIB = os.path.join(PKG, "libschedforge_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-std=c++20", "-O3", "-lineinfo",
+    "-std=c++20", "-O3", "-lineinfo", *os.environ.get("SFB_EXTRA_NVCC", "").split(),
     "-Xcompiler", "-fPIC,-fvisibility=default,-pthread",
     "--expt-relaxed-constexpr",
     "-I" + os.path.join(ROOT, "include"), "-I" + CSRC,

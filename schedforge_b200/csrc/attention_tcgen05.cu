@@ -51,6 +51,11 @@ struct FaParams {
     uint32_t* status;
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -243,24 +248,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
             uint32_t raw[KT / 32][32];
             ptx::tmem_ld_32x32(s_addr, raw[0]);
             ptx::tmem_ld_32x32(s_addr + 32, raw[1]);
-            ptx::tmem_ld_wait();
             ptx::tmem_ld_32x32(s_addr + 64, raw[2]);
             ptx::tmem_ld_32x32(s_addr + 96, raw[3]);
+            ptx::tmem_ld_wait();  // one load latency (~400 cycles) for the whole row
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
             for (int c = 0; c < KT / 64; ++c) {
-                if (c == 1) ptx::tmem_ld_wait();
                 if (needs_mask) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i)
                         if (key0 + c * 64 + i > limit) raw[2 * c + (i >> 5)][i & 31] = 0xff800000u;  // -inf, and 2^-inf = 0 below
                 }
 #pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(raw[2 * c + (i >> 5)][i & 31]));
-                    mx1 = fmaxf(mx1, __uint_as_float(raw[2 * c + ((i + 1) >> 5)][(i + 1) & 31]));
-                    mx2 = fmaxf(mx2, __uint_as_float(raw[2 * c + ((i + 2) >> 5)][(i + 2) & 31]));
-                    mx3 = fmaxf(mx3, __uint_as_float(raw[2 * c + ((i + 3) >> 5)][(i + 3) & 31]));
+                for (int i = 0; i < 64; i += 8) {  // three-input maximum: half the instructions of fmaxf chains
+                    const uint32_t* v = &raw[2 * c + (i >> 5)][i & 31];
+                    mx0 = max3(mx0, __uint_as_float(v[0]), __uint_as_float(v[1]));
+                    mx1 = max3(mx1, __uint_as_float(v[2]), __uint_as_float(v[3]));
+                    mx2 = max3(mx2, __uint_as_float(v[4]), __uint_as_float(v[5]));
+                    mx3 = max3(mx3, __uint_as_float(v[6]), __uint_as_float(v[7]));
                 }
             }
             // (scale > 0, so the maximum commutes with scaling)
