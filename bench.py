@@ -159,6 +159,8 @@ def kernel_case(args):
 
     gemm       the fused gate/up projection (tcgen05, SwiGLU epilogue), Llama-3-8B shape
                (--small: M=4096, N=16384, K=4096, 224 MB of operands, larger than L2)
+    gemm_decode  the same projection for the 128 rows of a decode step: blocked weights, streamed
+               once (--small: N=8192; three weight copies are rotated so that L2 does not help)
     attention  BASELINE configs[1]: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (--small: B1)
     decode     BASELINE configs[2]: paged split-KV decode, batch 64, context ~U[512, 8192], 16-token
                blocks, permuted block table (--small: batch 16)
@@ -183,6 +185,35 @@ def kernel_case(args):
         launch = lambda: L.check(lib.sfb_k_gemm_bf16(C.byref(g), sp))
         work, unit, peak, bound = 2.0 * m * n * k, "TFLOP/s", peaks["bf16_tflops"], "tensor"
         name, shape = "gemm_tcgen05_kernel<256>", {"m": m, "n": n, "k": k, "epilogue": "swiglu"}
+    elif args.kernel == "gemm_decode":
+        # gate/up projection of the decode step: 128 rows, every weight byte read once (HBM-bound)
+        m, n, k = 128, (8192 if args.small else 28672), 4096
+        a = (torch.randn((m, k), generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+        copies = 3  # rotate over weight copies larger than L2 together
+        o = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+        nbytes = lib.sfb_gemm_stream_workspace_bytes(n)
+        scratch = torch.zeros((nbytes // 4,), dtype=torch.float32, device="cuda")
+        gs = []
+        for _ in range(copies):
+            bt = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+            tiled = torch.empty((lib.sfb_tiled_weight_elems(n, k),), dtype=torch.bfloat16, device="cuda")
+            L.check(lib.sfb_k_tile_weight_bf16(C.c_void_p(bt.data_ptr()), C.c_void_p(tiled.data_ptr()), n, k, sp))
+            torch.cuda.synchronize()
+            g = L.GemmArgs()
+            g.a, g.bt, g.out, g.m, g.n, g.k = a.data_ptr(), tiled.data_ptr(), o.data_ptr(), m, n, k
+            g.epilogue, g.backend, g.swiglu_block, g.bt_tiled = L.EPI_SWIGLU, L.GEMM_TCGEN05, 64, 1
+            g.split_workspace, g.split_workspace_bytes = scratch.data_ptr(), nbytes
+            gs.append(g)
+            keep.append(tiled)
+        keep.append(scratch)
+        turn = [0]
+
+        def launch():
+            L.check(lib.sfb_k_gemm_bf16(C.byref(gs[turn[0] % copies]), sp))
+            turn[0] += 1
+        work = float(n * k * 2 + m * k * 2 + m * (n // 2) * 2)
+        unit, peak, bound = "GB/s", peaks["hbm_gbs"], "hbm"
+        name, shape = "gemm_tcgen05_kernel<128, true>", {"m": m, "n": n, "k": k, "epilogue": "swiglu", "weights": "64x64 blocks"}
     elif args.kernel == "attention":
         b, hq, hkv, s = (1 if args.small else 4), 32, 8, 4096
         q = torch.randn((b, hq, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
@@ -250,7 +281,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--kernel", default="", choices=["", "gemm", "attention", "decode"],
+    ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_decode", "attention", "decode"],
                     help="time ONE kernel through the kernel ABI instead of the layer (also the ncu target)")
     ap.add_argument("--small", action="store_true", help="--kernel: a case small enough for an ncu --set full capture")
     args = ap.parse_args()
