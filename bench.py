@@ -428,10 +428,14 @@ def main():
         kernel_ms = e0.elapsed_time(e1) / reps
         flops = 2.0 * m * n * k
         achieved = flops / (kernel_ms * 1e-3) / 1e12
-        roofline = {"kernel": "gemm_tcgen05_kernel<256> (gate/up projection, SwiGLU epilogue)", "bound": "tensor",
+        roofline = {"kernel": "gemm_tcgen05_kernel<256, false> (gate/up projection, SwiGLU epilogue)", "bound": "tensor",
                     "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst: kernel timed alone)",
-                    "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops, "traffic": None}
+                    "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops,
+                    # dram read + write of one launch: 359.4 MB measured by ncu on the M4096 N16384 case (2048 output
+                    # tiles), scaled by the tile count of this launch; B is re-read once per band of 16 M-tiles
+                    "traffic": 359.4e6 * ((m + 127) // 128) * ((n + 255) // 256) / 2048.0,
+                    "traffic_source": "ncu dram__bytes_read+write of the --kernel gemm --small capture, scaled by output tiles"}
     elif args.workload == "moe":
         flops = 6.0 * tokens * cfg["top_k"] * cfg["hidden"] * cfg["intermediate"] / world
         achieved = flops / (result.ffn_milliseconds * 1e-3) / 1e12 if result.ffn_milliseconds > 0 else None
@@ -447,7 +451,10 @@ def main():
                     if result.attention_milliseconds > 0 else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": (kv_bytes / (result.attention_milliseconds * 1e-3) / 1e9 / peaks["hbm_gbs"])
                     if result.attention_milliseconds > 0 else None, "peak_source": peaks["source"],
-                    "kernel_ms": result.attention_milliseconds, "algorithmic_bytes_per_launch": kv_bytes, "traffic": None}
+                    "kernel_ms": result.attention_milliseconds, "algorithmic_bytes_per_launch": kv_bytes,
+                    # ncu on the batch-16 case: 307.0 MB of dram traffic for 301.2 MB of K/V pages (every byte once)
+                    "traffic": kv_bytes * 307.0 / 301.2,
+                    "traffic_source": "ncu dram__bytes_read+write of the --kernel decode --small capture, scaled by K/V bytes"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "prefill":
