@@ -340,6 +340,13 @@ typedef struct sfb_compile_options {
     int no_pipeline;      /* != 0: sfb_decoder_execute copies the whole input, runs, copies the whole output;
                              0: dense bf16 prefill plans overlap the host copies of one group of sequences
                              with the computation of another */
+    int append_new_token; /* decode plans (sequence == 1, context_sequence > 0).  0 = the reference's
+                             semantics (src/decoder_compiler.cpp:238-241): RoPE position 0, the new token's
+                             K/V are dropped, attention sees the cached context only.  != 0 = a real
+                             autoregressive step: RoPE at position context_sequence, K/V of the new token
+                             appended to the paged cache (append_paged_kv, src/next_milestones.cpp:486-524)
+                             and attention over context_sequence + 1 keys.  A plan can be run again: the
+                             append always writes position context_sequence. */
 } sfb_compile_options;
 
 /* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */

@@ -106,6 +106,8 @@ struct DecoderExecutablePlan::Impl {
     int moe_swiglu_block = 0;   // expert W3|W1 interleave block (bf16)
     bool decode = false, paged = false;
     int page_tokens = 16, max_blocks = 0, num_blocks = 0, splits = 1;
+    bool append_new = false;        // autoregressive step: append the new token's K/V, attend over context + 1
+    int* context_len_attend = nullptr;  // context_len, or context_len + 1 when the new token is appended
 
     DeviceBuffer weights, workspace, kv_pool;
     WorkspacePlanner planner{true};
@@ -208,6 +210,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     m.decode = c.context_sequence > 0;
     m.paged = m.decode && c.sequence == 1;
     m.page_tokens = opt.page_tokens > 0 ? opt.page_tokens : 16;
+    m.append_new = m.paged && opt.append_new_token != 0;
     plan->policy.reuse_workspace = opt.no_workspace_reuse == 0;
     m.planner = WorkspacePlanner(plan->policy.reuse_workspace);
     const bool bf = m.dtype == SFB_BF16;
@@ -261,10 +264,13 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     h2d(m.rms1, need(data.rms1_weight, "rms1_weight"), sizeof(float) * H);
     h2d(m.rms2, need(data.rms2_weight, "rms2_weight"), sizeof(float) * H);
     {
-        std::vector<float> cs(static_cast<std::size_t>(c.sequence) * std::max(1, D / 2)), sn(cs.size());
-        if (D >= 2) throw_on(sfb_rope_table(c.sequence, D, c.rope_theta, cs.data(), sn.data()));
-        h2d(m.rope_cos, cs.data(), cs.size() * 4);
-        h2d(m.rope_sin, sn.data(), sn.size() * 4);
+        // positions 0..sequence-1; an appending decode step rotates its one token at position context_sequence
+        const int first_position = m.append_new ? c.context_sequence : 0;
+        const std::size_t row = static_cast<std::size_t>(std::max(1, D / 2));
+        std::vector<float> cs(static_cast<std::size_t>(first_position + c.sequence) * row), sn(cs.size());
+        if (D >= 2) throw_on(sfb_rope_table(first_position + c.sequence, D, c.rope_theta, cs.data(), sn.data()));
+        h2d(m.rope_cos, cs.data() + first_position * row, static_cast<std::size_t>(c.sequence) * row * 4);
+        h2d(m.rope_sin, sn.data() + first_position * row, static_cast<std::size_t>(c.sequence) * row * 4);
     }
     // fp32 staging buffer on the device for the transpose/convert packer
     std::size_t staging_elems = static_cast<std::size_t>(H) * std::max({H, c.intermediate, m.qkv_l});
@@ -399,17 +405,18 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         h2d(dk, lk.data(), lk.size() * 4);
         h2d(dv, lv.data(), lv.size() * 4);
         if (m.paged) {
-            m.max_blocks = ceil_div(ctx, m.page_tokens);
+            m.max_blocks = ceil_div(ctx + (m.append_new ? 1 : 0), m.page_tokens);
             m.num_blocks = c.batch * m.max_blocks;
             const std::size_t pool_elems = static_cast<std::size_t>(m.num_blocks) * m.hkv * m.page_tokens * D;
             const std::size_t table_bytes = sizeof(int) * m.num_blocks, len_bytes = sizeof(int) * c.batch;
             const std::size_t pool_bytes = (pool_elems * m.esz() + 1023) / 1024 * 1024;
-            m.kv_pool.allocate(2 * pool_bytes + table_bytes + len_bytes + 1024);
+            m.kv_pool.allocate(2 * pool_bytes + table_bytes + 2 * len_bytes + 1024);
             DeviceBuffer converted(bf ? 2 * cache_bytes : 0);
             char* kb = m.kv_pool.as<char>();
             m.k_pool = kb; m.v_pool = kb + pool_bytes;
             m.block_table = reinterpret_cast<int*>(kb + 2 * pool_bytes);
             m.context_len = m.block_table + m.num_blocks;
+            m.context_len_attend = m.append_new ? m.context_len + c.batch : m.context_len;
             char* tmp = converted.as<char>();
             std::vector<int> table(m.num_blocks), lens(c.batch, 0), full(c.batch, ctx);
             std::iota(table.begin(), table.end(), 0);
@@ -430,7 +437,11 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
                                            ctx, D, D, m.page_tokens, m.max_blocks, static_cast<sfb_dtype>(m.dtype), s));
             cuda_check(cudaStreamSynchronize(s), "paged cache build");
             h2d(m.context_len, full.data(), len_bytes);
-            m.splits = sfb_attention_decode_default_splits(c.batch, m.hkv, ctx);
+            if (m.append_new) {
+                std::vector<int> plus(c.batch, ctx + 1);
+                h2d(m.context_len_attend, plus.data(), len_bytes);
+            }
+            m.splits = sfb_attention_decode_default_splits(c.batch, m.hkv, ctx + (m.append_new ? 1 : 0));
             plan->attention_strategy = "split_kv_decode";
         } else {
             m.kv_pool.allocate(2 * cache_bytes + 1024);
@@ -595,12 +606,15 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         mark();  // 3
     }
     if (m.paged) {
+        if (m.append_new)  // the rotated key and the value of the new token go to position context_len of every sequence
+            throw_on(sfb_k_paged_kv_append(m.ws("key"), m.ws("value"), m.k_pool, m.v_pool, m.block_table, m.context_len,
+                                           c.batch, m.hkv, 1, D, D, m.page_tokens, m.max_blocks, dt, s));
         sfb_decode_args a{};
         a.q = m.ws("query"); a.k_pool = m.k_pool; a.v_pool = m.v_pool; a.block_table = m.block_table;
-        a.context_len = m.context_len; a.out = m.ws("attention"); a.partials = m.ws("decode_partials");
+        a.context_len = m.context_len_attend; a.out = m.ws("attention"); a.partials = m.ws("decode_partials");
         a.batch = c.batch; a.q_heads = m.hq; a.kv_heads = m.hkv; a.head_dim = D; a.head_dim_value = D;
         a.block_tokens = m.page_tokens; a.max_blocks = m.max_blocks; a.num_blocks = m.num_blocks;
-        a.max_context = c.context_sequence; a.splits = m.splits; a.scale = 0.0F; a.dtype = m.dtype;
+        a.max_context = c.context_sequence + (m.append_new ? 1 : 0); a.splits = m.splits; a.scale = 0.0F; a.dtype = m.dtype;
         throw_on(sfb_k_attention_decode_paged(&a, s));
     } else {
         sfb_attention_args a{};

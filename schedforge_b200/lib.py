@@ -64,7 +64,8 @@ class DecoderData(C.Structure):
 class CompileOptions(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dtype", "token_major_attention", "fuse_epilogues",
                                        "gemm_backend", "attention_backend", "page_tokens", "tp_rank",
-                                       "tp_size", "seed_block_table", "no_workspace_reuse", "no_pipeline")]
+                                       "tp_size", "seed_block_table", "no_workspace_reuse", "no_pipeline",
+                                       "append_new_token")]
 
 
 class DecoderResult(C.Structure):

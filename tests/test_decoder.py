@@ -213,3 +213,44 @@ def test_tensor_parallel_shards_reproduce_the_full_layer(port):
     assert rel_err(out, want) < BF16_TOL
     for p in plans:
         p.close()
+
+
+@pytest.mark.parametrize("dtype,head_dim,ctx", [(L.F32, 64, 37), (L.BF16, 64, 37), (L.BF16, 128, 48)])
+def test_autoregressive_step_equals_last_token_of_the_prefill(port, dtype, head_dim, ctx):
+    """append_new_token: the decode step over a cache of `ctx` tokens must give what a causal
+    prefill over ctx + 1 tokens gives for its last token.  The prefill side is the oracle's layer
+    (bit-identical to the reference build); the cache holds the rotated K and the V of the first
+    ctx tokens, computed with the oracle's own norm / GEMM / split+RoPE."""
+    batch, hq, hkv = 3, 4, 2
+    kw = dict(batch=batch, sequence=ctx + 1, hidden=hq * head_dim, intermediate=384, query_heads=hq, kv_heads=hkv,
+              head_dim=head_dim, rope_theta=10000.0)
+    oc, _, data = bf16_case(port, 21, **kw)
+    hidden = oc.hidden
+    want = port.decoder_layer(oc, data, native=True).reshape(batch, ctx + 1, hidden)[:, ctx, :]
+    x = data["input"].reshape(batch * (ctx + 1), hidden)
+    normalized = port.rms_norm(x, data["rms1_weight"], oc.rms_epsilon)
+    kvw = hkv * head_dim
+    wqkv = np.concatenate([data["query_weight"].reshape(hidden, hidden), data["key_weight"].reshape(hidden, kvw),
+                           data["value_weight"].reshape(hidden, kvw)], axis=1)
+    _, keys, values = port.split_qkv_rope(oc, port.matmul(normalized, wqkv, fma=True))  # [B, Hkv, ctx + 1, D]
+    step = dict(weights_of(data))
+    step["cached_key"] = np.ascontiguousarray(keys[:, :, :ctx, :])
+    step["cached_value"] = np.ascontiguousarray(values[:, :, :ctx, :])
+    if dtype == L.BF16:  # the plan stores the cache in bf16
+        step["cached_key"] = port.round_bf16(step["cached_key"])
+        step["cached_value"] = port.round_bf16(step["cached_value"])
+    c = api.decoder_config(**dict(kw, sequence=1, context_sequence=ctx))
+    plan = api.DecoderCompiler.compile(c, step, "", api.compile_options(dtype=dtype, append_new_token=True,
+                                                                        seed_block_table=5))
+    last = np.ascontiguousarray(data["input"].reshape(batch, ctx + 1, hidden)[:, ctx, :])
+    out, _ = plan.execute(last)
+    assert rel_err(out, want) < (F32_TOL if dtype == L.F32 else BF16_TOL)
+    again, _ = plan.execute(last)  # the append overwrites the same position: the plan can be run again
+    # (bf16 plans sum the partial tiles of their few-row GEMMs with fp32 reductions at L2, whose order is not fixed)
+    assert rel_err(again, out) < 1e-5
+    # without the flag the same plan input gives the reference's decode semantics, which differ
+    legacy = api.DecoderCompiler.compile(c, step, "", api.compile_options(dtype=dtype))
+    out_legacy, _ = legacy.execute(last)
+    assert rel_err(out_legacy, want) > 2 * BF16_TOL
+    plan.close()
+    legacy.close()
