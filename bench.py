@@ -281,6 +281,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer"],
+                    help="N > 1: all-reduce after the O and Down projections through NCCL, or fused into the GEMM "
+                         "epilogues over NVLink peer memory")
     ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_decode", "attention", "decode"],
                     help="time ONE kernel through the kernel ABI instead of the layer (also the ncu target)")
     ap.add_argument("--small", action="store_true", help="--kernel: a case small enough for an ncu --set full capture")
@@ -300,7 +303,7 @@ def main():
                 "decode": "llama3_8b_decoder_layer_decode_b128_ctx2048",
                 "moe": "mixtral_moe_decoder_layer_8x_top2_t8192"}[args.workload]
     config = {"workload": workload, "hidden": 4096, "intermediate": 14336, "q_heads": 32, "kv_heads": 8,
-              "head_dim": 128, "tokens_per_step": tokens, "parallelism": f"tp{world}",
+              "head_dim": 128, "tokens_per_step": tokens, "parallelism": f"tp{world}", "collective": "none",
               "l2": "weights + activations (>0.9 GB per step) exceed the 126 MB L2; no flush between steps"}
 
     if args.impl == "reference":
@@ -355,8 +358,21 @@ def main():
         with torch.cuda.stream(stream):
             dist.all_reduce(views[key])
 
+    collective = "none"
     if world > 1:
         plan.set_allreduce(allreduce)
+        collective = args.collective
+        if collective == "auto":  # one-shot pushes cost (N-1) x bytes per rank: two ranks, or the small decode outputs
+            collective = "peer" if (world == 2 or args.workload == "decode") and args.workload != "moe" else "nccl"
+        if collective == "peer":
+            def exchange(handle):
+                handles = [None] * world
+                dist.all_gather_object(handles, handle)
+                return handles
+            plan.enable_peer_allreduce(rank, world, exchange)
+            dist.barrier()
+    config["collective"] = {"none": "none", "nccl": "nccl all-reduce after O and Down",
+                            "peer": "all-reduce fused into the O and Down GEMM epilogues over NVLink peer memory"}[collective]
 
     def barrier():
         if world > 1:

@@ -97,6 +97,8 @@ typedef enum sfb_gemm_epilogue {
     SFB_EPI_ROPE_SPLIT = 3  /* n = hidden + 2*kv: rotary on Q,K and scatter to head-major   */
 } sfb_gemm_epilogue;
 
+#define SFB_MAX_PEERS 8
+
 typedef enum sfb_gemm_backend {
     SFB_GEMM_AUTO = 0,
     SFB_GEMM_SIMT = 1,     /* CUDA-core tiles, any shape                                   */
@@ -139,6 +141,12 @@ typedef struct sfb_gemm_args {
     /* bt_tiled != 0: bt holds the weight in 64x64 blocks (sfb_k_tile_weight_bf16) so that a
      * weight-streaming GEMM reads 8 KB contiguous runs; tcgen05 backend, dense mode only */
     int bt_tiled;
+    /* SFB_EPI_STORE / SFB_EPI_RESIDUAL with bf16 output, tcgen05 backend: every finished piece of
+     * the output is also stored to these peer_count buffers (same [m,n] layout; memory of other GPUs
+     * mapped into this process), so that a sum all-reduce of the sharded layer moves its data under
+     * the GEMM; sfb_k_peer_allreduce_finish completes it. */
+    void* peer_out[SFB_MAX_PEERS - 1];
+    int peer_count;
 } sfb_gemm_args;
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
@@ -403,6 +411,41 @@ sfb_status sfb_decoder_download_output(sfb_decoder_plan* plan, float* output);
 /* Tensor-parallel hook: called on the plan's stream after the O projection and after the
  * Down projection partial sums are in `buffer` (`count` elements of `dtype`); the callee
  * must all-reduce (sum) in place on `stream`.  NULL = single shard. */
+/* ---- sum all-reduce over NVLink peer memory, fused with the producing GEMM -----------------------
+ * Replaces, for the sharded plan, the collective that the reference does not have (it is a
+ * single-process CPU library); the unfused form is the sfb_allreduce_fn hook below.
+ * data: this rank's partial sums in, the sum out (bf16 [count]).  recv: this rank's receive buffer,
+ * slot s (slot_elems elements apart) holds rank s's partial sums, pushed there by rank s's GEMM
+ * epilogue (sfb_gemm_args.peer_out).  local_flags[s] is written by rank s; peer_flags[s] is the
+ * address of local_flags[rank] inside rank s's memory as mapped into this process.  epoch must
+ * grow by one with every use of the same buffers.  The wait is bounded (about two seconds); when
+ * it gives up, bit 0x100 of sfb_device_status is set and data keeps this rank's partial sums. */
+typedef struct sfb_peer_allreduce_args {
+    void* data;
+    const void* recv;
+    uint32_t* local_flags;
+    uint32_t* peer_flags[SFB_MAX_PEERS];
+    int rank, size;
+    uint32_t epoch;
+    int64_t count;
+    int64_t slot_elems;
+} sfb_peer_allreduce_args;
+sfb_status sfb_k_peer_allreduce_finish(const sfb_peer_allreduce_args* args, sfb_stream stream);
+
+/* Device memory that other processes of this node can map (CUDA IPC): allocate + export a 64-byte
+ * handle, map a peer's handle, unmap, free. */
+sfb_status sfb_peer_alloc(size_t bytes, void** ptr, void* handle64);
+sfb_status sfb_peer_open(const void* handle64, void** ptr);
+sfb_status sfb_peer_close(void* ptr);
+sfb_status sfb_peer_free(void* ptr);
+
+/* Sharded plan (tp_size > 1): use the fused form for the all-reduces after the O and Down
+ * projections.  local_base: this rank's buffer of sfb_decoder_peer_bytes(plan) bytes from
+ * sfb_peer_alloc (zero-filled); peer_bases[s]: rank s's buffer mapped with sfb_peer_open (entry
+ * tp_rank ignored).  Every rank of the group must make the same calls in the same order. */
+size_t sfb_decoder_peer_bytes(const sfb_decoder_plan* plan);
+sfb_status sfb_decoder_set_peer_allreduce(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases);
+
 typedef void (*sfb_allreduce_fn)(void* user, void* buffer, int64_t count, int dtype,
                                  sfb_stream stream);
 sfb_status sfb_decoder_set_allreduce(sfb_decoder_plan* plan, sfb_allreduce_fn fn, void* user);

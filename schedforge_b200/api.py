@@ -112,6 +112,39 @@ class DecoderExecutablePlan:
         self._callback = L.ALLREDUCE_FN(lambda user, buf, count, dtype, stream: fn(buf, count, dtype, stream))
         L.check(L.load().sfb_decoder_set_allreduce(self._h, self._callback, None))
 
+    def enable_peer_allreduce(self, rank, world, exchange):
+        """Fused all-reduce over NVLink peer memory for the O and Down projections of a sharded plan.
+
+        exchange(handle: bytes) -> list of every rank's 64-byte handle in rank order (for instance
+        torch.distributed.all_gather_object).  Every rank must call this at the same point."""
+        lib = L.load()
+        nbytes = lib.sfb_decoder_peer_bytes(self._h)
+        local, handle = C.c_void_p(), C.create_string_buffer(64)
+        L.check(lib.sfb_peer_alloc(C.c_size_t(nbytes), C.byref(local), handle))
+        handles = exchange(handle.raw)
+        bases = (C.c_void_p * world)()
+        self._peer_mapped = []
+        for s in range(world):
+            if s == rank:
+                continue
+            mapped = C.c_void_p()
+            L.check(lib.sfb_peer_open(C.create_string_buffer(handles[s], 64), C.byref(mapped)))
+            bases[s] = mapped.value
+            self._peer_mapped.append(mapped)
+        self._peer_local = local
+        L.check(lib.sfb_decoder_set_peer_allreduce(self._h, local, bases))
+
+    def disable_peer_allreduce(self):
+        """Unmaps the peers' buffers and frees the local one (call on every rank after a barrier)."""
+        lib = L.load()
+        if getattr(self, "_peer_local", None) is None:
+            return
+        L.check(lib.sfb_decoder_set_peer_allreduce(self._h, None, None))
+        for mapped in self._peer_mapped:
+            L.check(lib.sfb_peer_close(mapped))
+        L.check(lib.sfb_peer_free(self._peer_local))
+        self._peer_local, self._peer_mapped = None, []
+
     def read_tensor(self, name, dtype=np.float32):
         count = C.c_int64(0)
         L.check(L.load().sfb_decoder_read_tensor(self._h, name.encode(), None, C.c_int64(0), C.byref(count)))

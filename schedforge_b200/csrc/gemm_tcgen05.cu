@@ -73,6 +73,8 @@ struct TcParams {
     int n_tiles;
     int b_tiled;            // weight stored as 64x64 blocks, 8 KB contiguous each
     // equal K-block ranges per CTA (one M-tile only): fp32 [n_tiles][BM][BN] sums + one counter per tile
+    bf16* peer_out[SFB_MAX_PEERS - 1];  // copies of the output in other GPUs' memory (fused all-reduce)
+    int peer_count;
     float* accum;
     int* tile_counters;
     int shared_tiles;       // trailing tiles whose K blocks are cut into equal ranges (0 = none)
@@ -283,6 +285,7 @@ __device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float
     const int valid = p.n - col;
     if (p.epilogue == SFB_EPI_RESIDUAL) add_bf16x8(p.residual + index, f, valid);
     store8(p.out, p.out_f32, index, f, valid);
+    for (int i = 0; i < p.peer_count; ++i) store8(p.peer_out[i], 0, index, f, valid);  // peer stores over NVLink
 }
 
 // phase 2 for one warp: the staged values are output columns [col0, col0 + 32) of rows
@@ -666,6 +669,8 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     p.seq = g.seq; p.q_heads = g.q_heads; p.kv_heads = g.kv_heads; p.head_dim = g.head_dim;
     p.n_tiles = ceil_div(g.n, BN);
     p.b_tiled = g.bt_tiled;
+    p.peer_count = g.peer_count;
+    for (int i = 0; i < g.peer_count; ++i) p.peer_out[i] = static_cast<bf16*>(g.peer_out[i]);
     p.status = device_status_word();
     int max_m_tiles;
     if (g.group_offsets) {
@@ -715,6 +720,9 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
     if (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64 && g.swiglu_block != 128) return false;
     if (g.bt_tiled && (g.group_offsets || (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64))) return false;
     if (g.epilogue == SFB_EPI_ROPE_SPLIT && g.head_dim % 32 != 0) return false;
+    if (g.peer_count != 0 && (g.peer_count < 0 || g.peer_count >= SFB_MAX_PEERS || g.out_f32 || g.group_offsets ||
+                              (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL)))
+        return false;
     return true;
 }
 

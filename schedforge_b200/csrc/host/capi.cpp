@@ -134,6 +134,17 @@ sfb_status sfb_decoder_dump(const sfb_decoder_plan* plan, char* buffer, size_t c
     });
 }
 
+size_t sfb_decoder_peer_bytes(const sfb_decoder_plan* plan) {
+    return plan && plan->plan ? plan->plan->peer_bytes() : 0;
+}
+
+sfb_status sfb_decoder_set_peer_allreduce(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->set_peer_allreduce(local_base, peer_bases);
+    });
+}
+
 size_t sfb_decoder_workspace_bytes(const sfb_decoder_plan* plan) {
     return plan && plan->plan ? plan->plan->workspace_bytes : 0;
 }

@@ -127,6 +127,33 @@ struct DecoderExecutablePlan::Impl {
     bool has_input = false;
     // dense fused bf16 plan on one rank: the last GEMM writes the fp32 result itself, "output" is skipped
     bool direct_f32_output = false;
+    // fused all-reduce over peer memory: [2 slot sets][size slots][slot_bytes] + flags [2][size]
+    char* peer_local = nullptr;
+    char* peer_remote[SFB_MAX_PEERS] = {};
+    uint32_t peer_epoch[2] = {0, 0};
+    std::size_t peer_slot_bytes() const { return (static_cast<std::size_t>(T) * H * 2 + 255) / 256 * 256; }
+    std::size_t peer_flags_offset() const { return 2 * static_cast<std::size_t>(size) * peer_slot_bytes(); }
+    // this rank's slot of slot set `set` in every other rank's receive buffer, `offset` elements in
+    void fill_peer_out(sfb_gemm_args& g, int set, std::size_t offset) const {
+        for (int r = 0; r < size; ++r)
+            if (r != rank)
+                g.peer_out[g.peer_count++] =
+                    peer_remote[r] + (static_cast<std::size_t>(set) * size + rank) * peer_slot_bytes() + offset * 2;
+    }
+    // completes the all-reduce whose data the preceding GEMM pushed: `count` elements starting `offset` elements in
+    sfb_status peer_finish(int set, void* data, std::size_t offset, int64_t count, cudaStream_t s) {
+        sfb_peer_allreduce_args a{};
+        a.data = data;
+        a.recv = peer_local + static_cast<std::size_t>(set) * size * peer_slot_bytes() + offset * 2;
+        uint32_t* flags = reinterpret_cast<uint32_t*>(peer_local + peer_flags_offset());
+        a.local_flags = flags + set * SFB_MAX_PEERS;
+        for (int r = 0; r < size; ++r)
+            if (r != rank)
+                a.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_remote[r] + peer_flags_offset()) + set * SFB_MAX_PEERS + rank;
+        a.rank = rank; a.size = size; a.epoch = ++peer_epoch[set];
+        a.count = count; a.slot_elems = static_cast<int64_t>(peer_slot_bytes() / 2);
+        return sfb_k_peer_allreduce_finish(&a, s);
+    }
     std::vector<const void*> blocked_weights;  // weights re-laid in 64x64 blocks (decode-shaped plans)
     bool blocked(const void* w) const {
         return std::find(blocked_weights.begin(), blocked_weights.end(), w) != blocked_weights.end();
@@ -534,6 +561,30 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     return plan;
 }
 
+std::size_t DecoderExecutablePlan::peer_bytes() const {
+    const auto& m = *impl_;
+    return m.size > 1 ? m.peer_flags_offset() + 2 * SFB_MAX_PEERS * sizeof(uint32_t) + 256 : 0;
+}
+
+void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* peer_bases) {
+    auto& m = *impl_;
+    if (!local_base) {  // back to the hook
+        m.peer_local = nullptr;
+        return;
+    }
+    if (m.size < 2 || m.size > SFB_MAX_PEERS) throw std::invalid_argument("peer all-reduce needs a sharded plan of 2..8 ranks");
+    if (m.dtype != SFB_BF16 || !policy.fuse_epilogues || policy.gemm_backend == SFB_GEMM_SIMT || m.H % 8 != 0 ||
+        m.hidden_l % 8 != 0 || m.I_l % 8 != 0)
+        throw std::invalid_argument("peer all-reduce needs a bf16 plan with fused epilogues on the tcgen05 GEMM");
+    if (!peer_bases) throw std::invalid_argument("peer all-reduce: null peer table");
+    for (int s = 0; s < m.size; ++s) {
+        if (s != m.rank && !peer_bases[s]) throw std::invalid_argument("peer all-reduce: null peer buffer");
+        m.peer_remote[s] = static_cast<char*>(peer_bases[s]);
+    }
+    m.peer_local = static_cast<char*>(local_base);
+    m.peer_epoch[0] = m.peer_epoch[1] = 0;
+}
+
 void DecoderExecutablePlan::upload_input(const float* input) {
     if (!input) throw std::invalid_argument("decoder input is null");
     auto& m = *impl_;
@@ -564,7 +615,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     int ev = 0;
     auto mark = [&] { if (stage_events) cuda_check(cudaEventRecord(m.events[ev++], s), "event"); };
     auto gemm = [&](const void* a, const void* w, void* out, int mm, int n, int k, int epi, const void* res = nullptr,
-                    int sb = 0, const int* offsets = nullptr, int groups = 0, bool f32_out = false) {
+                    int sb = 0, const int* offsets = nullptr, int groups = 0, bool f32_out = false, int peer_set = -1) {
         if (!bf) {
             throw_on(sfb_k_gemm_f32(static_cast<const float*>(a), static_cast<const float*>(w),
                                     static_cast<float*>(out), mm, n, k, s));
@@ -584,11 +635,14 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             g.split_workspace_bytes = m.planner.bytes(m.planner.find("gemm_partials"));
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
+        if (peer_set >= 0) m.fill_peer_out(g, peer_set, 0);
         throw_on(sfb_k_gemm_bf16(&g, s));
     };
     auto allreduce = [&](void* buffer, int64_t count) {
         if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, buffer, count, m.dtype, s);
     };
+    const bool peer = m.size > 1 && m.peer_local != nullptr;
+    auto peer_finish = [&](int peer_set, void* buffer, int64_t count) { throw_on(m.peer_finish(peer_set, buffer, 0, count, s)); };
 
     mark();  // 0
     void* x = bf ? m.ws("input") : m.ws("input_f32");
@@ -632,8 +686,14 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     void* r1 = m.ws("attention_residual");
     const bool add_residual_here = m.rank == 0;  // under sharding the residual enters the sum once
     if (fused) {
-        gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x);
-        allreduce(r1, static_cast<int64_t>(T) * H);
+        if (peer) {
+            gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
+                 nullptr, 0, false, 0);
+            peer_finish(0, r1, static_cast<int64_t>(T) * H);
+        } else {
+            gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x);
+            allreduce(r1, static_cast<int64_t>(T) * H);
+        }
         mark(); mark();  // 5: projection, 6: (residual inside)
     } else {
         gemm(m.ws("attention"), m.wo, m.ws("projected"), T, H, m.hidden_l, SFB_EPI_STORE);
@@ -650,6 +710,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             gemm(m.ws("normalized2"), m.wgu, m.ws("activation"), T, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block);
             if (m.direct_f32_output) {
                 gemm(m.ws("activation"), m.wd, m.ws("output_f32"), T, H, I, SFB_EPI_RESIDUAL, r1, 0, nullptr, 0, true);
+            } else if (peer) {
+                gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0,
+                     nullptr, 0, false, 1);
+                peer_finish(1, out, static_cast<int64_t>(T) * H);
             } else {
                 gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1);
                 allreduce(out, static_cast<int64_t>(T) * H);
@@ -772,8 +836,9 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     const int H = m.H, I = m.I_l, D = m.D;
     const std::size_t row_f32 = static_cast<std::size_t>(H) * 4, row_bf = static_cast<std::size_t>(H) * 2;
     auto at = [](void* base, std::size_t bytes) { return static_cast<void*>(static_cast<char*>(base) + bytes); };
+    const bool peer = m.size > 1 && m.peer_local != nullptr;
     auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int b0,
-                    bool f32_out = false) {
+                    bool f32_out = false, int peer_set = -1) {
         sfb_gemm_args g{};
         g.a = a; g.bt = w; g.out = out; g.m = rows; g.n = n; g.k = k; g.epilogue = epi;
         g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb; g.out_f32 = f32_out ? 1 : 0;
@@ -785,7 +850,14 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             g.batch = nb; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
+        if (peer_set >= 0) m.fill_peer_out(g, peer_set, static_cast<std::size_t>(b0) * c.sequence * H);
         throw_on(sfb_k_gemm_bf16(&g, s));
+    };
+    // sum over the ranks of `rows` x H partial sums: fused peer form, or the caller's hook
+    auto reduce = [&](int peer_set, void* buffer, int b0) {
+        if (peer) throw_on(m.peer_finish(peer_set, buffer, static_cast<std::size_t>(b0) * c.sequence * H,
+                                         static_cast<int64_t>(rows) * H, s));
+        else if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, buffer, static_cast<int64_t>(rows) * H, m.dtype, s);
     };
     cudaEvent_t t0 = m.events[12], t1 = m.events[15];
     cuda_check(cudaEventRecord(t0, s), "event");
@@ -822,8 +894,8 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         a.dtype = SFB_BF16; a.backend = policy.attention_backend;
         throw_on(sfb_k_attention_prefill(&a, s));
         cuda_check(cudaEventRecord(ev[4], s), "event");
-        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, b0);
-        if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, r1, static_cast<int64_t>(rows) * H, m.dtype, s);
+        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, b0, false, peer ? 0 : -1);
+        reduce(0, r1, b0);
         throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
         cuda_check(cudaEventRecord(ev[5], s), "event");
         gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, b0);
@@ -831,8 +903,8 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             gemm(act, m.wd, out32, H, I, SFB_EPI_RESIDUAL, r1, 0, b0, true);
             cuda_check(cudaEventRecord(ev[6], s), "event");
         } else {
-            gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, b0);
-            if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, out, static_cast<int64_t>(rows) * H, m.dtype, s);
+            gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, b0, false, peer ? 1 : -1);
+            reduce(1, out, b0);
             cuda_check(cudaEventRecord(ev[6], s), "event");
             throw_on(sfb_k_convert(out, SFB_BF16, out32, SFB_F32, static_cast<int64_t>(rows) * H, s));
         }

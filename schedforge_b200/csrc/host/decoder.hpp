@@ -85,6 +85,9 @@ public:
     void run(cudaStream_t stream, RoutingTraceView trace, bool stage_events);
     void download_output(float* output);
     void set_allreduce(sfb_allreduce_fn fn, void* user) { allreduce_ = fn; allreduce_user_ = user; }
+    // Fused all-reduce over peer memory for the O and Down projections of a sharded plan.
+    std::size_t peer_bytes() const;
+    void set_peer_allreduce(void* local_base, void* const* peer_bases);
     std::string dump() const;
     // Copies the named intermediate to the host as float32; returns the element count.
     int64_t read_tensor(const std::string& name, float* host_out, int64_t capacity);

@@ -1,0 +1,175 @@
+// Sum all-reduce over NVLink peer memory for the sharded decoder layer, fused with the GEMM that
+// produces the partial sums.
+//
+// Every rank owns a receive buffer with one slot per rank.  The O and Down projections of a
+// tensor-parallel plan (gemm_tcgen05.cu) store each finished output piece twice from their
+// epilogue: into the local partial-sum buffer and, with plain peer stores, into this rank's slot of
+// every other rank's receive buffer, so the transfer runs tile by tile under the GEMM.  The
+// kernel below then (1) publishes "my partial sums are in your slot" with a system-scope release
+// store of an epoch number into every peer's flag array, (2) waits, with a bound, for the same
+// epoch from every peer and (3) replaces the local partial sums by the sum over all ranks, taken
+// in rank order so that every rank computes bit-identical results.
+//
+// Each rank pushes (size - 1) x bytes: this is the form for small messages (decode) and for two
+// ranks; larger groups with large outputs should use a two-shot collective instead.
+//
+// Reuse of a slot is safe without further handshakes when the same sequence of collectives
+// runs on every rank: a rank starts pushing use n+1 of a slot only after it has passed the wait
+// of a later collective on another slot set, which its peers signal after they have finished
+// reading use n (stream order on the peer).  The decoder plan alternates two slot sets.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace sfb {
+namespace {
+
+constexpr long long kPeerWaitCycles = 4000000000LL;  // ~2 s; then the status word is set and the sum is skipped
+constexpr uint32_t kCodePeerWait = 0x100;
+
+__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct PeerParams {
+    bf16* data;
+    const bf16* recv;
+    uint32_t* local_flags;
+    uint32_t* peer_flags[SFB_MAX_PEERS];
+    int rank, size;
+    uint32_t epoch;
+    long long count;
+    long long slot_elems;
+    uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256)
+peer_allreduce_finish_kernel(const PeerParams p) {
+    __shared__ int proceed;
+    if (blockIdx.x == 0 && threadIdx.x < p.size && static_cast<int>(threadIdx.x) != p.rank) {
+        __threadfence_system();  // the partial sums pushed by the preceding GEMM come before the flag
+        store_release_sys(p.peer_flags[threadIdx.x], p.epoch);
+    }
+    if (threadIdx.x == 0) {
+        bool ok = true;
+        const long long start = clock64();
+        for (int s = 0; s < p.size && ok; ++s) {
+            if (s == p.rank) continue;
+            uint32_t spins = 0;
+            while (static_cast<int>(load_acquire_sys(p.local_flags + s) - p.epoch) < 0) {
+                if ((++spins & 0xFFu) == 0 && clock64() - start > kPeerWaitCycles) {
+                    ok = false;
+                    atomicOr(p.status, kCodePeerWait);
+                    break;
+                }
+            }
+        }
+        proceed = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!proceed) return;
+    const long long pieces = p.count / 8;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < pieces; i += stride) {
+        float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+        for (int s = 0; s < p.size; ++s) {  // rank order: the same arithmetic on every rank
+            const bf16* src = s == p.rank ? p.data : p.recv + s * p.slot_elems;
+            const uint4 packed = *reinterpret_cast<const uint4*>(src + i * 8);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(h[j]);
+                acc[2 * j] += x.x;
+                acc[2 * j + 1] += x.y;
+            }
+        }
+        uint4 result;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        *reinterpret_cast<uint4*>(p.data + i * 8) = result;
+    }
+    // ragged tail (count % 8), one thread
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        for (long long i = pieces * 8; i < p.count; ++i) {
+            float acc = 0.0F;
+            for (int s = 0; s < p.size; ++s) acc += to_float((s == p.rank ? p.data : p.recv + s * p.slot_elems)[i]);
+            p.data[i] = from_float<bf16>(acc);
+        }
+    }
+}
+
+}  // namespace
+}  // namespace sfb
+
+using namespace sfb;
+
+extern "C" {
+
+sfb_status sfb_k_peer_allreduce_finish(const sfb_peer_allreduce_args* a, sfb_stream stream) {
+    SFB_REQUIRE(a && a->data && a->recv && a->local_flags, "peer all-reduce: null buffer");
+    SFB_REQUIRE(a->size >= 2 && a->size <= SFB_MAX_PEERS && a->rank >= 0 && a->rank < a->size && a->count > 0 &&
+                    a->slot_elems >= a->count,
+                "peer all-reduce: invalid group or size");
+    SFB_REQUIRE((reinterpret_cast<uintptr_t>(a->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->recv) & 15) == 0 &&
+                    a->slot_elems % 8 == 0,
+                "peer all-reduce: buffers must be 16-byte aligned");
+    PeerParams p{};
+    p.data = static_cast<bf16*>(a->data);
+    p.recv = static_cast<const bf16*>(a->recv);
+    p.local_flags = a->local_flags;
+    for (int s = 0; s < a->size; ++s) {
+        SFB_REQUIRE(s == a->rank || a->peer_flags[s], "peer all-reduce: null peer flag");
+        p.peer_flags[s] = a->peer_flags[s];
+    }
+    p.rank = a->rank;
+    p.size = a->size;
+    p.epoch = a->epoch;
+    p.count = a->count;
+    p.slot_elems = a->slot_elems;
+    p.status = device_status_word();
+    const long long pieces = a->count / 8 + 1;
+    const int grid = static_cast<int>(std::min<long long>((pieces + 255) / 256, static_cast<long long>(sm_count()) * 4));
+    peer_allreduce_finish_kernel<<<grid, 256, 0, as_stream(stream)>>>(p);
+    return check_launch("peer_allreduce_finish");
+}
+
+// ---- peer-visible device memory (CUDA IPC) -----------------------------------------------------
+
+sfb_status sfb_peer_alloc(size_t bytes, void** ptr, void* handle64) {
+    SFB_REQUIRE(bytes > 0 && ptr && handle64, "peer alloc: invalid argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    SFB_CUDA(cudaMalloc(ptr, bytes));
+    SFB_CUDA(cudaMemset(*ptr, 0, bytes));
+    SFB_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t handle;
+    SFB_CUDA(cudaIpcGetMemHandle(&handle, *ptr));
+    memcpy(handle64, &handle, sizeof(handle));
+    return SFB_OK;
+}
+
+sfb_status sfb_peer_open(const void* handle64, void** ptr) {
+    SFB_REQUIRE(handle64 && ptr, "peer open: invalid argument");
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, handle64, sizeof(handle));
+    SFB_CUDA(cudaIpcOpenMemHandle(ptr, handle, cudaIpcMemLazyEnablePeerAccess));
+    return SFB_OK;
+}
+
+sfb_status sfb_peer_close(void* ptr) {
+    if (ptr) SFB_CUDA(cudaIpcCloseMemHandle(ptr));
+    return SFB_OK;
+}
+
+sfb_status sfb_peer_free(void* ptr) {
+    if (ptr) SFB_CUDA(cudaFree(ptr));
+    return SFB_OK;
+}
+
+}  // extern "C"

@@ -27,7 +27,8 @@ class GemmArgs(C.Structure):
                 ("batch", C.c_int), ("seq", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int),
                 ("head_dim", C.c_int),
                 ("group_offsets", vp), ("groups", C.c_int), ("tile_table", vp),
-                ("split_workspace", vp), ("split_workspace_bytes", C.c_size_t), ("bt_tiled", C.c_int)]
+                ("split_workspace", vp), ("split_workspace_bytes", C.c_size_t), ("bt_tiled", C.c_int),
+                ("peer_out", vp * 7), ("peer_count", C.c_int)]
 
 
 class AttentionArgs(C.Structure):
@@ -103,7 +104,7 @@ EXPORTS = (
     "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_dispatch_static sfb_k_moe_combine "
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
     "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_upload_input "
-    "sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce "
+    "sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
     "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
     "sfb_attention_execute sfb_attention_decode "
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "
@@ -143,7 +144,7 @@ def load():
     lib.sfb_launch_count.restype = C.c_uint64
     lib.sfb_tiled_weight_elems.restype = C.c_int64
     for name in ("sfb_attention_decode_workspace", "sfb_moe_dispatch_scratch_bytes",
-                 "sfb_decoder_workspace_bytes", "sfb_gemm_stream_workspace_bytes"):
+                 "sfb_decoder_workspace_bytes", "sfb_gemm_stream_workspace_bytes", "sfb_decoder_peer_bytes"):
         if hasattr(lib, name):
             getattr(lib, name).restype = C.c_size_t
     if hasattr(lib, "sfb_decoder_stream"):

@@ -1,6 +1,8 @@
 """Rank program for tests/test_multi_gpu.py (launched with torch.distributed.run, one rank per
 GPU): tensor-parallel dense layer and expert-sharded MoE layer with a real NCCL all-reduce behind
-the plan's hook, checked against the unsharded CPU oracle on rank 0."""
+the plan's hook, checked against the unsharded CPU oracle on rank 0, and the same layers with the
+all-reduce fused into the GEMMs over NVLink peer memory."""
+import ctypes as C
 import os
 import sys
 
@@ -72,6 +74,33 @@ def main():
         dist.broadcast(ref, 0)
         if not torch.equal(mine, ref):
             failures.append(name + ":ranks differ")
+        # the same layer with the all-reduces after O and Down fused into the GEMMs over peer memory
+        # (the MoE combine keeps the hook); three passes reuse the slot sets
+        def exchange(handle):
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            return handles
+        plan.enable_peer_allreduce(rank, world, exchange)
+        dist.barrier()
+        for _ in range(3):
+            fused, _ = plan.execute(data["input"])
+        word = C.c_uint32(0)
+        L.check(L.load().sfb_device_status(C.byref(word)))
+        if word.value != 0:
+            failures.append(f"{name}:device status {word.value:#x}")
+        err = float(np.max(np.abs(fused - out)) / np.max(np.abs(out)))
+        if rank == 0:
+            print(f"{name}: fused peer all-reduce vs NCCL rel diff {err:.3e}", flush=True)
+        if not err < 1e-2:  # both are sums of the same bf16 partial sums, rounded in a different order
+            failures.append(name + ":fused differs")
+        mine = torch.from_numpy(fused).cuda()
+        ref = mine.clone()
+        dist.broadcast(ref, 0)
+        if not torch.equal(mine, ref):
+            failures.append(name + ":fused ranks differ")
+        torch.cuda.synchronize()
+        dist.barrier()
+        plan.disable_peer_allreduce()
         plan.close()
     dist.barrier()
     dist.destroy_process_group()
