@@ -411,6 +411,39 @@ sfb_status sfb_decoder_download_output(sfb_decoder_plan* plan, float* output);
 /* Tensor-parallel hook: called on the plan's stream after the O projection and after the
  * Down projection partial sums are in `buffer` (`count` elements of `dtype`); the callee
  * must all-reduce (sum) in place on `stream`.  NULL = single shard. */
+/* ExecutablePlanOptimizer::optimize (include/schedforge/decoder_compiler.h:140-178,
+ * src/decoder_compiler.cpp:726-861) on the GPU: 16 policies (fused or materialised epilogues x
+ * tensor-core or CUDA-core GEMM family x tensor-core or CUDA-core attention x workspace reuse) ranked
+ * analytically; the baseline (base_options) and the best-ranked measurement_budget candidates are
+ * measured with three warm-up passes and `repetitions` timed passes (median) on `input` (host
+ * float32 [T,H]); a faster winner is confirmed by three interleaved baseline/winner measurements.
+ * *plan receives the winning plan (the baseline when nothing beat it).  candidates_out (optional,
+ * `capacity` entries) receives the baseline followed by the ranked candidates. */
+typedef struct sfb_plan_cost {
+    double measured_milliseconds;
+    double analytical_score;
+    size_t workspace_bytes;
+    size_t materialization_bytes;
+    int measured;
+} sfb_plan_cost;
+typedef struct sfb_plan_candidate {
+    sfb_compile_options options;
+    sfb_plan_cost cost;
+} sfb_plan_candidate;
+typedef struct sfb_optimization_result {
+    sfb_plan_cost baseline;
+    sfb_plan_cost winner;
+    sfb_compile_options winner_options;
+    int candidates;
+    int hardware_measurements;
+    double speedup;
+} sfb_optimization_result;
+sfb_status sfb_decoder_optimize(const sfb_decoder_config* config, const sfb_decoder_data* data,
+                                const char* stablehlo_text, const sfb_compile_options* base_options,
+                                const float* input, int measurement_budget, int repetitions,
+                                sfb_optimization_result* result, sfb_plan_candidate* candidates_out, int capacity,
+                                sfb_decoder_plan** plan);
+
 /* ---- sum all-reduce over NVLink peer memory, fused with the producing GEMM -----------------------
  * Replaces, for the sharded plan, the collective that the reference does not have (it is a
  * single-process CPU library); the unfused form is the sfb_allreduce_fn hook below.

@@ -193,6 +193,26 @@ class DecoderCompiler:
         return DecoderExecutablePlan(handle, config, options, None)
 
 
+class ExecutablePlanOptimizer:
+    """ExecutablePlanOptimizer::optimize: returns (winning plan, OptimizationResult, candidates)."""
+
+    @staticmethod
+    def optimize(config, data, x, stablehlo_text="", options=None, measurement_budget=8, repetitions=2):
+        options = options or compile_options()
+        keep = {k: _f32(v) for k, v in data.items() if v is not None and k in L.DATA_FIELDS}
+        d = L.DecoderData()
+        for name in L.DATA_FIELDS:
+            setattr(d, name, _fp(keep.get(name)))
+        x = _f32(x)
+        result = L.OptimizationResult()
+        candidates = (L.PlanCandidate * 17)()
+        handle = C.c_void_p()
+        L.check(L.load().sfb_decoder_optimize(C.byref(config), C.byref(d), stablehlo_text.encode(), C.byref(options),
+                                              _fp(x), measurement_budget, repetitions, C.byref(result), candidates, 17,
+                                              C.byref(handle)))
+        return DecoderExecutablePlan(handle, config, result.winner_options, None), result, list(candidates)[:result.candidates]
+
+
 def execute_decoder_layer(plan, x, trace=None):
     return plan.execute(x, trace=trace)
 

@@ -83,6 +83,29 @@ sfb_status sfb_decoder_compile(const sfb_decoder_config* config, const sfb_decod
     });
 }
 
+sfb_status sfb_decoder_optimize(const sfb_decoder_config* config, const sfb_decoder_data* data,
+                                const char* stablehlo_text, const sfb_compile_options* base_options,
+                                const float* input, int measurement_budget, int repetitions,
+                                sfb_optimization_result* result, sfb_plan_candidate* candidates_out, int capacity,
+                                sfb_decoder_plan** plan) {
+    return guarded([&] {
+        if (!config || !data || !plan || !result) throw std::invalid_argument("null decoder optimize argument");
+        *plan = nullptr;
+        const DecoderConfig c = to_config(*config);
+        validate(c);
+        sfb_compile_options opt{};
+        if (base_options) opt = *base_options;
+        else { opt.dtype = SFB_BF16; opt.token_major_attention = 1; opt.fuse_epilogues = 1; }
+        if (opt.tp_size <= 0) opt.tp_size = 1;
+        const TensorGraph imported = stablehlo_text && *stablehlo_text
+            ? StableHLOImporter{}.importText(stablehlo_text) : build_decoder_layer_graph(c);
+        auto owned = std::make_unique<sfb_decoder_plan>();
+        owned->plan = optimize_decoder_plan(imported, c, *data, opt, input, measurement_budget, repetitions, result,
+                                            candidates_out, capacity);
+        *plan = owned.release();
+    });
+}
+
 void sfb_decoder_destroy(sfb_decoder_plan* plan) { delete plan; }
 
 sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float* output,

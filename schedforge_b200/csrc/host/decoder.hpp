@@ -102,6 +102,12 @@ private:
     void* allreduce_user_ = nullptr;
 };
 
+// ExecutablePlanOptimizer::optimize on the GPU (optimizer.cpp); returns the winning plan.
+std::unique_ptr<DecoderExecutablePlan> optimize_decoder_plan(
+    const TensorGraph& graph, const DecoderConfig& config, const sfb_decoder_data& data, const sfb_compile_options& base,
+    const float* input, int measurement_budget, int repetitions, sfb_optimization_result* result,
+    sfb_plan_candidate* candidates_out, int capacity);
+
 class DecoderCompiler {
 public:
     // Throws std::invalid_argument for an invalid configuration or missing fusion patterns.

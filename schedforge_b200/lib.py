@@ -69,6 +69,20 @@ class CompileOptions(C.Structure):
                                        "append_new_token")]
 
 
+class PlanCost(C.Structure):
+    _fields_ = [("measured_milliseconds", C.c_double), ("analytical_score", C.c_double),
+                ("workspace_bytes", C.c_size_t), ("materialization_bytes", C.c_size_t), ("measured", C.c_int)]
+
+
+class PlanCandidate(C.Structure):
+    _fields_ = [("options", CompileOptions), ("cost", PlanCost)]
+
+
+class OptimizationResult(C.Structure):
+    _fields_ = [("baseline", PlanCost), ("winner", PlanCost), ("winner_options", CompileOptions),
+                ("candidates", C.c_int), ("hardware_measurements", C.c_int), ("speedup", C.c_double)]
+
+
 class DecoderResult(C.Structure):
     _fields_ = [(n, C.c_double) for n in ("milliseconds", "attention_milliseconds",
                                           "projection_milliseconds", "norm_rope_milliseconds",
@@ -104,7 +118,7 @@ EXPORTS = (
     "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_dispatch_static sfb_k_moe_combine "
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
     "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_upload_input "
-    "sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
+    "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
     "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
     "sfb_attention_execute sfb_attention_decode "
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "

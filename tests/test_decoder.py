@@ -254,3 +254,26 @@ def test_autoregressive_step_equals_last_token_of_the_prefill(port, dtype, head_
     assert rel_err(out_legacy, want) > 2 * BF16_TOL
     plan.close()
     legacy.close()
+
+
+def test_plan_optimizer_measures_ranks_and_confirms(port):
+    """The reference's own bar for its optimizer (tests/test_schedforge.cpp:916-921): at least 16
+    candidates, at least 5 hardware measurements with a budget of 4, a measured winner, a positive
+    speedup and a usable plan; plus: the winner is never slower than the confirmed baseline."""
+    kw = dict(batch=2, sequence=128, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64)
+    oc, c, data = bf16_case(port, 31, **kw)
+    base = api.compile_options(fuse_epilogues=False)  # a deliberately weak baseline: materialised intermediates
+    plan, result, candidates = api.ExecutablePlanOptimizer.optimize(c, weights_of(data), data["input"], "", base,
+                                                                    measurement_budget=4, repetitions=3)
+    assert result.candidates >= 16 and len(candidates) >= 16
+    assert result.hardware_measurements >= 5
+    assert result.winner.measured and result.speedup > 0.0
+    assert result.winner.measured_milliseconds <= result.baseline.measured_milliseconds
+    assert result.winner.workspace_bytes > 0
+    scores = [cand.cost.analytical_score for cand in candidates[1:]]
+    assert scores == sorted(scores)                       # ranked by the analytic score
+    assert sum(cand.cost.measured for cand in candidates[1:]) == 4  # exactly the budget was measured
+    assert candidates[1].options.fuse_epilogues == 1      # fused tensor-core plans rank first
+    out, _ = plan.execute(data["input"])
+    assert rel_err(out, port.decoder_layer(oc, data, native=True)) < BF16_TOL
+    plan.close()
