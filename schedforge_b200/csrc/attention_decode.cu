@@ -69,6 +69,8 @@ decode_paged_mma_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     int* page_ids = reinterpret_cast<int*>(empty_bar + kStages) + 2;
 
     const int split = blockIdx.z, kvh = blockIdx.y, b = blockIdx.x;
+    grid_dependents_may_launch();
+    grid_dependency_wait();  // the queries (and an appended page) come from the kernels before
     const int ctx = p.context_len[b];
     int begin, end;
     split_range(ctx, p.chunk_tokens, split, begin, end);
@@ -252,7 +254,8 @@ sfb_status launch_group(const CUtensorMap& mk, const CUtensorMap& mv, const Deco
                         cudaStream_t stream) {
     SFB_CUDA(cudaFuncSetAttribute(decode_paged_mma_kernel<GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
-    decode_paged_mma_kernel<GROUP><<<grid, kThreads, smem, stream>>>(mk, mv, p, device_status_word());
+    SFB_CUDA(launch_dependent(decode_paged_mma_kernel<GROUP>, grid, dim3(kThreads), smem, stream, mk, mv, p,
+                              device_status_word()));
     return check_launch("attention_decode_paged_mma");
 }
 

@@ -244,6 +244,8 @@ __global__ void decode_combine_warp_kernel(const float* __restrict__ partials, T
                                            int splits, int dim_v) {
     const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    grid_dependents_may_launch();
+    grid_dependency_wait();  // the partials come from the kernel before
     if (row >= rows) return;
     const size_t record = static_cast<size_t>(dim_v) + 2;
     const float* rec = partials + static_cast<size_t>(row) * splits * record;
@@ -416,9 +418,11 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream str
     const int rows = a->batch * a->q_heads;
     if (splits <= 32 && a->head_dim_value % 32 == 0) {
         if (a->dtype == SFB_F32)
-            decode_combine_warp_kernel<float><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<float*>(a->out), rows, splits, a->head_dim_value);
+            SFB_CUDA(launch_dependent(decode_combine_warp_kernel<float>, dim3(ceil_div(rows, 4)), dim3(128), 0, s,
+                                      static_cast<const float*>(p.partials), static_cast<float*>(a->out), rows, splits, a->head_dim_value));
         else
-            decode_combine_warp_kernel<bf16><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<bf16*>(a->out), rows, splits, a->head_dim_value);
+            SFB_CUDA(launch_dependent(decode_combine_warp_kernel<bf16>, dim3(ceil_div(rows, 4)), dim3(128), 0, s,
+                                      static_cast<const float*>(p.partials), static_cast<bf16*>(a->out), rows, splits, a->head_dim_value));
     } else if (a->dtype == SFB_F32)
         decode_combine_kernel<float><<<ceil_div(rows, 4), 128, 0, s>>>(p.partials, static_cast<float*>(a->out), rows, splits, a->head_dim_value);
     else

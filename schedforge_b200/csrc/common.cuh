@@ -24,6 +24,32 @@ void count_launch(int n = 1);
 // Device status word written by bounded waits that gave up (see sfb_device_status).
 uint32_t* device_status_word();
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched with launch_dependent() may begin (prologue, loads that do not depend on
+// the previous kernel) while the previous kernel of the stream is still finishing; it must call
+// grid_dependency_wait() before it touches anything the previous kernel reads or writes.  Under
+// an ordinary launch both calls are no-ops.
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... Params, class... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+#endif
+
 inline sfb_status check_launch(const char* what) {
     count_launch();
     const cudaError_t error = cudaGetLastError();

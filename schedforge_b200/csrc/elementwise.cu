@@ -70,6 +70,8 @@ __global__ void __launch_bounds__(256)
 rms_norm_row_block_kernel(const bf16* __restrict__ x, const float* __restrict__ weight, bf16* __restrict__ y,
                           int width, float epsilon) {
     __shared__ float partial[8];
+    grid_dependents_may_launch();  // the GEMM that follows can start fetching its weights
+    grid_dependency_wait();
     const uint4* row4 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(blockIdx.x) * width);
     uint4* out4 = reinterpret_cast<uint4*>(y + static_cast<size_t>(blockIdx.x) * width);
     const int pieces = width / 8;
@@ -186,8 +188,8 @@ sfb_status sfb_k_rms_norm(const void* x, const float* weight, void* y, int rows,
     if (dtype == SFB_BF16 && rows <= 2048 && width % 8 == 0 && width >= 2048 &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(weight) & 15) == 0) {
-        rms_norm_row_block_kernel<<<rows, 256, 0, as_stream(stream)>>>(static_cast<const bf16*>(x), weight,
-                                                                       static_cast<bf16*>(y), width, epsilon);
+        SFB_CUDA(launch_dependent(rms_norm_row_block_kernel, dim3(rows), dim3(256), 0, as_stream(stream),
+                                  static_cast<const bf16*>(x), weight, static_cast<bf16*>(y), width, epsilon));
         return check_launch("rms_norm");
     }
     if (dtype == SFB_F32)

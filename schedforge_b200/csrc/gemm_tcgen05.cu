@@ -356,6 +356,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependents_may_launch();
+    // Weights do not depend on the kernel before this one: in a dense GEMM the producer fetches them
+    // first and only then waits for that kernel; every other role waits right away.
+    const bool early_weights = p.tile_table == nullptr;
+    if (!(warp == 0 && lane == 0 && early_weights)) grid_dependency_wait();
 
     const int m_tiles = load_m_tiles(p);
     const int k_blocks = (p.k + BK - 1) / BK;
@@ -382,18 +387,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 Segment sg;
                 uint32_t it = 0;
                 bool ok = true;
+                // the first ring-full of weight tiles goes out before the wait for the previous kernel
+                uint32_t early = 0;
+                if (early_weights) {
+                    Walk ahead = walk;
+                    Segment first;
+                    if (ahead.next(first)) {
+                        const TileCoord c = tile_coord(p, first.tile, m_tiles);
+                        for (int kb = first.kb0; kb < first.kb1 && early < static_cast<uint32_t>(SB); ++kb, ++early) {
+                            const uint32_t full = ptx::smem_u32(&full_b[early]);
+                            ptx::mbar_expect_tx(full, T::kStageBytes);
+                            load_b(smem_b + early * T::kBBytes, full, kb, c);
+                        }
+                    }
+                    grid_dependency_wait();
+                }
                 while (ok && walk.next(sg)) {
                     const TileCoord c = tile_coord(p, sg.tile, m_tiles);
                     for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                         const uint32_t s = it % SB, ph = (it / SB) & 1;
-                        if (!ptx::mbar_wait(ptx::smem_u32(&empty_b[s]), ph ^ 1, abort_flag, p.status, kCodeProducer)) {
-                            ok = false;
-                            break;
-                        }
                         const uint32_t full = ptx::smem_u32(&full_b[s]);
-                        ptx::mbar_expect_tx(full, T::kStageBytes);
+                        if (it >= early) {
+                            if (!ptx::mbar_wait(ptx::smem_u32(&empty_b[s]), ph ^ 1, abort_flag, p.status, kCodeProducer)) {
+                                ok = false;
+                                break;
+                            }
+                            ptx::mbar_expect_tx(full, T::kStageBytes);
+                            load_b(smem_b + s * T::kBBytes, full, kb, c);
+                        }
                         ptx::tma_load_2d(ptx::smem_u32(smem_a + s * T::kABytes), &tma_a, full, kb * BK, c.row_start);
-                        load_b(smem_b + s * T::kBBytes, full, kb, c);
                     }
                 }
             } else {
@@ -420,6 +442,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 Cursor ca{walk, {}, {}, 0, 0, false}, cb{walk, {}, {}, 0, 0, false};
                 open(ca);
                 open(cb);
+                // fill the weight ring before waiting for the previous kernel (the ring is empty: no waits)
+                while (cb.live && cb.it < static_cast<uint32_t>(SB)) {
+                    const uint32_t full = ptx::smem_u32(&full_b[cb.it]);
+                    ptx::mbar_expect_tx(full, T::kBBytes);
+                    load_b(smem_b + cb.it * T::kBBytes, full, cb.kb, cb.c);
+                    advance(cb);
+                }
+                grid_dependency_wait();
                 long long stall_start = 0;
                 uint32_t idle = 0;
                 while (ca.live || cb.live) {
@@ -700,7 +730,8 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
             grid = static_cast<int>(tiles >= sm_count() || units >= sm_count() ? sm_count() : units);
         }
     }
-    gemm_tcgen05_kernel<BN, STREAM><<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, p);
+    SFB_CUDA(launch_dependent(gemm_tcgen05_kernel<BN, STREAM>, dim3(grid), dim3(kThreads), T::kSmemBytes, stream, map_a,
+                              map_b, p));
     return check_launch("gemm_tcgen05");
 }
 
