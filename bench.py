@@ -161,8 +161,8 @@ def kernel_case(args):
                (--small: M=4096, N=16384, K=4096, 224 MB of operands, larger than L2)
     gemm_decode  the same projection for the 128 rows of a decode step: blocked weights, streamed
                once (--small: N=8192; three weight copies are rotated so that L2 does not help)
-    attention  BASELINE configs[1]: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (--small: B1)
-    decode     BASELINE configs[2]: paged split-KV decode, batch 64, context ~U[512, 8192], 16-token
+    attention  headline attention case: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (--small: B1)
+    decode     headline decode case: paged split-KV decode, batch 64, context ~U[512, 8192], 16-token
                blocks, permuted block table (--small: batch 16)
     """
     import torch

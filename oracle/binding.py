@@ -112,7 +112,7 @@ def pack_decoder_data(data, trace=None):
 
 
 def build(which="all"):
-    """Compile the checkers (the reference one only where /root/reference exists)."""
+    """Compile the checkers (the reference one only where the reference source tree is present)."""
     targets = []
     if which in ("all", "port"):
         targets.append("port")

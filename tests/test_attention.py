@@ -234,7 +234,7 @@ def test_prefill_bf16_head_dim_128(dev, port, backend, batch, hq, hkv, sq, sk, c
 
 
 def test_prefill_tcgen05_baseline_config2_slices(dev, port):
-    """BASELINE configs[1] shape (B4, Hq32, Hkv8, S4096, D128, causal): full run on the GPU, the
+    """Headline attention shape (B4, Hq32, Hkv8, S4096, D128, causal): full run on the GPU, the
     oracle on sampled (batch, head) slices and query rows (materialised softmax(QK^T)V)."""
     torch = dev.torch
     batch, hq, hkv, s = 4, 32, 8, 4096

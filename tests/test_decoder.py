@@ -1,5 +1,5 @@
 """Decoder layer parity through the plan ABI (sfb_decoder_compile / sfb_decoder_execute):
-the reference's own test shapes and seeds from the golden fixtures, BASELINE configs[0], and
+the reference's own test shapes and seeds from the golden fixtures, the tiny fp32 benchmark configuration, and
 bf16 tensor-core plans against the oracle on bf16-rounded data."""
 import os
 import sys
@@ -60,7 +60,7 @@ def test_fp32_plan_matches_reference_fixtures(name, text):
 
 
 def baseline_config1():
-    """BASELINE configs[0]: tiny dense prefill, weights ~N(0,0.02), activations ~N(0,1), seed 0."""
+    """The tiny fp32 benchmark configuration: dense prefill, weights ~N(0,0.02), activations ~N(0,1), seed 0."""
     kw = dict(batch=1, sequence=128, hidden=256, intermediate=688, query_heads=4, kv_heads=2, head_dim=64,
               rms_epsilon=1e-5, rope_theta=10000.0)
     rng = np.random.default_rng(0)
@@ -165,21 +165,26 @@ def test_bf16_moe_layer_and_bit_exact_routing(port):
     plan.close()
 
 
-def test_tensor_parallel_shards_reproduce_the_full_layer(port):
-    """Two tensor-parallel shards on ONE GPU with the all-reduce emulated through the plan's hook:
-    pass 1 captures each shard's O-projection partial, pass 2 adds the peer's partial where the
-    collective would run and captures the down-projection partials, whose sum is the layer output."""
+@pytest.mark.parametrize("shards,decode", [(2, False), (4, False), (8, False), (8, True)])
+def test_tensor_parallel_shards_reproduce_the_full_layer(port, shards, decode):
+    """Tensor-parallel shards on ONE GPU with the all-reduce emulated through the plan's hook:
+    pass 1 captures each shard's O-projection partial, pass 2 adds the peers' partials where the
+    collective would run and captures the down-projection partials, whose sum is the layer output.
+    Eight shards of eight KV heads is the one-KV-head-per-rank case of an 8-GPU node."""
     import ctypes as C
     import torch
-    kw = dict(batch=1, sequence=128, hidden=256, intermediate=512, query_heads=4, kv_heads=2, head_dim=64)
+    kw = dict(batch=2, sequence=64, hidden=512, intermediate=1024, query_heads=16, kv_heads=8, head_dim=32)
+    if decode:
+        kw.update(sequence=1, batch=4, context_sequence=100)
     oc, c, data = bf16_case(port, 6, **kw)
     want = port.decoder_layer(oc, data, native=True)
     lib = L.load()
-    count = 128 * 256
-    plans = [api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(tp_rank=r, tp_size=2))
-             for r in range(2)]
-    first = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
-    second = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    rows = kw["batch"] * kw["sequence"]
+    count = rows * kw["hidden"]
+    plans = [api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(tp_rank=r, tp_size=shards))
+             for r in range(shards)]
+    first = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(shards)]
+    second = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(shards)]
 
     def copy_out(buf, dst, stream):
         L.check(lib.sfb_k_convert(C.c_void_p(buf), L.BF16, C.c_void_p(dst.data_ptr()), L.BF16, C.c_int64(count),
@@ -201,15 +206,17 @@ def test_tensor_parallel_shards_reproduce_the_full_layer(port):
 
         def hook(buf, n, dtype, stream, rank=rank, calls=calls):
             if not calls:
-                L.check(lib.sfb_k_add(C.c_void_p(buf), C.c_void_p(first[1 - rank].data_ptr()), C.c_void_p(buf),
-                                      C.c_int64(count), L.BF16, C.c_void_p(stream)))
+                for peer in range(shards):
+                    if peer != rank:
+                        L.check(lib.sfb_k_add(C.c_void_p(buf), C.c_void_p(first[peer].data_ptr()), C.c_void_p(buf),
+                                              C.c_int64(count), L.BF16, C.c_void_p(stream)))
             else:
                 copy_out(buf, second[rank], stream)
             calls.append(buf)
         plan.set_allreduce(hook)
         plan.execute(data["input"])
     torch.cuda.synchronize()
-    out = (second[0].float() + second[1].float()).cpu().numpy().reshape(128, 256)
+    out = sum(t.float() for t in second).cpu().numpy().reshape(rows, kw["hidden"])
     assert rel_err(out, want) < BF16_TOL
     for p in plans:
         p.close()
