@@ -147,6 +147,9 @@ typedef struct sfb_gemm_args {
      * the GEMM; sfb_k_peer_allreduce_finish completes it. */
     void* peer_out[SFB_MAX_PEERS - 1];
     int peer_count;
+    /* SFB_EPI_ROPE_SPLIT on a row chunk: row r of A is token (r + rope_row_offset) of the
+     * [batch, seq] grid (q/key/value stay the full tensors) */
+    int rope_row_offset;
 } sfb_gemm_args;
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
@@ -193,6 +196,11 @@ typedef struct sfb_attention_args {
     int token_major;
     int dtype;    /* sfb_dtype of q/key/value/out */
     int backend;  /* 0 auto, 1 SIMT, 2 tcgen05 */
+    /* A slice of longer sequences (tcgen05 kernel only; 0 = dense): rows between two heads of q
+     * and of key/value in memory, when seq_q / seq_kv cover only part of the stored sequence.  With
+     * causal masking query i of the slice is row seq_kv - seq_q + i of the sequence, so a prefill can
+     * run in row chunks: chunk [r0, r1) passes q + r0 rows, seq_q = r1 - r0, seq_kv = r1. */
+    int q_head_rows, kv_head_rows;
 } sfb_attention_args;
 
 sfb_status sfb_k_attention_prefill(const sfb_attention_args* args, sfb_stream stream);

@@ -331,6 +331,8 @@ sfb_status sfb_k_attention_prefill(const sfb_attention_args* a, sfb_stream strea
                 a->head_dim > 0 && a->head_dim_value > 0 && a->q_heads % a->kv_heads == 0,
                 "invalid attention configuration");
     SFB_REQUIRE(!a->causal || a->seq_q <= a->seq_kv, "causal attention requires sequence_query <= sequence_kv");
+    SFB_REQUIRE((a->q_head_rows == 0 || a->q_head_rows >= a->seq_q) && (a->kv_head_rows == 0 || a->kv_head_rows >= a->seq_kv),
+                "attention: head strides shorter than the sequences");
     sfb_attention_args args = *a;
     if (args.scale <= 0.0F) args.scale = 1.0F / sqrtf(static_cast<float>(args.head_dim));
     int backend = args.backend;
@@ -340,6 +342,8 @@ sfb_status sfb_k_attention_prefill(const sfb_attention_args* a, sfb_stream strea
             return fail(SFB_UNSUPPORTED, "attention: shape not supported by the tcgen05 kernel");
         return attention_prefill_tcgen05(args, as_stream(stream));
     }
+    if ((args.q_head_rows > 0 && args.q_head_rows != args.seq_q) || (args.kv_head_rows > 0 && args.kv_head_rows != args.seq_kv))
+        return fail(SFB_UNSUPPORTED, "attention: slices of longer sequences need the tcgen05 kernel");
     if (args.head_dim_value > 32 * kMaxChunks || args.head_dim > 512)
         return fail(SFB_UNSUPPORTED, "attention: head_dim_value > 256 is not supported");
     PrefillParams p{args.q, args.key, args.value, args.out, args.batch, args.q_heads, args.kv_heads,

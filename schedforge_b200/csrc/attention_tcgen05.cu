@@ -46,6 +46,7 @@ constexpr float kRescaleThreshold = 8.0F;  // log2 units
 struct FaParams {
     bf16* out;
     int batch, q_heads, kv_heads, seq_q, seq_kv;
+    int q_head_rows, kv_head_rows;  // rows between two heads in memory (>= seq_q / seq_kv for a slice of longer sequences)
     int causal, token_major;
     float scale_log2;  // scale * log2(e)
     uint32_t* status;
@@ -101,8 +102,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
         n_tiles[t] = (limit + KT - 1) / KT;
     }
     const int n_max = max(n_tiles[0], n_tiles[1]);
-    const int q_row0 = (b * p.q_heads + head) * p.seq_q + q0;   // row in the [B*Hq*Sq, D] view
-    const int kv_row0 = (b * p.kv_heads + kvh) * p.seq_kv;      // row in the [B*Hkv*Sk, D] view
+    const int q_row0 = (b * p.q_heads + head) * p.q_head_rows + q0;   // row in the [B*Hq*rows, D] view
+    const int kv_row0 = (b * p.kv_heads + kvh) * p.kv_head_rows;      // row in the [B*Hkv*rows, D] view
 
     if (threadIdx.x == 0) {
         for (int t = 0; t < 2; ++t) {
@@ -370,8 +371,11 @@ sfb_status attention_prefill_tcgen05(const sfb_attention_args& a, cudaStream_t s
         configured = true;
     }
     CUtensorMap map_q, map_k, map_v;
-    const uint64_t q_rows = static_cast<uint64_t>(a.batch) * a.q_heads * a.seq_q;
-    const uint64_t kv_rows = static_cast<uint64_t>(a.batch) * a.kv_heads * a.seq_kv;
+    const int q_head_rows = a.q_head_rows > 0 ? a.q_head_rows : a.seq_q;
+    const int kv_head_rows = a.kv_head_rows > 0 ? a.kv_head_rows : a.seq_kv;
+    // (a slice that starts inside the stored sequence ends before the last head's rows do)
+    const uint64_t q_rows = static_cast<uint64_t>(a.batch) * a.q_heads * q_head_rows - (q_head_rows - a.seq_q);
+    const uint64_t kv_rows = static_cast<uint64_t>(a.batch) * a.kv_heads * kv_head_rows - (kv_head_rows - a.seq_kv);
     if (!encode_tensor_map_bf16_2d(&map_q, a.q, q_rows, D, QT, 64) ||
         !encode_tensor_map_bf16_2d(&map_k, a.key, kv_rows, D, KT, 64) ||
         !encode_tensor_map_bf16_2d(&map_v, a.value, kv_rows, D, KT, 64))
@@ -379,6 +383,7 @@ sfb_status attention_prefill_tcgen05(const sfb_attention_args& a, cudaStream_t s
     FaParams p{};
     p.out = static_cast<bf16*>(a.out);
     p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv;
+    p.q_head_rows = q_head_rows; p.kv_head_rows = kv_head_rows;
     p.causal = a.causal; p.token_major = a.token_major;
     p.scale_log2 = a.scale * 1.4426950408889634F;
     p.status = device_status_word();

@@ -93,6 +93,7 @@ struct SimtParams {
     int batch, seq, q_heads, kv_heads, head_dim;
     const int* group_offsets;
     int groups;
+    int rope_row_offset;
 };
 
 __device__ __forceinline__ void store_out(const SimtParams& p, size_t index, float v) {
@@ -117,7 +118,8 @@ __device__ __forceinline__ void apply_epilogue(const SimtParams& p, int row, int
             break;
         case SFB_EPI_ROPE_SPLIT: {
             const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
-            const int b = row / p.seq, t = row % p.seq;
+            const int token = row + p.rope_row_offset;
+            const int b = token / p.seq, t = token % p.seq;
             bf16* dst;
             int heads, local;
             bool rotate = true;
@@ -214,7 +216,8 @@ sfb_status validate_gemm(const sfb_gemm_args& g) {
             break;
         case SFB_EPI_ROPE_SPLIT:
             SFB_REQUIRE(g.q && g.key && g.value && g.rope_cos && g.rope_sin, "gemm: RoPE epilogue needs q/key/value and tables");
-            SFB_REQUIRE(g.batch > 0 && g.seq > 0 && g.batch * g.seq == g.m && g.head_dim % 2 == 0 &&
+            SFB_REQUIRE(g.batch > 0 && g.seq > 0 && g.rope_row_offset >= 0 &&
+                            g.rope_row_offset + g.m <= g.batch * g.seq && g.head_dim % 2 == 0 &&
                         g.n == (g.q_heads + 2 * g.kv_heads) * g.head_dim,
                         "gemm: RoPE epilogue shape mismatch");
             SFB_REQUIRE(!g.group_offsets, "gemm: RoPE epilogue is not available in grouped mode");
@@ -303,7 +306,7 @@ sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream) {
                  static_cast<const bf16*>(args->residual), args->swiglu_block,
                  static_cast<bf16*>(args->q), static_cast<bf16*>(args->key), static_cast<bf16*>(args->value),
                  args->rope_cos, args->rope_sin, args->batch, args->seq, args->q_heads, args->kv_heads,
-                 args->head_dim, args->group_offsets, args->groups};
+                 args->head_dim, args->group_offsets, args->groups, args->rope_row_offset};
     dim3 grid(ceil_div((args->n + 1) / 2, 16), ceil_div(args->m, 16), args->group_offsets ? args->groups : 1);
     gemm_bf16_simt_kernel<<<grid, 256, 0, as_stream(stream)>>>(p);
     return check_launch("gemm_bf16_simt");

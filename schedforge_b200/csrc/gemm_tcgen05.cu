@@ -67,7 +67,7 @@ struct TcParams {
     const bf16* residual;
     bf16 *q, *key, *value;
     const float *rope_cos, *rope_sin;
-    int seq, q_heads, kv_heads, head_dim;
+    int seq, q_heads, kv_heads, head_dim, rope_row_offset;
     const int* tile_table;  // grouped: [0] = number of M-tiles, entries from [4]
     int dense_m_tiles;
     int n_tiles;
@@ -258,7 +258,8 @@ __device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float
     if (col >= p.n) return;
     if (p.epilogue == SFB_EPI_ROPE_SPLIT) {  // head_dim % 32 == 0: the 8 columns lie in one head
         const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
-        const int b = row / p.seq, t = row - b * p.seq;
+        const int token = row + p.rope_row_offset;
+        const int b = token / p.seq, t = token - b * p.seq;
         bf16* dst;
         int heads, local;
         bool rotate = true;
@@ -697,6 +698,7 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     p.rope_cos = g.rope_cos;
     p.rope_sin = g.rope_sin;
     p.seq = g.seq; p.q_heads = g.q_heads; p.kv_heads = g.kv_heads; p.head_dim = g.head_dim;
+    p.rope_row_offset = g.rope_row_offset;
     p.n_tiles = ceil_div(g.n, BN);
     p.b_tiled = g.bt_tiled;
     p.peer_count = g.peer_count;

@@ -121,7 +121,8 @@ struct DecoderExecutablePlan::Impl {
     int *block_table = nullptr, *context_len = nullptr;
     void *kc = nullptr, *vc = nullptr;         // contiguous cached K/V (decode with sequence > 1)
     cudaEvent_t events[16] = {};
-    int pipeline_chunks = 1;
+    int pipeline_chunks = 1;      // host copies overlap compute in this many row chunks (1 = off)
+    std::vector<std::pair<int, int>> pipeline_ranges;  // (first row, rows) of every chunk: whole sequences or part of one
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
@@ -498,16 +499,37 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     if (bf && fused && !moe && !m.decode && c.batch >= 2 && opt.no_pipeline == 0) {
         m.pipeline_chunks = c.batch;
         while (m.pipeline_chunks > 8 || c.batch % m.pipeline_chunks != 0) --m.pipeline_chunks;
+        const int per_chunk = c.batch / m.pipeline_chunks * c.sequence;
+        for (int i = 0; i < m.pipeline_chunks; ++i) m.pipeline_ranges.push_back({i * per_chunk, per_chunk});
+        // Nothing overlaps the first upload and the last download, so the first and the last chunk
+        // are cut short: 512 rows at the head of the first sequence and at the tail of the last one.
+        // Causal attention of rows [r0, r1) of a sequence needs its keys [0, r1), which the chunks
+        // before have produced; only the tensor-core attention kernel takes such slices.
+        const int edge = 512;
+        if (c.causal && D == 128 && per_chunk == c.sequence && c.sequence >= 2 * edge && c.sequence % 256 == 0 &&
+            plan->policy.attention_backend != 1) {
+            std::vector<std::pair<int, int>> ranges;
+            ranges.push_back({0, edge});
+            ranges.push_back({edge, c.sequence - edge});
+            for (int i = 1; i + 1 < m.pipeline_chunks; ++i) ranges.push_back(m.pipeline_ranges[i]);
+            const int last = (m.pipeline_chunks - 1) * c.sequence;
+            ranges.push_back({last, c.sequence - edge});
+            ranges.push_back({last + c.sequence - edge, edge});
+            m.pipeline_ranges = ranges;
+            m.pipeline_chunks = static_cast<int>(ranges.size());
+        }
     }
-    m.direct_f32_output = bf && fused && !moe && m.size == 1;
     const bool piped = m.pipeline_chunks > 1;  // host copies overlap compute: I/O staging must not alias anything
     wp.add("input_f32", TH * 4, 0, (bf && !piped) ? 0 : 13);
     if (bf) wp.add("input", TH * e, 0, 13);
     wp.add("normalized1", TH * e, 1, 2);
     if (!fused) wp.add("fused_qkv", static_cast<std::size_t>(T) * m.qkv_l * e, 2, 3);
     wp.add("query", static_cast<std::size_t>(T) * m.hidden_l * e, 2, 4);
-    wp.add("key", static_cast<std::size_t>(T) * m.kvw_l * e, 2, 4);
-    wp.add("value", static_cast<std::size_t>(T) * m.kvw_l * e, 2, 4);
+    // chunks that are part of a sequence attend to the keys and values of the chunks before them
+    bool sliced = false;
+    for (const auto& range : m.pipeline_ranges) sliced = sliced || range.second < c.sequence;
+    wp.add("key", static_cast<std::size_t>(T) * m.kvw_l * e, 2, sliced ? 13 : 4);
+    wp.add("value", static_cast<std::size_t>(T) * m.kvw_l * e, 2, sliced ? 13 : 4);
     if (m.paged)
         wp.add("decode_partials", sfb_attention_decode_workspace(c.batch, m.hq, D, m.splits), 4, 4);
     wp.add("attention", static_cast<std::size_t>(T) * m.hidden_l * e, 4, 5);
@@ -832,30 +854,30 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     if (!input || !output) throw std::invalid_argument("decoder input or output is null");
     const DecoderConfig& c = config;
     cudaStream_t s = stream_;
-    const int chunks = m.pipeline_chunks, nb = c.batch / chunks, rows = nb * c.sequence;
+    const int chunks = m.pipeline_chunks, S = c.sequence;
+    int rows = 0;  // rows of the chunk at hand
     const int H = m.H, I = m.I_l, D = m.D;
     const std::size_t row_f32 = static_cast<std::size_t>(H) * 4, row_bf = static_cast<std::size_t>(H) * 2;
     auto at = [](void* base, std::size_t bytes) { return static_cast<void*>(static_cast<char*>(base) + bytes); };
     const bool peer = m.size > 1 && m.peer_local != nullptr;
-    auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int b0,
+    auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int g0,
                     bool f32_out = false, int peer_set = -1) {
         sfb_gemm_args g{};
         g.a = a; g.bt = w; g.out = out; g.m = rows; g.n = n; g.k = k; g.epilogue = epi;
         g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb; g.out_f32 = f32_out ? 1 : 0;
         if (epi == SFB_EPI_ROPE_SPLIT) {
-            g.q = at(m.ws("query"), static_cast<std::size_t>(b0) * m.hq * c.sequence * D * 2);
-            g.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
-            g.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
+            g.q = m.ws("query"); g.key = m.ws("key"); g.value = m.ws("value");  // the full tensors: row g0 + r is token (b, t)
             g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
-            g.batch = nb; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
+            g.batch = c.batch; g.seq = S; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
+            g.rope_row_offset = g0;
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
-        if (peer_set >= 0) m.fill_peer_out(g, peer_set, static_cast<std::size_t>(b0) * c.sequence * H);
+        if (peer_set >= 0) m.fill_peer_out(g, peer_set, static_cast<std::size_t>(g0) * H);
         throw_on(sfb_k_gemm_bf16(&g, s));
     };
     // sum over the ranks of `rows` x H partial sums: fused peer form, or the caller's hook
-    auto reduce = [&](int peer_set, void* buffer, int b0) {
-        if (peer) throw_on(m.peer_finish(peer_set, buffer, static_cast<std::size_t>(b0) * c.sequence * H,
+    auto reduce = [&](int peer_set, void* buffer, int g0) {
+        if (peer) throw_on(m.peer_finish(peer_set, buffer, static_cast<std::size_t>(g0) * H,
                                          static_cast<int64_t>(rows) * H, s));
         else if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, buffer, static_cast<int64_t>(rows) * H, m.dtype, s);
     };
@@ -865,8 +887,12 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     const bool add_residual_here = m.rank == 0;
     for (int ch = 0; ch < chunks; ++ch) {
         cudaEvent_t* ev = &m.chunk_events[static_cast<std::size_t>(ch) * 7];
-        const int b0 = ch * nb;
-        const std::size_t r0 = static_cast<std::size_t>(b0) * c.sequence;
+        const int g0 = m.pipeline_ranges[ch].first;      // first row of the chunk in the [T, H] input
+        rows = m.pipeline_ranges[ch].second;
+        const bool slices = rows < S;                    // the chunk is part of one sequence
+        const int nb = slices ? 1 : rows / S;
+        const int b0 = g0 / S, t0_in_sequence = g0 % S;  // its sequence and position inside it
+        const std::size_t r0 = static_cast<std::size_t>(g0);
         cuda_check(cudaMemcpyAsync(at(m.ws("input_f32"), r0 * row_f32), input + r0 * H, rows * row_f32,
                                    cudaMemcpyHostToDevice, m.copy_in), "input upload");
         cuda_check(cudaEventRecord(ev[0], m.copy_in), "event");
@@ -882,29 +908,32 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         cuda_check(cudaEventRecord(ev[2], s), "event");
         throw_on(sfb_k_convert(at(m.ws("input_f32"), r0 * row_f32), SFB_F32, x, SFB_BF16, static_cast<int64_t>(rows) * H, s));
         throw_on(sfb_k_rms_norm(x, m.rms1, n1, rows, H, c.rms_epsilon, SFB_BF16, s));
-        gemm(n1, m.wqkv, nullptr, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, b0);
+        gemm(n1, m.wqkv, nullptr, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, g0);
         cuda_check(cudaEventRecord(ev[3], s), "event");
         sfb_attention_args a{};
-        a.q = at(m.ws("query"), static_cast<std::size_t>(b0) * m.hq * c.sequence * D * 2);
-        a.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
-        a.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * c.sequence * D * 2);
+        a.q = at(m.ws("query"), (static_cast<std::size_t>(b0) * m.hq * S + t0_in_sequence) * D * 2);
+        a.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * S * D * 2);
+        a.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * S * D * 2);
         a.out = attn;
-        a.batch = nb; a.q_heads = m.hq; a.kv_heads = m.hkv; a.seq_q = c.sequence; a.seq_kv = c.sequence;
+        a.batch = nb; a.q_heads = m.hq; a.kv_heads = m.hkv;
+        a.seq_q = slices ? rows : S;
+        a.seq_kv = slices ? t0_in_sequence + rows : S;  // rows [r0, r1) of a sequence attend to its keys [0, r1)
+        if (slices) { a.q_head_rows = S; a.kv_head_rows = S; }
         a.head_dim = D; a.head_dim_value = D; a.causal = c.causal; a.scale = 0.0F; a.token_major = 1;
         a.dtype = SFB_BF16; a.backend = policy.attention_backend;
         throw_on(sfb_k_attention_prefill(&a, s));
         cuda_check(cudaEventRecord(ev[4], s), "event");
-        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, b0, false, peer ? 0 : -1);
-        reduce(0, r1, b0);
+        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, g0, false, peer ? 0 : -1);
+        reduce(0, r1, g0);
         throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
         cuda_check(cudaEventRecord(ev[5], s), "event");
-        gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, b0);
+        gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, g0);
         if (m.direct_f32_output) {
-            gemm(act, m.wd, out32, H, I, SFB_EPI_RESIDUAL, r1, 0, b0, true);
+            gemm(act, m.wd, out32, H, I, SFB_EPI_RESIDUAL, r1, 0, g0, true);
             cuda_check(cudaEventRecord(ev[6], s), "event");
         } else {
-            gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, b0, false, peer ? 1 : -1);
-            reduce(1, out, b0);
+            gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, g0, false, peer ? 1 : -1);
+            reduce(1, out, g0);
             cuda_check(cudaEventRecord(ev[6], s), "event");
             throw_on(sfb_k_convert(out, SFB_BF16, out32, SFB_F32, static_cast<int64_t>(rows) * H, s));
         }

@@ -28,14 +28,15 @@ class GemmArgs(C.Structure):
                 ("head_dim", C.c_int),
                 ("group_offsets", vp), ("groups", C.c_int), ("tile_table", vp),
                 ("split_workspace", vp), ("split_workspace_bytes", C.c_size_t), ("bt_tiled", C.c_int),
-                ("peer_out", vp * 7), ("peer_count", C.c_int)]
+                ("peer_out", vp * 7), ("peer_count", C.c_int), ("rope_row_offset", C.c_int)]
 
 
 class AttentionArgs(C.Structure):
     _fields_ = [("q", vp), ("key", vp), ("value", vp), ("out", vp)] + \
                [(n, C.c_int) for n in ("batch", "q_heads", "kv_heads", "seq_q", "seq_kv", "head_dim",
                                        "head_dim_value", "causal")] + \
-               [("scale", C.c_float), ("token_major", C.c_int), ("dtype", C.c_int), ("backend", C.c_int)]
+               [("scale", C.c_float), ("token_major", C.c_int), ("dtype", C.c_int), ("backend", C.c_int),
+                ("q_head_rows", C.c_int), ("kv_head_rows", C.c_int)]
 
 
 class DecodeArgs(C.Structure):

@@ -29,7 +29,7 @@ DECODER_CASES = {
                          moe=True, experts=4, top_k=2), 83),
     "decoder_decode": (dict(batch=1, sequence=1, hidden=16, intermediate=32, query_heads=4, kv_heads=2, head_dim=4,
                             context_sequence=16), 87),
-    # BASELINE configs[0] shape with the reference's generator
+    # the tiny fp32 benchmark shape with the reference's generator
     "decoder_cfg1_shape": (dict(batch=1, sequence=128, hidden=256, intermediate=688, query_heads=4, kv_heads=2,
                                 head_dim=64), 0),
     "decoder_batched": (dict(batch=2, sequence=24, hidden=64, intermediate=96, query_heads=4, kv_heads=2, head_dim=16), 5),

@@ -53,4 +53,4 @@ def test_struct_layouts_match_header(sfb):
     assert C.sizeof(sfb.MoeConfig) == 5 * 4
     assert C.sizeof(sfb.GraphSummary) == 7 * 4
     assert C.sizeof(sfb.DecoderResult) == 9 * 8 + 8
-    assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.peer_count.offset == C.sizeof(sfb.GemmArgs) - 8
+    assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.rope_row_offset.offset == C.sizeof(sfb.GemmArgs) - 4

@@ -260,3 +260,36 @@ def test_prefill_tcgen05_baseline_config2_slices(dev, port):
                                             kk[None, None, :row + 1], vv[None, None, :row + 1])[0, 0, 0]
             got = out[b, h, row].float().cpu().numpy()
             assert np.max(np.abs(got - want)) < 2e-2 * max(np.max(np.abs(want)), 0.05), (b, h, int(row))
+
+
+def test_prefill_tcgen05_row_slices_equal_the_whole_sequence(dev, port):
+    """A causal prefill run as row chunks (queries [r0, r1) against keys [0, r1), head strides of
+    the whole sequence) must give exactly the rows of the one-shot run: this is what the pipelined
+    plan execute relies on."""
+    torch = dev.torch
+    hq, hkv, s, chunk = 4, 2, 1024, 256
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn((1, hq, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    k = torch.randn((1, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn((1, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    whole = torch.zeros((s, hq * 128), dtype=torch.bfloat16, device="cuda")   # token-major
+    sliced = torch.zeros_like(whole)
+    lib = L.load()
+    a = L.AttentionArgs(q.data_ptr(), k.data_ptr(), v.data_ptr(), whole.data_ptr(), 1, hq, hkv, s, s, 128, 128, 1, 0.0, 1,
+                        L.BF16, 2)
+    L.check(lib.sfb_k_attention_prefill(C.byref(a), C.c_void_p(dev.stream())))
+    for r0 in range(0, s, chunk):
+        a = L.AttentionArgs(q.data_ptr() + r0 * 128 * 2, k.data_ptr(), v.data_ptr(), sliced.data_ptr() + r0 * hq * 128 * 2,
+                            1, hq, hkv, chunk, r0 + chunk, 128, 128, 1, 0.0, 1, L.BF16, 2, s, s)
+        L.check(lib.sfb_k_attention_prefill(C.byref(a), C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    assert torch.equal(whole, sliced)
+    oc = ob.AttentionConfig(1, hq, hkv, s, s, 128, 128, 1, 0.0)
+    want = port.attention_reference(oc, q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy())
+    got = whole.float().cpu().numpy().reshape(1, s, hq, 128).transpose(0, 2, 1, 3)
+    assert rel_err(got, want) < 2e-2
+    # the CUDA-core kernel does not take slices and says so
+    a = L.AttentionArgs(q.data_ptr(), k.data_ptr(), v.data_ptr(), sliced.data_ptr(), 1, hq, hkv, chunk, chunk, 128, 128, 1,
+                        0.0, 1, L.BF16, 1, s, s)
+    with pytest.raises(L.SfbError):
+        L.check(lib.sfb_k_attention_prefill(C.byref(a), C.c_void_p(dev.stream())))

@@ -181,7 +181,9 @@ def test_tensor_parallel_shards_reproduce_the_full_layer(port, shards, decode):
     lib = L.load()
     rows = kw["batch"] * kw["sequence"]
     count = rows * kw["hidden"]
-    plans = [api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(tp_rank=r, tp_size=shards))
+    # (one-shot execute: the hook then sees the whole [T, H] partial sums in one call)
+    plans = [api.DecoderCompiler.compile(c, weights_of(data), "",
+                                         api.compile_options(tp_rank=r, tp_size=shards, no_pipeline=True))
              for r in range(shards)]
     first = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(shards)]
     second = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(shards)]
@@ -284,3 +286,20 @@ def test_plan_optimizer_measures_ranks_and_confirms(port):
     out, _ = plan.execute(data["input"])
     assert rel_err(out, port.decoder_layer(oc, data, native=True)) < BF16_TOL
     plan.close()
+
+
+def test_pipelined_execute_in_row_chunks_equals_the_one_shot_plan(port):
+    """Two sequences of 1024 tokens, head_dim 128: sfb_decoder_execute overlaps its host copies with compute in
+    four chunks of 512 rows (half sequences; attention runs on row slices).  Same numbers as the one-shot form."""
+    kw = dict(batch=2, sequence=1024, hidden=512, intermediate=1024, query_heads=4, kv_heads=2, head_dim=128,
+              rope_theta=500000.0)
+    oc, c, data = bf16_case(port, 41, **kw)
+    piped = api.DecoderCompiler.compile(c, weights_of(data))
+    one_shot = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(no_pipeline=True))
+    out_piped, _ = piped.execute(data["input"])
+    out_one, _ = one_shot.execute(data["input"])
+    assert np.array_equal(out_piped, out_one)
+    assert rel_err(out_piped, port.decoder_layer(oc, data, native=True)) < BF16_TOL
+    assert np.array_equal(piped.execute(data["input"])[0], out_piped)  # and again on the used workspace
+    piped.close()
+    one_shot.close()
