@@ -254,7 +254,7 @@ __device__ __forceinline__ void add_bf16x8(const bf16* src, float (&f)[8], int v
 }
 
 // Epilogue of output columns [col, col + 8) of `row` (not SwiGLU); col is a multiple of 8.
-__device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float (&f)[8]) {
+__device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float (&f)[8], bool residual_added = false) {
     if (col >= p.n) return;
     if (p.epilogue == SFB_EPI_ROPE_SPLIT) {  // head_dim % 32 == 0: the 8 columns lie in one head
         const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
@@ -284,7 +284,7 @@ __device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float
     }
     const size_t index = static_cast<size_t>(row) * p.n + col;
     const int valid = p.n - col;
-    if (p.epilogue == SFB_EPI_RESIDUAL) add_bf16x8(p.residual + index, f, valid);
+    if (p.epilogue == SFB_EPI_RESIDUAL && !residual_added) add_bf16x8(p.residual + index, f, valid);
     store8(p.out, p.out_f32, index, f, valid);
     for (int i = 0; i < p.peer_count; ++i) store8(p.peer_out[i], 0, index, f, valid);  // peer stores over NVLink
 }
@@ -293,15 +293,38 @@ __device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float
 // [row0, row0 + 32); `plain` = they are final (SwiGLU) and only need storing into [m, width].
 __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stage, int lane, int row0, int row_end,
                                             int col0, bool plain, int width) {
-#pragma unroll 2
+    // The residual rows come from DRAM: all four loads of this lane go out before the first is used
+    // (one at a time, they made the epilogue of a tile as long as its main loop).
+    const bool prefetch = !plain && p.epilogue == SFB_EPI_RESIDUAL && (p.n & 7) == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
+    uint4 residual[4];
+    if (prefetch) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = row0 + i * 8 + (lane >> 2), col = col0 + (lane & 3) * 8;
+            residual[i] = (row < row_end && col < width)
+                ? __ldg(reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(row) * p.n + col))
+                : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+#pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int r = i * 8 + (lane >> 2), first = (lane & 3) * 8;
         const int row = row0 + r, col = col0 + first;
         if (row >= row_end || col >= width) continue;
         float f[8];
         stage_read8(stage, r, first, f);
+        if (prefetch) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&residual[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(h[j]);
+                f[2 * j] += x.x;
+                f[2 * j + 1] += x.y;
+            }
+        }
         if (plain) store8(p.out, p.out_f32, static_cast<size_t>(row) * width + col, f, width - col);
-        else emit8(p, row, col, f);
+        else emit8(p, row, col, f, prefetch);
     }
 }
 

@@ -959,14 +959,6 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         result->attention_milliseconds += span(ev[3], ev[4]);
         result->ffn_milliseconds += span(ev[5], ev[6]);
     }
-    if (getenv("SFB_PIPELINE_TRACE")) {
-        for (int ch = 0; ch < chunks; ++ch) {
-            cudaEvent_t* ev = &m.chunk_events[static_cast<std::size_t>(ch) * 7];
-            fprintf(stderr, "chunk %d: upload done %.3f, start %.3f, qkv %.3f, attn %.3f, o+norm %.3f, ffn %.3f, end %.3f\n", ch,
-                    span(t0, ev[0]), span(t0, ev[2]), span(t0, ev[3]), span(t0, ev[4]), span(t0, ev[5]), span(t0, ev[6]), span(t0, ev[1]));
-        }
-        fprintf(stderr, "all done %.3f\n", span(t0, t1));
-    }
     result->h2d_milliseconds = span(t0, m.chunk_events[0]);                       // exposed part: first chunk
     result->d2h_milliseconds = span(m.chunk_events[static_cast<std::size_t>(chunks - 1) * 7 + 1], t1);  // last chunk
     result->milliseconds = span(t0, t1);
