@@ -4,6 +4,8 @@
 // accumulates each logit as a sequential float sum (multiply rounded, add rounded,
 // features ascending), and the dispatch ranks every assignment by counting earlier
 // assignments to the same expert instead of racing on atomics.
+#include <algorithm>
+
 #include "common.cuh"
 
 #include <mutex>
@@ -16,33 +18,13 @@ constexpr int kMaxTopK = 8;
 constexpr int kFeatureChunk = 128;
 constexpr int kChunk = 1024;  // assignments per dispatch block
 
-// blockDim = tokens_per_block * experts.  Thread (t, e) owns logit[t][e].
-template <class T>
-__global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
-                                 const float* __restrict__ bias, int tokens, int hidden, int experts,
-                                 int top_k, int tokens_per_block, int* __restrict__ expert_ids,
-                                 float* __restrict__ expert_weights, int* __restrict__ counts) {
-    extern __shared__ float smem[];
-    float* xs = smem;                                              // [tpb][chunk+1]
-    float* ws = xs + tokens_per_block * (kFeatureChunk + 1);       // [chunk][E]
-    float* logits = ws + kFeatureChunk * experts;                  // [tpb][E]
-    const int e = threadIdx.x % experts, tl = threadIdx.x / experts;
-    const int token0 = blockIdx.x * tokens_per_block;
-    float acc = 0.0F;
-    for (int f0 = 0; f0 < hidden; f0 += kFeatureChunk) {
-        const int fn = min(kFeatureChunk, hidden - f0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < tokens_per_block * kFeatureChunk; i += blockDim.x) {
-            const int t = i / kFeatureChunk, f = i % kFeatureChunk;
-            xs[t * (kFeatureChunk + 1) + f] = (token0 + t < tokens && f < fn)
-                ? to_float(x[static_cast<size_t>(token0 + t) * hidden + f0 + f]) : 0.0F;
-        }
-        for (int i = threadIdx.x; i < fn * experts; i += blockDim.x)
-            ws[i] = router[static_cast<size_t>(f0) * experts + i];
-        __syncthreads();
-        const float* xrow = xs + tl * (kFeatureChunk + 1);
-        for (int f = 0; f < fn; ++f) acc = __fadd_rn(acc, __fmul_rn(xrow[f], ws[f * experts + e]));
-    }
+// Second half of the router for thread (tl, e) that holds logit `acc`: bias, softmax over the experts,
+// top-k (descending logit, ties to the lower id), renormalised weights, histogram.
+template <class Dummy = void>
+__device__ __forceinline__ void route_finish(float acc, float* logits, const float* __restrict__ bias, int tokens,
+                                             int experts, int top_k, int token0, int tl, int e,
+                                             int* __restrict__ expert_ids, float* __restrict__ expert_weights,
+                                             int* __restrict__ counts) {
     if (bias) acc = __fadd_rn(acc, bias[e]);
     logits[tl * experts + e] = acc;
     __syncthreads();
@@ -74,6 +56,135 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
         expert_weights[static_cast<size_t>(token) * top_k + s] = __fdiv_rn(__fdiv_rn(expf(l[id] - mx), den), selected);
         atomicAdd(&counts[id], 1);  // integer histogram: order-independent
     }
+}
+
+// blockDim = tokens_per_block * experts.  Thread (t, e) owns logit[t][e].
+// The features are walked in chunks of 128 through shared memory.  A logit is a serial chain of
+// 4096 rounded additions by definition (the oracle's order), so everything else must stay off that
+// path: the next chunk's activations and router columns are fetched into registers (16-byte
+// loads) before the current chunk is summed and parked in shared memory afterwards.
+template <class T>
+__global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                                 const float* __restrict__ bias, int tokens, int hidden, int experts,
+                                 int top_k, int tokens_per_block, int* __restrict__ expert_ids,
+                                 float* __restrict__ expert_weights, int* __restrict__ counts) {
+    extern __shared__ float smem[];
+    float* xs = smem;                                              // [tpb][chunk+1]
+    float* ws = xs + tokens_per_block * (kFeatureChunk + 1);       // [chunk][E]
+    float* logits = ws + kFeatureChunk * experts;                  // [tpb][E]
+    const int e = threadIdx.x % experts, tl = threadIdx.x / experts;
+    const int token0 = blockIdx.x * tokens_per_block;
+    constexpr int kGroupsMax = 4;  // groups of 8 features per thread and chunk (host picks the block size accordingly)
+    const int x_groups = tokens_per_block * (kFeatureChunk / 8);   // 8 features each
+    const int w_groups = kFeatureChunk * experts / 4;              // 4 floats each
+    const bool vector_x = (hidden % 8 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+    const bool vector_w = (experts % 4 == 0) && (reinterpret_cast<uintptr_t>(router) % 16 == 0);
+    float xr[kGroupsMax][8];
+    float4 wr[kGroupsMax];
+    auto fetch = [&](int f0) {
+        const int fn = min(kFeatureChunk, hidden - f0);
+#pragma unroll
+        for (int k = 0; k < kGroupsMax; ++k) {
+            const int g = threadIdx.x + k * blockDim.x;
+            if (g < x_groups) {
+                const int t = g / (kFeatureChunk / 8), f = (g % (kFeatureChunk / 8)) * 8;
+                const bool row_ok = token0 + t < tokens;
+                const T* src = x + static_cast<size_t>(token0 + t) * hidden + f0 + f;
+                if (row_ok && vector_x && f + 8 <= fn) {
+                    if constexpr (sizeof(T) == 2) {
+                        const uint4 packed = *reinterpret_cast<const uint4*>(src);
+                        const bf16* v = reinterpret_cast<const bf16*>(&packed);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) xr[k][j] = to_float(v[j]);
+                    } else {
+                        const float4 lo = reinterpret_cast<const float4*>(src)[0], hi = reinterpret_cast<const float4*>(src)[1];
+                        xr[k][0] = lo.x; xr[k][1] = lo.y; xr[k][2] = lo.z; xr[k][3] = lo.w;
+                        xr[k][4] = hi.x; xr[k][5] = hi.y; xr[k][6] = hi.z; xr[k][7] = hi.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) xr[k][j] = (row_ok && f + j < fn) ? to_float(src[j]) : 0.0F;
+                }
+            }
+            if (g < w_groups) {
+                const int i = g * 4;
+                const float* src = router + static_cast<size_t>(f0) * experts + i;
+                if (vector_w && i + 4 <= fn * experts) {
+                    wr[k] = *reinterpret_cast<const float4*>(src);
+                } else {
+                    wr[k].x = i < fn * experts ? src[0] : 0.0F;
+                    wr[k].y = i + 1 < fn * experts ? src[1] : 0.0F;
+                    wr[k].z = i + 2 < fn * experts ? src[2] : 0.0F;
+                    wr[k].w = i + 3 < fn * experts ? src[3] : 0.0F;
+                }
+            }
+        }
+    };
+    auto park = [&]() {
+#pragma unroll
+        for (int k = 0; k < kGroupsMax; ++k) {
+            const int g = threadIdx.x + k * blockDim.x;
+            if (g < x_groups) {
+                const int t = g / (kFeatureChunk / 8), f = (g % (kFeatureChunk / 8)) * 8;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xs[t * (kFeatureChunk + 1) + f + j] = xr[k][j];
+            }
+            if (g < w_groups) {
+                float* dst = ws + g * 4;
+                dst[0] = wr[k].x; dst[1] = wr[k].y; dst[2] = wr[k].z; dst[3] = wr[k].w;
+            }
+        }
+    };
+    float acc = 0.0F;
+    fetch(0);
+    for (int f0 = 0; f0 < hidden; f0 += kFeatureChunk) {
+        const int fn = min(kFeatureChunk, hidden - f0);
+        __syncthreads();  // the previous chunk has been consumed
+        park();
+        __syncthreads();
+        if (f0 + kFeatureChunk < hidden) fetch(f0 + kFeatureChunk);  // in flight while this chunk is summed
+        const float* xrow = xs + tl * (kFeatureChunk + 1);
+        int f = 0;
+        for (; f + 8 <= fn; f += 8) {
+            float product[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) product[j] = __fmul_rn(xrow[f + j], ws[(f + j) * experts + e]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, product[j]);
+        }
+        for (; f < fn; ++f) acc = __fadd_rn(acc, __fmul_rn(xrow[f], ws[f * experts + e]));
+    }
+    route_finish(acc, logits, bias, tokens, experts, top_k, token0, tl, e, expert_ids, expert_weights, counts);
+}
+
+// Plain form of the router (any number of experts): the chunk is staged with scalar loads.
+template <class T>
+__global__ void moe_route_simple_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                                 const float* __restrict__ bias, int tokens, int hidden, int experts,
+                                 int top_k, int tokens_per_block, int* __restrict__ expert_ids,
+                                 float* __restrict__ expert_weights, int* __restrict__ counts) {
+    extern __shared__ float smem[];
+    float* xs = smem;                                              // [tpb][chunk+1]
+    float* ws = xs + tokens_per_block * (kFeatureChunk + 1);       // [chunk][E]
+    float* logits = ws + kFeatureChunk * experts;                  // [tpb][E]
+    const int e = threadIdx.x % experts, tl = threadIdx.x / experts;
+    const int token0 = blockIdx.x * tokens_per_block;
+    float acc = 0.0F;
+    for (int f0 = 0; f0 < hidden; f0 += kFeatureChunk) {
+        const int fn = min(kFeatureChunk, hidden - f0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < tokens_per_block * kFeatureChunk; i += blockDim.x) {
+            const int t = i / kFeatureChunk, f = i % kFeatureChunk;
+            xs[t * (kFeatureChunk + 1) + f] = (token0 + t < tokens && f < fn)
+                ? to_float(x[static_cast<size_t>(token0 + t) * hidden + f0 + f]) : 0.0F;
+        }
+        for (int i = threadIdx.x; i < fn * experts; i += blockDim.x)
+            ws[i] = router[static_cast<size_t>(f0) * experts + i];
+        __syncthreads();
+        const float* xrow = xs + tl * (kFeatureChunk + 1);
+        for (int f = 0; f < fn; ++f) acc = __fadd_rn(acc, __fmul_rn(xrow[f], ws[f * experts + e]));
+    }
+    route_finish(acc, logits, bias, tokens, experts, top_k, token0, tl, e, expert_ids, expert_weights, counts);
 }
 
 __global__ void dispatch_histogram_kernel(const int* __restrict__ expert_ids, int assignments, int experts,
@@ -163,6 +274,48 @@ __global__ void dispatch_gather_kernel(const T* __restrict__ x, const int* __res
 
 // One thread per (token, feature): contributions in ascending dispatched position, each
 // `acc = acc + w*y` as a rounded multiply then a rounded add; then residual + acc.
+// bf16, hidden % 8 == 0: one warp per token, a lane owns 8 adjacent features at a time (16-byte loads
+// and stores); the slots are sorted once per token.  Same arithmetic per element as the kernel below.
+__global__ void __launch_bounds__(256)
+moe_combine_rows_kernel(const bf16* __restrict__ y, const int* __restrict__ dest_of,
+                        const float* __restrict__ routing_weights, const bf16* __restrict__ residual,
+                        bf16* __restrict__ out, int tokens, int hidden, int top_k) {
+    const int warps = (gridDim.x * blockDim.x) >> 5, lane = threadIdx.x & 31;
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tokens; t += warps) {
+        int dest[kMaxTopK];
+        float weight[kMaxTopK];
+        for (int s = 0; s < top_k; ++s) dest[s] = dest_of[static_cast<size_t>(t) * top_k + s];
+        for (int a = 1; a < top_k; ++a) {  // insertion sort, top_k <= 8
+            const int v = dest[a];
+            int b = a - 1;
+            while (b >= 0 && dest[b] > v) { dest[b + 1] = dest[b]; --b; }
+            dest[b + 1] = v;
+        }
+        for (int s = 0; s < top_k; ++s) weight[s] = routing_weights[dest[s]];
+        for (int f = lane * 8; f < hidden; f += 256) {
+            float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+            for (int s = 0; s < top_k; ++s) {
+                const uint4 packed = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(dest[s]) * hidden + f);
+                const bf16* v = reinterpret_cast<const bf16*>(&packed);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(weight[s], to_float(v[j])));
+            }
+            uint4 result;
+            bf16* r = reinterpret_cast<bf16*>(&result);
+            if (residual) {
+                const uint4 packed = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * hidden + f);
+                const bf16* v = reinterpret_cast<const bf16*>(&packed);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] = from_float<bf16>(__fadd_rn(to_float(v[j]), acc[j]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] = from_float<bf16>(acc[j]);
+            }
+            *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + f) = result;
+        }
+    }
+}
+
 template <class T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest_of,
                                    const float* __restrict__ routing_weights, const T* __restrict__ residual,
@@ -258,22 +411,30 @@ sfb_status sfb_k_moe_route(const void* x, sfb_dtype x_dtype, const float* router
         return fail(SFB_UNSUPPORTED, "moe_route: experts > 64 or top_k > 8");
     cudaStream_t s = as_stream(stream);
     SFB_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * experts, s));
-    int tpb = 256 / experts;
+    // The prefetching kernel gives every thread at most four 16-byte groups of activations and four of
+    // router weights per chunk, which needs at least 4 experts and 8 tokens per block.
+    const bool fast = experts >= 4;
+    int tpb = fast ? 16 : 256 / experts;
+    while (tpb * experts > 1024 && tpb > 8) tpb /= 2;
     if (tpb < 1) tpb = 1;
-    if (tpb > 32) tpb = 32;
+    if (!fast && tpb > 32) tpb = 32;
     const int block = tpb * experts;
     const int grid = ceil_div(tokens, tpb);
     const size_t smem = sizeof(float) * (static_cast<size_t>(tpb) * (kFeatureChunk + 1) +
                                          static_cast<size_t>(kFeatureChunk) * experts + static_cast<size_t>(tpb) * experts);
-    if (x_dtype == SFB_F32) {
-        if (smem > 48 * 1024) SFB_CUDA(cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        moe_route_kernel<float><<<grid, block, smem, s>>>(static_cast<const float*>(x), router, bias, tokens, hidden,
-                                                          experts, top_k, tpb, expert_ids, expert_weights, counts);
-    } else {
-        if (smem > 48 * 1024) SFB_CUDA(cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        moe_route_kernel<bf16><<<grid, block, smem, s>>>(static_cast<const bf16*>(x), router, bias, tokens, hidden,
-                                                         experts, top_k, tpb, expert_ids, expert_weights, counts);
-    }
+    auto launch = [&](auto kernel, auto* typed_x) -> sfb_status {
+        if (smem > 48 * 1024)
+            SFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        kernel<<<grid, block, smem, s>>>(typed_x, router, bias, tokens, hidden, experts, top_k, tpb, expert_ids,
+                                         expert_weights, counts);
+        return SFB_OK;
+    };
+    if (x_dtype == SFB_F32)
+        SFB_TRY(fast ? launch(moe_route_kernel<float>, static_cast<const float*>(x))
+                     : launch(moe_route_simple_kernel<float>, static_cast<const float*>(x)));
+    else
+        SFB_TRY(fast ? launch(moe_route_kernel<bf16>, static_cast<const bf16*>(x))
+                     : launch(moe_route_simple_kernel<bf16>, static_cast<const bf16*>(x)));
     return check_launch("moe_route");
 }
 
@@ -348,6 +509,11 @@ sfb_status sfb_k_moe_combine(const void* y, const int* dest_of, const float* rou
         moe_combine_kernel<float><<<grid, 256, 0, as_stream(stream)>>>(
             static_cast<const float*>(y), dest_of, routing_weights, static_cast<const float*>(residual),
             static_cast<float*>(out), tokens, hidden, top_k);
+    else if (hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(residual) & 15) == 0)
+        moe_combine_rows_kernel<<<std::min(ceil_div(tokens, 8), sm_count() * 16), 256, 0, as_stream(stream)>>>(
+            static_cast<const bf16*>(y), dest_of, routing_weights, static_cast<const bf16*>(residual),
+            static_cast<bf16*>(out), tokens, hidden, top_k);
     else
         moe_combine_kernel<bf16><<<grid, 256, 0, as_stream(stream)>>>(
             static_cast<const bf16*>(y), dest_of, routing_weights, static_cast<const bf16*>(residual),
