@@ -54,3 +54,15 @@ def test_struct_layouts_match_header(sfb):
     assert C.sizeof(sfb.GraphSummary) == 7 * 4
     assert C.sizeof(sfb.DecoderResult) == 9 * 8 + 8
     assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.rope_row_offset.offset == C.sizeof(sfb.GemmArgs) - 4
+
+
+def test_weight_layout_and_scratch_size_helpers_need_no_device(sfb):
+    """Element count of the 64x64-blocked weight copy and the byte count of the few-row GEMM scratch."""
+    lib = sfb.load()
+    assert lib.sfb_tiled_weight_elems(128, 64) == 2 * 4096
+    assert lib.sfb_tiled_weight_elems(130, 65) == 3 * 2 * 4096     # ragged edges are padded to whole blocks
+    assert lib.sfb_tiled_weight_elems(0, 64) == 0
+    one_tile = 128 * 128 * 4
+    assert lib.sfb_gemm_stream_workspace_bytes(128) == one_tile + 16
+    assert lib.sfb_gemm_stream_workspace_bytes(4096) == 32 * one_tile + 128
+    assert lib.sfb_gemm_stream_workspace_bytes(0) == 0
