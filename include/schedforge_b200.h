@@ -150,6 +150,11 @@ typedef struct sfb_gemm_args {
     /* SFB_EPI_ROPE_SPLIT on a row chunk: row r of A is token (r + rope_row_offset) of the
      * [batch, seq] grid (q/key/value stay the full tensors) */
     int rope_row_offset;
+    /* weight-only INT8 (m <= 128, dense, tcgen05): bt_scales != NULL says that bt holds int8 values in
+     * 64x64 blocks (sfb_k_quantize_weight_int8) and bt_scales one fp32 factor per output column,
+     * padded with anything up to a multiple of 128 entries; y = (x . q^T) * scale, then the epilogue.
+     * Follows quantize_matmul_weights / quantized_invoke, src/next_milestones.cpp:611-637, 50-69. */
+    const float* bt_scales;
 } sfb_gemm_args;
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
@@ -162,6 +167,14 @@ size_t sfb_gemm_stream_workspace_bytes(int n);
  * blocked copy.  src and dst must not overlap.  No counterpart in the reference, whose CPU
  * packing is the plain transpose of pack_transposed (src/decoder_compiler.cpp:57-66). */
 int64_t sfb_tiled_weight_elems(int n, int k);
+/* Per-output-channel symmetric INT8 quantization of a [n,k] bf16 weight (quantize_matmul_weights,
+ * src/next_milestones.cpp:611-637: scale = max|w| / 127 or 1 for an all-zero row, q = round-half-away(w / scale)
+ * clamped to [-127, 127]) written in the blocked layout of sfb_k_tile_weight_bf16 with one byte per
+ * element (sfb_tiled_weight_elems(n, k) bytes); scales: n floats.  sfb_k_dequantize_weight_int8 writes
+ * q * scale back as a [n,k] row-major bf16 weight. */
+sfb_status sfb_k_quantize_weight_int8(const void* bt, void* q_tiled, float* scales, int n, int k, sfb_stream stream);
+sfb_status sfb_k_dequantize_weight_int8(const void* q_tiled, const float* scales, void* bt, int n, int k,
+                                        sfb_stream stream);
 sfb_status sfb_k_tile_weight_bf16(const void* bt, void* tiled, int n, int k, sfb_stream stream);
 
 /* cos/sin tables for interleaved-pair rotary embedding, computed on the HOST with the

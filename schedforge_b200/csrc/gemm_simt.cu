@@ -248,6 +248,56 @@ __global__ void tile_weight_kernel(const bf16* __restrict__ bt, bf16* __restrict
     }
 }
 
+// One block per output row: absolute maximum over k, then the rounded quotients into the blocked layout.
+__global__ void __launch_bounds__(256)
+quantize_weight_int8_kernel(const bf16* __restrict__ bt, int8_t* __restrict__ q, float* __restrict__ scales, int n,
+                            int k) {
+    __shared__ float partial[8];
+    const int row = blockIdx.x;
+    const bf16* src = bt + static_cast<size_t>(row) * k;
+    float maximum = 0.0F;
+    for (int c = threadIdx.x; c < k; c += 256) maximum = fmaxf(maximum, fabsf(to_float(src[c])));
+    maximum = warp_max(maximum);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = maximum;
+    __syncthreads();
+    maximum = partial[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, partial[i]);
+    const float scale = maximum > 0.0F ? __fdiv_rn(maximum, 127.0F) : 1.0F;
+    if (threadIdx.x == 0) scales[row] = scale;
+    const int k_blocks = (k + 63) / 64, k_padded = k_blocks * 64;
+    int8_t* block_row = q + (static_cast<size_t>(row / 64) * k_blocks) * 4096 + (row % 64) * 64;
+    for (int c = threadIdx.x; c < k_padded; c += 256) {
+        float value = 0.0F;
+        if (c < k) value = fminf(fmaxf(roundf(__fdiv_rn(to_float(src[c]), scale)), -127.0F), 127.0F);
+        block_row[static_cast<size_t>(c / 64) * 4096 + (c % 64)] = static_cast<int8_t>(value);
+    }
+}
+
+// rows of the last 64-row block that do not exist
+__global__ void zero_int8_rows_kernel(int8_t* __restrict__ q, int n, int k) {
+    const int k_blocks = (k + 63) / 64, rows = (n + 63) / 64 * 64;
+    const long long total = static_cast<long long>(rows - n) * k_blocks * 64;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = n + static_cast<int>(i / (static_cast<long long>(k_blocks) * 64));
+        const int c = static_cast<int>(i % (static_cast<long long>(k_blocks) * 64));
+        q[(static_cast<size_t>(row / 64) * k_blocks + c / 64) * 4096 + (row % 64) * 64 + (c % 64)] = 0;
+    }
+}
+
+__global__ void dequantize_weight_int8_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                                              bf16* __restrict__ bt, int n, int k) {
+    const int k_blocks = (k + 63) / 64;
+    const long long total = static_cast<long long>(n) * k;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / k), c = static_cast<int>(i % k);
+        const int8_t value = q[(static_cast<size_t>(row / 64) * k_blocks + c / 64) * 4096 + (row % 64) * 64 + (c % 64)];
+        bt[i] = from_float<bf16>(__fmul_rn(static_cast<float>(value), scales[row]));
+    }
+}
+
 }  // namespace
 
 }  // namespace sfb
@@ -287,13 +337,35 @@ sfb_status sfb_k_tile_weight_bf16(const void* bt, void* tiled, int n, int k, sfb
     return check_launch("tile_weight");
 }
 
+sfb_status sfb_k_quantize_weight_int8(const void* bt, void* q_tiled, float* scales, int n, int k, sfb_stream stream) {
+    SFB_REQUIRE(bt && q_tiled && scales && n > 0 && k > 0, "quantize_weight: invalid shape or null operand");
+    cudaStream_t s = as_stream(stream);
+    quantize_weight_int8_kernel<<<n, 256, 0, s>>>(static_cast<const bf16*>(bt), static_cast<int8_t*>(q_tiled), scales, n, k);
+    SFB_TRY(check_launch("quantize_weight_int8"));
+    if (n % 64 != 0) {
+        zero_int8_rows_kernel<<<64, 256, 0, s>>>(static_cast<int8_t*>(q_tiled), n, k);
+        SFB_TRY(check_launch("quantize_weight_int8_pad"));
+    }
+    return SFB_OK;
+}
+
+sfb_status sfb_k_dequantize_weight_int8(const void* q_tiled, const float* scales, void* bt, int n, int k,
+                                        sfb_stream stream) {
+    SFB_REQUIRE(bt && q_tiled && scales && n > 0 && k > 0, "dequantize_weight: invalid shape or null operand");
+    const long long total = static_cast<long long>(n) * k;
+    const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, static_cast<long long>(sm_count()) * 16));
+    dequantize_weight_int8_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const int8_t*>(q_tiled), scales,
+                                                                       static_cast<bf16*>(bt), n, k);
+    return check_launch("dequantize_weight_int8");
+}
+
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream) {
     SFB_REQUIRE(args, "gemm: null arguments");
     SFB_TRY(validate_gemm(*args));
     SFB_REQUIRE(!args->bt_tiled || (!args->group_offsets && args->backend != SFB_GEMM_SIMT),
                 "gemm: the blocked weight layout needs the dense tcgen05 kernel");
     int backend = args->backend;
-    if (args->bt_tiled || args->peer_count != 0) backend = SFB_GEMM_TCGEN05;  // only that kernel knows these
+    if (args->bt_tiled || args->peer_count != 0 || args->bt_scales) backend = SFB_GEMM_TCGEN05;  // only that kernel knows these
     if (backend == SFB_GEMM_AUTO)
         backend = gemm_bf16_tcgen05_supported(*args) ? SFB_GEMM_TCGEN05 : SFB_GEMM_SIMT;
     if (backend == SFB_GEMM_TCGEN05) {

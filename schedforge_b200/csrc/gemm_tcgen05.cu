@@ -73,6 +73,7 @@ struct TcParams {
     int n_tiles;
     int b_tiled;            // weight stored as 64x64 blocks, 8 KB contiguous each
     // equal K-block ranges per CTA (one M-tile only): fp32 [n_tiles][BM][BN] sums + one counter per tile
+    const float* col_scale;             // weight-only INT8: one factor per output column, applied before the epilogue
     bf16* peer_out[SFB_MAX_PEERS - 1];  // copies of the output in other GPUs' memory (fused all-reduce)
     int peer_count;
     float* accum;
@@ -328,6 +329,111 @@ __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stag
     }
 }
 
+// Epilogue of one work item for an epilogue thread: `acc` is the tensor-memory address of the
+// accumulator (lane quarter and buffer included), `tmem_empty_bar` the barrier that hands it back.
+template <int BN, bool SCALED>
+__device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segment& sg, const TileCoord& c, int k_blocks,
+                                                 uint32_t acc, uint32_t tmem_empty_bar, float* stage,
+                                                 volatile uint32_t* last_flag, int quarter, int pass, int lane,
+                                                 bool leader) {
+    constexpr uint32_t kEpilogueThreads = 32 * kEpilogueWarps;
+    const int row_in_tile = quarter * 32 + lane;
+    const int row0 = c.row_start + quarter * 32;
+    const bool row_ok = row0 + lane < c.row_end;
+    const bool swiglu = p.epilogue == SFB_EPI_SWIGLU;
+    // An output chunk is 32 columns: one 32-column group of the accumulator, or for SwiGLU
+    // a gate group and its up group from the other half of the tile.
+    const int chunks = swiglu ? BN / 64 : BN / 32;
+    const int width = swiglu ? p.n / 2 : p.n;
+    const int out0 = swiglu ? c.n_index * (BN / 2) : c.n_index * BN;
+    const bool whole = sg.kb0 == 0 && sg.kb1 == k_blocks;
+    uint32_t r0[32], r1[32];
+    // Sums of a tile: [BN / 4 column groups][BM rows][4], so that a warp touches 512 contiguous bytes.
+    float* sums = p.accum + static_cast<size_t>(sg.tile) * BM * BN + row_in_tile * 4;
+    if (!whole) {
+        // Part of a tile: add the partial sums, then find out whether they completed the tile.
+#pragma unroll 1
+        for (int g = pass; g < BN / 32; g += 2) {
+            if (c.n_index * BN + g * 32 >= p.n) break;
+            ptx::tmem_ld_32x32(acc + g * 32, r0);
+            ptx::tmem_ld_wait();
+            if (!row_ok) continue;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                ptx::red_add_f32x4(sums + (g * 8 + i) * (BM * 4), __uint_as_float(r0[4 * i]),
+                                   __uint_as_float(r0[4 * i + 1]), __uint_as_float(r0[4 * i + 2]),
+                                   __uint_as_float(r0[4 * i + 3]));
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(tmem_empty_bar);
+        __threadfence();
+        ptx::named_barrier(1, kEpilogueThreads);
+        if (leader) {
+            const int mine = sg.kb1 - sg.kb0;
+            *last_flag = (atomicAdd(p.tile_counters + sg.tile, mine) + mine == k_blocks) ? 1u : 0u;
+        }
+        ptx::named_barrier(1, kEpilogueThreads);
+        if (*last_flag == 0) return;
+        // this CTA completed the tile: it reads the sums back (past L1), restores the zeros
+        // and runs the epilogue
+        __threadfence();
+        if (leader) p.tile_counters[sg.tile] = 0;
+    }
+    // 32 accumulator columns starting at `group_col`, from tensor memory or from the sums
+    auto fetch = [&](int group_col, uint32_t (&dst)[32]) {
+        if (whole) {
+            ptx::tmem_ld_32x32(acc + group_col, dst);
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float4* src = reinterpret_cast<float4*>(sums + (group_col / 4 + i) * (BM * 4));
+            float4 f = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+            if (row_ok) {
+                f = __ldcg(src);
+                __stcg(src, make_float4(0.0F, 0.0F, 0.0F, 0.0F));
+            }
+            dst[4 * i] = __float_as_uint(f.x); dst[4 * i + 1] = __float_as_uint(f.y);
+            dst[4 * i + 2] = __float_as_uint(f.z); dst[4 * i + 3] = __float_as_uint(f.w);
+        }
+    };
+#pragma unroll 1
+    for (int ch = pass; ch < chunks; ch += 2) {
+        const int col0 = out0 + ch * 32;
+        const bool live = col0 < width;
+        if (live) {
+            fetch(ch * 32, r0);
+            if (swiglu) fetch(BN / 2 + ch * 32, r1);
+            if (whole) ptx::tmem_ld_wait();
+        }
+        if (whole && ch + 2 >= chunks) {  // this thread has read all it needs: hand the accumulator back
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(tmem_empty_bar);
+        }
+        if (!live) continue;
+        if constexpr (SCALED) {  // weight-only INT8: the sums are over integer weights, one factor per output column
+            const float* scale0 = p.col_scale + c.n_index * BN + ch * 32;
+            const float* scale1 = scale0 + BN / 2;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                r0[i] = __float_as_uint(__uint_as_float(r0[i]) * __ldg(scale0 + i));
+                if (swiglu) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * __ldg(scale1 + i));
+            }
+        }
+        if (swiglu) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float gate = __uint_as_float(r0[i]);
+                r0[i] = __float_as_uint(__fdividef(gate, 1.0F + __expf(-gate)) * __uint_as_float(r1[i]));
+            }
+        }
+        stage_write(stage, lane, r0);
+        __syncwarp();
+        emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width);
+        __syncwarp();
+    }
+}
+
 template <int BN, bool STREAM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -553,10 +659,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     } else {
         const int quarter = warp & 3;            // tensor-memory lanes this warp may read
         const int pass = (warp - 2) >> 2;        // the two warps of a quarter alternate over the chunks
-        const int row_in_tile = quarter * 32 + lane;
         const bool leader = threadIdx.x == 64;  // first epilogue thread
         float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
-        constexpr uint32_t kEpilogueThreads = 32 * kEpilogueWarps;
         uint32_t count = 0;
         Segment sg;
         for (; walk.next(sg); ++count) {
@@ -565,91 +669,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue)) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            const int row0 = c.row_start + quarter * 32;
-            const bool row_ok = row0 + lane < c.row_end;
-            const bool swiglu = p.epilogue == SFB_EPI_SWIGLU;
-            // An output chunk is 32 columns: one 32-column group of the accumulator, or for SwiGLU
-            // a gate group and its up group from the other half of the tile.
-            const int chunks = swiglu ? BN / 64 : BN / 32;
-            const int width = swiglu ? p.n / 2 : p.n;
-            const int out0 = swiglu ? c.n_index * (BN / 2) : c.n_index * BN;
-            const bool whole = sg.kb0 == 0 && sg.kb1 == k_blocks;
-            uint32_t r0[32], r1[32];
-            // Sums of a tile: [BN / 4 column groups][BM rows][4], so that a warp touches 512 contiguous bytes.
-            float* sums = p.accum + static_cast<size_t>(sg.tile) * BM * BN + row_in_tile * 4;
-            if (!whole) {
-                // Part of a tile: add the partial sums, then find out whether they completed the tile.
-#pragma unroll 1
-                for (int g = pass; g < BN / 32; g += 2) {
-                    if (c.n_index * BN + g * 32 >= p.n) break;
-                    ptx::tmem_ld_32x32(acc + g * 32, r0);
-                    ptx::tmem_ld_wait();
-                    if (!row_ok) continue;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        ptx::red_add_f32x4(sums + (g * 8 + i) * (BM * 4), __uint_as_float(r0[4 * i]),
-                                           __uint_as_float(r0[4 * i + 1]), __uint_as_float(r0[4 * i + 2]),
-                                           __uint_as_float(r0[4 * i + 3]));
-                }
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(ptx::smem_u32(&tmem_empty[buf]));
-                __threadfence();
-                ptx::named_barrier(1, kEpilogueThreads);
-                if (leader) {
-                    const int mine = sg.kb1 - sg.kb0;
-                    *last_flag = (atomicAdd(p.tile_counters + sg.tile, mine) + mine == k_blocks) ? 1u : 0u;
-                }
-                ptx::named_barrier(1, kEpilogueThreads);
-                if (*last_flag == 0) continue;
-                // this CTA completed the tile: it reads the sums back (past L1), restores the zeros
-                // and runs the epilogue
-                __threadfence();
-                if (leader) p.tile_counters[sg.tile] = 0;
-            }
-            // 32 accumulator columns starting at `group_col`, from tensor memory or from the sums
-            auto fetch = [&](int group_col, uint32_t (&dst)[32]) {
-                if (whole) {
-                    ptx::tmem_ld_32x32(acc + group_col, dst);
-                    return;
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float4* src = reinterpret_cast<float4*>(sums + (group_col / 4 + i) * (BM * 4));
-                    float4 f = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-                    if (row_ok) {
-                        f = __ldcg(src);
-                        __stcg(src, make_float4(0.0F, 0.0F, 0.0F, 0.0F));
-                    }
-                    dst[4 * i] = __float_as_uint(f.x); dst[4 * i + 1] = __float_as_uint(f.y);
-                    dst[4 * i + 2] = __float_as_uint(f.z); dst[4 * i + 3] = __float_as_uint(f.w);
-                }
-            };
-#pragma unroll 1
-            for (int ch = pass; ch < chunks; ch += 2) {
-                const int col0 = out0 + ch * 32;
-                const bool live = col0 < width;
-                if (live) {
-                    fetch(ch * 32, r0);
-                    if (swiglu) fetch(BN / 2 + ch * 32, r1);
-                    if (whole) ptx::tmem_ld_wait();
-                }
-                if (whole && ch + 2 >= chunks) {  // this thread has read all it needs: hand the accumulator back
-                    ptx::tc_fence_before();
-                    ptx::mbar_arrive(ptx::smem_u32(&tmem_empty[buf]));
-                }
-                if (!live) continue;
-                if (swiglu) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float gate = __uint_as_float(r0[i]);
-                        r0[i] = __float_as_uint(__fdividef(gate, 1.0F + __expf(-gate)) * __uint_as_float(r1[i]));
-                    }
-                }
-                stage_write(stage, lane, r0);
-                __syncwarp();
-                emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width);
-                __syncwarp();
-            }
+            epilogue_segment<BN, false>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter, pass,
+                                 lane, leader);
         }
     }
 
@@ -664,6 +685,270 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, T::kTmemCols);
+    }
+}
+
+// ---- weight-only INT8, one M-tile (decode) -----------------------------------------------------------
+// The same work split and epilogue as the streaming bf16 kernel above, with half the weight bytes:
+// the weight arrives as int8 in 64x64 blocks (4 KB each) through a ring of TMA stages; the eight
+// epilogue warps turn each 128 x 64 int8 tile into the bf16, 128-byte-swizzled tile the MMA reads
+// (exact: |q| <= 127) while the copies of the following tiles are in flight, and run the epilogue
+// of a work item after its last tile; the per-column scale is applied to the fp32 sums first.
+struct W8 {
+    static constexpr int BN = 128;
+    static constexpr int kABytes = BM * BK * 2;   // activations, bf16
+    static constexpr int kQBytes = BN * BK;       // weights, int8
+    static constexpr int kCBytes = BN * BK * 2;   // converted weights, bf16
+    static constexpr int SA = 4, SQ = 10, SC = 3;
+    static constexpr int kStagingBytes = kEpilogueWarps * 32 * 32 * 4;
+    static constexpr int kBarrierBytes = 512;
+    static constexpr int kSmemBytes = SA * kABytes + SQ * kQBytes + SC * kCBytes + kStagingBytes + kBarrierBytes + 1024;
+    static constexpr int kTmemCols = 2 * BN;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+    static_assert(8 * (2 * SA + 2 * SQ + 2 * SC + 4) + 16 <= kBarrierBytes, "barrier block too small");
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_q,
+                       const __grid_constant__ TcParams p) {
+    constexpr int BN = W8::BN, SA = W8::SA, SQ = W8::SQ, SC = W8::SC;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_c = smem_a + SA * W8::kABytes;
+    uint8_t* smem_q = smem_c + SC * W8::kCBytes;
+    float* staging = reinterpret_cast<float*>(smem_q + SQ * W8::kQBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(staging) + W8::kStagingBytes);
+    uint64_t* full_a = bars;
+    uint64_t* empty_a = full_a + SA;
+    uint64_t* full_q = empty_a + SA;    // int8 tile landed (TMA bytes)
+    uint64_t* empty_q = full_q + SQ;    // all 256 converting threads have read it
+    uint64_t* full_c = empty_q + SQ;    // all 256 converting threads have written the bf16 tile
+    uint64_t* empty_c = full_c + SC;    // the MMAs that read it have completed
+    uint64_t* tmem_full = empty_c + SC;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
+    constexpr uint32_t kConverters = 32 * kEpilogueWarps;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SA; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_a[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_a[s]), 1);
+        }
+        for (int s = 0; s < SQ; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_q[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_q[s]), kConverters);
+        }
+        for (int s = 0; s < SC; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_c[s]), kConverters);
+            ptx::mbar_init(ptx::smem_u32(&empty_c[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&tmem_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tmem_empty[b]), kConverters);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+        ptx::prefetch_tensormap(&tma_a);
+        ptx::prefetch_tensormap(&tma_q);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), W8::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    grid_dependents_may_launch();
+    if (!(warp == 0 && lane == 0)) grid_dependency_wait();
+
+    const int m_tiles = 1;
+    const int k_blocks = (p.k + BK - 1) / BK;
+    Walk walk = make_walk(p, m_tiles, k_blocks);
+
+    // int8 tile of K block `kb` for output columns [n_index * 128, +128): two 64-row blocks of 4 KB
+    auto load_q = [&](uint8_t* dst, uint32_t bar, int kb, int n_index) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int block = (n_index * 2 + j) * k_blocks + kb;
+            ptx::tma_load_2d(ptx::smem_u32(dst + j * 4096), &tma_q, bar, 0, block * 64);
+        }
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            struct Cursor {
+                Walk walk;
+                Segment sg;
+                TileCoord c;
+                int kb;
+                uint32_t it;
+                bool live;
+            };
+            auto open = [&](Cursor& cu) {
+                cu.live = cu.walk.next(cu.sg);
+                if (cu.live) {
+                    cu.c = tile_coord(p, cu.sg.tile, m_tiles);
+                    cu.kb = cu.sg.kb0;
+                }
+            };
+            auto advance = [&](Cursor& cu) {
+                ++cu.it;
+                if (++cu.kb == cu.sg.kb1) open(cu);
+            };
+            Cursor ca{walk, {}, {}, 0, 0, false}, cq{walk, {}, {}, 0, 0, false};
+            open(ca);
+            open(cq);
+            while (cq.live && cq.it < static_cast<uint32_t>(SQ)) {  // weights do not depend on the kernel before
+                const uint32_t full = ptx::smem_u32(&full_q[cq.it]);
+                ptx::mbar_expect_tx(full, W8::kQBytes);
+                load_q(smem_q + cq.it * W8::kQBytes, full, cq.kb, cq.c.n_index);
+                advance(cq);
+            }
+            grid_dependency_wait();
+            long long stall_start = 0;
+            uint32_t idle = 0;
+            while (ca.live || cq.live) {
+                bool progressed = false;
+                if (cq.live) {
+                    const uint32_t s = cq.it % SQ, ph = (cq.it / SQ) & 1;
+                    if (ptx::mbar_try_wait(ptx::smem_u32(&empty_q[s]), ph ^ 1)) {
+                        const uint32_t full = ptx::smem_u32(&full_q[s]);
+                        ptx::mbar_expect_tx(full, W8::kQBytes);
+                        load_q(smem_q + s * W8::kQBytes, full, cq.kb, cq.c.n_index);
+                        advance(cq);
+                        progressed = true;
+                    }
+                }
+                if (ca.live) {
+                    const uint32_t s = ca.it % SA, ph = (ca.it / SA) & 1;
+                    if (ptx::mbar_try_wait(ptx::smem_u32(&empty_a[s]), ph ^ 1)) {
+                        const uint32_t full = ptx::smem_u32(&full_a[s]);
+                        ptx::mbar_expect_tx(full, W8::kABytes);
+                        ptx::tma_load_2d(ptx::smem_u32(smem_a + s * W8::kABytes), &tma_a, full, ca.kb * BK, ca.c.row_start);
+                        advance(ca);
+                        progressed = true;
+                    }
+                }
+                if (progressed) {
+                    idle = 0;
+                } else if (idle++ == 0) {
+                    stall_start = clock64();
+                } else if ((idle & 0x3FFu) == 0) {  // bounded like every other wait
+                    if (*abort_flag) break;
+                    if (clock64() - stall_start > ptx::kWaitCycles) {
+                        *abort_flag = 1;
+                        atomicOr(p.status, kCodeProducer);
+                        break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+            uint32_t it = 0, count = 0;
+            bool ok = true;
+            Segment sg;
+            for (; ok && walk.next(sg); ++count) {
+                const uint32_t buf = count & 1, tph = (count >> 1) & 1;
+                if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty[buf]), tph ^ 1, abort_flag, p.status, kCodeMma)) break;
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem_base + buf * BN;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                    const uint32_t sa = it % SA, pha = (it / SA) & 1;
+                    const uint32_t sc = it % SC, phc = (it / SC) & 1;
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_c[sc]), phc, abort_flag, p.status, kCodeMma) ||
+                        !ptx::mbar_wait(ptx::smem_u32(&full_a[sa]), pha, abort_flag, p.status, kCodeMma)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(smem_a + sa * W8::kABytes));
+                    const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(smem_c + sc * W8::kCBytes));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)
+                        ptx::umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb > sg.kb0) || kk != 0);
+                    ptx::umma_commit(ptx::smem_u32(&empty_c[sc]));
+                    ptx::umma_commit(ptx::smem_u32(&empty_a[sa]));
+                }
+                if (ok) ptx::umma_commit(ptx::smem_u32(&tmem_full[buf]));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int pass = (warp - 2) >> 2;
+        const bool leader = threadIdx.x == 64;
+        float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
+        // converting thread: 32 of the 64 K values of one of the 128 weight rows of a tile
+        const int tid = threadIdx.x - 64;
+        const int row = tid >> 1, half = tid & 1;
+        const uint32_t src_offset = (row >> 6) * 4096 + (row & 63) * 64 + half * 32;
+        uint32_t it = 0, count = 0;
+        bool ok = true;
+        Segment sg;
+        for (; ok && walk.next(sg); ++count) {
+            const TileCoord c = tile_coord(p, sg.tile, m_tiles);
+            for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                const uint32_t sq = it % SQ, phq = (it / SQ) & 1;
+                const uint32_t sc = it % SC, phc = (it / SC) & 1;
+                if (!ptx::mbar_wait(ptx::smem_u32(&full_q[sq]), phq, abort_flag, p.status, kCodeEpilogue) ||
+                    !ptx::mbar_wait(ptx::smem_u32(&empty_c[sc]), phc ^ 1, abort_flag, p.status, kCodeEpilogue)) {
+                    ok = false;
+                    break;
+                }
+                const uint4* src = reinterpret_cast<const uint4*>(smem_q + sq * W8::kQBytes + src_offset);
+                uint8_t* dst_row = smem_c + sc * W8::kCBytes + row * 128;
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const uint4 packed = src[v];
+                    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+                    uint32_t out[8];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        // bytes as q + 128 in the low mantissa bits of 2^23, minus (2^23 + 128): exactly q
+                        const uint32_t biased = words[w] ^ 0x80808080u;
+                        const float f0 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7540)) - 8388736.0F;
+                        const float f1 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7541)) - 8388736.0F;
+                        const float f2 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7542)) - 8388736.0F;
+                        const float f3 = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7543)) - 8388736.0F;
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(f0, f1), hi = __floats2bfloat162_rn(f2, f3);
+                        out[2 * w] = *reinterpret_cast<const uint32_t*>(&lo);
+                        out[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+                    }
+                    // 16 K values = two 16-byte pieces of the row, placed as the 128-byte swizzle wants them
+                    const int piece = half * 4 + v * 2;
+                    *reinterpret_cast<uint4*>(dst_row + ((piece ^ (row & 7)) * 16)) = make_uint4(out[0], out[1], out[2], out[3]);
+                    *reinterpret_cast<uint4*>(dst_row + (((piece + 1) ^ (row & 7)) * 16)) = make_uint4(out[4], out[5], out[6], out[7]);
+                }
+                ptx::fence_proxy_async();  // the MMA reads these bytes through the async proxy
+                ptx::mbar_arrive(ptx::smem_u32(&full_c[sc]));
+                ptx::mbar_arrive(ptx::smem_u32(&empty_q[sq]));
+            }
+            if (!ok) break;
+            const uint32_t buf = count & 1, tph = (count >> 1) & 1;
+            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue)) break;
+            ptx::tc_fence_after();
+            const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            epilogue_segment<BN, true>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter,
+                                       pass, lane, leader);
+        }
+    }
+
+    __syncwarp();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, W8::kTmemCols);
     }
 }
 
@@ -760,6 +1045,55 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     return check_launch("gemm_tcgen05");
 }
 
+sfb_status launch_w8(const sfb_gemm_args& g, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        SFB_CUDA(cudaFuncSetAttribute(gemm_w8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W8::kSmemBytes));
+        configured = true;
+    }
+    CUtensorMap map_a, map_q;
+    if (!encode_tensor_map_bf16_2d(&map_a, g.a, static_cast<uint64_t>(g.m), static_cast<uint64_t>(g.k), BM, BK))
+        return SFB_CUDA_ERROR;
+    const uint64_t blocks = static_cast<uint64_t>(ceil_div(g.n, 64)) * ceil_div(g.k, 64);
+    if (!encode_tensor_map_u8_2d(&map_q, g.bt, blocks * 64, 64, 64, 64)) return SFB_CUDA_ERROR;
+    TcParams p{};
+    p.out = g.out;
+    p.m = g.m; p.n = g.n; p.k = g.k;
+    p.epilogue = g.epilogue;
+    p.out_f32 = g.out_f32;
+    p.residual = static_cast<const bf16*>(g.residual);
+    p.q = static_cast<bf16*>(g.q);
+    p.key = static_cast<bf16*>(g.key);
+    p.value = static_cast<bf16*>(g.value);
+    p.rope_cos = g.rope_cos;
+    p.rope_sin = g.rope_sin;
+    p.seq = g.seq; p.q_heads = g.q_heads; p.kv_heads = g.kv_heads; p.head_dim = g.head_dim;
+    p.rope_row_offset = g.rope_row_offset;
+    p.n_tiles = ceil_div(g.n, W8::BN);
+    p.b_tiled = 1;
+    p.col_scale = g.bt_scales;
+    p.peer_count = g.peer_count;
+    for (int i = 0; i < g.peer_count; ++i) p.peer_out[i] = static_cast<bf16*>(g.peer_out[i]);
+    p.status = device_status_word();
+    p.tile_table = nullptr;
+    p.dense_m_tiles = 1;
+    const long long tiles = p.n_tiles;
+    int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    if (g.split_workspace && (reinterpret_cast<uintptr_t>(g.split_workspace) & 15) == 0 &&
+        g.split_workspace_bytes >= sfb_gemm_stream_workspace_bytes(g.n)) {
+        const int left = static_cast<int>(tiles % sm_count());
+        if (left != 0 && left <= sm_count() * 7 / 8) {
+            p.shared_tiles = left;
+            p.accum = static_cast<float*>(g.split_workspace);
+            p.tile_counters = reinterpret_cast<int*>(p.accum + static_cast<size_t>(p.n_tiles) * BM * W8::BN);
+            const long long units = static_cast<long long>(left) * ceil_div(g.k, BK);
+            grid = static_cast<int>(tiles >= sm_count() || units >= sm_count() ? sm_count() : units);
+        }
+    }
+    SFB_CUDA(launch_dependent(gemm_w8_tcgen05_kernel, dim3(grid), dim3(kThreads), W8::kSmemBytes, stream, map_a, map_q, p));
+    return check_launch("gemm_w8_tcgen05");
+}
+
 int pick_bn(const sfb_gemm_args& g) {
     if (g.epilogue == SFB_EPI_SWIGLU) return 2 * g.swiglu_block;
     if (g.bt_tiled || stream_shape(g)) return 128;
@@ -776,6 +1110,9 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
     if (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64 && g.swiglu_block != 128) return false;
     if (g.bt_tiled && (g.group_offsets || (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64))) return false;
     if (g.epilogue == SFB_EPI_ROPE_SPLIT && g.head_dim % 32 != 0) return false;
+    if (g.bt_scales && (!stream_shape(g) || (g.epilogue == SFB_EPI_SWIGLU && g.swiglu_block != 64) ||
+                        (reinterpret_cast<uintptr_t>(g.bt_scales) & 15)))
+        return false;  // int8 weights: one M-tile, dense, 128-column tiles
     if (g.peer_count != 0 && (g.peer_count < 0 || g.peer_count >= SFB_MAX_PEERS || g.out_f32 || g.group_offsets ||
                               (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL)))
         return false;
@@ -783,6 +1120,7 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
 }
 
 sfb_status gemm_bf16_tcgen05(const sfb_gemm_args& g, cudaStream_t stream) {
+    if (g.bt_scales) return launch_w8(g, stream);
     if (pick_bn(g) == 256) return launch<256, false>(g, stream);
     if (stream_shape(g)) return launch<128, true>(g, stream);
     return launch<128, false>(g, stream);

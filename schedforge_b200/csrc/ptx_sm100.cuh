@@ -233,6 +233,8 @@ __device__ __forceinline__ void tmem_st_wait() {
 // Encodes a 2-D bf16 row-major tensor [rows, cols] (cols contiguous) with a box of
 // [box_rows, box_cols] and 128-byte swizzle.  cols*2 must be a multiple of 16 bytes.
 // Implemented in tensor_map.cu through the driver entry point (no link-time libcuda).
+bool encode_tensor_map_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                             uint32_t box_cols);
 bool encode_tensor_map_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                                uint32_t box_rows, uint32_t box_cols);
 // 3-D variant: [d2, d1, d0] with d0 contiguous; strides in elements for d1 and d2.

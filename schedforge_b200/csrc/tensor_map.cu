@@ -47,6 +47,25 @@ bool encode_tensor_map_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows
     return true;
 }
 
+// Bytes, no swizzle: rows of `cols` bytes (a multiple of 16); the box lands row-major in shared memory.
+bool encode_tensor_map_u8_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                             uint32_t box_cols) {
+    EncodeTiled encode = encode_fn();
+    if (!encode) { set_error("cuTensorMapEncodeTiled is not available"); return false; }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled(u8) failed with CUresult " + std::to_string(static_cast<int>(r)));
+        return false;
+    }
+    return true;
+}
+
 bool encode_tensor_map_bf16_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t stride1, uint64_t stride2, uint32_t box0, uint32_t box1, uint32_t box2) {
     EncodeTiled encode = encode_fn();

@@ -53,7 +53,7 @@ def test_struct_layouts_match_header(sfb):
     assert C.sizeof(sfb.MoeConfig) == 5 * 4
     assert C.sizeof(sfb.GraphSummary) == 7 * 4
     assert C.sizeof(sfb.DecoderResult) == 9 * 8 + 8
-    assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.rope_row_offset.offset == C.sizeof(sfb.GemmArgs) - 4
+    assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.bt_scales.offset == C.sizeof(sfb.GemmArgs) - 8
 
 
 def test_weight_layout_and_scratch_size_helpers_need_no_device(sfb):

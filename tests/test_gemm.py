@@ -13,10 +13,11 @@ BF16_TOL = 2e-2  # max-abs relative, bf16 outputs with fp32 accumulation
 
 
 def gemm_bf16(sfb, dev, a, bt, epilogue=0, backend=0, out_f32=False, residual=None, swiglu_block=0,
-              rope=None, offsets=None, groups=0, n=None, scratch=None, blocked=False):
+              rope=None, offsets=None, groups=0, n=None, scratch=None, blocked=False, int8_scales=None):
     torch = dev.torch
     m, k = a.shape
     n = n if n is not None else bt.shape[-2]
+    assert int8_scales is None or not blocked
     g = sfb.GemmArgs()
     g.a, g.bt = a.data_ptr(), bt.data_ptr()
     g.m, g.n, g.k = m, n, k
@@ -53,6 +54,8 @@ def gemm_bf16(sfb, dev, a, bt, epilogue=0, backend=0, out_f32=False, residual=No
         g.tile_table = table.data_ptr()
     if scratch is not None:
         g.split_workspace, g.split_workspace_bytes = scratch[0].data_ptr(), scratch[1]
+    if int8_scales is not None:
+        g.bt_scales = int8_scales.data_ptr()
     sfb.check(sfb.load().sfb_k_gemm_bf16(C.byref(g), C.c_void_p(dev.stream())))
     torch.cuda.synchronize()
     word = C.c_uint32(0)
@@ -257,3 +260,88 @@ def test_gemm_tcgen05_llama_shape_sampled_rows(sfb, dev, port):
     a_rows = a[torch.from_numpy(rows).cuda()].float().cpu().numpy()
     want = port.matmul(a_rows, bt.float().cpu().numpy().T.copy(), fma=True)
     assert rel_err(dev.np(got)[rows], want) < BF16_TOL
+
+
+# ---- weight-only INT8 (few rows) ----------------------------------------------------------------------
+
+def _quantize_like_the_reference(w_nk):
+    """quantize_matmul_weights, src/next_milestones.cpp:611-637, per output channel."""
+    maximum = np.max(np.abs(w_nk), axis=1)
+    scale = np.where(maximum > 0, (maximum / np.float32(127.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    value = (w_nk / scale[:, None]).astype(np.float32)
+    rounded = np.sign(value) * np.floor(np.abs(value) + np.float32(0.5))  # std::round: halves away from zero
+    return np.clip(rounded, -127, 127).astype(np.int8), scale
+
+
+def _blocked(q_nk):
+    n, k = q_nk.shape
+    nb, kb = (n + 63) // 64, (k + 63) // 64
+    padded = np.zeros((nb * 64, kb * 64), q_nk.dtype)
+    padded[:n, :k] = q_nk
+    return padded.reshape(nb, 64, kb, 64).transpose(0, 2, 1, 3).copy()
+
+
+def _quantize_on_device(sfb, dev, w_nk):
+    torch = dev.torch
+    n, k = w_nk.shape
+    lib = sfb.load()
+    q = torch.zeros((lib.sfb_tiled_weight_elems(n, k),), dtype=torch.int8, device="cuda")
+    scales = torch.zeros(((n + 127) // 128 * 128,), dtype=torch.float32, device="cuda")
+    dw = dev.bf16(w_nk)
+    sfb.check(lib.sfb_k_quantize_weight_int8(C.c_void_p(dw.data_ptr()), C.c_void_p(q.data_ptr()),
+                                             C.c_void_p(scales.data_ptr()), n, k, C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    return q, scales
+
+
+@pytest.mark.parametrize("n,k", [(128, 64), (200, 1000), (512, 4096)])
+def test_int8_weight_quantization_is_the_reference_formula(sfb, dev, port, n, k):
+    rng = np.random.default_rng(n + k)
+    w = port.round_bf16((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+    w[3] = 0.0  # an all-zero output channel keeps scale 1
+    q, scales = _quantize_on_device(sfb, dev, w)
+    want_q, want_scale = _quantize_like_the_reference(w)
+    assert np.array_equal(scales.cpu().numpy()[:n], want_scale)
+    assert np.array_equal(q.cpu().numpy().reshape(_blocked(want_q).shape), _blocked(want_q))
+    back = dev.zeros((n, k), dev.torch.bfloat16)
+    sfb.check(sfb.load().sfb_k_dequantize_weight_int8(C.c_void_p(q.data_ptr()), C.c_void_p(scales.data_ptr()),
+                                                      C.c_void_p(back.data_ptr()), n, k, C.c_void_p(dev.stream())))
+    assert np.array_equal(dev.np(back), port.round_bf16(want_q.astype(np.float32) * want_scale[:, None]))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 4096), (17, 200, 2048), (1, 512, 8200), (100, 6144, 1024)])
+def test_gemm_int8_weights_few_rows(sfb, dev, port, m, n, k):
+    """y = (x . q^T) * scale with q, scale from the reference's quantizer (quantized_invoke,
+    src/next_milestones.cpp:50-69), bf16 activations, fp32 sums; plain, residual and fp32 outputs."""
+    a, w = _inputs(port, m, n, k, seed=21, scale=0.02)
+    w_nk = np.ascontiguousarray(w.T)
+    q, scales = _quantize_on_device(sfb, dev, w_nk)
+    want_q, want_scale = _quantize_like_the_reference(w_nk)
+    want = (a.astype(np.float64) @ want_q.astype(np.float64).T * want_scale[None, :]).astype(np.float32)
+    res = port.round_bf16(np.random.default_rng(22).standard_normal((m, n)).astype(np.float32))
+    scratch = _scratch(sfb, dev, n)
+    for _ in range(2):
+        got32 = gemm_bf16(sfb, dev, dev.bf16(a), q, backend=2, out_f32=True, scratch=scratch, n=n, int8_scales=scales)
+        assert rel_err(dev.np(got32), want) < 1e-4
+        got = gemm_bf16(sfb, dev, dev.bf16(a), q, epilogue=sfb.EPI_RESIDUAL, residual=dev.bf16(res), scratch=scratch, n=n,
+                        int8_scales=scales)
+        assert rel_err(dev.np(got), want + res) < BF16_TOL
+    assert not dev.np(scratch[0]).any()
+
+
+def test_gemm_int8_weights_swiglu(sfb, dev, port):
+    m, inter, k, block = 100, 320, 1024, 64
+    rng = np.random.default_rng(23)
+    a = port.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    wg = port.round_bf16((rng.standard_normal((inter, k)) * 0.1).astype(np.float32))
+    wu = port.round_bf16((rng.standard_normal((inter, k)) * 0.1).astype(np.float32))
+    bt = np.concatenate([np.concatenate([wg[i:i + block], wu[i:i + block]]) for i in range(0, inter, block)])
+    q, scales = _quantize_on_device(sfb, dev, bt)
+    qg, sg = _quantize_like_the_reference(wg)
+    qu, su = _quantize_like_the_reference(wu)
+    gate = (a.astype(np.float64) @ qg.astype(np.float64).T * sg[None, :]).astype(np.float32)
+    up = (a.astype(np.float64) @ qu.astype(np.float64).T * su[None, :]).astype(np.float32)
+    want = port.swiglu(np.concatenate([gate, up], axis=1), inter)
+    got = gemm_bf16(sfb, dev, dev.bf16(a), q, epilogue=sfb.EPI_SWIGLU, backend=2, swiglu_block=block,
+                    scratch=_scratch(sfb, dev, 2 * inter), n=2 * inter, int8_scales=scales)
+    assert rel_err(dev.np(got), want) < BF16_TOL
