@@ -281,6 +281,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "int8"],
+                    help="int8: per-output-channel weight-only INT8 (the reference's quantized layer); not the default")
     ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer"],
                     help="N > 1: all-reduce after the O and Down projections through NCCL, or fused into the GEMM "
                          "epilogues over NVLink peer memory")
@@ -344,7 +346,9 @@ def main():
     out_host = torch.empty((tokens, cfg["hidden"]), dtype=torch.float32).pin_memory()
     c = api.decoder_config(**cfg)
     plan = api.DecoderCompiler.compile(c, data, "", api.compile_options(tp_rank=rank, tp_size=world,
-                                                                         seed_block_table=1 if args.workload == "decode" else 0))
+                                                                         seed_block_table=1 if args.workload == "decode" else 0,
+                                                                         weight_int8=args.weights == "int8"))
+    config["weights"] = args.weights
     del data
     stream = torch.cuda.ExternalStream(plan.stream)
     views = {}

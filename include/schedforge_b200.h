@@ -376,6 +376,12 @@ typedef struct sfb_compile_options {
                              appended to the paged cache (append_paged_kv, src/next_milestones.cpp:486-524)
                              and attention over context_sequence + 1 keys.  A plan can be run again: the
                              append always writes position context_sequence. */
+    int weight_int8;      /* != 0 (bf16 plans, dense FFN): per-output-channel symmetric INT8 weights as
+                             quantize_decoder_weights / execute_quantized_decoder_layer
+                             (src/next_milestones.cpp:660-697).  Plans of at most 128 rows keep the four
+                             projections as int8 and stream half the bytes; larger plans (compute bound)
+                             multiply by the dequantised q * scale weights in bf16.  The quantizer sees the
+                             bf16-rounded weights. */
 } sfb_compile_options;
 
 /* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */

@@ -81,6 +81,31 @@ def decoder_config(batch=1, sequence=16, hidden=64, intermediate=128, query_head
                          context_sequence)
 
 
+INT8_WEIGHTS = {"query_weight": ("hidden", "hidden"), "key_weight": ("hidden", "kv"), "value_weight": ("hidden", "kv"),
+                "output_weight": ("hidden", "hidden"), "gate_weight": ("hidden", "intermediate"),
+                "up_weight": ("hidden", "intermediate"), "down_weight": ("intermediate", "hidden")}
+
+
+def quantize_dequantize(w_in_out):
+    """quantize_matmul_weights (src/next_milestones.cpp:611-637) per output channel of an [in, out]
+    weight, then q * scale again: the weights the reference's INT8 layer effectively multiplies by."""
+    w = np.asarray(w_in_out, np.float32)
+    maximum = np.max(np.abs(w), axis=0)
+    scale = np.where(maximum > 0, (maximum / np.float32(127.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    value = (w / scale[None, :]).astype(np.float32)
+    q = np.clip(np.sign(value) * np.floor(np.abs(value) + np.float32(0.5)), -127, 127).astype(np.float32)
+    return (q * scale[None, :]).astype(np.float32)
+
+
+def int8_weight_data(c, data):
+    """DecoderData with the seven dense weights replaced by their INT8 round trip."""
+    dims = {"hidden": c.hidden, "kv": c.kv_heads * c.head_dim, "intermediate": c.intermediate}
+    out = dict(data)
+    for name, (rows, cols) in INT8_WEIGHTS.items():
+        out[name] = quantize_dequantize(np.asarray(data[name], np.float32).reshape(dims[rows], dims[cols])).reshape(-1)
+    return out
+
+
 def decoder_shapes(c):
     """Element counts of every DecoderData tensor for configuration `c`."""
     t, h, i = c.batch * c.sequence, c.hidden, c.intermediate
@@ -564,6 +589,13 @@ class RefDecoder:
         out = np.empty((self.c.batch * self.c.sequence, self.c.hidden), np.float32)
         self.o._check(self.o.fn("decoder_reference")(self.h, fp(out)))
         return out
+
+    def quantized(self, per_channel=True):
+        """Weight-only INT8 layer of the reference; returns (output, max error vs its scalar reference)."""
+        out = np.empty((self.c.batch * self.c.sequence, self.c.hidden), np.float32)
+        err = C.c_double(0)
+        self.o._check(self.o.fn("decoder_quantized")(self.h, int(per_channel), fp(out), C.byref(err)))
+        return out, err.value
 
     def plan_info(self):
         s, k, w = C.c_int(0), C.c_int(0), C.c_longlong(0)

@@ -359,6 +359,18 @@ int sfref_decoder_reference(void* handle, float* output) {
     });
 }
 
+// The reference's weight-only INT8 layer: quantize_decoder_weights + execute_quantized_decoder_layer
+// (src/next_milestones.cpp:660-697), one pass; max_error is against its scalar layer reference.
+int sfref_decoder_quantized(void* handle, int per_channel, float* output, double* max_error) {
+    return guarded([&] {
+        auto* h = static_cast<DecoderHandle*>(handle);
+        const auto weights = schedforge::quantize_decoder_weights(h->config, h->data, per_channel != 0);
+        const auto result = schedforge::execute_quantized_decoder_layer(h->config, h->data, weights, 0, 1);
+        out(result.output, output);
+        if (max_error) *max_error = result.max_error;
+    });
+}
+
 // ---- pieces of the layer (anonymous-namespace functions of the reference) ---
 int sfref_rms_norm(const float* input, const float* weight, int rows, int width,
                    float epsilon, float* output) {

@@ -155,6 +155,15 @@ struct DecoderExecutablePlan::Impl {
         a.count = count; a.slot_elems = static_cast<int64_t>(peer_slot_bytes() / 2);
         return sfb_k_peer_allreduce_finish(&a, s);
     }
+    // weight-only INT8: per projection the int8 blocked copy and its per-column scales
+    struct Int8Weight { const void* weight; void* q; float* scales; };
+    std::vector<Int8Weight> int8_weights;
+    DeviceBuffer int8_arena;
+    const Int8Weight* int8(const void* w) const {
+        for (const auto& entry : int8_weights)
+            if (entry.weight == w) return &entry;
+        return nullptr;
+    }
     std::vector<const void*> blocked_weights;  // weights re-laid in 64x64 blocks (decode-shaped plans)
     bool blocked(const void* w) const {
         return std::find(blocked_weights.begin(), blocked_weights.end(), w) != blocked_weights.end();
@@ -387,9 +396,35 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         }
     }
     staging.release();
+    if (opt.weight_int8 != 0) {
+        if (!bf) throw std::invalid_argument("INT8 weights need a bf16 plan");
+        if (moe) throw std::invalid_argument("INT8 decoder currently requires dense FFN weights");
+        struct Item { void* w; int n, k; };
+        const Item items[4] = {{m.wqkv, m.qkv_l, H}, {m.wo, H, m.hidden_l}, {m.wgu, 2 * I, H}, {m.wd, H, I}};
+        const bool keep_int8 = T <= 128 && plan->policy.gemm_backend != SFB_GEMM_SIMT && fused;
+        std::size_t bytes = 0;
+        for (const auto& item : items)
+            bytes += (static_cast<std::size_t>(sfb_tiled_weight_elems(item.n, item.k)) + 255) / 256 * 256 +
+                     static_cast<std::size_t>(ceil_div(item.n, 128)) * 128 * sizeof(float);
+        m.int8_arena.allocate(bytes);
+        char* cursor = m.int8_arena.as<char>();
+        for (const auto& item : items) {
+            void* q = cursor;
+            cursor += (static_cast<std::size_t>(sfb_tiled_weight_elems(item.n, item.k)) + 255) / 256 * 256;
+            float* scales = reinterpret_cast<float*>(cursor);
+            cursor += static_cast<std::size_t>(ceil_div(item.n, 128)) * 128 * sizeof(float);
+            cuda_check(cudaMemsetAsync(scales, 0, static_cast<std::size_t>(ceil_div(item.n, 128)) * 128 * sizeof(float), s), "scale clear");
+            throw_on(sfb_k_quantize_weight_int8(item.w, q, scales, item.n, item.k, s));
+            if (keep_int8) m.int8_weights.push_back({item.w, q, scales});
+            else throw_on(sfb_k_dequantize_weight_int8(q, scales, item.w, item.n, item.k, s));  // q * scale, bf16
+        }
+        cuda_check(cudaStreamSynchronize(s), "weight quantization");
+        if (!keep_int8) m.int8_arena.release();
+        for (auto& constant : plan->constants) constant.layout += keep_int8 ? "_int8_blocked64" : "_int8_values";
+    }
     // Plans with few rows stream every weight once per pass: store the dense weights in 64x64
     // blocks so that the GEMM reads 8 KB contiguous runs instead of 128-byte row pieces.
-    if (bf && T <= 128 && plan->policy.gemm_backend != SFB_GEMM_SIMT) {
+    if (bf && T <= 128 && plan->policy.gemm_backend != SFB_GEMM_SIMT && m.int8_weights.empty()) {
         auto reblock = [&](void* w, int n, int k) {
             if (!w || n % 64 != 0 || k % 64 != 0) return;
             const std::size_t bytes = static_cast<std::size_t>(n) * k * 2;
@@ -657,6 +692,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             g.split_workspace_bytes = m.planner.bytes(m.planner.find("gemm_partials"));
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
+        if (const auto* quantized = m.int8(w)) {
+            g.bt = quantized->q;
+            g.bt_scales = quantized->scales;
+        }
         if (peer_set >= 0) m.fill_peer_out(g, peer_set, 0);
         throw_on(sfb_k_gemm_bf16(&g, s));
     };
@@ -872,6 +911,10 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             g.rope_row_offset = g0;
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
+        if (const auto* quantized = m.int8(w)) {
+            g.bt = quantized->q;
+            g.bt_scales = quantized->scales;
+        }
         if (peer_set >= 0) m.fill_peer_out(g, peer_set, static_cast<std::size_t>(g0) * H);
         throw_on(sfb_k_gemm_bf16(&g, s));
     };

@@ -303,3 +303,24 @@ def test_pipelined_execute_in_row_chunks_equals_the_one_shot_plan(port):
     assert np.array_equal(piped.execute(data["input"])[0], out_piped)  # and again on the used workspace
     piped.close()
     one_shot.close()
+
+
+@pytest.mark.parametrize("kw", [
+    dict(batch=5, sequence=1, hidden=1024, intermediate=512, query_heads=8, kv_heads=2, head_dim=128, context_sequence=300),
+    dict(batch=1, sequence=96, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64),   # few rows: int8 kept
+    dict(batch=2, sequence=192, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64),  # many rows: q * scale in bf16
+])
+def test_weight_only_int8_plan_matches_the_quantized_oracle(port, kw):
+    """weight_int8: the oracle layer on q * scale weights is what the reference's INT8 layer computes
+    (pinned on the CPU against the reference build); the bf16 activations add the usual tolerance."""
+    oc, c, data = bf16_case(port, 51, **kw)
+    want = port.decoder_layer(oc, ob.int8_weight_data(oc, data), native=True)
+    plain = port.decoder_layer(oc, data, native=True)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(weight_int8=True))
+    out, _ = plan.execute(data["input"])
+    assert rel_err(out, want) < BF16_TOL
+    assert rel_err(out, plain) > rel_err(out, want)   # it is the quantized layer, not the plain one
+    assert "_int8" in plan.dump()
+    plan.close()
+    with pytest.raises(L.SfbError):
+        api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(weight_int8=True, dtype=L.F32))

@@ -172,3 +172,24 @@ def test_importer_fixture_is_consistent(ref):
     assert ref.import_stablehlo(MOE_TEXT, moe=True) == want["moe"]
     assert ref.import_stablehlo(NO_QKV_TEXT) == want["no_qkv"]
     assert want["decoder"]["operations"] == 25 and want["decoder"]["fused_qkv"] and want["decoder"]["fused_gate_up"]
+
+
+@pytest.mark.parametrize("name", ["decoder_dense", "decoder_decode", "decoder_batched", "decoder_cfg1_shape"])
+def test_int8_weight_round_trip_reproduces_the_reference_quantized_layer(port, ref, name):
+    """The reference's weight-only INT8 layer (quantize_decoder_weights + execute_quantized_decoder_layer)
+    against the oracle layer run on q * scale weights: equal up to the association of `x * q * scale`,
+    and, on the reference's own test shapes, inside its bar (0.15 absolute against its unquantized scalar layer)."""
+    c, data, _ = decoder_case(name)
+    dec = ref.decoder_create(c, data)
+    try:
+        want, max_error = dec.quantized(per_channel=True)
+    finally:
+        dec.close()
+    if name in ("decoder_dense", "decoder_decode"):  # the shapes of the reference's own INT8 test
+        assert max_error < 0.15
+    got = port.decoder_layer(c, ob.int8_weight_data(c, data), native=False)
+    assert np.max(np.abs(got - want)) <= 2e-5 * max(1.0, np.max(np.abs(want)))
+    # the round trip really changes the weights, and a second round trip changes nothing
+    assert np.max(np.abs(got - port.decoder_layer(c, data, native=False))) > 1e-5
+    again = ob.int8_weight_data(c, ob.int8_weight_data(c, data))
+    assert np.array_equal(again["down_weight"], ob.int8_weight_data(c, data)["down_weight"])
