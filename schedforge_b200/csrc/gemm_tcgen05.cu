@@ -730,7 +730,7 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* last_flag = tmem_slot + 2;
-    constexpr uint32_t kConverters = 32 * kEpilogueWarps;
+    constexpr uint32_t kConverters = kEpilogueWarps / 2;  // arrivals per tile: one per warp of the group of four that converts it
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -748,7 +748,7 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&tmem_full[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&tmem_empty[b]), kConverters);
+            ptx::mbar_init(ptx::smem_u32(&tmem_empty[b]), 32 * kEpilogueWarps);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -885,16 +885,17 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         const int pass = (warp - 2) >> 2;
         const bool leader = threadIdx.x == 64;
         float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
-        // converting thread: 32 of the 64 K values of one of the 128 weight rows of a tile
-        const int tid = threadIdx.x - 64;
-        const int row = tid >> 1, half = tid & 1;
-        const uint32_t src_offset = (row >> 6) * 4096 + (row & 63) * 64 + half * 32;
+        // converting thread: the 64 K values of one of the 128 weight rows, in every second tile
+        // (the other group of four warps converts the tiles in between, so two conversions overlap)
+        const int row = (threadIdx.x - 64) & 127;
+        const uint32_t src_offset = (row >> 6) * 4096 + (row & 63) * 64;
         uint32_t it = 0, count = 0;
         bool ok = true;
         Segment sg;
         for (; ok && walk.next(sg); ++count) {
             const TileCoord c = tile_coord(p, sg.tile, m_tiles);
             for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                if ((it & 1u) != static_cast<uint32_t>(pass)) continue;
                 const uint32_t sq = it % SQ, phq = (it / SQ) & 1;
                 const uint32_t sc = it % SC, phc = (it / SC) & 1;
                 if (!ptx::mbar_wait(ptx::smem_u32(&full_q[sq]), phq, abort_flag, p.status, kCodeEpilogue) ||
@@ -905,7 +906,7 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                 const uint4* src = reinterpret_cast<const uint4*>(smem_q + sq * W8::kQBytes + src_offset);
                 uint8_t* dst_row = smem_c + sc * W8::kCBytes + row * 128;
 #pragma unroll
-                for (int v = 0; v < 2; ++v) {
+                for (int v = 0; v < 4; ++v) {
                     const uint4 packed = src[v];
                     const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
                     uint32_t out[8];
@@ -922,13 +923,16 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                         out[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&hi);
                     }
                     // 16 K values = two 16-byte pieces of the row, placed as the 128-byte swizzle wants them
-                    const int piece = half * 4 + v * 2;
+                    const int piece = v * 2;
                     *reinterpret_cast<uint4*>(dst_row + ((piece ^ (row & 7)) * 16)) = make_uint4(out[0], out[1], out[2], out[3]);
                     *reinterpret_cast<uint4*>(dst_row + (((piece + 1) ^ (row & 7)) * 16)) = make_uint4(out[4], out[5], out[6], out[7]);
                 }
                 ptx::fence_proxy_async();  // the MMA reads these bytes through the async proxy
-                ptx::mbar_arrive(ptx::smem_u32(&full_c[sc]));
-                ptx::mbar_arrive(ptx::smem_u32(&empty_q[sq]));
+                __syncwarp();
+                if (lane == 0) {  // one arrival per warp: 128 threads on one barrier would serialise
+                    ptx::mbar_arrive(ptx::smem_u32(&full_c[sc]));
+                    ptx::mbar_arrive(ptx::smem_u32(&empty_q[sq]));
+                }
             }
             if (!ok) break;
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
