@@ -48,8 +48,8 @@ template <int BN, bool STREAM>
 struct Tile {
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
-    static constexpr int kStagesB = STREAM ? (192 * 1024 - 4 * kABytes) / kBBytes : (BN == 256 ? 4 : 6);
-    static constexpr int kStagesA = STREAM ? 4 : kStagesB;
+    static constexpr int kStagesA = STREAM ? 6 : (BN == 256 ? 4 : 6);
+    static constexpr int kStagesB = STREAM ? (192 * 1024 - kStagesA * kABytes) / kBBytes : kStagesA;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBarrierBytes = 512;
