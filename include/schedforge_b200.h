@@ -579,6 +579,15 @@ sfb_status sfb_moe_execute(const sfb_moe_config* config, const float* input, int
                            const float* w1, const float* w3, const float* w2,
                            const int* expert_ids, const float* expert_weights, const int* counts,
                            int dtype, int gemm_backend, float* out, double* milliseconds);
+/* quantize_moe_weights + execute_quantized_moe, src/next_milestones.cpp:699-738 (per expert matrix,
+ * per output channel: scale = max|w| / 127, q = round-half-away(w / scale) clamped to +-127; the experts
+ * then multiply by q * scale).  bf16 arithmetic on the grouped tcgen05 GEMMs; per_channel = 0 (one scale per
+ * matrix) is rejected with SFB_INVALID_ARGUMENT.  The reference's bar is 0.2 absolute against reference_moe
+ * on the unquantized weights (tests/test_schedforge.cpp:911). */
+sfb_status sfb_moe_execute_quantized(const sfb_moe_config* config, const float* input, int tokens,
+                                     const float* w1, const float* w3, const float* w2,
+                                     const int* expert_ids, const float* expert_weights, const int* counts,
+                                     int per_channel, int gemm_backend, float* out, double* milliseconds);
 /* plan_moe_tasks, src/moe_compiler.cpp:530-558: rows (expert, begin, end, bucket). */
 sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, int split_threshold,
                               int* tasks, int capacity, int* task_count);

@@ -97,6 +97,13 @@ def quantize_dequantize(w_in_out):
     return (q * scale[None, :]).astype(np.float32)
 
 
+def int8_expert_weights(w, experts, rows, cols):
+    """Expert weights [experts, rows(in), cols(out)] after the INT8 round trip of quantize_moe_weights
+    (src/next_milestones.cpp:699-714): every expert matrix on its own, per output channel."""
+    w = np.asarray(w, np.float32).reshape(experts, rows, cols)
+    return np.stack([quantize_dequantize(w[e]) for e in range(experts)]).reshape(-1)
+
+
 def int8_weight_data(c, data):
     """DecoderData with the seven dense weights replaced by their INT8 round trip."""
     dims = {"hidden": c.hidden, "kv": c.kv_heads * c.head_dim, "intermediate": c.intermediate}
@@ -558,6 +565,17 @@ class Ref(_Base):
         self._check(self.fn("execute_moe")(C.byref(c), fp(x), x.shape[0], fp(router), fp(w1), fp(w3),
                                            fp(w2), ip(ids), fp(weights), ip(counts), threads, fp(out), ms))
         return (out, list(ms)) if want_ms else out
+
+    def moe_quantized(self, c, x, w1, w3, w2, ids, weights, counts=None, per_channel=True):
+        """quantize_moe_weights + execute_quantized_moe (src/next_milestones.cpp:699-738);
+        returns (output, max error against reference_moe on the unquantized weights)."""
+        x, w1, w3, w2, ids, weights = f32(x), f32(w1), f32(w3), f32(w2), i32(ids), f32(weights)
+        counts = i32(counts) if counts is not None else np.bincount(ids.ravel(), minlength=c.experts).astype(np.int32)
+        out = np.empty((x.shape[0], c.hidden), np.float32)
+        err = C.c_double(0)
+        self._check(self.fn("quantized_moe")(C.byref(c), fp(x), x.shape[0], fp(w1), fp(w3), fp(w2), ip(ids),
+                                             fp(weights), ip(counts), int(per_channel), fp(out), C.byref(err)))
+        return out, err.value
 
     def decoder_create(self, c, data, stablehlo_text="", threads=0, trace=None):
         d, keep = pack_decoder_data(data, trace)

@@ -703,4 +703,23 @@ int sfref_execute_moe(const sfref_moe_config* c, const float* input, int tokens,
     });
 }
 
+// Weight-only INT8 experts: quantize_moe_weights + execute_quantized_moe with a given trace.
+// max_error = against reference_moe on the unquantized weights (the reference's own bar is 0.2).
+int sfref_quantized_moe(const sfref_moe_config* c, const float* input, int tokens,
+                        const float* w1, const float* w3, const float* w2,
+                        const int* expert_ids, const float* expert_weights, const int* counts,
+                        int per_channel, float* output, double* max_error) {
+    return guarded([&] {
+        const auto config = to_config(*c);
+        std::vector<float> router(static_cast<std::size_t>(config.hidden) * config.experts, 0.0F);
+        auto data = to_moe_data(config, router.data(), w1, w3, w2);
+        data.input = vec(input, static_cast<std::size_t>(tokens) * config.hidden);
+        const auto trace = to_trace(config, tokens, expert_ids, expert_weights, counts);
+        const auto weights = schedforge::quantize_moe_weights(config, data, per_channel != 0);
+        const auto result = schedforge::execute_quantized_moe(config, data, trace, weights, 0, 1);
+        out(result.output, output);
+        if (max_error) *max_error = result.max_error;
+    });
+}
+
 }  // extern "C"

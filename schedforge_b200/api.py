@@ -337,6 +337,19 @@ def execute_moe(config, x, w1, w3, w2, ids, weights, counts, dtype=L.F32, gemm_b
     return out, ms.value
 
 
+def execute_quantized_moe(config, x, w1, w3, w2, ids, weights, counts, per_channel=True, gemm_backend=L.GEMM_AUTO):
+    """quantize_moe_weights + execute_quantized_moe of the reference (src/next_milestones.cpp:699-738):
+    the experts multiply by the INT8 round trip of their weights."""
+    x, w1, w3, w2 = _f32(x), _f32(w1), _f32(w3), _f32(w2)
+    ids, weights, counts = _i32(ids), _f32(weights), _i32(counts)
+    out = np.empty((x.shape[0], config.hidden), np.float32)
+    ms = C.c_double(0)
+    L.check(L.load().sfb_moe_execute_quantized(C.byref(config), _fp(x), x.shape[0], _fp(w1), _fp(w3), _fp(w2),
+                                               _ip(ids), _fp(weights), _ip(counts), int(per_channel), gemm_backend,
+                                               _fp(out), C.byref(ms)))
+    return out, ms.value
+
+
 def plan_moe_tasks(config, counts, split_threshold=0):
     counts = _i32(counts)
     tasks = np.empty((4096, 4), np.int32)

@@ -369,9 +369,50 @@ sfb_status sfb_moe_dispatch_tokens(const sfb_moe_config* config, const float* in
     });
 }
 
+namespace {
+// Weight-only INT8 round trip of a packed [n, k] bf16 weight (rows = output channels), in place:
+// quantize_matmul_weights per output channel, then q * scale (src/next_milestones.cpp:611-637).
+void int8_round_trip(void* w, long long n, int k, cudaStream_t s) {
+    constexpr long long kRowsPerPass = 1 << 16;  // bounds the int8 scratch
+    for (long long first = 0; first < n; first += kRowsPerPass) {
+        const int rows = static_cast<int>(std::min(kRowsPerPass, n - first));
+        DeviceBuffer q(static_cast<size_t>(sfb_tiled_weight_elems(rows, k))),
+            scales(static_cast<size_t>(ceil_div(rows, 128)) * 128 * sizeof(float));
+        cuda_check(cudaMemsetAsync(scales.get(), 0, static_cast<size_t>(ceil_div(rows, 128)) * 128 * sizeof(float), s), "scale clear");
+        char* slab = static_cast<char*>(w) + static_cast<size_t>(first) * k * 2;
+        throw_on(sfb_k_quantize_weight_int8(slab, q.get(), scales.as<float>(), rows, k, s));
+        throw_on(sfb_k_dequantize_weight_int8(q.get(), scales.as<float>(), slab, rows, k, s));
+        cuda_check(cudaStreamSynchronize(s), "weight quantization");
+    }
+}
+
+sfb_status moe_execute(const sfb_moe_config* config, const float* input, int tokens, const float* w1,
+                       const float* w3, const float* w2, const int* expert_ids, const float* expert_weights,
+                       const int* counts, int dtype, int gemm_backend, bool int8, float* out, double* milliseconds);
+}  // namespace
+
 sfb_status sfb_moe_execute(const sfb_moe_config* config, const float* input, int tokens, const float* w1,
                            const float* w3, const float* w2, const int* expert_ids, const float* expert_weights,
                            const int* counts, int dtype, int gemm_backend, float* out, double* milliseconds) {
+    return moe_execute(config, input, tokens, w1, w3, w2, expert_ids, expert_weights, counts, dtype, gemm_backend, false,
+                       out, milliseconds);
+}
+
+sfb_status sfb_moe_execute_quantized(const sfb_moe_config* config, const float* input, int tokens, const float* w1,
+                                     const float* w3, const float* w2, const int* expert_ids,
+                                     const float* expert_weights, const int* counts, int per_channel, int gemm_backend,
+                                     float* out, double* milliseconds) {
+    if (!per_channel) {
+        return guarded([] { throw std::invalid_argument("quantized MoE: only per-output-channel scales are built"); });
+    }
+    return moe_execute(config, input, tokens, w1, w3, w2, expert_ids, expert_weights, counts, SFB_BF16, gemm_backend, true,
+                       out, milliseconds);
+}
+
+namespace {
+sfb_status moe_execute(const sfb_moe_config* config, const float* input, int tokens, const float* w1,
+                       const float* w3, const float* w2, const int* expert_ids, const float* expert_weights,
+                       const int* counts, int dtype, int gemm_backend, bool int8, float* out, double* milliseconds) {
     return guarded([&] {
         if (!config || !input || !w1 || !w3 || !w2 || !expert_ids || !expert_weights || !counts || !out)
             throw std::invalid_argument("MoE plan has no expert kernels");
@@ -403,6 +444,10 @@ sfb_status sfb_moe_execute(const sfb_moe_config* config, const float* input, int
                 pack_weight_transposed(stage.as<float>(), I, 0, H, 0, I, d13, block, 2 * block, block, s);
                 cuda_check(cudaMemcpyAsync(stage.get(), w2 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
                 pack_weight_transposed(stage.as<float>(), H, 0, I, 0, H, w2t.as<char>() + static_cast<size_t>(e) * ee * 2, 1 << 30, 0, 0, s);
+            }
+            if (int8) {  // every row of the packed slabs is one output channel of one expert matrix
+                int8_round_trip(w13.get(), static_cast<long long>(E) * 2 * I, H, s);
+                int8_round_trip(w2t.get(), static_cast<long long>(E) * H, I, s);
             }
             timer.start(s);
             throw_on(sfb_k_moe_dispatch(x.get(), dt, ids.as<int>(), wts.as<float>(), cnt.as<int>(), tokens, H, E, K, xs.get(),
@@ -453,6 +498,7 @@ sfb_status sfb_moe_execute(const sfb_moe_config* config, const float* input, int
         fetch(result.get(), static_cast<size_t>(tokens) * H, dtype, out, s);
     });
 }
+}  // namespace
 
 sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, int split_threshold, int* tasks,
                               int capacity, int* task_count) {

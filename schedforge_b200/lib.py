@@ -124,7 +124,7 @@ EXPORTS = (
     "sfb_attention_execute sfb_attention_decode "
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "
     "sfb_paged_release sfb_paged_info sfb_paged_gather sfb_paged_decode "
-    "sfb_moe_route_topk sfb_moe_dispatch_tokens sfb_moe_execute sfb_moe_plan_tasks "
+    "sfb_moe_route_topk sfb_moe_dispatch_tokens sfb_moe_execute sfb_moe_execute_quantized sfb_moe_plan_tasks "
     "sfb_shard_columns sfb_shard_rows"
 ).split()
 

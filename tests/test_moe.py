@@ -49,6 +49,27 @@ def test_expert_ffn_fp32_matches_reference_fixture(name):
                         z["expert_weights"], z["counts"])
 
 
+@pytest.mark.parametrize("name", ["moe_small", "moe_medium"])
+def test_int8_experts_match_oracle_on_round_tripped_weights(port, name):
+    """execute_quantized_moe: bf16 arithmetic on q * scale expert weights against the oracle's fp32 MoE on the
+    same weights (2e-2 of the largest output), and inside the reference's own bar (0.2 absolute) against the
+    unquantized fixture output."""
+    c, oc, z = moe_fixture(name)
+    args = (z["expert_ids"], z["expert_weights"], z["counts"])
+    out, ms = api.execute_quantized_moe(c, z["in_input"], z["in_w1"], z["in_w3"], z["in_w2"], *args)
+    bf = lambda a: port.round_bf16(np.asarray(a, np.float32))
+    q1 = ob.int8_expert_weights(bf(z["in_w1"]), oc.experts, oc.hidden, oc.intermediate)
+    q3 = ob.int8_expert_weights(bf(z["in_w3"]), oc.experts, oc.hidden, oc.intermediate)
+    q2 = ob.int8_expert_weights(bf(z["in_w2"]), oc.experts, oc.intermediate, oc.hidden)
+    want = port.moe_reference(oc, bf(z["in_input"]), q1, q3, q2, z["expert_ids"], z["expert_weights"])
+    assert rel_err(out, want) < 2e-2
+    assert np.max(np.abs(out - z["out_reference"])) < 0.2
+    plain, _ = api.execute_moe(c, z["in_input"], z["in_w1"], z["in_w3"], z["in_w2"], *args, dtype=L.BF16)
+    assert not np.array_equal(plain, out)
+    with pytest.raises(L.InvalidArgument, match="per-output-channel"):
+        api.execute_quantized_moe(c, z["in_input"], z["in_w1"], z["in_w3"], z["in_w2"], *args, per_channel=False)
+
+
 @pytest.mark.parametrize("dtype", [L.F32, L.BF16])
 @pytest.mark.parametrize("tokens,hidden,experts,top_k,bias", [(1000, 512, 8, 2, False), (333, 260, 16, 4, True),
                                                               (4096, 1024, 8, 2, True)])

@@ -174,6 +174,31 @@ def test_importer_fixture_is_consistent(ref):
     assert want["decoder"]["operations"] == 25 and want["decoder"]["fused_qkv"] and want["decoder"]["fused_gate_up"]
 
 
+@pytest.mark.parametrize("name", ["moe_small", "moe_medium", "reference_test_shape"])
+def test_int8_expert_round_trip_reproduces_the_reference_quantized_moe(port, ref, name):
+    """quantize_moe_weights + execute_quantized_moe of the reference build against the oracle's MoE run on
+    q * scale expert weights; on the shape of the reference's own INT8 MoE test its bar (0.2) holds too."""
+    if name == "reference_test_shape":  # tests/test_schedforge.cpp:902-914 of the reference
+        c = ob.MoeConfig(8, 16, 24, 4, 2)
+        d = ref.make_moe_data(c, 91)
+        x, w1, w3, w2 = d["input"], d["w1"], d["w3"], d["w2"]
+        ids, weights, counts = ref.route_topk(c, x, d["router_weight"])
+    else:
+        z = load(name)
+        c = ob.MoeConfig(*[int(v) for v in z["config"]])
+        x, w1, w3, w2 = z["in_input"], z["in_w1"], z["in_w3"], z["in_w2"]
+        ids, weights, counts = z["expert_ids"], z["expert_weights"], z["counts"]
+    want, max_error = ref.moe_quantized(c, x, w1, w3, w2, ids, weights, counts)
+    if name == "reference_test_shape":
+        assert max_error < 0.2
+    q1 = ob.int8_expert_weights(w1, c.experts, c.hidden, c.intermediate)
+    q3 = ob.int8_expert_weights(w3, c.experts, c.hidden, c.intermediate)
+    q2 = ob.int8_expert_weights(w2, c.experts, c.intermediate, c.hidden)
+    got = port.moe_reference(c, x, q1, q3, q2, ids, weights)
+    assert np.max(np.abs(got - want)) <= 2e-5 * max(1.0, np.max(np.abs(want)))
+    assert np.max(np.abs(got - port.moe_reference(c, x, w1, w3, w2, ids, weights))) > 1e-6   # the weights did change
+
+
 @pytest.mark.parametrize("name", ["decoder_dense", "decoder_decode", "decoder_batched", "decoder_cfg1_shape"])
 def test_int8_weight_round_trip_reproduces_the_reference_quantized_layer(port, ref, name):
     """The reference's weight-only INT8 layer (quantize_decoder_weights + execute_quantized_decoder_layer)
