@@ -471,6 +471,52 @@ sfb_status sfb_decoder_optimize(const sfb_decoder_config* config, const sfb_deco
                                 sfb_optimization_result* result, sfb_plan_candidate* candidates_out, int capacity,
                                 sfb_decoder_plan** plan);
 
+/* ---- decoder benchmark matrix ---------------------------------------------------------------------
+ * realistic_decoder_profiles / benchmark_decoder_profile / write_decoder_benchmark_csv /
+ * write_decoder_plan_candidates_csv (include/schedforge/decoder_compiler.h:180-203,236-247;
+ * src/decoder_compiler.cpp:864-1060): the same 24 profiles (3 scales x {prefill 128, 512, 2048; decode over
+ * 128, 512, 2048, 4096 cached tokens} + 3 tiny MoE layers), the same estimates, synthetic data (seed 101, routing
+ * trace seed 103), evidence kinds and CSV columns.  A profile above either budget is recorded as compile-only
+ * without touching the device; the others are measured on the device plan (median of `repetitions` passes after
+ * one warm-up, host buffers), after sfb_decoder_optimize with a budget of 6 when optimize_plan != 0.
+ * CSV columns without a device counterpart keep their place: llvm_compile_ms and memory_planning_ms are 0,
+ * threads 0, placement "compact"; dispatch_ms holds the host<->device copy time of a pass. */
+#define SFB_MAX_PLAN_CANDIDATES 17
+enum { SFB_EVIDENCE_SKIPPED = 0, SFB_EVIDENCE_COMPILE_ONLY = 1, SFB_EVIDENCE_MEASURED = 2 }; /* DecoderEvidenceKind */
+typedef struct sfb_decoder_profile {
+    char name[64];
+    sfb_decoder_config config;
+    int routing;                      /* RoutingDistribution: 0 uniform, 1 moderate-skew, 2 heavy-skew */
+    uint64_t estimated_flops;
+    uint64_t estimated_weight_bytes;
+    uint64_t estimated_activation_bytes;
+} sfb_decoder_profile;
+typedef struct sfb_decoder_benchmark_record {
+    sfb_decoder_profile profile;
+    int evidence;
+    sfb_decoder_result measured;
+    double max_error;                 /* 0: the device run is not compared with a scalar layer here */
+    sfb_plan_cost plan_cost;
+    double compile_milliseconds, llvm_compile_milliseconds, memory_planning_milliseconds;
+    double optimizer_speedup, optimizer_baseline_milliseconds;
+    int hardware_measurements;
+    int candidate_count;
+    sfb_plan_candidate candidates[SFB_MAX_PLAN_CANDIDATES];
+    char selected_policy[192];
+    char note[96];
+} sfb_decoder_benchmark_record;
+int sfb_decoder_profile_count(void);
+sfb_status sfb_decoder_profile_get(int index, sfb_decoder_profile* out);
+sfb_status sfb_benchmark_decoder_profile(const sfb_decoder_profile* profile, const char* stablehlo_text,
+                                         const sfb_compile_options* options, uint64_t max_real_flops,
+                                         uint64_t max_real_weight_bytes, int optimize_plan, int repetitions,
+                                         sfb_decoder_benchmark_record* record);
+sfb_status sfb_write_decoder_benchmark_csv(const char* path, const sfb_decoder_benchmark_record* records, int count);
+sfb_status sfb_write_decoder_plan_candidates_csv(const char* path, const sfb_decoder_benchmark_record* records,
+                                                 int count);
+/* DecoderExecutablePlan::compile_milliseconds: host time of sfb_decoder_compile for this plan. */
+double sfb_decoder_compile_milliseconds(const sfb_decoder_plan* plan);
+
 /* ---- sum all-reduce over NVLink peer memory, fused with the producing GEMM -----------------------
  * Replaces, for the sharded plan, the collective that the reference does not have (it is a
  * single-process CPU library); the unfused form is the sfb_allreduce_fn hook below.
@@ -591,6 +637,12 @@ sfb_status sfb_moe_execute_quantized(const sfb_moe_config* config, const float* 
 /* plan_moe_tasks, src/moe_compiler.cpp:530-558: rows (expert, begin, end, bucket). */
 sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, int split_threshold,
                               int* tasks, int capacity, int* task_count);
+/* make_routing_trace (src/moe_compiler.cpp:457-489; distribution 0 uniform, 1 moderate-skew, 2 heavy-skew) and the
+ * input tensor of make_decoder_data (src/decoder_compiler.cpp:483-492): the reference's seeded generators
+ * (std::mt19937), so that a benchmark run here and one of the reference see the same tokens and routes. */
+sfb_status sfb_make_routing_trace(const sfb_moe_config* config, int distribution, unsigned seed, int* expert_ids,
+                                  float* expert_weights, int* counts);
+sfb_status sfb_make_decoder_input(const sfb_decoder_config* config, unsigned seed, float* input);
 
 /* Column shard of a [rows, cols] row-major host matrix / row shard, used by the
  * tensor-parallel plan build and exposed for tests: copies shard `rank` of `size`. */

@@ -526,6 +526,13 @@ class Ref(_Base):
                                                   fp(weights), ip(counts)))
         return ids, weights, counts
 
+    def decoder_profiles(self):
+        """realistic_decoder_profiles as text lines, then the headers of the two CSV writers and the
+        compile-only row of profile 14 (see sfref_decoder_profiles)."""
+        buf = C.create_string_buffer(1 << 16)
+        self._check(self.fn("decoder_profiles")(buf, len(buf)))
+        return buf.value.decode()
+
     def dispatch_tokens(self, c, x, ids, weights, counts, copy_values=True):
         x, ids, weights, counts = f32(x), i32(ids), f32(weights), i32(counts)
         tokens = ids.shape[0]

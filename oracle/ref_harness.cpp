@@ -18,6 +18,9 @@
 #include "schedforge/next_milestones.h"
 
 #include <cstring>
+#include <filesystem>
+#include <fstream>
+#include <sstream>
 #include <memory>
 #include <string>
 
@@ -719,6 +722,42 @@ int sfref_quantized_moe(const sfref_moe_config* c, const float* input, int token
         const auto result = schedforge::execute_quantized_moe(config, data, trace, weights, 0, 1);
         out(result.output, output);
         if (max_error) *max_error = result.max_error;
+    });
+}
+
+// realistic_decoder_profiles as text, one profile per line:
+// name|batch|sequence|context|hidden|intermediate|q_heads|kv_heads|head_dim|ffn|experts|top_k|routing|flops|weight_bytes|activation_bytes
+// followed by the header lines of the two CSV writers (written with no records) and the compile-only
+// row of profile 14 as the reference's own test produces it (tests/test_schedforge.cpp:927-942).
+int sfref_decoder_profiles(char* buffer, int capacity) {
+    return guarded([&] {
+        std::ostringstream out;
+        const auto profiles = schedforge::realistic_decoder_profiles();
+        for (const auto& p : profiles) {
+            const auto& c = p.config;
+            out << p.name << '|' << c.batch << '|' << c.sequence << '|' << c.context_sequence << '|' << c.hidden << '|'
+                << c.intermediate << '|' << c.query_heads << '|' << c.kv_heads << '|' << c.head_dim << '|'
+                << (c.ffn == schedforge::DecoderFFNKind::MoE ? 1 : 0) << '|' << c.experts << '|' << c.top_k << '|'
+                << schedforge::routing_distribution_name(p.routing) << '|' << p.estimated_flops << '|'
+                << p.estimated_weight_bytes << '|' << p.estimated_activation_bytes << '\n';
+        }
+        const auto dir = std::filesystem::temp_directory_path();
+        const auto slurp = [](const std::filesystem::path& path) {
+            std::ifstream in(path);
+            return std::string((std::istreambuf_iterator<char>(in)), std::istreambuf_iterator<char>());
+        };
+        schedforge::write_decoder_benchmark_csv(dir / "sfref_profiles.csv", {});
+        out << "#benchmark_header " << slurp(dir / "sfref_profiles.csv");
+        schedforge::write_decoder_plan_candidates_csv(dir / "sfref_candidates.csv", {});
+        out << "#candidates_header " << slurp(dir / "sfref_candidates.csv");
+        const auto graph = schedforge::build_decoder_layer_graph(profiles[14].config);
+        const auto record = schedforge::benchmark_decoder_profile(profiles[14], graph, 2, 1, 1, false, 1);
+        schedforge::write_decoder_benchmark_csv(dir / "sfref_profiles.csv", {record});
+        const std::string text = slurp(dir / "sfref_profiles.csv");
+        out << "#compile_only_row " << text.substr(text.find('\n') + 1);
+        const std::string all = out.str();
+        if (static_cast<int>(all.size()) + 1 > capacity) throw std::runtime_error("profile buffer too small");
+        std::memcpy(buffer, all.c_str(), all.size() + 1);
     });
 }
 

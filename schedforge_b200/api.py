@@ -358,6 +358,60 @@ def plan_moe_tasks(config, counts, split_threshold=0):
     return tasks[:n.value].copy()
 
 
+def make_routing_trace(config, distribution, seed):
+    """make_routing_trace of the reference (distribution 0 uniform, 1 moderate-skew, 2 heavy-skew)."""
+    ids = np.empty((config.tokens, config.top_k), np.int32)
+    weights = np.empty((config.tokens, config.top_k), np.float32)
+    counts = np.empty(config.experts, np.int32)
+    L.check(L.load().sfb_make_routing_trace(C.byref(config), distribution, C.c_uint(seed), _ip(ids), _fp(weights),
+                                            _ip(counts)))
+    return ids, weights, counts
+
+
+def make_decoder_input(config, seed):
+    """The input tensor make_decoder_data of the reference draws for this configuration and seed."""
+    x = np.empty((config.batch * config.sequence, config.hidden), np.float32)
+    L.check(L.load().sfb_make_decoder_input(C.byref(config), C.c_uint(seed), _fp(x)))
+    return x
+
+
+def realistic_decoder_profiles():
+    """realistic_decoder_profiles of the reference: 24 DecoderProfile records."""
+    lib = L.load()
+    out = []
+    for index in range(lib.sfb_decoder_profile_count()):
+        p = L.DecoderProfile()
+        L.check(lib.sfb_decoder_profile_get(index, C.byref(p)))
+        out.append(p)
+    return out
+
+
+def benchmark_decoder_profile(profile, stablehlo_text="", options=None, max_real_flops=1 << 62,
+                              max_real_weight_bytes=1 << 62, optimize_plan=False, repetitions=3):
+    """benchmark_decoder_profile of the reference on the device plan; returns a DecoderBenchmarkRecord."""
+    record = L.DecoderBenchmarkRecord()
+    L.check(L.load().sfb_benchmark_decoder_profile(C.byref(profile), stablehlo_text.encode() or None,
+                                                   C.byref(options) if options is not None else None,
+                                                   max_real_flops, max_real_weight_bytes, int(optimize_plan),
+                                                   repetitions, C.byref(record)))
+    return record
+
+
+def _record_array(records):
+    array = (L.DecoderBenchmarkRecord * max(1, len(records)))()
+    for i, r in enumerate(records):
+        C.memmove(C.byref(array[i]), C.byref(r), C.sizeof(L.DecoderBenchmarkRecord))
+    return array
+
+
+def write_decoder_benchmark_csv(path, records):
+    L.check(L.load().sfb_write_decoder_benchmark_csv(str(path).encode(), _record_array(records), len(records)))
+
+
+def write_decoder_plan_candidates_csv(path, records):
+    L.check(L.load().sfb_write_decoder_plan_candidates_csv(str(path).encode(), _record_array(records), len(records)))
+
+
 def shard_columns(a, rank, size):
     a = _f32(a)
     out = np.empty((a.shape[0], a.shape[1] // size), np.float32)

@@ -108,6 +108,10 @@ sfb_status sfb_decoder_optimize(const sfb_decoder_config* config, const sfb_deco
 
 void sfb_decoder_destroy(sfb_decoder_plan* plan) { delete plan; }
 
+double sfb_decoder_compile_milliseconds(const sfb_decoder_plan* plan) {
+    return plan && plan->plan ? plan->plan->compile_milliseconds : 0.0;
+}
+
 sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float* output,
                                const int* trace_expert_ids, const float* trace_expert_weights,
                                const int* trace_counts, sfb_decoder_result* result) {

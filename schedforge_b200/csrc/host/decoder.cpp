@@ -401,7 +401,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         if (moe) throw std::invalid_argument("INT8 decoder currently requires dense FFN weights");
         struct Item { void* w; int n, k; };
         const Item items[4] = {{m.wqkv, m.qkv_l, H}, {m.wo, H, m.hidden_l}, {m.wgu, 2 * I, H}, {m.wd, H, I}};
-        const bool keep_int8 = T <= 128 && plan->policy.gemm_backend != SFB_GEMM_SIMT && fused;
+        const bool keep_int8 = T <= 128 && plan->policy.gemm_backend != SFB_GEMM_SIMT && fused && m.swiglu_block == 64;
         std::size_t bytes = 0;
         for (const auto& item : items)
             bytes += (static_cast<std::size_t>(sfb_tiled_weight_elems(item.n, item.k)) + 255) / 256 * 256 +
@@ -437,7 +437,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         reblock(m.wqkv, m.qkv_l, H);
         reblock(m.wo, H, m.hidden_l);
         if (!moe) {
-            reblock(m.wgu, 2 * I, H);
+            if (!fused || m.swiglu_block == 64) reblock(m.wgu, 2 * I, H);  // the SwiGLU epilogue of the few-row kernel pairs 64-column blocks
             reblock(m.wd, H, I);
         }
         for (auto& constant : plan->constants)

@@ -92,6 +92,26 @@ class DecoderResult(C.Structure):
                [("kernel_launches", C.c_uint64)]
 
 
+class DecoderProfile(C.Structure):
+    _fields_ = [("name", C.c_char * 64), ("config", DecoderConfig), ("routing", C.c_int),
+                ("estimated_flops", C.c_uint64), ("estimated_weight_bytes", C.c_uint64),
+                ("estimated_activation_bytes", C.c_uint64)]
+
+
+MAX_PLAN_CANDIDATES = 17
+EVIDENCE_SKIPPED, EVIDENCE_COMPILE_ONLY, EVIDENCE_MEASURED = 0, 1, 2
+
+
+class DecoderBenchmarkRecord(C.Structure):
+    _fields_ = [("profile", DecoderProfile), ("evidence", C.c_int), ("measured", DecoderResult),
+                ("max_error", C.c_double), ("plan_cost", PlanCost), ("compile_milliseconds", C.c_double),
+                ("llvm_compile_milliseconds", C.c_double), ("memory_planning_milliseconds", C.c_double),
+                ("optimizer_speedup", C.c_double), ("optimizer_baseline_milliseconds", C.c_double),
+                ("hardware_measurements", C.c_int), ("candidate_count", C.c_int),
+                ("candidates", PlanCandidate * MAX_PLAN_CANDIDATES), ("selected_policy", C.c_char * 192),
+                ("note", C.c_char * 96)]
+
+
 class GraphSummary(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("operations", "values", "inputs", "matmuls", "fused_qkv",
                                        "fused_gate_up", "fused_rope")]
@@ -125,6 +145,9 @@ EXPORTS = (
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "
     "sfb_paged_release sfb_paged_info sfb_paged_gather sfb_paged_decode "
     "sfb_moe_route_topk sfb_moe_dispatch_tokens sfb_moe_execute sfb_moe_execute_quantized sfb_moe_plan_tasks "
+    "sfb_make_routing_trace sfb_make_decoder_input sfb_decoder_profile_count sfb_decoder_profile_get "
+    "sfb_benchmark_decoder_profile sfb_write_decoder_benchmark_csv sfb_write_decoder_plan_candidates_csv "
+    "sfb_decoder_compile_milliseconds "
     "sfb_shard_columns sfb_shard_rows"
 ).split()
 
@@ -158,6 +181,8 @@ def load():
     lib.sfb_version.restype = C.c_char_p
     lib.sfb_launch_count.restype = C.c_uint64
     lib.sfb_tiled_weight_elems.restype = C.c_int64
+    lib.sfb_decoder_compile_milliseconds.restype = C.c_double
+    lib.sfb_benchmark_decoder_profile.argtypes = [vp, C.c_char_p, vp, C.c_uint64, C.c_uint64, C.c_int, C.c_int, vp]
     for name in ("sfb_attention_decode_workspace", "sfb_moe_dispatch_scratch_bytes",
                  "sfb_decoder_workspace_bytes", "sfb_gemm_stream_workspace_bytes", "sfb_decoder_peer_bytes"):
         if hasattr(lib, name):

@@ -116,6 +116,16 @@ def main():
                "canonical_moe": ref.canonical_graph_names(ob.decoder_config(moe=True))}
     with open(os.path.join(HERE, "importer.json"), "w") as f:
         json.dump(summary, f, indent=1, sort_keys=True)
+    # the benchmark matrix: 24 profiles with their estimates, both CSV headers, one compile-only row
+    with open(os.path.join(HERE, "decoder_profiles.txt"), "w") as f:
+        f.write(ref.decoder_profiles())
+    # make_routing_trace for the three distributions (benchmark_decoder_profile uses seed 103)
+    traces = {}
+    for distribution, experts in ((0, 8), (1, 8), (2, 16)):
+        cfg = ob.MoeConfig(32, 512, 1376, experts, 2)
+        ids, weights, counts = ref.make_routing_trace(cfg, distribution, 103)
+        traces.update({f"ids{distribution}": ids, f"weights{distribution}": weights, f"counts{distribution}": counts})
+    np.savez(os.path.join(HERE, "routing_traces.npz"), **traces)
     # bf16 rounding known answers
     x = np.array([1.0, 1.00390625, 1.01171875, -2.5e-3, 3.1415927, 65504.0, 1e-30, 0.1], np.float32)
     np.savez(os.path.join(HERE, "bf16_round.npz"), x=x, y=ref.round_bf16(x))

@@ -113,8 +113,10 @@ def test_bf16_dense_prefill(port, fuse, backend):
     plan.close()
 
 
-def test_bf16_cfg1_shape_with_ragged_ffn_width(port):
+@pytest.mark.parametrize("intermediate", [688, 1376])   # 2*I a multiple of 64 or not: blocked or row-major gate/up
+def test_bf16_cfg1_shape_with_ragged_ffn_width(port, intermediate):
     kw, _ = baseline_config1()
+    kw = dict(kw, intermediate=intermediate)
     oc, c, data = bf16_case(port, 2, **kw)
     want = port.decoder_layer(oc, data, native=True)
     plan = api.DecoderCompiler.compile(c, weights_of(data))
@@ -324,3 +326,32 @@ def test_weight_only_int8_plan_matches_the_quantized_oracle(port, kw):
     plan.close()
     with pytest.raises(L.SfbError):
         api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(weight_int8=True, dtype=L.F32))
+
+
+def test_benchmark_profile_matrix_measures_on_the_device(port, tmp_path):
+    """benchmark_decoder_profile on the device plan: a prefill, a decode and a skewed MoE profile of the reference's
+    matrix, one of them through the plan optimizer, and one profile above the budget; both CSV files carry one
+    row per record / candidate."""
+    profiles = {p.name.decode(): p for p in api.realistic_decoder_profiles()}
+    records = [api.benchmark_decoder_profile(profiles["tiny-prefill-s128"], optimize_plan=True, repetitions=2),
+               api.benchmark_decoder_profile(profiles["tiny-decode-kv512"], repetitions=2),
+               api.benchmark_decoder_profile(profiles["tiny-moe-heavy-skew"], repetitions=2),
+               api.benchmark_decoder_profile(profiles["large-prefill-s2048"], max_real_flops=1 << 30)]
+    for r in records[:3]:
+        assert r.evidence == L.EVIDENCE_MEASURED and r.measured.milliseconds > 0 and r.measured.tokens_per_second > 0
+        assert r.plan_cost.workspace_bytes > 0 and r.compile_milliseconds > 0
+        assert r.selected_policy.decode().startswith("decoder.policy layout=")
+    assert records[0].candidate_count == 17 and records[0].hardware_measurements >= 5 and records[0].optimizer_speedup > 0
+    assert "attention=split-kv-decode" in records[1].selected_policy.decode()
+    assert records[3].evidence == L.EVIDENCE_COMPILE_ONLY and records[3].measured.milliseconds == 0.0
+    api.write_decoder_benchmark_csv(tmp_path / "decoder.csv", records)
+    lines = (tmp_path / "decoder.csv").read_text().splitlines()
+    header = lines[0].split(",")
+    assert len(lines) == 5 and all(len(l.split(",")) == len(header) for l in lines[1:])
+    row = dict(zip(header, lines[3].split(",")))
+    assert row["profile"] == "tiny-moe-heavy-skew" and row["ffn"] == "moe" and row["experts"] == "16"
+    assert row["routing"] == "heavy-skew" and float(row["latency_ms"]) > 0 and row["evidence"] == "measured"
+    api.write_decoder_plan_candidates_csv(tmp_path / "candidates.csv", records)
+    cand = (tmp_path / "candidates.csv").read_text().splitlines()
+    assert len(cand) == 1 + 17 and sum(l.split(",")[2] == "1" for l in cand[1:]) >= 1
+    assert sum(l.split(",")[3] == "1" for l in cand[1:]) >= 5                    # measured candidates

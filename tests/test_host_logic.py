@@ -116,3 +116,61 @@ def test_weight_shards():
     assert np.array_equal(api.shard_rows(a, 2, 3), a[4:6])
     with pytest.raises(L.InvalidArgument):
         api.shard_columns(a, 0, 3)
+
+
+# ---- decoder benchmark matrix (realistic_decoder_profiles / CSV writers) ---------------------------
+def golden_profiles():
+    lines = open(os.path.join(GOLDEN, "decoder_profiles.txt")).read().splitlines()
+    rows = [l.split("|") for l in lines if not l.startswith("#")]
+    tagged = {l.split(" ", 1)[0]: l.split(" ", 1)[1] for l in lines if l.startswith("#")}
+    return rows, tagged
+
+
+def test_profile_matrix_matches_reference_fixture():
+    rows, _ = golden_profiles()
+    profiles = api.realistic_decoder_profiles()
+    assert len(profiles) == len(rows) == 24
+    names = {0: "uniform", 1: "moderate-skew", 2: "heavy-skew"}
+    for p, row in zip(profiles, rows):
+        c = p.config
+        got = [p.name.decode(), c.batch, c.sequence, c.context_sequence, c.hidden, c.intermediate, c.query_heads,
+               c.kv_heads, c.head_dim, c.ffn_moe, c.experts, c.top_k, names[p.routing], p.estimated_flops,
+               p.estimated_weight_bytes, p.estimated_activation_bytes]
+        assert [str(v) for v in got] == row
+    assert profiles[0].config.hidden == 512 and profiles[14].config.hidden == 4096   # the reference's own checks
+
+
+def test_benchmark_csv_schemas_and_compile_only_row_match_reference(tmp_path):
+    _, tagged = golden_profiles()
+    profile = api.realistic_decoder_profiles()[14]
+    record = api.benchmark_decoder_profile(profile, max_real_flops=1, max_real_weight_bytes=1)   # no device work
+    assert record.evidence == L.EVIDENCE_COMPILE_ONLY and record.measured.milliseconds == 0.0
+    assert record.profile.estimated_weight_bytes > 0
+    path = tmp_path / "out" / "decoder.csv"
+    api.write_decoder_benchmark_csv(path, [record])
+    header, row = path.read_text().splitlines()
+    assert header == tagged["#benchmark_header"]
+    assert "profile,evidence" in header and "tokens_per_second" in header and "compile-only" in row
+    want = tagged["#compile_only_row"].split(",")
+    got = row.split(",")
+    assert len(got) == len(want) == len(header.split(","))
+    # all columns but the reference's host plan figures (workspace, compile and memory planning times)
+    skip = {header.split(",").index(n) for n in ("workspace_bytes", "compile_ms", "memory_planning_ms", "memory_planning_pct")}
+    assert [g for i, g in enumerate(got) if i not in skip] == [w for i, w in enumerate(want) if i not in skip]
+    api.write_decoder_plan_candidates_csv(tmp_path / "candidates.csv", [record])
+    assert (tmp_path / "candidates.csv").read_text().splitlines() == [tagged["#candidates_header"]]
+    api.write_decoder_benchmark_csv(tmp_path / "empty.csv", [])
+    assert (tmp_path / "empty.csv").read_text().splitlines() == [tagged["#benchmark_header"]]
+
+
+def test_seeded_generators_match_reference_fixtures():
+    z = np.load(os.path.join(GOLDEN, "routing_traces.npz"))
+    for distribution, experts in ((0, 8), (1, 8), (2, 16)):
+        ids, weights, counts = api.make_routing_trace(api.moe_config(32, 512, 1376, experts, 2), distribution, 103)
+        assert np.array_equal(ids, z[f"ids{distribution}"]) and np.array_equal(counts, z[f"counts{distribution}"])
+        assert np.array_equal(weights, z[f"weights{distribution}"])
+    dense = np.load(os.path.join(GOLDEN, "decoder_dense.npz"))     # make_decoder_data(config, 81)
+    c = api.decoder_config(batch=1, sequence=4, hidden=16, intermediate=32, query_heads=4, kv_heads=2, head_dim=4)
+    assert np.array_equal(api.make_decoder_input(c, 81).ravel(), dense["in_input"].ravel())
+    with pytest.raises(L.InvalidArgument):
+        api.make_routing_trace(api.moe_config(4, 8, 8, 2, 3), 0, 1)
