@@ -1,4 +1,4 @@
-// Flash-attention prefill on the 5th-generation tensor cores (bf16, head_dim = 128).
+// Flash-attention prefill on the 5th-generation tensor cores (bf16, head_dim = 128 or 64).
 //
 // One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row Q tiles and walks
 // the keys in tiles of 128.  384 threads, 320 of them in four roles:
@@ -28,17 +28,22 @@
 namespace sfb {
 namespace {
 
-constexpr int D = 128;          // head_dim == head_dim_value
 constexpr int QT = 128;         // rows per Q tile
 constexpr int KT = 128;         // keys per KV tile
 constexpr int KSTAGES = 2;
 constexpr int VSTAGES = 2;
 constexpr int kThreads = 384;         // three warpgroups; warps 10 and 11 only take part in the register hand-over
-constexpr int kQBytes = QT * D * 2;        // 32 KiB per Q tile (two 16 KiB halves of 64 dims)
-constexpr int kKBytes = KT * D * 2;        // 32 KiB (two halves of 64 dims)
-constexpr int kVBytes = KT * D * 2;        // 32 KiB (two halves of 64 value dims)
-constexpr int kSmemBytes = 2 * kQBytes + KSTAGES * kKBytes + VSTAGES * kVBytes + 512 + 1024;
-constexpr uint32_t kTmemCols = 512;        // S_t (and P_t over its first 64 columns) at t*128; O_t at 256 + t*128
+constexpr int kHalfBytes = 128 * 64 * 2;   // 128 rows of 64 dims: the unit every Q, K and V tile is made of
+// D = head_dim == head_dim_value, 128 or 64: a tile is D / 64 such halves (32 or 16 KiB)
+template <int D>
+struct Fa {
+    static constexpr int kHalves = D / 64;
+    static constexpr int kQBytes = kHalves * kHalfBytes;
+    static constexpr int kKBytes = kHalves * kHalfBytes;
+    static constexpr int kVBytes = kHalves * kHalfBytes;
+    static constexpr int kSmemBytes = 2 * kQBytes + KSTAGES * kKBytes + VSTAGES * kVBytes + 512 + 1024;
+};
+constexpr uint32_t kTmemCols = 512;        // S_t (and P_t over its first 64 columns) at t*128; O_t at 256 + t*D
 constexpr uint32_t kOCol = 256;
 constexpr uint32_t kCodeAttn = 0x10;
 constexpr float kRescaleThreshold = 8.0F;  // log2 units
@@ -63,14 +68,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                                  const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ FaParams p) {
+    constexpr int kHalves = Fa<D>::kHalves, kQBytes = Fa<D>::kQBytes, kKBytes = Fa<D>::kKBytes, kVBytes = Fa<D>::kVBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_smem = smem;                                  // [2][2 halves][128][64]
-    uint8_t* k_smem = q_smem + 2 * kQBytes;                  // [KSTAGES][2 halves][128 keys][64 dims]
-    uint8_t* v_smem = k_smem + KSTAGES * kKBytes;            // [VSTAGES][2 halves][128 keys][64 dv]
+    uint8_t* q_smem = smem;                                  // [2][halves][128][64]
+    uint8_t* k_smem = q_smem + 2 * kQBytes;                  // [KSTAGES][halves][128 keys][64 dims]
+    uint8_t* v_smem = k_smem + KSTAGES * kKBytes;            // [VSTAGES][halves][128 keys][64 dv]
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + VSTAGES * kVBytes);
     uint64_t* q_full = bars;                 // [2]
     uint64_t* k_full = bars + 2;             // [KSTAGES]
@@ -147,8 +154,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 if (n_tiles[t] == 0) continue;
                 const uint32_t bar = ptx::smem_u32(&q_full[t]);
                 ptx::mbar_expect_tx(bar, kQBytes);
-                ptx::tma_load_2d(ptx::smem_u32(q_smem + t * kQBytes), &tma_q, bar, 0, q_row0 + t * QT);
-                ptx::tma_load_2d(ptx::smem_u32(q_smem + t * kQBytes + kQBytes / 2), &tma_q, bar, 64, q_row0 + t * QT);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h)
+                    ptx::tma_load_2d(ptx::smem_u32(q_smem + t * kQBytes + h * kHalfBytes), &tma_q, bar, 64 * h, q_row0 + t * QT);
             }
             for (int j = 0; j < n_max; ++j) {
                 const int ks = j % KSTAGES, vs = j % VSTAGES;
@@ -156,13 +164,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 if (!ptx::mbar_wait(ptx::smem_u32(&k_empty[ks]), ((j / KSTAGES) & 1) ^ 1, abort_flag, p.status, kCodeAttn | 1)) break;
                 const uint32_t kb = ptx::smem_u32(&k_full[ks]);
                 ptx::mbar_expect_tx(kb, kKBytes);
-                ptx::tma_load_2d(ptx::smem_u32(k_smem + ks * kKBytes), &tma_k, kb, 0, row);
-                ptx::tma_load_2d(ptx::smem_u32(k_smem + ks * kKBytes + kKBytes / 2), &tma_k, kb, 64, row);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h)
+                    ptx::tma_load_2d(ptx::smem_u32(k_smem + ks * kKBytes + h * kHalfBytes), &tma_k, kb, 64 * h, row);
                 if (!ptx::mbar_wait(ptx::smem_u32(&v_empty[vs]), ((j / VSTAGES) & 1) ^ 1, abort_flag, p.status, kCodeAttn | 1)) break;
                 const uint32_t vb = ptx::smem_u32(&v_full[vs]);
                 ptx::mbar_expect_tx(vb, kVBytes);
-                ptx::tma_load_2d(ptx::smem_u32(v_smem + vs * kVBytes), &tma_v, vb, 0, row);
-                ptx::tma_load_2d(ptx::smem_u32(v_smem + vs * kVBytes + kVBytes / 2), &tma_v, vb, 64, row);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h)
+                    ptx::tma_load_2d(ptx::smem_u32(v_smem + vs * kVBytes + h * kHalfBytes), &tma_v, vb, 64 * h, row);
             }
         }
     } else if (warp == 9) {
@@ -175,8 +185,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 const uint32_t ka = ptx::smem_u32(k_smem + (j % KSTAGES) * kKBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t da = ptx::umma_desc_k_sw128(qa + (kk / 4) * (kQBytes / 2) + (kk % 4) * 32);
-                    const uint64_t db = ptx::umma_desc_k_sw128(ka + (kk / 4) * (kKBytes / 2) + (kk % 4) * 32);
+                    const uint64_t da = ptx::umma_desc_k_sw128(qa + (kk / 4) * kHalfBytes + (kk % 4) * 32);
+                    const uint64_t db = ptx::umma_desc_k_sw128(ka + (kk / 4) * kHalfBytes + (kk % 4) * 32);
                     ptx::umma_bf16(tmem_base + t * KT, da, db, idesc_qk, kk != 0);
                 }
                 ptx::umma_commit(ptx::smem_u32(&s_full[t]));
@@ -185,7 +195,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
                 const uint32_t va = ptx::smem_u32(v_smem + (j % VSTAGES) * kVBytes);
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
-                    const uint64_t db = ptx::umma_desc_mn_sw128(va + kk * 16 * 128, kVBytes / 2, 1024);
+                    const uint64_t db = ptx::umma_desc_mn_sw128(va + kk * 16 * 128, kHalfBytes, 1024);
                     ptx::umma_bf16_ts(tmem_base + kOCol + t * D, tmem_base + t * KT + kk * 8, db, idesc_pv, (j | kk) != 0);
                 }
             };
@@ -358,16 +368,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q, cons
 }  // namespace
 
 bool attention_prefill_tcgen05_supported(const sfb_attention_args& a) {
-    return a.dtype == SFB_BF16 && a.head_dim == D && a.head_dim_value == D &&
+    return a.dtype == SFB_BF16 && (a.head_dim == 128 || a.head_dim == 64) && a.head_dim_value == a.head_dim &&
            (reinterpret_cast<uintptr_t>(a.q) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.key) & 15) == 0 &&
            (reinterpret_cast<uintptr_t>(a.value) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
 }
 
-sfb_status attention_prefill_tcgen05(const sfb_attention_args& a, cudaStream_t stream) {
+namespace {
+template <int D>
+sfb_status launch_prefill(const sfb_attention_args& a, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        SFB_CUDA(cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemBytes));
+        SFB_CUDA(cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Fa<D>::kSmemBytes));
         configured = true;
     }
     CUtensorMap map_q, map_k, map_v;
@@ -389,8 +401,13 @@ sfb_status attention_prefill_tcgen05(const sfb_attention_args& a, cudaStream_t s
     p.status = device_status_word();
     const int q_blocks = ceil_div(a.seq_q, 2 * QT);
     const int grid = a.batch * a.q_heads * q_blocks;
-    attention_prefill_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    attention_prefill_tcgen05_kernel<D><<<grid, kThreads, Fa<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
     return check_launch("attention_prefill_tcgen05");
+}
+}  // namespace
+
+sfb_status attention_prefill_tcgen05(const sfb_attention_args& a, cudaStream_t stream) {
+    return a.head_dim == 64 ? launch_prefill<64>(a, stream) : launch_prefill<128>(a, stream);
 }
 
 }  // namespace sfb

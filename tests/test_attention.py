@@ -212,16 +212,17 @@ def test_paged_append_kernel_then_decode_roundtrip(dev, port):
     (1, 8, 2, 1000, 1000, True, 6.0, True),    # long rows with large scores: running-max growth
     (3, 2, 2, 70, 70, True, 1.0, False),       # less than one Q tile
 ])
-def test_prefill_bf16_head_dim_128(dev, port, backend, batch, hq, hkv, sq, sk, causal, qscale, token_major):
+@pytest.mark.parametrize("d", [128, 64])
+def test_prefill_bf16_head_dim_128_and_64(dev, port, backend, batch, hq, hkv, sq, sk, causal, qscale, token_major, d):
     rng = np.random.default_rng(sq + sk)
-    q = port.round_bf16((rng.standard_normal((batch, hq, sq, 128)) * qscale).astype(np.float32))
-    k = port.round_bf16(rng.standard_normal((batch, hkv, sk, 128)).astype(np.float32))
-    v = port.round_bf16(rng.standard_normal((batch, hkv, sk, 128)).astype(np.float32))
-    oc = ob.AttentionConfig(batch, hq, hkv, sq, sk, 128, 128, int(causal), 0.0)
+    q = port.round_bf16((rng.standard_normal((batch, hq, sq, d)) * qscale).astype(np.float32))
+    k = port.round_bf16(rng.standard_normal((batch, hkv, sk, d)).astype(np.float32))
+    v = port.round_bf16(rng.standard_normal((batch, hkv, sk, d)).astype(np.float32))
+    oc = ob.AttentionConfig(batch, hq, hkv, sq, sk, d, d, int(causal), 0.0)
     want = port.attention_reference(oc, q, k, v)
     dq, dk, dv = dev.bf16(q), dev.bf16(k), dev.bf16(v)
-    out = dev.zeros((batch * sq * hq * 128,), dev.torch.bfloat16)
-    a = L.AttentionArgs(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), out.data_ptr(), batch, hq, hkv, sq, sk, 128, 128,
+    out = dev.zeros((batch * sq * hq * d,), dev.torch.bfloat16)
+    a = L.AttentionArgs(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), out.data_ptr(), batch, hq, hkv, sq, sk, d, d,
                         int(causal), 0.0, int(token_major), L.BF16, backend)
     L.check(L.load().sfb_k_attention_prefill(C.byref(a), C.c_void_p(dev.stream())))
     dev.torch.cuda.synchronize()
@@ -229,7 +230,7 @@ def test_prefill_bf16_head_dim_128(dev, port, backend, batch, hq, hkv, sq, sk, c
     L.check(L.load().sfb_device_status(C.byref(word)))
     assert word.value == 0, f"device wait timed out, status word {word.value:#x}"
     got = dev.np(out)
-    got = got.reshape(batch, sq, hq, 128).transpose(0, 2, 1, 3) if token_major else got.reshape(batch, hq, sq, 128)
+    got = got.reshape(batch, sq, hq, d).transpose(0, 2, 1, 3) if token_major else got.reshape(batch, hq, sq, d)
     assert rel_err(got, want) < 2e-2
 
 
