@@ -252,6 +252,11 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     m.planner = WorkspacePlanner(plan->policy.reuse_workspace);
     const bool bf = m.dtype == SFB_BF16;
     const bool fused = plan->policy.fuse_epilogues;
+    // A dense FFN width that is no multiple of 64 would send gate/up (no SwiGLU block the tensor-core epilogue
+    // accepts) to the CUDA-core GEMM: the packed weights get zero columns up to the next multiple instead.
+    // SiLU(0) * 0 = 0 in the padded activation columns meets zero rows of the padded down projection.
+    const bool pad_ffn = bf && fused && !moe && G == 1 && c.intermediate % 64 != 0 && opt.gemm_backend != SFB_GEMM_SIMT;
+    if (pad_ffn) m.I_l = (c.intermediate + 63) / 64 * 64;
     const int T = m.T, H = m.H, I = m.I_l, D = m.D;
     auto pick_block = [&](int width) {  // gate/up interleave that the tensor-core epilogue accepts
         if (T > 128 && width % 128 == 0) return 128;
@@ -310,7 +315,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         h2d(m.rope_sin, sn.data() + first_position * row, static_cast<std::size_t>(c.sequence) * row * 4);
     }
     // fp32 staging buffer on the device for the transpose/convert packer
-    std::size_t staging_elems = static_cast<std::size_t>(H) * std::max({H, c.intermediate, m.qkv_l});
+    std::size_t staging_elems = static_cast<std::size_t>(H) * std::max({H, c.intermediate, m.I_l, m.qkv_l});
     DeviceBuffer staging;
     if (bf) staging.allocate(staging_elems * 4);
     const int whole = 1 << 30;
@@ -350,7 +355,20 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         const float* wg = need(data.gate_weight, "gate_weight");
         const float* wu = need(data.up_weight, "up_weight");
         const float* wd_h = need(data.down_weight, "down_weight");
-        const int Ifull = c.intermediate;
+        int Ifull = c.intermediate;
+        std::vector<float> wg_padded, wu_padded, wd_padded;
+        if (pad_ffn) {
+            wg_padded.assign(static_cast<std::size_t>(H) * I, 0.0F);
+            wu_padded.assign(static_cast<std::size_t>(H) * I, 0.0F);
+            wd_padded.assign(static_cast<std::size_t>(I) * H, 0.0F);
+            for (int row = 0; row < H; ++row) {
+                std::memcpy(wg_padded.data() + static_cast<std::size_t>(row) * I, wg + static_cast<std::size_t>(row) * Ifull, sizeof(float) * Ifull);
+                std::memcpy(wu_padded.data() + static_cast<std::size_t>(row) * I, wu + static_cast<std::size_t>(row) * Ifull, sizeof(float) * Ifull);
+            }
+            std::memcpy(wd_padded.data(), wd_h, sizeof(float) * static_cast<std::size_t>(Ifull) * H);
+            wg = wg_padded.data(); wu = wu_padded.data(); wd_h = wd_padded.data();
+            Ifull = I;
+        }
         if (bf) {
             pack(wg, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, 0);
             pack(wu, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, m.swiglu_block);
@@ -364,7 +382,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             h2d(m.wgu, packed.data(), packed.size() * 4);
             h2d(m.wd, wd_h + static_cast<std::size_t>(r) * I * H, static_cast<std::size_t>(I) * H * 4);
         }
-        plan->constants.push_back({"packed_gate_up_weight", {H, Ifull, Ifull}, {H, 2 * Ifull},
+        plan->constants.push_back({"packed_gate_up_weight", {H, c.intermediate, c.intermediate}, {H, 2 * Ifull},
                                    bf ? "gate_up_interleaved_" + std::to_string(m.swiglu_block) : "gate_up_concat_f32",
                                    static_cast<std::size_t>(H) * 2 * I * wsz});
     } else {

@@ -270,6 +270,16 @@ sfb_status sfb_benchmark_decoder_profile(const sfb_decoder_profile* profile, con
         struct Guard { sfb_decoder_plan* p; ~Guard() { sfb_decoder_destroy(p); } } guard{plan};
         std::snprintf(record->selected_policy, sizeof(record->selected_policy), "%s", policy_text(chosen, c).c_str());
         std::vector<float> output(data.input.size());
+        // page-lock the two buffers that cross PCIe on every pass (a failed registration only costs speed)
+        struct Pinned {
+            void* p;
+            bool ok;
+            Pinned(const void* ptr, std::size_t bytes)
+                : p(const_cast<void*>(ptr)), ok(cudaHostRegister(p, bytes, cudaHostRegisterDefault) == cudaSuccess) {
+                if (!ok) (void)cudaGetLastError();
+            }
+            ~Pinned() { if (ok) cudaHostUnregister(p); }
+        } pin_in(data.input.data(), data.input.size() * sizeof(float)), pin_out(output.data(), output.size() * sizeof(float));
         const int* ids = data.trace_ids.empty() ? nullptr : data.trace_ids.data();
         const float* weights = data.trace_weights.empty() ? nullptr : data.trace_weights.data();
         const int* counts = data.trace_counts.empty() ? nullptr : data.trace_counts.data();
