@@ -1,4 +1,4 @@
-"""Two-GPU run of the sharded plans with NCCL (skipped on a single-GPU box)."""
+"""Run of the sharded plans on 2, 4 or 8 GPUs with NCCL and with the fused peer all-reduce (skipped on a single-GPU box)."""
 import os
 import subprocess
 import sys
@@ -8,13 +8,14 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_two_rank_sharded_layers_match_the_oracle():
+def test_sharded_layers_on_all_gpus_match_the_oracle():
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    ranks = 8 if torch.cuda.device_count() >= 8 else 4 if torch.cuda.device_count() >= 4 else 2
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+    result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks),
                              "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(here, "mgpu_worker.py")],
                             capture_output=True, text=True, timeout=600, env=env)
     assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
