@@ -429,6 +429,15 @@ sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float
                                const int* trace_expert_ids, const float* trace_expert_weights,
                                const int* trace_counts, sfb_decoder_result* result);
 
+/* execute_decoder_layer for a rank of a sharded plan that owns rows [row_begin, row_begin + row_count) of the
+ * [T,H] input: only these rows cross this rank's PCIe link (input_rows in, the same rows of the output out).
+ * The ranks' ranges must be disjoint and cover all rows; the plan's all-reduce hook gathers the input (each
+ * row is zero on every other rank, so the sum is exact).  bf16 plans with a hook; the full range works on
+ * any plan and equals sfb_decoder_execute without the row-chunk pipeline.  No counterpart in the reference,
+ * which is a single-process library. */
+sfb_status sfb_decoder_execute_rows(sfb_decoder_plan* plan, const float* input_rows, float* output_rows,
+                                    int row_begin, int row_count, sfb_decoder_result* result);
+
 /* The same layer with the input already resident (last sfb_decoder_execute /
  * sfb_decoder_upload_input) and the output left on the device: kernels only. */
 sfb_status sfb_decoder_upload_input(sfb_decoder_plan* plan, const float* input);

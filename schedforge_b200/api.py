@@ -91,6 +91,19 @@ class DecoderExecutablePlan:
         L.check(L.load().sfb_decoder_execute(self._h, C.c_void_p(in_ptr), C.c_void_p(out_ptr), None, None, None,
                                              C.byref(result) if result is not None else None))
 
+    def execute_rows_ptr(self, in_ptr, out_ptr, row_begin, row_count, result=None):
+        """This rank's rows of the input in, the same rows of the output out (raw host addresses); see
+        sfb_decoder_execute_rows."""
+        L.check(L.load().sfb_decoder_execute_rows(self._h, C.c_void_p(in_ptr), C.c_void_p(out_ptr), row_begin, row_count,
+                                                  C.byref(result) if result is not None else None))
+
+    def execute_rows(self, x_rows, row_begin):
+        x_rows = _f32(x_rows)
+        out = np.empty_like(x_rows)
+        result = L.DecoderResult()
+        self.execute_rows_ptr(x_rows.ctypes.data, out.ctypes.data, row_begin, x_rows.shape[0], result)
+        return out, result
+
     def upload_input(self, x):
         x = _f32(x)
         L.check(L.load().sfb_decoder_upload_input(self._h, _fp(x)))

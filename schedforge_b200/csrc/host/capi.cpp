@@ -108,6 +108,14 @@ sfb_status sfb_decoder_optimize(const sfb_decoder_config* config, const sfb_deco
 
 void sfb_decoder_destroy(sfb_decoder_plan* plan) { delete plan; }
 
+sfb_status sfb_decoder_execute_rows(sfb_decoder_plan* plan, const float* input_rows, float* output_rows, int row_begin,
+                                    int row_count, sfb_decoder_result* result) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->execute_rows(input_rows, output_rows, row_begin, row_count, result);
+    });
+}
+
 double sfb_decoder_compile_milliseconds(const sfb_decoder_plan* plan) {
     return plan && plan->plan ? plan->plan->compile_milliseconds : 0.0;
 }

@@ -902,6 +902,59 @@ void DecoderExecutablePlan::execute(const float* input, float* output, RoutingTr
     result->kernel_launches = sfb_launch_count() - launches_before;
 }
 
+// One pass of a sharded plan where every rank brings and takes only ITS rows over its own PCIe link:
+// the rows are uploaded into a zeroed input tensor, the sum all-reduce of the hook then acts as the
+// all-gather (every row is non-zero on exactly one rank, so the sum is exact), the layer runs on the
+// replicated input and the rank downloads its rows of the replicated output.
+void DecoderExecutablePlan::execute_rows(const float* input_rows, float* output_rows, int row_begin, int row_count,
+                                         sfb_decoder_result* result) {
+    auto& m = *impl_;
+    if (!input_rows || !output_rows) throw std::invalid_argument("decoder input is null");
+    if (row_begin < 0 || row_count <= 0 || row_begin + row_count > m.T)
+        throw std::invalid_argument("decoder row range lies outside the plan");
+    const bool whole = row_begin == 0 && row_count == m.T;
+    if (!whole && (m.dtype != SFB_BF16 || !allreduce_))
+        throw std::invalid_argument("a row range needs a bf16 plan with an all-reduce hook");
+    cudaStream_t s = stream_;
+    const uint64_t launches_before = sfb_launch_count();
+    const std::size_t first = static_cast<std::size_t>(row_begin) * m.H, count = static_cast<std::size_t>(row_count) * m.H;
+    cudaEvent_t h0 = m.events[12], h1 = m.events[13], d0 = m.events[14], d1 = m.events[15];
+    cuda_check(cudaEventRecord(h0, s), "event");
+    cuda_check(cudaMemcpyAsync(m.ws<float>("input_f32") + first, input_rows, count * 4, cudaMemcpyHostToDevice, s), "input upload");
+    if (m.dtype == SFB_BF16) {
+        char* input = static_cast<char*>(m.ws("input"));
+        if (!whole) cuda_check(cudaMemsetAsync(input, 0, static_cast<std::size_t>(m.T) * m.H * 2, s), "input clear");
+        throw_on(sfb_k_convert(m.ws<float>("input_f32") + first, SFB_F32, input + first * 2, SFB_BF16, static_cast<int64_t>(count), s));
+        if (!whole) allreduce_(allreduce_user_, input, static_cast<int64_t>(m.T) * m.H, SFB_BF16, s);
+    }
+    m.has_input = true;
+    cuda_check(cudaEventRecord(h1, s), "event");
+    run(s, RoutingTraceView{}, true);
+    cuda_check(cudaEventRecord(d0, s), "event");
+    const float* src = m.dtype == SFB_BF16 ? m.ws<float>("output_f32") : m.ws<float>("output");
+    cuda_check(cudaMemcpyAsync(output_rows, src + first, count * 4, cudaMemcpyDeviceToHost, s), "output download");
+    cuda_check(cudaEventRecord(d1, s), "event");
+    cuda_check(cudaEventSynchronize(d1), "event sync");
+    if (!result) return;
+    auto span = [&](cudaEvent_t a, cudaEvent_t b) {
+        float ms = 0.0F;
+        cuda_check(cudaEventElapsedTime(&ms, a, b), "event time");
+        return static_cast<double>(ms);
+    };
+    auto* e = m.events;
+    *result = {};
+    result->h2d_milliseconds = span(h0, h1);
+    result->d2h_milliseconds = span(d0, d1);
+    result->norm_rope_milliseconds = span(e[0], e[1]) + span(e[2], e[3]) + span(e[6], e[7]);
+    result->projection_milliseconds = span(e[1], e[2]) + span(e[4], e[5]);
+    result->attention_milliseconds = span(e[3], e[4]);
+    result->residual_milliseconds = span(e[5], e[6]) + span(e[8], e[9]);
+    result->ffn_milliseconds = span(e[7], e[8]);
+    result->milliseconds = span(h0, d1);
+    result->tokens_per_second = result->milliseconds > 0.0 ? m.T * 1000.0 / result->milliseconds : 0.0;
+    result->kernel_launches = sfb_launch_count() - launches_before;
+}
+
 // Dense bf16 prefill with fused epilogues, one chunk of whole sequences at a time: the host->device
 // copy of chunk c+1 and the device->host copy of chunk c-1 run on their own streams while chunk c
 // computes.  Sequences are independent in every stage (row-wise GEMMs and norms, per-sequence

@@ -81,6 +81,7 @@ public:
     // One layer pass.  input/output: host float32 [T, H].
     void execute(const float* input, float* output, RoutingTraceView trace, sfb_decoder_result* result);
     void execute_pipelined(const float* input, float* output, sfb_decoder_result* result);
+    void execute_rows(const float* input_rows, float* output_rows, int row_begin, int row_count, sfb_decoder_result* result);
     void upload_input(const float* input);
     void run(cudaStream_t stream, RoutingTraceView trace, bool stage_events);
     void download_output(float* output);

@@ -138,7 +138,7 @@ EXPORTS = (
     "sfb_k_paged_kv_append sfb_k_paged_kv_gather "
     "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_dispatch_static sfb_k_moe_combine "
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
-    "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_upload_input "
+    "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_execute_rows sfb_decoder_upload_input "
     "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
     "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
     "sfb_attention_execute sfb_attention_decode "

@@ -75,6 +75,14 @@ def main():
         dist.broadcast(ref, 0)
         if not torch.equal(mine, ref):
             failures.append(name + ":ranks differ")
+        # every rank brings only its rows: the hook gathers the input, each rank takes its rows of the output
+        t_rows = oc.batch * oc.sequence
+        if t_rows % world == 0 and not moe:
+            rows = t_rows // world
+            x2d = data["input"].reshape(t_rows, oc.hidden)
+            mine_rows, _ = plan.execute_rows(x2d[rank * rows:(rank + 1) * rows], rank * rows)
+            if not np.array_equal(mine_rows, out.reshape(t_rows, oc.hidden)[rank * rows:(rank + 1) * rows]):
+                failures.append(name + ":row-sharded execute differs")
         # the same layer with the all-reduces after O and Down fused into the GEMMs over peer memory
         # (the MoE combine keeps the hook); three passes reuse the slot sets
         def exchange(handle):

@@ -355,3 +355,19 @@ def test_benchmark_profile_matrix_measures_on_the_device(port, tmp_path):
     cand = (tmp_path / "candidates.csv").read_text().splitlines()
     assert len(cand) == 1 + 17 and sum(l.split(",")[2] == "1" for l in cand[1:]) >= 1
     assert sum(l.split(",")[3] == "1" for l in cand[1:]) >= 5                    # measured candidates
+
+
+def test_execute_rows_whole_range_and_guards(port):
+    # 256 rows: above the few-row GEMMs, whose partial sums meet in L2 in an order that differs from run to run
+    kw = dict(batch=2, sequence=128, hidden=256, intermediate=512, query_heads=4, kv_heads=2, head_dim=64)
+    oc, c, data = bf16_case(port, 3, **kw)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(no_pipeline=True))
+    want, _ = plan.execute(data["input"])
+    x = np.asarray(data["input"], np.float32).reshape(256, 256)
+    got, result = plan.execute_rows(x, 0)
+    assert np.array_equal(got.ravel(), want.ravel()) and result.milliseconds > 0
+    with pytest.raises(L.InvalidArgument, match="all-reduce hook"):
+        plan.execute_rows(x[:64], 0)          # a part of the rows needs the other ranks
+    with pytest.raises(L.InvalidArgument, match="outside the plan"):
+        plan.execute_rows(x, 64)
+    plan.close()
