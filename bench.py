@@ -161,7 +161,7 @@ def kernel_case(args):
                (--small: M=4096, N=16384, K=4096, 224 MB of operands, larger than L2)
     gemm_decode  the same projection for the 128 rows of a decode step: blocked weights, streamed
                once (--small: N=8192; three weight copies are rotated so that L2 does not help)
-    attention  headline attention case: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (--small: B1)
+    attention  headline attention case: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (--small: B1; --head-dim 64)
     decode     headline decode case: paged split-KV decode, batch 64, context ~U[512, 8192], 16-token
                blocks, permuted block table (--small: batch 16)
     """
@@ -215,17 +215,17 @@ def kernel_case(args):
         unit, peak, bound = "GB/s", peaks["hbm_gbs"], "hbm"
         name, shape = "gemm_tcgen05_kernel<128, true>", {"m": m, "n": n, "k": k, "epilogue": "swiglu", "weights": "64x64 blocks"}
     elif args.kernel == "attention":
-        b, hq, hkv, s = (1 if args.small else 4), 32, 8, 4096
-        q = torch.randn((b, hq, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
-        kk = torch.randn((b, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
-        v = torch.randn((b, hkv, s, 128), generator=gen, device="cuda").to(torch.bfloat16)
-        o = torch.empty((b, hq, s, 128), dtype=torch.bfloat16, device="cuda")
-        a = L.AttentionArgs(q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(), b, hq, hkv, s, s, 128, 128, 1,
+        b, hq, hkv, s, d = (1 if args.small else 4), 32, 8, 4096, args.head_dim
+        q = torch.randn((b, hq, s, d), generator=gen, device="cuda").to(torch.bfloat16)
+        kk = torch.randn((b, hkv, s, d), generator=gen, device="cuda").to(torch.bfloat16)
+        v = torch.randn((b, hkv, s, d), generator=gen, device="cuda").to(torch.bfloat16)
+        o = torch.empty((b, hq, s, d), dtype=torch.bfloat16, device="cuda")
+        a = L.AttentionArgs(q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(), b, hq, hkv, s, s, d, d, 1,
                             0.0, 0, L.BF16, 2)
         launch = lambda: L.check(lib.sfb_k_attention_prefill(C.byref(a), sp))
         pairs = b * hq * s * (s + 1) / 2
-        work, unit, peak, bound = 2.0 * pairs * 256, "TFLOP/s", peaks["bf16_tflops"], "tensor"
-        name, shape = "attention_prefill_tcgen05_kernel", {"batch": b, "q_heads": hq, "kv_heads": hkv, "seq": s, "head_dim": 128, "causal": True}
+        work, unit, peak, bound = 2.0 * pairs * 2 * d, "TFLOP/s", peaks["bf16_tflops"], "tensor"
+        name, shape = f"attention_prefill_tcgen05_kernel<{d}>", {"batch": b, "q_heads": hq, "kv_heads": hkv, "seq": s, "head_dim": d, "causal": True}
     else:
         batch, hq, hkv, d, block = (16 if args.small else 64), 32, 8, 128, 16
         ctx = torch.randint(512, 8193, (batch,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
@@ -288,6 +288,7 @@ def main():
                          "epilogues over NVLink peer memory")
     ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_decode", "attention", "decode"],
                     help="time ONE kernel through the kernel ABI instead of the layer (also the ncu target)")
+    ap.add_argument("--head-dim", type=int, default=128, choices=[128, 64], help="--kernel attention: head dimension")
     ap.add_argument("--small", action="store_true", help="--kernel: a case small enough for an ncu --set full capture")
     args = ap.parse_args()
     if args.kernel:
