@@ -397,12 +397,24 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
             dst[4 * i + 2] = __float_as_uint(f.z); dst[4 * i + 3] = __float_as_uint(f.w);
         }
     };
+    // A completed cut-up tile: the sums of this warp's second chunk are requested together with the first
+    // (one L2 round trip on the kernel's critical path instead of two); r1 is free when there is no SwiGLU.
+    const bool ahead = !whole && !swiglu && pass + 2 < chunks && out0 + (pass + 2) * 32 < width;
+    if (ahead) {
+        if (out0 + pass * 32 < width) fetch(pass * 32, r0);
+        fetch((pass + 2) * 32, r1);
+    }
 #pragma unroll 1
     for (int ch = pass; ch < chunks; ch += 2) {
         const int col0 = out0 + ch * 32;
         const bool live = col0 < width;
         if (live) {
-            fetch(ch * 32, r0);
+            if (ahead && ch == pass + 2) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r0[i] = r1[i];
+            } else if (!(ahead && ch == pass)) {
+                fetch(ch * 32, r0);
+            }
             if (swiglu) fetch(BN / 2 + ch * 32, r1);
             if (whole) ptx::tmem_ld_wait();
         }
