@@ -228,7 +228,10 @@ sfb_status sfb_k_attention_prefill(const sfb_attention_args* args, sfb_stream st
  * log-sum-exp rule (merge_online, src/attention_compiler.cpp:132-145; empty splits are
  * skipped).  Replaces execute_decode_attention / execute_paged_decode_attention,
  * src/attention_compiler.cpp:968-1007, src/next_milestones.cpp:583-609, 137-184.
- * `partials` needs sfb_attention_decode_workspace() bytes.  splits <= 0 picks a value. */
+ * `partials` needs sfb_attention_decode_workspace() bytes.  splits <= 0 picks a value.
+ * A context_len[b] beyond what the table covers (max_blocks * block_tokens, or max_context) is
+ * cut to that bound and a block id outside [0, num_blocks) is skipped; either sets bit 0x200 of
+ * sfb_device_status instead of reading out of bounds. */
 typedef struct sfb_decode_args {
     const void* q;          /* [batch, q_heads, head_dim]                                  */
     const void* k_pool;
@@ -251,12 +254,15 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* args, sfb_stream 
 
 /* Writes `tokens` new tokens per sequence into the paged pool.  new_k/new_v are
  * [batch, kv_heads, tokens, dim]; the token at logical position start_len[b] + t goes to
- * block block_table[b][pos / block_tokens], slot pos % block_tokens.
+ * block block_table[b][pos / block_tokens], slot pos % block_tokens.  start_len and block_table
+ * live on the device and may have been written by another kernel, so the kernel checks them: a
+ * position past the table (pos / block_tokens >= max_blocks) or a block id outside [0, num_blocks)
+ * is skipped and bit 0x200 of sfb_device_status is set (num_blocks <= 0 switches the block check off).
  * Replaces the copy loop of append_paged_kv, src/next_milestones.cpp:502-522. */
 sfb_status sfb_k_paged_kv_append(const void* new_k, const void* new_v, void* k_pool, void* v_pool,
                                  const int* block_table, const int* start_len, int batch,
                                  int kv_heads, int tokens, int head_dim, int head_dim_value,
-                                 int block_tokens, int max_blocks, sfb_dtype dtype,
+                                 int block_tokens, int max_blocks, int num_blocks, sfb_dtype dtype,
                                  sfb_stream stream);
 
 /* Paged pool -> contiguous [batch, kv_heads, length, dim] (all sequences `length` long).
@@ -382,6 +388,10 @@ typedef struct sfb_compile_options {
                              projections as int8 and stream half the bytes; larger plans (compute bound)
                              multiply by the dequantised q * scale weights in bf16.  The quantizer sees the
                              bf16-rounded weights. */
+    int local_expert_weights; /* MoE plans with tp_size > 1: != 0 says that w1 / w3 / w2 of sfb_decoder_data hold
+                             only this rank's experts/tp_size experts (expert tp_rank * experts/tp_size first), so
+                             that a rank never has to materialise the other ranks' expert weights on its host;
+                             0 = the full [experts, ...] arrays, of which the rank takes its slice. */
 } sfb_compile_options;
 
 /* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */

@@ -71,7 +71,7 @@ decode_paged_mma_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     const int split = blockIdx.z, kvh = blockIdx.y, b = blockIdx.x;
     grid_dependents_may_launch();
     grid_dependency_wait();  // the queries (and an appended page) come from the kernels before
-    const int ctx = p.context_len[b];
+    const int ctx = guarded_context(p, b);
     int begin, end;
     split_range(ctx, p.chunk_tokens, split, begin, end);
     if (begin >= end) {  // nothing of this sequence falls into this split: neutral partial
@@ -108,7 +108,14 @@ decode_paged_mma_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_
     const int n_pages = last_block - first_block;
     const int n_stages = (n_pages + kPagesPerStage - 1) / kPagesPerStage;
     const int* table = p.block_table + static_cast<size_t>(b) * p.max_blocks;
-    for (int i = threadIdx.x; i < n_pages; i += kThreads) page_ids[i] = table[first_block + i];
+    for (int i = threadIdx.x; i < n_pages; i += kThreads) {
+        int page = table[first_block + i];
+        if (page < 0 || page >= p.num_blocks) {  // outside the pool: the copy then lies outside the tensor map and reads zeros
+            page = p.num_blocks;
+            atomicOr(status, kCodeDecodeBounds);
+        }
+        page_ids[i] = page;
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);

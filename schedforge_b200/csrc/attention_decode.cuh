@@ -15,7 +15,23 @@ struct DecodeParams {
     int batch, q_heads, kv_heads, dim, dim_v, block_tokens, max_blocks, splits;
     float scale;
     int chunk_tokens;
+    // Guards against a bad length or table entry written by an earlier kernel: a context longer than the table
+    // covers is cut to context_limit, a block id outside [0, num_blocks) is skipped (its keys count as zeros);
+    // either one ORs kCodeDecodeBounds into the device status word instead of touching memory out of bounds.
+    int context_limit, num_blocks;
+    uint32_t* status;
 };
+
+constexpr uint32_t kCodeDecodeBounds = 0x200;
+
+__device__ __forceinline__ int guarded_context(const DecodeParams& p, int b) {
+    int ctx = p.context_len[b];
+    if (ctx > p.context_limit || ctx < 0) {
+        ctx = ctx < 0 ? 0 : p.context_limit;
+        if (threadIdx.x == 0) atomicOr(p.status, kCodeDecodeBounds);
+    }
+    return ctx;
+}
 
 // Split s covers tokens [s*chunk, (s+1)*chunk) of every sequence (chunk is a multiple of four KV
 // blocks), so all non-empty splits carry the same amount of work whatever the context length;

@@ -149,7 +149,7 @@ decode_paged_generic_kernel(DecodeParams p) {
     const int head = blockIdx.x % p.q_heads, b = blockIdx.x / p.q_heads;
     const int kvh = head * p.kv_heads / p.q_heads;
     const int D = p.dim, Dv = p.dim_v, P = p.block_tokens;
-    const int ctx = p.context_len[b];
+    const int ctx = guarded_context(p, b);
     int begin, end;
     split_range(ctx, p.chunk_tokens, split, begin, end);
     const T* qrow = static_cast<const T*>(p.q) + (static_cast<size_t>(b) * p.q_heads + head) * D;
@@ -165,7 +165,11 @@ decode_paged_generic_kernel(DecodeParams p) {
         const int key = k0 + threadIdx.x;
         float score = -INFINITY;
         if (key < end) {
-            const int page = table[key / P];
+            int page = table[key / P];
+            if (p.num_blocks > 0 && (page < 0 || page >= p.num_blocks)) {  // outside the pool: read block 0 instead, flag it
+                page = 0;
+                atomicOr(p.status, kCodeDecodeBounds);
+            }
             phys[threadIdx.x] = page;
             const T* krow = kpool + ((static_cast<size_t>(page) * p.kv_heads + kvh) * P + key % P) * D;
             float dot = 0.0F;
@@ -272,7 +276,7 @@ template <class T>
 __global__ void paged_append_kernel(const T* __restrict__ new_k, const T* __restrict__ new_v, T* __restrict__ k_pool,
                                     T* __restrict__ v_pool, const int* __restrict__ table,
                                     const int* __restrict__ start_len, int batch, int kv_heads, int tokens, int dim,
-                                    int dim_v, int P, int max_blocks) {
+                                    int dim_v, int P, int max_blocks, int num_blocks, uint32_t* status) {
     const int width = dim + dim_v;
     const int64_t total = static_cast<int64_t>(batch) * kv_heads * tokens * width;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -283,7 +287,10 @@ __global__ void paged_append_kernel(const T* __restrict__ new_k, const T* __rest
         const int h = static_cast<int>((r / tokens) % kv_heads);
         const int b = static_cast<int>(r / tokens / kv_heads);
         const int pos = start_len[b] + t;
+        // a position past the table or a block id outside the pool (num_blocks > 0) is skipped and flagged
+        if (pos < 0 || pos / P >= max_blocks) { atomicOr(status, kCodeDecodeBounds); continue; }
         const int page = table[static_cast<size_t>(b) * max_blocks + pos / P];
+        if (page < 0 || (num_blocks > 0 && page >= num_blocks)) { atomicOr(status, kCodeDecodeBounds); continue; }
         const size_t row = (static_cast<size_t>(page) * kv_heads + h) * P + pos % P;
         const size_t src = (static_cast<size_t>(b) * kv_heads + h) * tokens + t;
         if (c < dim) k_pool[row * dim + c] = new_k[src * dim + c];
@@ -396,11 +403,16 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream str
     DecodeParams p{a->q, a->k_pool, a->v_pool, a->block_table, a->context_len, a->out,
                    static_cast<float*>(a->partials), a->batch, a->q_heads, a->kv_heads, a->head_dim,
                    a->head_dim_value, a->block_tokens, a->max_blocks, splits,
-                   a->scale > 0.0F ? a->scale : 1.0F / sqrtf(static_cast<float>(a->head_dim)), 0};
+                   a->scale > 0.0F ? a->scale : 1.0F / sqrtf(static_cast<float>(a->head_dim)), 0, 0, 0, nullptr};
     {
         const int bound = a->max_context > 0 ? a->max_context : a->max_blocks * a->block_tokens;
         const int granule = 4 * a->block_tokens;
         p.chunk_tokens = ceil_div(ceil_div(bound, splits), granule) * granule;
+        const long long covered = static_cast<long long>(splits) * p.chunk_tokens;
+        const long long table_tokens = static_cast<long long>(a->max_blocks) * a->block_tokens;
+        p.context_limit = static_cast<int>(covered < table_tokens ? covered : table_tokens);
+        p.num_blocks = a->num_blocks;
+        p.status = device_status_word();
     }
     cudaStream_t s = as_stream(stream);
     const int group = a->q_heads / a->kv_heads;
@@ -437,22 +449,24 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream str
 sfb_status sfb_k_paged_kv_append(const void* new_k, const void* new_v, void* k_pool, void* v_pool,
                                  const int* block_table, const int* start_len, int batch,
                                  int kv_heads, int tokens, int head_dim, int head_dim_value,
-                                 int block_tokens, int max_blocks, sfb_dtype dtype, sfb_stream stream) {
+                                 int block_tokens, int max_blocks, int num_blocks, sfb_dtype dtype, sfb_stream stream) {
     SFB_REQUIRE(new_k && new_v && k_pool && v_pool && block_table && start_len, "paged append: null tensor");
-    SFB_REQUIRE(batch > 0 && kv_heads > 0 && tokens > 0 && head_dim > 0 && head_dim_value > 0 && block_tokens > 0,
+    SFB_REQUIRE(batch > 0 && kv_heads > 0 && tokens > 0 && head_dim > 0 && head_dim_value > 0 && block_tokens > 0 &&
+                    max_blocks > 0,
                 "paged KV append shape mismatch");
+    uint32_t* status = device_status_word();
     const int64_t work = static_cast<int64_t>(batch) * kv_heads * tokens * (head_dim + head_dim_value);
     const int grid = stream_grid(work);
     if (dtype == SFB_F32)
         paged_append_kernel<float><<<grid, 256, 0, as_stream(stream)>>>(
             static_cast<const float*>(new_k), static_cast<const float*>(new_v), static_cast<float*>(k_pool),
             static_cast<float*>(v_pool), block_table, start_len, batch, kv_heads, tokens, head_dim, head_dim_value,
-            block_tokens, max_blocks);
+            block_tokens, max_blocks, num_blocks, status);
     else
         paged_append_kernel<bf16><<<grid, 256, 0, as_stream(stream)>>>(
             static_cast<const bf16*>(new_k), static_cast<const bf16*>(new_v), static_cast<bf16*>(k_pool),
             static_cast<bf16*>(v_pool), block_table, start_len, batch, kv_heads, tokens, head_dim, head_dim_value,
-            block_tokens, max_blocks);
+            block_tokens, max_blocks, num_blocks, status);
     return check_launch("paged_kv_append");
 }
 

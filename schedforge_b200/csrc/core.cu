@@ -9,7 +9,8 @@ namespace sfb {
 namespace {
 thread_local std::string g_last_error;
 std::atomic<uint64_t> g_launches{0};
-uint32_t* g_status_word = nullptr;
+constexpr int kMaxDevices = 64;
+uint32_t* g_status_word[kMaxDevices] = {};  // one word per device, allocated with that device current
 std::mutex g_status_mutex;
 }  // namespace
 
@@ -27,18 +28,21 @@ sfb_status cuda_fail(cudaError_t error, const char* what) {
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 
-// One 4-byte word per process in device memory, zero-initialised.  Kernels with bounded
-// waits OR a code into it when a wait runs out instead of spinning forever.
+// One 4-byte word per device in that device's memory, zero-initialised.  Kernels with bounded
+// waits OR a code into it when a wait runs out instead of spinning forever.  The word of the
+// CURRENT device is returned, so a kernel always gets memory of the GPU it runs on.
 uint32_t* device_status_word() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
     std::lock_guard<std::mutex> lock(g_status_mutex);
-    if (!g_status_word) {
-        if (cudaMalloc(&g_status_word, sizeof(uint32_t)) != cudaSuccess) {
-            g_status_word = nullptr;
+    if (!g_status_word[device]) {
+        if (cudaMalloc(&g_status_word[device], sizeof(uint32_t)) != cudaSuccess) {
+            g_status_word[device] = nullptr;
             return nullptr;
         }
-        cudaMemset(g_status_word, 0, sizeof(uint32_t));
+        cudaMemset(g_status_word[device], 0, sizeof(uint32_t));
     }
-    return g_status_word;
+    return g_status_word[device];
 }
 
 int sm_count() {

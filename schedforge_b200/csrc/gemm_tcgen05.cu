@@ -678,7 +678,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (; walk.next(sg); ++count) {
             const TileCoord c = tile_coord(p, sg.tile, m_tiles);
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
-            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue)) break;
+            bool go = ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue);
+            // With cut-up tiles the epilogue threads meet at barriers that have no time limit, so they must all
+            // take the same decision here: one thread that saw the abort flag takes the whole group out.
+            if (p.shared_tiles > 0) go = ptx::named_barrier_all(2, 32 * kEpilogueWarps, go);
+            if (!go) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             epilogue_segment<BN, false>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter, pass,
@@ -946,9 +950,10 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                     ptx::mbar_arrive(ptx::smem_u32(&empty_q[sq]));
                 }
             }
-            if (!ok) break;
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
-            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue)) break;
+            bool go = ok && ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue);
+            if (p.shared_tiles > 0) go = ptx::named_barrier_all(2, 32 * kEpilogueWarps, go);  // one decision for the group
+            if (!go) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             epilogue_segment<BN, true>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter,

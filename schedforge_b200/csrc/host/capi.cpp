@@ -129,6 +129,10 @@ sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float
         trace.expert_ids = trace_expert_ids;
         trace.expert_weights = trace_expert_weights;
         trace.counts = trace_counts;
+        if ((trace_expert_ids || trace_expert_weights || trace_counts) && !trace)  // a trace is all three arrays or none
+            throw std::invalid_argument("routing trace does not match MoE configuration");
+        if (trace && plan->plan->config.ffn != DecoderFFNKind::MoE)
+            throw std::invalid_argument("routing trace does not match MoE configuration");
         plan->plan->execute(input, output, trace, result);
     });
 }

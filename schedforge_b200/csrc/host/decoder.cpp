@@ -126,6 +126,29 @@ struct DecoderExecutablePlan::Impl {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
+    // Device status word (bounded waits that gave up) of the plan's device and a pinned host copy that every
+    // host-synchronising call refreshes in stream order, so a timed-out wait surfaces as SFB_DEVICE_TIMEOUT.
+    uint32_t* status_device = nullptr;
+    uint32_t* status_host = nullptr;
+    void queue_status_read(cudaStream_t s) {
+        if (status_device && status_host)
+            cuda_check(cudaMemcpyAsync(status_host, status_device, sizeof(uint32_t), cudaMemcpyDeviceToHost, s), "status read");
+    }
+    // after the stream has been synchronised: a non-zero word means that some kernel of the pass gave up waiting,
+    // so the output is not the layer's; the word is cleared and the split-K scratch (sums and tile counters that an
+    // aborted few-row GEMM leaves behind) is zeroed again so that the next pass starts clean
+    void check_status(cudaStream_t s) {
+        if (!status_host || *status_host == 0) return;
+        const uint32_t word = *status_host;
+        *status_host = 0;
+        cuda_check(cudaMemsetAsync(status_device, 0, sizeof(uint32_t), s), "status clear");
+        if (has("gemm_partials"))
+            cuda_check(cudaMemsetAsync(ws("gemm_partials"), 0, planner.bytes(planner.find("gemm_partials")), s), "scratch clear");
+        cuda_check(cudaStreamSynchronize(s), "status clear sync");
+        char text[96];
+        std::snprintf(text, sizeof(text), "a bounded device-side wait gave up (status word 0x%x)", word);
+        throw DeviceError(SFB_DEVICE_TIMEOUT, text);
+    }
     // dense fused bf16 plan on one rank: the last GEMM writes the fp32 result itself, "output" is skipped
     bool direct_f32_output = false;
     // fused all-reduce over peer memory: [2 slot sets][size slots][slot_bytes] + flags [2][size]
@@ -186,6 +209,7 @@ DecoderExecutablePlan::~DecoderExecutablePlan() {
             if (e) cudaEventDestroy(e);
         if (impl_->copy_in) cudaStreamDestroy(impl_->copy_in);
         if (impl_->copy_out) cudaStreamDestroy(impl_->copy_out);
+        if (impl_->status_host) cudaFreeHost(impl_->status_host);
     }
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -394,10 +418,11 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         const float* w3 = need(data.w3, "w3");
         const float* w2 = need(data.w2, "w2");
         const int Ifull = c.intermediate;
+        const int first_expert = opt.local_expert_weights != 0 ? 0 : m.e_begin;  // index into the caller's arrays
         if (bf) {
             m.w13 = wb + o_w13; m.w2 = wb + o_w2;
             for (int e = 0; e < m.E_l; ++e) {
-                const std::size_t src = static_cast<std::size_t>(m.e_begin + e) * expert_elems;
+                const std::size_t src = static_cast<std::size_t>(first_expert + e) * expert_elems;
                 char* d13 = static_cast<char*>(m.w13) + static_cast<std::size_t>(e) * 2 * expert_elems * 2;
                 // SiLU applies to the W3 product, which multiplies the raw W1 product: [W3 | W1] = [gate | up]
                 pack(w3 + src, H, Ifull, 0, H, 0, Ifull, d13, m.moe_swiglu_block, 2 * m.moe_swiglu_block, 0);
@@ -407,7 +432,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         } else {
             m.w1f = reinterpret_cast<float*>(wb + o_w1f); m.w3f = reinterpret_cast<float*>(wb + o_w3f);
             m.w2f = reinterpret_cast<float*>(wb + o_w2f);
-            const std::size_t src = static_cast<std::size_t>(m.e_begin) * expert_elems, n = static_cast<std::size_t>(m.E_l) * expert_elems;
+            const std::size_t src = static_cast<std::size_t>(first_expert) * expert_elems, n = static_cast<std::size_t>(m.E_l) * expert_elems;
             h2d(m.w1f, w1 + src, n * 4);
             h2d(m.w3f, w3 + src, n * 4);
             h2d(m.w2f, w2 + src, n * 4);
@@ -515,7 +540,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
                 ak = tmp; av = tmp + cache_bytes;
             }
             throw_on(sfb_k_paged_kv_append(ak, av, m.k_pool, m.v_pool, m.block_table, m.context_len, c.batch, m.hkv,
-                                           ctx, D, D, m.page_tokens, m.max_blocks, static_cast<sfb_dtype>(m.dtype), s));
+                                           ctx, D, D, m.page_tokens, m.max_blocks, m.num_blocks, static_cast<sfb_dtype>(m.dtype), s));
             cuda_check(cudaStreamSynchronize(s), "paged cache build");
             h2d(m.context_len, full.data(), len_bytes);
             if (m.append_new) {
@@ -625,6 +650,9 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     plan->workspace_bytes = wp.total_bytes();
     (void)plan_start;
     for (auto& ev : m.events) cuda_check(cudaEventCreate(&ev), "cudaEventCreate");
+    m.status_device = device_status_word();
+    cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&m.status_host), sizeof(uint32_t), cudaHostAllocDefault), "status word");
+    *m.status_host = 0;
     if (piped) {
         cuda_check(cudaStreamCreateWithFlags(&m.copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
         cuda_check(cudaStreamCreateWithFlags(&m.copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -675,9 +703,11 @@ void DecoderExecutablePlan::download_output(float* output) {
     if (!output) throw std::invalid_argument("decoder output is null");
     auto& m = *impl_;
     const float* src = m.dtype == SFB_BF16 ? m.ws<float>("output_f32") : m.ws<float>("output");
+    m.queue_status_read(stream_);
     cuda_check(cudaMemcpyAsync(output, src, static_cast<std::size_t>(m.T) * m.H * 4, cudaMemcpyDeviceToHost, stream_),
                "output download");
     cuda_check(cudaStreamSynchronize(stream_), "output download sync");
+    m.check_status(stream_);
 }
 
 void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool stage_events) {
@@ -741,7 +771,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     if (m.paged) {
         if (m.append_new)  // the rotated key and the value of the new token go to position context_len of every sequence
             throw_on(sfb_k_paged_kv_append(m.ws("key"), m.ws("value"), m.k_pool, m.v_pool, m.block_table, m.context_len,
-                                           c.batch, m.hkv, 1, D, D, m.page_tokens, m.max_blocks, dt, s));
+                                           c.batch, m.hkv, 1, D, D, m.page_tokens, m.max_blocks, m.num_blocks, dt, s));
         sfb_decode_args a{};
         a.q = m.ws("query"); a.k_pool = m.k_pool; a.v_pool = m.v_pool; a.block_table = m.block_table;
         a.context_len = m.context_len_attend; a.out = m.ws("attention"); a.partials = m.ws("decode_partials");
@@ -813,6 +843,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         float* wts = m.ws<float>("expert_weights");
         int* counts = m.ws<int>("counts");
         if (trace) {
+            validate_routing_trace(T, m.K, m.E, trace.expert_ids, trace.expert_weights, trace.counts);
             cuda_check(cudaMemcpyAsync(ids, trace.expert_ids, sizeof(int) * A, cudaMemcpyHostToDevice, s), "trace upload");
             cuda_check(cudaMemcpyAsync(wts, trace.expert_weights, sizeof(float) * A, cudaMemcpyHostToDevice, s), "trace upload");
             cuda_check(cudaMemcpyAsync(counts, trace.counts, sizeof(int) * m.E, cudaMemcpyHostToDevice, s), "trace upload");
@@ -932,9 +963,11 @@ void DecoderExecutablePlan::execute_rows(const float* input_rows, float* output_
     run(s, RoutingTraceView{}, true);
     cuda_check(cudaEventRecord(d0, s), "event");
     const float* src = m.dtype == SFB_BF16 ? m.ws<float>("output_f32") : m.ws<float>("output");
+    m.queue_status_read(s);
     cuda_check(cudaMemcpyAsync(output_rows, src + first, count * 4, cudaMemcpyDeviceToHost, s), "output download");
     cuda_check(cudaEventRecord(d1, s), "event");
     cuda_check(cudaEventSynchronize(d1), "event sync");
+    m.check_status(s);
     if (!result) return;
     auto span = [&](cudaEvent_t a, cudaEvent_t b) {
         float ms = 0.0F;
@@ -1057,9 +1090,11 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     }
     cuda_check(cudaEventRecord(m.events[14], m.copy_out), "event");
     cuda_check(cudaStreamWaitEvent(s, m.events[14], 0), "stream wait");
+    m.queue_status_read(s);
     cuda_check(cudaEventRecord(t1, s), "event");
     cuda_check(cudaEventSynchronize(t1), "event sync");
     m.has_input = true;  // the whole input is resident (as bf16) for later resident runs
+    m.check_status(s);
     if (!result) return;
     auto span = [&](cudaEvent_t a, cudaEvent_t b) {
         float ms = 0.0F;

@@ -71,6 +71,22 @@ void shard_columns(const float* src, int rows, int cols, int rank, int size, flo
                     static_cast<std::size_t>(width) * sizeof(float));
 }
 
+void validate_routing_trace(int tokens, int top_k, int experts, const int* expert_ids, const float* expert_weights,
+                            const int* counts) {
+    const char* message = "routing trace does not match MoE configuration";
+    if (!expert_ids || !expert_weights || !counts || tokens <= 0 || top_k <= 0 || experts <= 0)
+        throw std::invalid_argument(message);
+    std::vector<long long> histogram(static_cast<std::size_t>(experts), 0);
+    const long long assignments = static_cast<long long>(tokens) * top_k;
+    for (long long i = 0; i < assignments; ++i) {
+        const int e = expert_ids[i];
+        if (e < 0 || e >= experts) throw std::invalid_argument(message);
+        ++histogram[static_cast<std::size_t>(e)];
+    }
+    for (int e = 0; e < experts; ++e)
+        if (counts[e] != histogram[static_cast<std::size_t>(e)]) throw std::invalid_argument(message);
+}
+
 void shard_rows(const float* src, int rows, int cols, int rank, int size, float* dst) {
     const int height = rows / size;
     std::memcpy(dst, src + static_cast<std::size_t>(rank) * height * cols,

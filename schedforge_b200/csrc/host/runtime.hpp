@@ -71,6 +71,14 @@ private:
     bool reuse_;
 };
 
+// A caller-supplied routing trace goes to kernels that index shared and global memory with its expert ids and
+// place rows by its counts, so it is checked on the host first (O(tokens * top_k)): all three arrays present,
+// every id inside [0, experts), counts equal to the histogram of the ids.  Throws std::invalid_argument
+// "routing trace does not match MoE configuration", the reference's message for a malformed trace
+// (dispatch_tokens, src/moe_compiler.cpp:498-501).
+void validate_routing_trace(int tokens, int top_k, int experts, const int* expert_ids, const float* expert_weights,
+                            const int* counts);
+
 // Host-side matrix shards used by the tensor-parallel plan build.
 void shard_columns(const float* src, int rows, int cols, int rank, int size, float* dst);
 void shard_rows(const float* src, int rows, int cols, int rank, int size, float* dst);

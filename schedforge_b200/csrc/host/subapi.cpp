@@ -193,7 +193,7 @@ sfb_status sfb_paged_append(sfb_paged_kv* cache, const float* keys, const float*
         Staged dk(keys, rows * c.dim, c.dtype, s), dv(values, rows * c.dim_v, c.dtype, s);
         throw_on(sfb_k_paged_kv_append(dk.get(), dv.get(), c.k_pool.get(), c.v_pool.get(), c.table.as<int>(),
                                        c.lens.as<int>(), c.batch, c.kv_heads, tokens, c.dim, c.dim_v, c.page_tokens,
-                                       c.pages(), static_cast<sfb_dtype>(c.dtype), s));
+                                       c.pages(), c.pages() * c.batch, static_cast<sfb_dtype>(c.dtype), s));
         cuda_check(cudaStreamSynchronize(s), "append sync");
         c.length += tokens;
     });
@@ -348,6 +348,7 @@ sfb_status sfb_moe_dispatch_tokens(const sfb_moe_config* config, const float* in
         validate_moe(*config);
         const auto& c = *config;
         if (tokens <= 0 || (values && !input)) throw std::invalid_argument("MoE input is smaller than routing trace");
+        validate_routing_trace(tokens, c.top_k, c.experts, expert_ids, expert_weights, counts);
         cudaStream_t s = nullptr;
         const size_t A = static_cast<size_t>(tokens) * c.top_k;
         Staged x(values ? input : nullptr, values ? static_cast<size_t>(tokens) * c.hidden : 1, dtype, s);
@@ -419,6 +420,7 @@ sfb_status moe_execute(const sfb_moe_config* config, const float* input, int tok
         validate_moe(*config);
         const auto& c = *config;
         if (tokens <= 0 || tokens > c.tokens) throw std::invalid_argument("runtime token count exceeds compiled MoE guard");
+        validate_routing_trace(tokens, c.top_k, c.experts, expert_ids, expert_weights, counts);
         cudaStream_t s = nullptr;
         const int H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;
         const size_t A = static_cast<size_t>(tokens) * K, ee = static_cast<size_t>(H) * I;

@@ -55,6 +55,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// The same barrier with an AND vote: every one of the `threads` threads receives true only if all passed true.
+__device__ __forceinline__ bool named_barrier_all(uint32_t id, uint32_t threads, bool value) {
+    uint32_t result;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 p, %3, 0;\n"
+        "bar.red.and.pred q, %1, %2, p;\n"
+        "selp.u32 %0, 1, 0, q;\n"
+        "}\n"
+        : "=r"(result)
+        : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(value))
+        : "memory");
+    return result != 0;
+}
 // fp32 x4 reduction into global memory (performed at L2, no return value).
 __device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d)

@@ -176,6 +176,52 @@ def test_split_kv_decode_kernel_ragged_contexts(dev, port, bf16, hq, hkv, d, spl
         assert rel_err(got[b], want) < (2e-2 if bf16 else 1e-4), (b, int(ctx[b]))
 
 
+def test_paged_kernels_skip_positions_and_blocks_outside_the_cache(dev, port):
+    """A length past the block table or a block id outside the pool (as a faulty producer kernel could
+    write them) must not be followed: the append skips the token, the decode cuts the context to what the
+    table covers, and both report through the device status word (bit 0x200)."""
+    rng = np.random.default_rng(9)
+    batch, hq, hkv, d, block, max_blocks = 2, 8, 2, 128, 16, 4
+    num_blocks = batch * max_blocks
+    torch = dev.torch
+    lib, s = L.load(), C.c_void_p(dev.stream())
+    word = C.c_uint32(0)
+    L.check(lib.sfb_device_status(C.byref(word)))  # start from a clear word
+    k_pool = dev.zeros((num_blocks, hkv, block, d), torch.bfloat16)
+    v_pool = dev.zeros((num_blocks, hkv, block, d), torch.bfloat16)
+    table = np.arange(num_blocks, dtype=np.int32).reshape(batch, max_blocks)
+    table[1, 0] = num_blocks + 5                      # sequence 1: first block id lies outside the pool
+    dtab = dev.i32(table)
+    k = dev.bf16(np.ones((batch, hkv, 1, d), np.float32))
+    # sequence 0 appends at position 64 = one past the table (4 blocks x 16 tokens), sequence 1 into the bad block
+    start = dev.i32(np.array([max_blocks * block, 3]))
+    L.check(lib.sfb_k_paged_kv_append(C.c_void_p(k.data_ptr()), C.c_void_p(k.data_ptr()), C.c_void_p(k_pool.data_ptr()),
+                                      C.c_void_p(v_pool.data_ptr()), C.c_void_p(dtab.data_ptr()), C.c_void_p(start.data_ptr()),
+                                      batch, hkv, 1, d, d, block, max_blocks, num_blocks, L.BF16, s))
+    L.check(lib.sfb_device_status(C.byref(word)))
+    assert word.value & 0x200
+    assert float(dev.np(k_pool).sum()) == 0.0 and float(dev.np(v_pool).sum()) == 0.0   # nothing was written
+    # decode: a context of 1000 tokens against a table that covers 64 is cut to 64 keys
+    kp = port.round_bf16(rng.standard_normal((num_blocks, hkv, block, d)).astype(np.float32))
+    vp = port.round_bf16(rng.standard_normal((num_blocks, hkv, block, d)).astype(np.float32))
+    q = port.round_bf16(rng.standard_normal((batch, hq, d)).astype(np.float32))
+    good = np.arange(num_blocks, dtype=np.int32).reshape(batch, max_blocks)
+    dk, dv, dq, dgood = dev.bf16(kp), dev.bf16(vp), dev.bf16(q), dev.i32(good)
+    outs = []
+    for lens in ([1000, 64], [64, 64]):
+        dctx = dev.i32(np.array(lens))
+        out = dev.zeros((batch, hq, d), torch.bfloat16)
+        splits = 2
+        part = dev.zeros((lib.sfb_attention_decode_workspace(batch, hq, d, splits) // 4,), torch.float32)
+        a = L.DecodeArgs(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dgood.data_ptr(), dctx.data_ptr(), out.data_ptr(),
+                         part.data_ptr(), batch, hq, hkv, d, d, block, max_blocks, num_blocks, 64, splits, 0.0, L.BF16)
+        L.check(lib.sfb_k_attention_decode_paged(C.byref(a), s))
+        L.check(lib.sfb_device_status(C.byref(word)))
+        outs.append((dev.np(out), word.value))
+    assert outs[0][1] & 0x200 and outs[1][1] == 0
+    assert np.array_equal(outs[0][0], outs[1][0])
+
+
 def test_paged_append_kernel_then_decode_roundtrip(dev, port):
     """append kernel writes exactly what gather kernel reads back (bf16, permuted table)."""
     rng = np.random.default_rng(8)
@@ -196,7 +242,7 @@ def test_paged_append_kernel_then_decode_roundtrip(dev, port):
     for kk, vv, st, n in ((k1, v1, start0, first), (k2, v2, start1, rest)):
         L.check(lib.sfb_k_paged_kv_append(C.c_void_p(kk.data_ptr()), C.c_void_p(vv.data_ptr()), C.c_void_p(k_pool.data_ptr()),
                                           C.c_void_p(v_pool.data_ptr()), C.c_void_p(dtab.data_ptr()), C.c_void_p(st.data_ptr()),
-                                          batch, hkv, n, d, d, block, max_blocks, L.BF16, s))
+                                          batch, hkv, n, d, d, block, max_blocks, int(k_pool.shape[0]), L.BF16, s))
     gk, gv = dev.zeros((batch, hkv, tokens, d), torch.bfloat16), dev.zeros((batch, hkv, tokens, d), torch.bfloat16)
     L.check(lib.sfb_k_paged_kv_gather(C.c_void_p(k_pool.data_ptr()), C.c_void_p(v_pool.data_ptr()), C.c_void_p(gk.data_ptr()),
                                       C.c_void_p(gv.data_ptr()), C.c_void_p(dtab.data_ptr()), batch, hkv, tokens, d, d,

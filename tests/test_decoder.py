@@ -371,3 +371,33 @@ def test_execute_rows_whole_range_and_guards(port):
     with pytest.raises(L.InvalidArgument, match="outside the plan"):
         plan.execute_rows(x, 64)
     plan.close()
+
+
+def test_device_wait_that_runs_out_surfaces_as_device_timeout(port, dev):
+    """Failure detection at the plan level without a fault: shard 0 of a two-shard plan is given a peer
+    buffer whose flags nothing ever sets (ordinary memory of this GPU stands in for the absent rank), so
+    the bounded wait of the fused all-reduce gives up.  sfb_decoder_execute must then return
+    SFB_DEVICE_TIMEOUT instead of SFB_OK with unsummed partials, clear the status word, and the same plan
+    must run normally afterwards."""
+    import ctypes as C
+    kw = dict(batch=1, sequence=160, hidden=256, intermediate=512, query_heads=4, kv_heads=2, head_dim=64)
+    oc, c, data = bf16_case(port, 61, **kw)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(tp_rank=0, tp_size=2, no_pipeline=True))
+    lib = L.load()
+    nbytes = lib.sfb_decoder_peer_bytes(plan._h)
+    local = dev.zeros((nbytes,), dev.torch.uint8)
+    absent = dev.zeros((nbytes,), dev.torch.uint8)
+    bases = (C.c_void_p * 2)(None, absent.data_ptr())
+    L.check(lib.sfb_decoder_set_peer_allreduce(plan._h, C.c_void_p(local.data_ptr()), bases))
+    with pytest.raises(L.SfbError) as failure:
+        plan.execute(data["input"])
+    assert failure.value.status == L.SFB_DEVICE_TIMEOUT and "wait gave up" in failure.value.message
+    word = C.c_uint32(7)
+    L.check(lib.sfb_device_status(C.byref(word)))
+    assert word.value == 0                      # reported once, then cleared
+    # back to the hook form with a hook that adds nothing: shard 0 alone runs to completion
+    L.check(lib.sfb_decoder_set_peer_allreduce(plan._h, None, None))
+    plan.set_allreduce(lambda buf, count, dtype, stream: None)
+    out, _ = plan.execute(data["input"])
+    assert np.all(np.isfinite(out))
+    plan.close()

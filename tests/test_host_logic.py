@@ -174,3 +174,34 @@ def test_seeded_generators_match_reference_fixtures():
     assert np.array_equal(api.make_decoder_input(c, 81).ravel(), dense["in_input"].ravel())
     with pytest.raises(L.InvalidArgument):
         api.make_routing_trace(api.moe_config(4, 8, 8, 2, 3), 0, 1)
+
+
+def test_malformed_routing_trace_is_rejected_on_the_host(sfb):
+    """A caller's routing trace indexes device memory by expert id and places rows by its counts, so it is
+    checked on the host before anything is copied or launched: an id outside [0, experts), counts that are
+    not the histogram of the ids, or a missing array give the reference's invalid_argument ("routing trace
+    does not match MoE configuration", src/moe_compiler.cpp:498-501).  No device is needed to be refused."""
+    import ctypes as C
+    from schedforge_b200 import api
+    config = api.moe_config(4, 8, 16, 4, 2)
+    x = np.zeros((4, 8), np.float32)
+    weights = np.full((4, 2), 0.5, np.float32)
+    good = np.array([[0, 1], [2, 3], [0, 2], [1, 3]], np.int32)
+    counts = np.array([2, 2, 2, 2], np.int32)
+    outside = good.copy()
+    outside[2, 1] = 4
+    negative = good.copy()
+    negative[0, 0] = -1
+    for ids, cnt in ((outside, counts), (negative, counts), (good, np.array([3, 1, 2, 2], np.int32))):
+        with pytest.raises(sfb.InvalidArgument, match="routing trace does not match MoE configuration"):
+            api.dispatch_tokens(config, x, ids, weights, cnt)
+        w = np.zeros((4, 8, 16), np.float32)
+        with pytest.raises(sfb.InvalidArgument, match="routing trace does not match MoE configuration"):
+            api.execute_moe(config, x, w, w, w.reshape(4, 16, 8), ids, weights, cnt)
+    lib = sfb.load()
+    offsets, tokens = np.zeros(5, np.int32), np.zeros(8, np.int32)
+    ip, fp = C.POINTER(C.c_int), C.POINTER(C.c_float)
+    status = lib.sfb_moe_dispatch_tokens(C.byref(config), x.ctypes.data_as(fp), 4, good.ctypes.data_as(ip), None,
+                                         counts.ctypes.data_as(ip), 0, None, offsets.ctypes.data_as(ip),
+                                         tokens.ctypes.data_as(ip), tokens.ctypes.data_as(ip), weights.ctypes.data_as(fp))
+    assert status == sfb.SFB_INVALID_ARGUMENT
