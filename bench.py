@@ -376,20 +376,29 @@ class Layer:
         if world > 1:
             self.plan.set_allreduce(allreduce)
             collective = args.collective
-            if collective == "auto":  # one-shot pushes cost (N-1) x bytes per rank: two ranks, or the small decode outputs
-                collective = "peer" if (world == 2 or workload == "decode") and workload != "moe" else "nccl"
-            if collective == "peer":
+            if collective == "auto":
+                # one-shot pushes cost (N-1) x bytes per rank: two ranks, or the small decode outputs; more ranks with
+                # large outputs scatter the rows to their owners and gather the sums (two-shot)
+                if workload == "moe":
+                    collective = "nccl"
+                elif world == 2 or workload == "decode":
+                    collective = "peer"
+                else:
+                    collective = "two-shot"
+            if collective in ("peer", "two-shot"):
                 def exchange(handle):
                     handles = [None] * world
                     dist.all_gather_object(handles, handle)
                     return handles
-                self.plan.enable_peer_allreduce(rank, world, exchange)
+                self.plan.enable_peer_allreduce(rank, world, exchange, 2 if collective == "two-shot" else 1)
                 dist.barrier()
             self.collective = collective
 
     def collective_text(self):
         return {"none": "none", "nccl": "nccl all-reduce after O and Down",
-                "peer": "all-reduce fused into the O and Down GEMM epilogues over NVLink peer memory"}[self.collective]
+                "peer": "all-reduce fused into the O and Down GEMM epilogues over NVLink peer memory",
+                "two-shot": "reduce-scatter fused into the O and Down GEMM epilogues over NVLink peer memory, sum + residual + "
+                            "all-gather by the row owners (peer stores)"}[self.collective]
 
     def close(self):
         import torch
@@ -397,7 +406,7 @@ class Layer:
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier()
-            if self.collective == "peer":
+            if self.collective in ("peer", "two-shot"):
                 self.plan.disable_peer_allreduce()
         self.plan.close()
 
@@ -480,7 +489,8 @@ def time_layer(layer, args, sampler):
               "ms_per_step": ms, "tokens_per_s": tokens * 1000.0 / ms,
               "e2e": {"value": tokens * 1000.0 / e2e_ms, "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": args.steps,
                       "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
-                      "io": "each rank copies its 1/N of the rows; the all-reduce hook gathers the input" if sharded_io
+                      "io": ("each rank copies its 1/N of the rows; " + ("peer stores gather the input" if layer.collective == "two-shot"
+                                                                            else "the all-reduce hook gathers the input")) if sharded_io
                       else "whole input and output on every rank"},
               "gpu_launches": int(launches), "collective": layer.collective_text(),
               "stages_ms": {"attention": result.attention_milliseconds, "projection": result.projection_milliseconds,
@@ -605,7 +615,7 @@ def main():
     ap.add_argument("--no-sub", action="store_true", help="headline only: skip the decode / moe / kernel sub-records")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "int8"],
                     help="int8: per-output-channel weight-only INT8 (the reference's quantized layer); not the default")
-    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer", "two-shot"],
                     help="N > 1: all-reduce after the O and Down projections through NCCL, or fused into the GEMM "
                          "epilogues over NVLink peer memory")
     ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_decode", "attention", "decode"],

@@ -147,6 +147,12 @@ typedef struct sfb_gemm_args {
      * the GEMM; sfb_k_peer_allreduce_finish completes it. */
     void* peer_out[SFB_MAX_PEERS - 1];
     int peer_count;
+    /* Two-shot form (scatter_rows > 0; SFB_EPI_STORE / SFB_EPI_RESIDUAL, bf16, tcgen05): row r belongs to rank
+     * r / scatter_rows and is stored ONLY to scatter_out[that rank] at row r % scatter_rows (layout
+     * [scatter_rows, n]; the entry of this rank points into its own memory); `out` is not written.
+     * sfb_k_peer_reduce_gather on the owner completes the sum. */
+    void* scatter_out[SFB_MAX_PEERS];
+    int scatter_rows;
     /* SFB_EPI_ROPE_SPLIT on a row chunk: row r of A is token (r + rope_row_offset) of the
      * [batch, seq] grid (q/key/value stay the full tensors) */
     int rope_row_offset;
@@ -155,10 +161,45 @@ typedef struct sfb_gemm_args {
      * padded with anything up to a multiple of 128 entries; y = (x . q^T) * scale, then the epilogue.
      * Follows quantize_matmul_weights / quantized_invoke, src/next_milestones.cpp:611-637, 50-69. */
     const float* bt_scales;
+    /* RMSNorm folded into the GEMM (tcgen05 backend, dense mode).  The caller has multiplied the norm weight
+     * into the weight (bt[n, k] *= norm_weight[k]) and passes A un-normalised; row r of the accumulator is
+     * multiplied by 1 / sqrt(sum_t row_ss[t * row_ss_stride + r] / k + rms_epsilon) before the epilogue, which
+     * is rms_norm (src/decoder_compiler.cpp:41-62) moved behind the product.  row_ss: device float32,
+     * row_ss_tiles partial sums of squares per row of A (one for a row written at once, several when the
+     * producing GEMM left one per column tile, see ss_out).  NULL = no scaling. */
+    const float* row_ss;
+    int row_ss_tiles;
+    int row_ss_stride;
+    float rms_epsilon;
+    /* SFB_EPI_STORE / SFB_EPI_RESIDUAL with bf16 output (tcgen05): the kernel also leaves the sums of squares
+     * of the values it stored, per row and per (128 output columns, epilogue half):
+     * ss_out[(column / 128 * 2 + half) * ss_out_stride + row]; sfb_gemm_ss_tiles(n) slots in all, which the
+     * caller zero-fills once (a ragged last column group may leave a slot untouched).  The next GEMM takes
+     * them as row_ss.  NULL = not collected. */
+    float* ss_out;
+    int ss_out_stride;
+    /* SFB_EPI_ROPE_SPLIT of a decode step (tcgen05): kv_k_pool != NULL also writes the rotated key and the
+     * value of token t of sequence b into the paged cache at position kv_position + t (block
+     * kv_table[b * kv_max_blocks + position / kv_block_tokens], pool layout of sfb_decode_args).  A position
+     * past the table or a block id outside [0, kv_num_blocks) is skipped and sets bit 0x200 of
+     * sfb_device_status.  This is the copy loop of append_paged_kv (src/next_milestones.cpp:502-522) done where
+     * K and V are produced.  (A step at position p passes rope_cos / rope_sin advanced by p rows.) */
+    void* kv_k_pool;
+    void* kv_v_pool;
+    const int* kv_table;
+    int kv_position, kv_block_tokens, kv_max_blocks, kv_num_blocks;
 } sfb_gemm_args;
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
 size_t sfb_gemm_stream_workspace_bytes(int n);
+/* Number of per-row slots sfb_gemm_args.ss_out receives for n output columns. */
+int sfb_gemm_ss_tiles(int n);
+
+/* dst[r, :] = bf16(src[r, :]) and ss[r] = sum of squares of the rounded row: the float32 -> bf16 conversion of
+ * the layer input that also prepares the folded RMSNorm of the first GEMM (row_ss with one slot per row).
+ * sfb_k_row_sumsq computes ss alone from a bf16 tensor (after an all-reduce through a library). */
+sfb_status sfb_k_convert_rows_sumsq(const float* src, void* dst_bf16, float* ss, int rows, int width, sfb_stream stream);
+sfb_status sfb_k_row_sumsq(const void* x_bf16, float* ss, int rows, int width, sfb_stream stream);
 
 /* Blocked weight layout for decode-shaped (few rows, HBM-bound) GEMMs.  The [n,k] row-major
  * bf16 weight is cut into 64x64 blocks; block (j, b) = rows [64j, 64j+64) x columns
@@ -246,6 +287,8 @@ typedef struct sfb_decode_args {
     int splits;
     float scale;
     int dtype;
+    int uniform_context;    /* > 0: every sequence holds this many tokens and context_len is not read (may be
+                               NULL): the case of a batch that decodes in lock step, whose length the host knows */
 } sfb_decode_args;
 
 size_t sfb_attention_decode_workspace(int batch, int q_heads, int head_dim_value, int splits);
@@ -380,14 +423,20 @@ typedef struct sfb_compile_options {
                              K/V are dropped, attention sees the cached context only.  != 0 = a real
                              autoregressive step: RoPE at position context_sequence, K/V of the new token
                              appended to the paged cache (append_paged_kv, src/next_milestones.cpp:486-524)
-                             and attention over context_sequence + 1 keys.  A plan can be run again: the
-                             append always writes position context_sequence. */
+                             and attention over context_sequence + 1 keys.  sfb_decoder_execute can be run
+                             again (it appends at the current cache length without advancing it);
+                             sfb_decoder_step advances. */
     int weight_int8;      /* != 0 (bf16 plans, dense FFN): per-output-channel symmetric INT8 weights as
                              quantize_decoder_weights / execute_quantized_decoder_layer
                              (src/next_milestones.cpp:660-697).  Plans of at most 128 rows keep the four
                              projections as int8 and stream half the bytes; larger plans (compute bound)
                              multiply by the dequantised q * scale weights in bf16.  The quantizer sees the
                              bf16-rounded weights. */
+    int kv_capacity;      /* decode plans with append_new_token: tokens the paged cache can hold (0 -> context_sequence
+                             + 1); sfb_decoder_step appends one token per call until the cache is full */
+    int no_norm_fusion;   /* 0: bf16 plans with fused epilogues fold both RMSNorms into the GEMM that follows (norm
+                             weight multiplied into the packed weight, 1/rms applied to the accumulator rows);
+                             != 0: stand-alone RMSNorm kernels */
     int local_expert_weights; /* MoE plans with tp_size > 1: != 0 says that w1 / w3 / w2 of sfb_decoder_data hold
                              only this rank's experts/tp_size experts (expert tp_rank * experts/tp_size first), so
                              that a rank never has to materialise the other ranks' expert weights on its host;
@@ -448,15 +497,28 @@ sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float
 sfb_status sfb_decoder_execute_rows(sfb_decoder_plan* plan, const float* input_rows, float* output_rows,
                                     int row_begin, int row_count, sfb_decoder_result* result);
 
+/* Autoregressive decode loop on a plan compiled with append_new_token (sequence == 1, context_sequence > 0):
+ * one call = one token per sequence.  The step rotates the token at position `length`, appends its K/V to the
+ * paged cache there, attends over length + 1 keys and then advances the length; a token that opens a page takes
+ * it from the BACK of the free list, like append_paged_kv (src/next_milestones.cpp:486-524).  The cache has ONE
+ * page table and ONE length for the whole batch, like the reference's PagedKVCache.  SFB_INVALID_ARGUMENT
+ * "paged KV capacity exceeded" when the cache (kv_capacity of sfb_compile_options) is full.
+ * sfb_decoder_execute on such a plan runs the same pass WITHOUT advancing (it can be repeated).
+ * sfb_decoder_kv_info: info[0..3] = length, pages in the table, free pages, total pages (as sfb_paged_info).
+ * sfb_decoder_kv_truncate / sfb_decoder_kv_release: truncate_paged_kv / release_paged_kv_pages
+ * (src/next_milestones.cpp:526-550) with the same guards and messages. */
+sfb_status sfb_decoder_step(sfb_decoder_plan* plan, const float* input, float* output, sfb_decoder_result* result);
+sfb_status sfb_decoder_kv_info(const sfb_decoder_plan* plan, int* info, int* page_table, int table_capacity,
+                               int* free_pages, int free_capacity);
+sfb_status sfb_decoder_kv_truncate(sfb_decoder_plan* plan, int new_length);
+sfb_status sfb_decoder_kv_release(sfb_decoder_plan* plan, const int* pages, int count);
+
 /* The same layer with the input already resident (last sfb_decoder_execute /
  * sfb_decoder_upload_input) and the output left on the device: kernels only. */
 sfb_status sfb_decoder_upload_input(sfb_decoder_plan* plan, const float* input);
 sfb_status sfb_decoder_execute_resident(sfb_decoder_plan* plan, sfb_stream stream);
 sfb_status sfb_decoder_download_output(sfb_decoder_plan* plan, float* output);
 
-/* Tensor-parallel hook: called on the plan's stream after the O projection and after the
- * Down projection partial sums are in `buffer` (`count` elements of `dtype`); the callee
- * must all-reduce (sum) in place on `stream`.  NULL = single shard. */
 /* ExecutablePlanOptimizer::optimize (include/schedforge/decoder_compiler.h:140-178,
  * src/decoder_compiler.cpp:726-861) on the GPU: 16 policies (fused or materialised epilogues x
  * tensor-core or CUDA-core GEMM family x tensor-core or CUDA-core attention x workspace reuse) ranked
@@ -557,6 +619,40 @@ typedef struct sfb_peer_allreduce_args {
 } sfb_peer_allreduce_args;
 sfb_status sfb_k_peer_allreduce_finish(const sfb_peer_allreduce_args* args, sfb_stream stream);
 
+/* Two-shot form of the same all-reduce for large outputs on several ranks (no counterpart in the reference):
+ * rank r owns rows [r * rows_own, (r + 1) * rows_own) of a [size * rows_own, width] bf16 tensor.
+ *   1. reduce-scatter under the GEMM: with sfb_gemm_args.scatter_rows = rows_own the O / Down projection stores
+ *      each output piece only to scatter_out[owner of the row] (this rank's slot in the owner's receive buffer,
+ *      row-local layout [rows_own, width]), so a rank sends (size - 1) / size of the tensor;
+ *   2. this kernel on the owner: waits (bounded) until every peer has delivered, adds the `slots` partial rows in
+ *      rank order in fp32 (+ the owner's rows of `residual`), rounds to bf16, writes the finished rows into
+ *      gathered[rank] (its own full tensor) and, when gather != 0, into gathered[s] of every peer with plain peer
+ *      stores (the all-gather), together with the per-row sums of squares of the rounded rows in ss[s] (optional;
+ *      what the folded RMSNorm of the next GEMM consumes), then waits (bounded) for the peers' rows.
+ * slots == 0: all-gather of rows the rank already holds (`source`, [rows_own, width]; source_ss optional).
+ * local_flags: 2 * SFB_MAX_PEERS words of this collective in this rank's memory ([s] = partial sums of rank s
+ * delivered, [SFB_MAX_PEERS + s] = finished rows of rank s delivered); peer_flags[s] = the address of entry
+ * [rank] of rank s's local_flags, as mapped into this process.  done_counter: one zeroed word per collective.
+ * epoch grows by one with every use.  A wait that gives up sets bit 0x100 of sfb_device_status. */
+typedef struct sfb_peer_gather_args {
+    const void* recv;
+    int64_t slot_elems;
+    int slots;
+    const void* source;
+    const float* source_ss;
+    const void* residual;
+    void* gathered[SFB_MAX_PEERS];
+    float* ss[SFB_MAX_PEERS];
+    uint32_t* local_flags;
+    uint32_t* peer_flags[SFB_MAX_PEERS];
+    uint32_t* done_counter;
+    int rank, size;
+    uint32_t epoch;
+    int rows_own, width;
+    int gather;
+} sfb_peer_gather_args;
+sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* args, sfb_stream stream);
+
 /* Device memory that other processes of this node can map (CUDA IPC): allocate + export a 64-byte
  * handle, map a peer's handle, unmap, free. */
 sfb_status sfb_peer_alloc(size_t bytes, void** ptr, void* handle64);
@@ -571,6 +667,17 @@ sfb_status sfb_peer_free(void* ptr);
 size_t sfb_decoder_peer_bytes(const sfb_decoder_plan* plan);
 sfb_status sfb_decoder_set_peer_allreduce(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases);
 
+/* The same with the form chosen: mode 1 = the one-shot form above (each rank pushes its whole partial tensor to
+ * every peer: two ranks, or the small outputs of decode plans), mode 2 = the two-shot form (sfb_k_peer_reduce_gather:
+ * reduce-scatter under the GEMM, then the row owners add the residual, sum, take the sums of squares for the folded
+ * RMSNorm and all-gather the finished rows with peer stores; needs rows % tp_size == 0), mode 0 = two-shot for more
+ * than two ranks and more than 128 rows, else one-shot.  With the two-shot form sfb_decoder_execute_rows gathers
+ * the input rows with peer stores as well instead of going through the hook. */
+sfb_status sfb_decoder_set_peer_collective(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases, int mode);
+
+/* Tensor-parallel hook: called on the plan's stream after the O projection and after the
+ * Down projection partial sums are in `buffer` (`count` elements of `dtype`); the callee
+ * must all-reduce (sum) in place on `stream`.  NULL = single shard. */
 typedef void (*sfb_allreduce_fn)(void* user, void* buffer, int64_t count, int dtype,
                                  sfb_stream stream);
 sfb_status sfb_decoder_set_allreduce(sfb_decoder_plan* plan, sfb_allreduce_fn fn, void* user);

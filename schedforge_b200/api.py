@@ -38,11 +38,11 @@ def decoder_config(batch=1, sequence=16, hidden=64, intermediate=128, query_head
 def compile_options(dtype=L.BF16, token_major_attention=True, fuse_epilogues=True, gemm_backend=L.GEMM_AUTO,
                     attention_backend=0, page_tokens=16, tp_rank=0, tp_size=1, seed_block_table=0,
                     no_workspace_reuse=False, no_pipeline=False, append_new_token=False, weight_int8=False,
-                    local_expert_weights=False):
+                    kv_capacity=0, no_norm_fusion=False, local_expert_weights=False):
     return L.CompileOptions(dtype, int(token_major_attention), int(fuse_epilogues), gemm_backend,
                             attention_backend, page_tokens, tp_rank, tp_size, seed_block_table,
                             int(no_workspace_reuse), int(no_pipeline), int(append_new_token), int(weight_int8),
-                            int(local_expert_weights))
+                            int(kv_capacity), int(no_norm_fusion), int(local_expert_weights))
 
 
 class StableHLOImporter:
@@ -88,6 +88,29 @@ class DecoderExecutablePlan:
                                              C.byref(result)))
         return out, result
 
+    def step(self, x, out=None):
+        """One autoregressive step (sfb_decoder_step): appends the token's K/V, attends, advances the cache."""
+        x = _f32(x)
+        if out is None:
+            out = np.empty((self.rows, self.config.hidden), np.float32)
+        result = L.DecoderResult()
+        L.check(L.load().sfb_decoder_step(self._h, _fp(x), _fp(out), C.byref(result)))
+        return out, result
+
+    def kv_info(self):
+        info = np.zeros(4, np.int32)
+        table, free = np.zeros(65536, np.int32), np.zeros(65536, np.int32)
+        L.check(L.load().sfb_decoder_kv_info(self._h, _ip(info), _ip(table), table.size, _ip(free), free.size))
+        return {"length": int(info[0]), "page_table": table[:info[1]].copy(), "free_pages": free[:info[2]].copy(),
+                "pages": int(info[3])}
+
+    def kv_truncate(self, new_length):
+        L.check(L.load().sfb_decoder_kv_truncate(self._h, int(new_length)))
+
+    def kv_release(self, pages):
+        pages = _i32(pages)
+        L.check(L.load().sfb_decoder_kv_release(self._h, _ip(pages), pages.size))
+
     def execute_ptr(self, in_ptr, out_ptr, result=None):
         """Same call with raw host addresses (e.g. pinned torch tensors)."""
         L.check(L.load().sfb_decoder_execute(self._h, C.c_void_p(in_ptr), C.c_void_p(out_ptr), None, None, None,
@@ -127,8 +150,10 @@ class DecoderExecutablePlan:
         self._callback = L.ALLREDUCE_FN(lambda user, buf, count, dtype, stream: fn(buf, count, dtype, stream))
         L.check(L.load().sfb_decoder_set_allreduce(self._h, self._callback, None))
 
-    def enable_peer_allreduce(self, rank, world, exchange):
+    def enable_peer_allreduce(self, rank, world, exchange, mode=1):
         """Fused all-reduce over NVLink peer memory for the O and Down projections of a sharded plan.
+        mode 1 = one-shot, 2 = two-shot (reduce-scatter under the GEMM, sum + all-gather by the row owners),
+        0 = pick (sfb_decoder_set_peer_collective).
 
         exchange(handle: bytes) -> list of every rank's 64-byte handle in rank order (for instance
         torch.distributed.all_gather_object).  Every rank must call this at the same point."""
@@ -147,7 +172,7 @@ class DecoderExecutablePlan:
             bases[s] = mapped.value
             self._peer_mapped.append(mapped)
         self._peer_local = local
-        L.check(lib.sfb_decoder_set_peer_allreduce(self._h, local, bases))
+        L.check(lib.sfb_decoder_set_peer_collective(self._h, local, bases, int(mode)))
 
     def disable_peer_allreduce(self):
         """Unmaps the peers' buffers and frees the local one (call on every rank after a barrier)."""

@@ -20,12 +20,13 @@ struct DecodeParams {
     // either one ORs kCodeDecodeBounds into the device status word instead of touching memory out of bounds.
     int context_limit, num_blocks;
     uint32_t* status;
+    int uniform_context;  // > 0: the length of every sequence (context_len is not read)
 };
 
 constexpr uint32_t kCodeDecodeBounds = 0x200;
 
 __device__ __forceinline__ int guarded_context(const DecodeParams& p, int b) {
-    int ctx = p.context_len[b];
+    int ctx = p.uniform_context > 0 ? p.uniform_context : p.context_len[b];
     if (ctx > p.context_limit || ctx < 0) {
         ctx = ctx < 0 ? 0 : p.context_limit;
         if (threadIdx.x == 0) atomicOr(p.status, kCodeDecodeBounds);

@@ -393,7 +393,8 @@ int sfb_attention_decode_default_splits(int batch, int kv_heads, int max_context
 }
 
 sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream stream) {
-    SFB_REQUIRE(a && a->q && a->k_pool && a->v_pool && a->block_table && a->context_len && a->out && a->partials,
+    SFB_REQUIRE(a && a->q && a->k_pool && a->v_pool && a->block_table && (a->context_len || a->uniform_context > 0) &&
+                    a->out && a->partials,
                 "paged decode: null tensor");
     SFB_REQUIRE(a->batch > 0 && a->q_heads > 0 && a->kv_heads > 0 && a->head_dim > 0 && a->head_dim_value > 0 &&
                 a->block_tokens > 0 && a->max_blocks > 0 && a->q_heads % a->kv_heads == 0,
@@ -403,7 +404,7 @@ sfb_status sfb_k_attention_decode_paged(const sfb_decode_args* a, sfb_stream str
     DecodeParams p{a->q, a->k_pool, a->v_pool, a->block_table, a->context_len, a->out,
                    static_cast<float*>(a->partials), a->batch, a->q_heads, a->kv_heads, a->head_dim,
                    a->head_dim_value, a->block_tokens, a->max_blocks, splits,
-                   a->scale > 0.0F ? a->scale : 1.0F / sqrtf(static_cast<float>(a->head_dim)), 0, 0, 0, nullptr};
+                   a->scale > 0.0F ? a->scale : 1.0F / sqrtf(static_cast<float>(a->head_dim)), 0, 0, 0, nullptr, a->uniform_context};
     {
         const int bound = a->max_context > 0 ? a->max_context : a->max_blocks * a->block_tokens;
         const int granule = 4 * a->block_tokens;

@@ -103,6 +103,66 @@ rms_norm_row_block_kernel(const bf16* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// float32 rows -> bf16 rows plus the sum of squares of each rounded row (SRC = float), or the sum of squares
+// of bf16 rows alone (SRC = bf16, dst unused).  One 256-thread block per row for at most 128 rows (decode), one warp per row
+// otherwise; width % 8 == 0 takes 16/32-byte accesses.
+template <class SRC, bool BLOCK_PER_ROW>
+__global__ void __launch_bounds__(256)
+rows_sumsq_kernel(const SRC* __restrict__ src, bf16* __restrict__ dst, float* __restrict__ ss, int rows, int width) {
+    __shared__ float partial[8];
+    const int lane = threadIdx.x & 31;
+    const int row = BLOCK_PER_ROW ? blockIdx.x : (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int first = BLOCK_PER_ROW ? threadIdx.x : lane, step = BLOCK_PER_ROW ? 256 : 32;
+    float sum = 0.0F;
+    if (row < rows) {
+        const SRC* in = src + static_cast<size_t>(row) * width;
+        if ((width & 7) == 0) {
+            for (int c = first; c < width / 8; c += step) {
+                float f[8];
+                if constexpr (sizeof(SRC) == 4) {
+                    const float4 a = reinterpret_cast<const float4*>(in)[2 * c], b = reinterpret_cast<const float4*>(in)[2 * c + 1];
+                    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+                    uint4 packed;
+                    bf16* r = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { r[i] = from_float<bf16>(f[i]); f[i] = to_float(r[i]); }
+                    reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * width)[c] = packed;
+                } else {
+                    const uint4 packed = reinterpret_cast<const uint4*>(in)[c];
+                    const bf16* v = reinterpret_cast<const bf16*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] = to_float(v[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum = fmaf(f[i], f[i], sum);
+            }
+        } else {
+            for (int c = first; c < width; c += step) {
+                float f = to_float(in[c]);
+                if constexpr (sizeof(SRC) == 4) {
+                    const bf16 r = from_float<bf16>(f);
+                    dst[static_cast<size_t>(row) * width + c] = r;
+                    f = to_float(r);
+                }
+                sum = fmaf(f, f, sum);
+            }
+        }
+    }
+    sum = warp_sum(sum);
+    if constexpr (BLOCK_PER_ROW) {
+        if (lane == 0) partial[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float total = 0.0F;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) total += partial[i];
+            ss[row] = total;
+        }
+    } else if (lane == 0 && row < rows) {
+        ss[row] = sum;
+    }
+}
+
 template <class T>
 __global__ void add_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ z,
                            int64_t count) {
@@ -241,6 +301,23 @@ sfb_status sfb_k_convert(const void* src, sfb_dtype src_dtype, void* dst, sfb_dt
     else
         convert_kernel<bf16, bf16><<<grid, block, 0, s>>>(static_cast<const bf16*>(src), static_cast<bf16*>(dst), count);
     return check_launch("convert");
+}
+
+sfb_status sfb_k_convert_rows_sumsq(const float* src, void* dst_bf16, float* ss, int rows, int width, sfb_stream stream) {
+    SFB_REQUIRE(src && dst_bf16 && ss && rows > 0 && width > 0, "convert: empty tensor");
+    cudaStream_t s = as_stream(stream);
+    if (rows <= 128) rows_sumsq_kernel<float, true><<<rows, 256, 0, s>>>(src, static_cast<bf16*>(dst_bf16), ss, rows, width);
+    else rows_sumsq_kernel<float, false><<<ceil_div(rows, 8), 256, 0, s>>>(src, static_cast<bf16*>(dst_bf16), ss, rows, width);
+    return check_launch("convert_rows_sumsq");
+}
+
+sfb_status sfb_k_row_sumsq(const void* x_bf16, float* ss, int rows, int width, sfb_stream stream) {
+    SFB_REQUIRE(x_bf16 && ss && rows > 0 && width > 0, "row sums of squares: empty tensor");
+    cudaStream_t s = as_stream(stream);
+    const bf16* x = static_cast<const bf16*>(x_bf16);
+    if (rows <= 128) rows_sumsq_kernel<bf16, true><<<rows, 256, 0, s>>>(x, nullptr, ss, rows, width);
+    else rows_sumsq_kernel<bf16, false><<<ceil_div(rows, 8), 256, 0, s>>>(x, nullptr, ss, rows, width);
+    return check_launch("row_sumsq");
 }
 
 sfb_status sfb_rope_table(int seq, int head_dim, float theta, float* cos_out, float* sin_out) {

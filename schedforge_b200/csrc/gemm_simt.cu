@@ -365,7 +365,9 @@ sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream) {
     SFB_REQUIRE(!args->bt_tiled || (!args->group_offsets && args->backend != SFB_GEMM_SIMT),
                 "gemm: the blocked weight layout needs the dense tcgen05 kernel");
     int backend = args->backend;
-    if (args->bt_tiled || args->peer_count != 0 || args->bt_scales) backend = SFB_GEMM_TCGEN05;  // only that kernel knows these
+    if (args->bt_tiled || args->peer_count != 0 || args->scatter_rows != 0 || args->bt_scales || args->row_ss || args->ss_out ||
+        args->kv_k_pool)
+        backend = SFB_GEMM_TCGEN05;  // only that kernel knows these
     if (backend == SFB_GEMM_AUTO)
         backend = gemm_bf16_tcgen05_supported(*args) ? SFB_GEMM_TCGEN05 : SFB_GEMM_SIMT;
     if (backend == SFB_GEMM_TCGEN05) {

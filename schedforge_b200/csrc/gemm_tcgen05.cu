@@ -76,10 +76,23 @@ struct TcParams {
     const float* col_scale;             // weight-only INT8: one factor per output column, applied before the epilogue
     bf16* peer_out[SFB_MAX_PEERS - 1];  // copies of the output in other GPUs' memory (fused all-reduce)
     int peer_count;
+    bf16* scatter_out[SFB_MAX_PEERS];   // two-shot form: this rank's slot in the receive buffer of every row owner
+    int scatter_rows;                   // rows per owner (0 = off)
     float* accum;
     int* tile_counters;
     int shared_tiles;       // trailing tiles whose K blocks are cut into equal ranges (0 = none)
     uint32_t* status;
+    // RMSNorm folded into this GEMM: accumulator row r is multiplied by 1/sqrt(sum_t row_ss[t][r] / k + eps)
+    const float* row_ss;
+    int row_ss_tiles, row_ss_stride;
+    float rms_eps;
+    // per-row sums of squares of the stored bf16 outputs, one slot per (128 output columns, epilogue half)
+    float* ss_out;
+    int ss_out_stride;
+    // RoPE epilogue of a decode step: the paged cache that receives K and V
+    bf16 *kv_k_pool, *kv_v_pool;
+    const int* kv_table;
+    int kv_position, kv_block_tokens, kv_max_blocks, kv_num_blocks;
 };
 
 struct TileCoord {
@@ -254,19 +267,32 @@ __device__ __forceinline__ void add_bf16x8(const bf16* src, float (&f)[8], int v
     }
 }
 
-// Epilogue of output columns [col, col + 8) of `row` (not SwiGLU); col is a multiple of 8.
-__device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float (&f)[8], bool residual_added = false) {
-    if (col >= p.n) return;
+// Sum of squares of up to 8 values as they read back after rounding to bf16.
+__device__ __forceinline__ float sumsq_bf16x8(const float (&f)[8], int valid) {
+    float ss = 0.0F;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float v = __bfloat162float(__float2bfloat16_rn(f[i]));
+        if (i < valid) ss = fmaf(v, v, ss);
+    }
+    return ss;
+}
+
+// Epilogue of output columns [col, col + 8) of `row` (not SwiGLU); col is a multiple of 8.  Returns the sum of
+// squares of the stored values when the kernel collects them for the RMSNorm of the next GEMM (else 0).
+__device__ __forceinline__ float emit8(const TcParams& p, int row, int col, float (&f)[8], bool residual_added = false) {
+    if (col >= p.n) return 0.0F;
     if (p.epilogue == SFB_EPI_ROPE_SPLIT) {  // head_dim % 32 == 0: the 8 columns lie in one head
         const int hidden = p.q_heads * p.head_dim, kvw = p.kv_heads * p.head_dim;
         const int token = row + p.rope_row_offset;
         const int b = token / p.seq, t = token - b * p.seq;
         bf16* dst;
+        bf16* pool = nullptr;
         int heads, local;
         bool rotate = true;
         if (col < hidden) { dst = p.q; heads = p.q_heads; local = col; }
-        else if (col < hidden + kvw) { dst = p.key; heads = p.kv_heads; local = col - hidden; }
-        else { dst = p.value; heads = p.kv_heads; local = col - hidden - kvw; rotate = false; }
+        else if (col < hidden + kvw) { dst = p.key; heads = p.kv_heads; local = col - hidden; pool = p.kv_k_pool; }
+        else { dst = p.value; heads = p.kv_heads; local = col - hidden - kvw; rotate = false; pool = p.kv_v_pool; }
         const int head = local / p.head_dim, d0 = local - head * p.head_dim;
         if (rotate) {
             const size_t at = static_cast<size_t>(t) * (p.head_dim / 2) + d0 / 2;
@@ -281,19 +307,37 @@ __device__ __forceinline__ void emit8(const TcParams& p, int row, int col, float
             }
         }
         store8(dst, 0, ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d0, f, 8);
-        return;
+        if (pool) {
+            // the new token's key / value also goes to slot kv_position + t of sequence b in the paged cache; a
+            // position past the table or a block outside the pool is skipped and flagged, never written
+            const int pos = p.kv_position + t, block = pos / p.kv_block_tokens;
+            int page = -1;
+            if (block < p.kv_max_blocks) page = p.kv_table[static_cast<size_t>(b) * p.kv_max_blocks + block];
+            if (page >= 0 && page < p.kv_num_blocks)
+                store8(pool, 0, ((static_cast<size_t>(page) * p.kv_heads + head) * p.kv_block_tokens + pos % p.kv_block_tokens) *
+                                        p.head_dim + d0, f, 8);
+            else
+                atomicOr(p.status, 0x200u);
+        }
+        return 0.0F;
     }
     const size_t index = static_cast<size_t>(row) * p.n + col;
     const int valid = p.n - col;
     if (p.epilogue == SFB_EPI_RESIDUAL && !residual_added) add_bf16x8(p.residual + index, f, valid);
+    if (p.scatter_rows > 0) {  // reduce-scatter: the piece goes to the owner of its row only (a peer store unless that is this rank)
+        const int owner = row / p.scatter_rows;
+        store8(p.scatter_out[owner], 0, static_cast<size_t>(row - owner * p.scatter_rows) * p.n + col, f, valid);
+        return 0.0F;
+    }
     store8(p.out, p.out_f32, index, f, valid);
     for (int i = 0; i < p.peer_count; ++i) store8(p.peer_out[i], 0, index, f, valid);  // peer stores over NVLink
+    return p.ss_out ? sumsq_bf16x8(f, valid) : 0.0F;
 }
 
 // phase 2 for one warp: the staged values are output columns [col0, col0 + 32) of rows
 // [row0, row0 + 32); `plain` = they are final (SwiGLU) and only need storing into [m, width].
 __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stage, int lane, int row0, int row_end,
-                                            int col0, bool plain, int width) {
+                                            int col0, bool plain, int width, float (&row_ss)[4]) {
     // The residual rows come from DRAM: all four loads of this lane go out before the first is used
     // (one at a time, they made the epilogue of a tile as long as its main loop).
     const bool prefetch = !plain && p.epilogue == SFB_EPI_RESIDUAL && (p.n & 7) == 0 &&
@@ -325,7 +369,23 @@ __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stag
             }
         }
         if (plain) store8(p.out, p.out_f32, static_cast<size_t>(row) * width + col, f, width - col);
-        else emit8(p, row, col, f, prefetch);
+        else row_ss[i] += emit8(p, row, col, f, prefetch);
+    }
+}
+
+// Sums of squares collected by one warp over the chunks of one 128-column group: the four lanes of a row
+// are added and the row's slot (group, epilogue half `pass`) is written.
+__device__ __forceinline__ void flush_row_ss(const TcParams& p, float (&row_ss)[4], int lane, int row0, int row_end,
+                                             int col_group, int pass) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float v = row_ss[i];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        const int row = row0 + i * 8 + (lane >> 2);
+        if ((lane & 3) == 0 && row < row_end)
+            p.ss_out[static_cast<size_t>(col_group * 2 + pass) * p.ss_out_stride + row] = v;
+        row_ss[i] = 0.0F;
     }
 }
 
@@ -335,7 +395,7 @@ template <int BN, bool SCALED>
 __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segment& sg, const TileCoord& c, int k_blocks,
                                                  uint32_t acc, uint32_t tmem_empty_bar, float* stage,
                                                  volatile uint32_t* last_flag, int quarter, int pass, int lane,
-                                                 bool leader) {
+                                                 bool leader, float row_inv) {
     constexpr uint32_t kEpilogueThreads = 32 * kEpilogueWarps;
     const int row_in_tile = quarter * 32 + lane;
     const int row0 = c.row_start + quarter * 32;
@@ -404,6 +464,8 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
         if (out0 + pass * 32 < width) fetch(pass * 32, r0);
         fetch((pass + 2) * 32, r1);
     }
+    float row_ss[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+    const bool collect = p.ss_out != nullptr && !swiglu;
 #pragma unroll 1
     for (int ch = pass; ch < chunks; ch += 2) {
         const int col0 = out0 + ch * 32;
@@ -432,6 +494,13 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
                 if (swiglu) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * __ldg(scale1 + i));
             }
         }
+        if (p.row_ss) {  // folded RMSNorm: the whole accumulator row carries the factor 1/rms(row of A)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                r0[i] = __float_as_uint(__uint_as_float(r0[i]) * row_inv);
+                if (swiglu) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * row_inv);
+            }
+        }
         if (swiglu) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -441,9 +510,20 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
         }
         stage_write(stage, lane, r0);
         __syncwarp();
-        emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width);
+        emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width, row_ss);
         __syncwarp();
+        // the chunks of this warp advance by 64 columns: the last one inside a 128-column group closes its slot
+        if (collect && ((col0 + 64) / 128 != col0 / 128 || ch + 2 >= chunks || col0 + 64 >= width))
+            flush_row_ss(p, row_ss, lane, row0, c.row_end, col0 / 128, pass);
     }
+}
+
+// 1 / rms of row `row` of A from the partial sums of squares its producer left (see TcParams::row_ss).
+__device__ __forceinline__ float folded_row_inv(const TcParams& p, int row, bool row_ok) {
+    if (!p.row_ss || !row_ok) return 1.0F;
+    float ss = 0.0F;
+    for (int t = 0; t < p.row_ss_tiles; ++t) ss += __ldcg(p.row_ss + static_cast<size_t>(t) * p.row_ss_stride + row);
+    return 1.0F / sqrtf(ss / static_cast<float>(p.k) + p.rms_eps);
 }
 
 template <int BN, bool STREAM>
@@ -678,6 +758,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (; walk.next(sg); ++count) {
             const TileCoord c = tile_coord(p, sg.tile, m_tiles);
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
+            // read while the tile's main loop is still running
+            const float row_inv = folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end);
             bool go = ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue);
             // With cut-up tiles the epilogue threads meet at barriers that have no time limit, so they must all
             // take the same decision here: one thread that saw the abort flag takes the whole group out.
@@ -686,7 +768,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             epilogue_segment<BN, false>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter, pass,
-                                 lane, leader);
+                                 lane, leader, row_inv);
         }
     }
 
@@ -957,7 +1039,8 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             epilogue_segment<BN, true>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter,
-                                       pass, lane, leader);
+                                       pass, lane, leader,
+                                       folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end));
         }
     }
 
@@ -994,6 +1077,25 @@ __global__ void build_tile_table_kernel(const int* __restrict__ offsets, int gro
 }
 
 bool stream_shape(const sfb_gemm_args& g) { return g.m <= BM && !g.group_offsets; }
+
+// folded RMSNorm, sums of squares of the output, decode-step RoPE position and paged K/V append
+void fill_fold_params(TcParams& p, const sfb_gemm_args& g) {
+    p.row_ss = g.row_ss;
+    p.row_ss_tiles = g.row_ss_tiles;
+    p.row_ss_stride = g.row_ss_stride;
+    p.rms_eps = g.rms_epsilon;
+    p.scatter_rows = g.scatter_rows;
+    for (int i = 0; i < SFB_MAX_PEERS; ++i) p.scatter_out[i] = static_cast<bf16*>(g.scatter_out[i]);
+    p.ss_out = g.out_f32 || g.scatter_rows > 0 ? nullptr : g.ss_out;
+    p.ss_out_stride = g.ss_out_stride;
+    p.kv_k_pool = static_cast<bf16*>(g.kv_k_pool);
+    p.kv_v_pool = static_cast<bf16*>(g.kv_v_pool);
+    p.kv_table = g.kv_table;
+    p.kv_position = g.kv_position;
+    p.kv_block_tokens = g.kv_block_tokens;
+    p.kv_max_blocks = g.kv_max_blocks;
+    p.kv_num_blocks = g.kv_num_blocks;
+}
 
 template <int BN, bool STREAM>
 sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
@@ -1033,6 +1135,7 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     p.peer_count = g.peer_count;
     for (int i = 0; i < g.peer_count; ++i) p.peer_out[i] = static_cast<bf16*>(g.peer_out[i]);
     p.status = device_status_word();
+    fill_fold_params(p, g);
     int max_m_tiles;
     if (g.group_offsets) {
         SFB_REQUIRE(g.tile_table, "gemm: grouped tcgen05 mode needs tile_table scratch");
@@ -1096,6 +1199,7 @@ sfb_status launch_w8(const sfb_gemm_args& g, cudaStream_t stream) {
     p.peer_count = g.peer_count;
     for (int i = 0; i < g.peer_count; ++i) p.peer_out[i] = static_cast<bf16*>(g.peer_out[i]);
     p.status = device_status_word();
+    fill_fold_params(p, g);
     p.tile_table = nullptr;
     p.dense_m_tiles = 1;
     const long long tiles = p.n_tiles;
@@ -1137,6 +1241,20 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
     if (g.peer_count != 0 && (g.peer_count < 0 || g.peer_count >= SFB_MAX_PEERS || g.out_f32 || g.group_offsets ||
                               (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL)))
         return false;
+    if (g.scatter_rows != 0) {
+        if (g.scatter_rows < 0 || g.out_f32 || g.group_offsets || g.peer_count != 0 ||
+            (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL) || ceil_div(g.m, g.scatter_rows) > SFB_MAX_PEERS)
+            return false;
+        for (int i = 0; i < ceil_div(g.m, g.scatter_rows); ++i)
+            if (!g.scatter_out[i]) return false;
+    }
+    if (g.row_ss && (g.group_offsets || g.row_ss_tiles <= 0 || g.row_ss_stride < g.m)) return false;
+    if (g.ss_out && (g.group_offsets || g.ss_out_stride < g.m ||
+                     (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL)))
+        return false;
+    if (g.kv_k_pool && (g.epilogue != SFB_EPI_ROPE_SPLIT || !g.kv_v_pool || !g.kv_table || g.kv_block_tokens <= 0 ||
+                        g.kv_max_blocks <= 0 || g.kv_position < 0))
+        return false;
     return true;
 }
 
@@ -1148,6 +1266,8 @@ sfb_status gemm_bf16_tcgen05(const sfb_gemm_args& g, cudaStream_t stream) {
 }
 
 }  // namespace sfb
+
+extern "C" int sfb_gemm_ss_tiles(int n) { return n > 0 ? 2 * sfb::ceil_div(n, 128) : 0; }
 
 extern "C" size_t sfb_gemm_stream_workspace_bytes(int n) {
     if (n <= 0) return 0;

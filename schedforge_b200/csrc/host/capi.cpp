@@ -137,6 +137,35 @@ sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float
     });
 }
 
+sfb_status sfb_decoder_step(sfb_decoder_plan* plan, const float* input, float* output, sfb_decoder_result* result) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->step(input, output, result);
+    });
+}
+
+sfb_status sfb_decoder_kv_info(const sfb_decoder_plan* plan, int* info, int* page_table, int table_capacity,
+                               int* free_pages, int free_capacity) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->kv_info(info, page_table, table_capacity, free_pages, free_capacity);
+    });
+}
+
+sfb_status sfb_decoder_kv_truncate(sfb_decoder_plan* plan, int new_length) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->kv_truncate(new_length);
+    });
+}
+
+sfb_status sfb_decoder_kv_release(sfb_decoder_plan* plan, const int* pages, int count) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->kv_release(pages, count);
+    });
+}
+
 sfb_status sfb_decoder_upload_input(sfb_decoder_plan* plan, const float* input) {
     return guarded([&] {
         if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
@@ -181,6 +210,13 @@ sfb_status sfb_decoder_set_peer_allreduce(sfb_decoder_plan* plan, void* local_ba
     return guarded([&] {
         if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
         plan->plan->set_peer_allreduce(local_base, peer_bases);
+    });
+}
+
+sfb_status sfb_decoder_set_peer_collective(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases, int mode) {
+    return guarded([&] {
+        if (!plan || !plan->plan) throw std::invalid_argument("null decoder plan");
+        plan->plan->set_peer_allreduce(local_base, peer_bases, mode);
     });
 }
 

@@ -107,7 +107,35 @@ struct DecoderExecutablePlan::Impl {
     bool decode = false, paged = false;
     int page_tokens = 16, max_blocks = 0, num_blocks = 0, splits = 1;
     bool append_new = false;        // autoregressive step: append the new token's K/V, attend over context + 1
-    int* context_len_attend = nullptr;  // context_len, or context_len + 1 when the new token is appended
+    // RMSNorm folded into the following GEMM: norm weight inside the packed weight, 1/rms applied to accumulator rows
+    bool fold1 = false, fold2 = false;
+    float rms_eps = 1.0e-5F;
+    // where the sums of squares of the current pass live (workspace, or the gathered copies of a two-shot plan)
+    const float* cur_ss1 = nullptr;
+    const float* cur_ss2 = nullptr;
+    int cur_ss2_tiles = 1;
+    int scatter_set = -1;           // >= 0: the GEMM being set up scatters its rows to their owners (two-shot form)
+    int ss2_tiles = 1;              // partial sums of squares per row of attention_residual that feed the second fold
+    bool kv_in_epilogue = false;    // the QKV epilogue writes the new token's K/V into the paged cache itself
+    // Paged cache accounting of a decode plan, kept like the reference's PagedKVCache (one page table and one
+    // length for the whole batch, pages taken from the back of the free list; src/next_milestones.cpp:486-550).
+    // Page p of sequence b is physical block block_ids[p * batch + b] of the pool.
+    int kv_length = 0, kv_capacity = 0;
+    std::vector<int> page_table, free_pages, block_ids;
+    int* len_pinned = nullptr;      // start lengths for the stand-alone append kernel (plans without the fused append)
+    int len_uploaded = -1;
+    // Device block table for ALL logical blocks: the pages in use, then the free pages in the order they will be
+    // handed out, so that a step that crosses a page boundary finds its entry already there.
+    void sync_table(int batch, cudaStream_t s) {
+        std::vector<int> order(page_table);
+        for (auto it = free_pages.rbegin(); it != free_pages.rend(); ++it) order.push_back(*it);
+        std::vector<int> table(static_cast<std::size_t>(batch) * max_blocks, 0);
+        for (int b = 0; b < batch; ++b)
+            for (std::size_t i = 0; i < order.size() && i < static_cast<std::size_t>(max_blocks); ++i)
+                table[static_cast<std::size_t>(b) * max_blocks + i] = block_ids[static_cast<std::size_t>(order[i]) * batch + b];
+        cuda_check(cudaMemcpyAsync(block_table, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice, s), "block table");
+        cuda_check(cudaStreamSynchronize(s), "block table sync");
+    }
 
     DeviceBuffer weights, workspace, kv_pool;
     WorkspacePlanner planner{true};
@@ -144,6 +172,8 @@ struct DecoderExecutablePlan::Impl {
         cuda_check(cudaMemsetAsync(status_device, 0, sizeof(uint32_t), s), "status clear");
         if (has("gemm_partials"))
             cuda_check(cudaMemsetAsync(ws("gemm_partials"), 0, planner.bytes(planner.find("gemm_partials")), s), "scratch clear");
+        if (peer_local)  // the block counters of the two-shot kernels must start at zero again
+            cuda_check(cudaMemsetAsync(peer_local + counters_offset(), 0, 64, s), "counter clear");
         cuda_check(cudaStreamSynchronize(s), "status clear sync");
         char text[96];
         std::snprintf(text, sizeof(text), "a bounded device-side wait gave up (status word 0x%x)", word);
@@ -163,6 +193,54 @@ struct DecoderExecutablePlan::Impl {
             if (r != rank)
                 g.peer_out[g.peer_count++] =
                     peer_remote[r] + (static_cast<std::size_t>(set) * size + rank) * peer_slot_bytes() + offset * 2;
+    }
+    // ---- two-shot form (reduce-scatter under the GEMM, sum + all-gather by the row owners), see peer_allreduce.cu.
+    // Behind the one-shot slots and their flags the peer buffer holds: two-shot flags and counters, the receive
+    // slots [2 sets][size][T / size rows], three gathered tensors (layer input, attention_residual, output) that
+    // every rank's finish kernel fills on every rank, and the gathered sums of squares of the first two.
+    int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot
+    bool input_in_peer = false;    // the resident input is the gathered copy (sfb_decoder_execute_rows on a two-shot plan)
+    uint32_t gather_epoch[3] = {0, 0, 0};
+    std::size_t th_bytes() const { return (static_cast<std::size_t>(T) * H * 2 + 1023) / 1024 * 1024; }
+    std::size_t slot2_bytes() const { return (static_cast<std::size_t>(T / size) * H * 2 + 255) / 256 * 256; }
+    std::size_t flags2_offset() const { return peer_flags_offset() + 256; }
+    std::size_t counters_offset() const { return peer_flags_offset() + 1024; }
+    std::size_t recv2_offset() const { return peer_flags_offset() + 2048; }
+    std::size_t gathered_offset(int which) const { return recv2_offset() + 2 * size * slot2_bytes() + which * th_bytes(); }
+    std::size_t ss_offset(int which) const { return gathered_offset(3) + which * ((static_cast<std::size_t>(T) * 4 + 255) / 256 * 256); }
+    std::size_t peer_total_bytes() const { return ss_offset(2) + 256; }
+    char* peer_base(int r) const { return r == rank ? peer_local : peer_remote[r]; }
+    template <class P = void> P* gathered(int which) const { return reinterpret_cast<P*>(peer_local + gathered_offset(which)); }
+    float* gathered_ss(int which) const { return reinterpret_cast<float*>(peer_local + ss_offset(which)); }
+    bool two_shot() const { return size > 1 && peer_local != nullptr && peer_mode == 2; }
+    // this rank's slot of slot set `set` in the receive buffer of every row owner
+    void fill_scatter_out(sfb_gemm_args& g, int set) const {
+        g.scatter_rows = T / size;
+        for (int r = 0; r < size; ++r)
+            g.scatter_out[r] = peer_base(r) + recv2_offset() + (static_cast<std::size_t>(set) * size + rank) * slot2_bytes();
+    }
+    // Owner side of collective `coll` (0 = all-gather of the input rows, 1 = after O, 2 = after Down): sums the slots of
+    // set coll - 1 (+ residual rows), writes gathered tensor `coll` and optionally its sums of squares on every rank.
+    sfb_status reduce_gather(int coll, const void* source, const float* source_ss, const void* residual, bool with_ss, cudaStream_t s) {
+        sfb_peer_gather_args a{};
+        const int rows_own = T / size;
+        if (coll > 0) {
+            a.recv = peer_local + recv2_offset() + static_cast<std::size_t>(coll - 1) * size * slot2_bytes();
+            a.slot_elems = static_cast<int64_t>(slot2_bytes() / 2);
+            a.slots = size;
+        }
+        a.source = source; a.source_ss = source_ss; a.residual = residual;
+        for (int r = 0; r < size; ++r) {
+            a.gathered[r] = peer_base(r) + gathered_offset(coll);
+            a.ss[r] = with_ss ? reinterpret_cast<float*>(peer_base(r) + ss_offset(coll)) : nullptr;
+            if (r != rank)
+                a.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_remote[r] + flags2_offset()) + coll * 2 * SFB_MAX_PEERS + rank;
+        }
+        a.local_flags = reinterpret_cast<uint32_t*>(peer_local + flags2_offset()) + coll * 2 * SFB_MAX_PEERS;
+        a.done_counter = reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + coll;
+        a.rank = rank; a.size = size; a.epoch = ++gather_epoch[coll];
+        a.rows_own = rows_own; a.width = H; a.gather = 1;
+        return sfb_k_peer_reduce_gather(&a, s);
     }
     // completes the all-reduce whose data the preceding GEMM pushed: `count` elements starting `offset` elements in
     sfb_status peer_finish(int set, void* data, std::size_t offset, int64_t count, cudaStream_t s) {
@@ -210,6 +288,7 @@ DecoderExecutablePlan::~DecoderExecutablePlan() {
         if (impl_->copy_in) cudaStreamDestroy(impl_->copy_in);
         if (impl_->copy_out) cudaStreamDestroy(impl_->copy_out);
         if (impl_->status_host) cudaFreeHost(impl_->status_host);
+        if (impl_->len_pinned) cudaFreeHost(impl_->len_pinned);
     }
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -289,6 +368,34 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     };
     m.swiglu_block = fused ? pick_block(I) : I;  // unfused: plain [gate | up] halves
     m.moe_swiglu_block = pick_block(c.intermediate);
+    {
+        // Both RMSNorms can be folded into the GEMM behind them when that GEMM (and, for the second norm, the O
+        // projection that leaves the sums of squares) runs on the tensor-core kernel.  INT8 plans keep the
+        // stand-alone norm: the reference quantizes the plain weights (src/next_milestones.cpp:660-675).
+        auto on_tensor_cores = [&](int epilogue, int n, int k, int block) {
+            sfb_gemm_args g{};
+            void* aligned = reinterpret_cast<void*>(std::uintptr_t{1024});
+            g.a = g.bt = aligned; g.out = aligned; g.residual = aligned;
+            g.q = g.key = g.value = aligned;
+            g.rope_cos = g.rope_sin = static_cast<const float*>(aligned);
+            g.m = T; g.n = n; g.k = k; g.epilogue = epilogue; g.swiglu_block = block;
+            g.batch = c.batch; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
+            return gemm_bf16_tcgen05_supported(g);
+        };
+        const bool eligible = bf && fused && opt.gemm_backend != SFB_GEMM_SIMT && opt.weight_int8 == 0 &&
+                              opt.no_norm_fusion == 0 && D % 2 == 0;
+        m.fold1 = eligible && on_tensor_cores(SFB_EPI_ROPE_SPLIT, m.qkv_l, H, 0);
+        m.fold2 = eligible && !moe && on_tensor_cores(SFB_EPI_SWIGLU, 2 * I, H, m.swiglu_block) &&
+                  on_tensor_cores(SFB_EPI_RESIDUAL, H, m.hidden_l, 0);
+        m.ss2_tiles = G == 1 ? sfb_gemm_ss_tiles(H) : 1;  // a sharded plan sums the squares after its all-reduce
+        m.kv_in_epilogue = m.append_new && bf && fused && opt.gemm_backend != SFB_GEMM_SIMT && D % 2 == 0 &&
+                           on_tensor_cores(SFB_EPI_ROPE_SPLIT, m.qkv_l, H, 0);
+    }
+    // a single-shard dense plan on the tensor-core GEMM lets the down projection write the fp32 result itself
+    m.direct_f32_output = bf && fused && !moe && G == 1 && opt.gemm_backend != SFB_GEMM_SIMT && H % 8 == 0 && I % 8 == 0;
+    const int ctx = c.context_sequence;
+    m.kv_capacity = m.append_new ? std::max(opt.kv_capacity, ctx + 1) : ctx;
+    const int rope_positions = m.append_new ? m.kv_capacity : c.sequence;
 
     cuda_check(cudaStreamCreateWithFlags(&plan->stream_, cudaStreamNonBlocking), "cudaStreamCreate");
     cudaStream_t s = plan->stream_;
@@ -297,8 +404,8 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     const std::size_t wsz = bf ? 2 : 4;
     WeightArena arena;
     const std::size_t o_rms1 = arena.reserve(sizeof(float) * H), o_rms2 = arena.reserve(sizeof(float) * H);
-    const std::size_t o_cos = arena.reserve(sizeof(float) * c.sequence * std::max(1, D / 2));
-    const std::size_t o_sin = arena.reserve(sizeof(float) * c.sequence * std::max(1, D / 2));
+    const std::size_t o_cos = arena.reserve(sizeof(float) * rope_positions * std::max(1, D / 2));
+    const std::size_t o_sin = arena.reserve(sizeof(float) * rope_positions * std::max(1, D / 2));
     const std::size_t o_wqkv = arena.reserve(wsz * H * m.qkv_l), o_wo = arena.reserve(wsz * m.hidden_l * H);
     std::size_t o_wgu = 0, o_wd = 0, o_router = 0, o_bias = 0, o_w13 = 0, o_w2 = 0, o_w1f = 0, o_w3f = 0, o_w2f = 0;
     const std::size_t expert_elems = static_cast<std::size_t>(H) * c.intermediate;
@@ -330,13 +437,13 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     h2d(m.rms1, need(data.rms1_weight, "rms1_weight"), sizeof(float) * H);
     h2d(m.rms2, need(data.rms2_weight, "rms2_weight"), sizeof(float) * H);
     {
-        // positions 0..sequence-1; an appending decode step rotates its one token at position context_sequence
-        const int first_position = m.append_new ? c.context_sequence : 0;
+        // positions 0..sequence-1; an appending decode plan rotates its one token at the position it is appended
+        // at, anywhere below the cache capacity (the run passes the table advanced by that many rows)
         const std::size_t row = static_cast<std::size_t>(std::max(1, D / 2));
-        std::vector<float> cs(static_cast<std::size_t>(first_position + c.sequence) * row), sn(cs.size());
-        if (D >= 2) throw_on(sfb_rope_table(first_position + c.sequence, D, c.rope_theta, cs.data(), sn.data()));
-        h2d(m.rope_cos, cs.data() + first_position * row, static_cast<std::size_t>(c.sequence) * row * 4);
-        h2d(m.rope_sin, sn.data() + first_position * row, static_cast<std::size_t>(c.sequence) * row * 4);
+        std::vector<float> cs(static_cast<std::size_t>(rope_positions) * row), sn(cs.size());
+        if (D >= 2) throw_on(sfb_rope_table(rope_positions, D, c.rope_theta, cs.data(), sn.data()));
+        h2d(m.rope_cos, cs.data(), cs.size() * 4);
+        h2d(m.rope_sin, sn.data(), sn.size() * 4);
     }
     // fp32 staging buffer on the device for the transpose/convert packer
     std::size_t staging_elems = static_cast<std::size_t>(H) * std::max({H, c.intermediate, m.I_l, m.qkv_l});
@@ -344,10 +451,10 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     if (bf) staging.allocate(staging_elems * 4);
     const int whole = 1 << 30;
     auto pack = [&](const float* host, int rows_k, int cols, int k_begin, int k_count, int c_begin, int c_count,
-                    void* dst, int block, int stride, int offset) {
+                    void* dst, int block, int stride, int offset, const float* norm_weight = nullptr) {
         h2d(staging.get(), host, static_cast<std::size_t>(rows_k) * cols * 4);
         pack_weight_transposed(staging.as<float>(), cols, k_begin, k_count, c_begin, c_count, dst, block, stride,
-                               offset, s);
+                               offset, s, norm_weight);
         cuda_check(cudaStreamSynchronize(s), "weight pack");
     };
     const float* wq = need(data.query_weight, "query_weight");
@@ -356,9 +463,10 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     const float* wo_h = need(data.output_weight, "output_weight");
     const int kvw = c.kv_width();
     if (bf) {
-        pack(wq, H, H, 0, H, r * m.hidden_l, m.hidden_l, m.wqkv, whole, 0, 0);
-        pack(wk, H, kvw, 0, H, r * m.kvw_l, m.kvw_l, m.wqkv, whole, 0, m.hidden_l);
-        pack(wv, H, kvw, 0, H, r * m.kvw_l, m.kvw_l, m.wqkv, whole, 0, m.hidden_l + m.kvw_l);
+        const float* n1 = m.fold1 ? m.rms1 : nullptr;  // folded: W'[k, n] = rms1_weight[k] * W[k, n]
+        pack(wq, H, H, 0, H, r * m.hidden_l, m.hidden_l, m.wqkv, whole, 0, 0, n1);
+        pack(wk, H, kvw, 0, H, r * m.kvw_l, m.kvw_l, m.wqkv, whole, 0, m.hidden_l, n1);
+        pack(wv, H, kvw, 0, H, r * m.kvw_l, m.kvw_l, m.wqkv, whole, 0, m.hidden_l + m.kvw_l, n1);
         pack(wo_h, H, H, r * m.hidden_l, m.hidden_l, 0, H, m.wo, whole, 0, 0);
     } else {
         std::vector<float> packed(static_cast<std::size_t>(H) * m.qkv_l);
@@ -372,7 +480,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         h2d(m.wo, wo_h + static_cast<std::size_t>(r) * m.hidden_l * H, static_cast<std::size_t>(m.hidden_l) * H * 4);
     }
     plan->constants.push_back({"packed_qkv_weight", {H, c.hidden, kvw, kvw}, {H, c.qkv_width()},
-                               bf ? "qkv_transposed_bf16_k_major" : "qkv_concat_f32",
+                               bf ? (m.fold1 ? "qkv_transposed_bf16_k_major_rms_folded" : "qkv_transposed_bf16_k_major") : "qkv_concat_f32",
                                static_cast<std::size_t>(H) * m.qkv_l * wsz});
     if (!moe) {
         m.wgu = wb + o_wgu; m.wd = wb + o_wd;
@@ -394,8 +502,9 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             Ifull = I;
         }
         if (bf) {
-            pack(wg, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, 0);
-            pack(wu, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, m.swiglu_block);
+            const float* n2 = m.fold2 ? m.rms2 : nullptr;
+            pack(wg, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, 0, n2);
+            pack(wu, H, Ifull, 0, H, r * I, I, m.wgu, m.swiglu_block, 2 * m.swiglu_block, m.swiglu_block, n2);
             pack(wd_h, Ifull, H, r * I, I, 0, H, m.wd, whole, 0, 0);
         } else {
             std::vector<float> packed(static_cast<std::size_t>(H) * 2 * I);
@@ -407,7 +516,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             h2d(m.wd, wd_h + static_cast<std::size_t>(r) * I * H, static_cast<std::size_t>(I) * H * 4);
         }
         plan->constants.push_back({"packed_gate_up_weight", {H, c.intermediate, c.intermediate}, {H, 2 * Ifull},
-                                   bf ? "gate_up_interleaved_" + std::to_string(m.swiglu_block) : "gate_up_concat_f32",
+                                   bf ? "gate_up_interleaved_" + std::to_string(m.swiglu_block) + (m.fold2 ? "_rms_folded" : "") : "gate_up_concat_f32",
                                    static_cast<std::size_t>(H) * 2 * I * wsz});
     } else {
         m.router = reinterpret_cast<float*>(wb + o_router);
@@ -490,7 +599,6 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     }
 
     // ---- KV cache for decode plans ------------------------------------------------------------
-    const int ctx = c.context_sequence;
     if (m.decode) {
         const float* ck = need(data.cached_key, "cached_key");
         const float* cv = need(data.cached_value, "cached_value");
@@ -511,7 +619,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         h2d(dk, lk.data(), lk.size() * 4);
         h2d(dv, lv.data(), lv.size() * 4);
         if (m.paged) {
-            m.max_blocks = ceil_div(ctx + (m.append_new ? 1 : 0), m.page_tokens);
+            m.max_blocks = ceil_div(m.kv_capacity, m.page_tokens);
             m.num_blocks = c.batch * m.max_blocks;
             const std::size_t pool_elems = static_cast<std::size_t>(m.num_blocks) * m.hkv * m.page_tokens * D;
             const std::size_t table_bytes = sizeof(int) * m.num_blocks, len_bytes = sizeof(int) * c.batch;
@@ -522,15 +630,25 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             m.k_pool = kb; m.v_pool = kb + pool_bytes;
             m.block_table = reinterpret_cast<int*>(kb + 2 * pool_bytes);
             m.context_len = m.block_table + m.num_blocks;
-            m.context_len_attend = m.append_new ? m.context_len + c.batch : m.context_len;
             char* tmp = converted.as<char>();
-            std::vector<int> table(m.num_blocks), lens(c.batch, 0), full(c.batch, ctx);
-            std::iota(table.begin(), table.end(), 0);
+            std::vector<int> lens(c.batch, 0);
+            m.block_ids.resize(m.num_blocks);
+            std::iota(m.block_ids.begin(), m.block_ids.end(), 0);
             if (opt.seed_block_table != 0) {
                 std::mt19937 generator(static_cast<unsigned>(opt.seed_block_table));
-                std::shuffle(table.begin(), table.end(), generator);
+                std::shuffle(m.block_ids.begin(), m.block_ids.end(), generator);
             }
-            h2d(m.block_table, table.data(), table_bytes);
+            // make_paged_kv_cache + append_paged_kv of the cached context: the free list starts as 0..pages-1 and
+            // every page comes from its back (src/next_milestones.cpp:472-500)
+            m.free_pages.resize(m.max_blocks);
+            std::iota(m.free_pages.begin(), m.free_pages.end(), 0);
+            for (int page = 0; page < ceil_div(ctx, m.page_tokens); ++page) {
+                m.page_table.push_back(m.free_pages.back());
+                m.free_pages.pop_back();
+            }
+            m.kv_length = ctx;
+            m.sync_table(c.batch, s);
+            cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&m.len_pinned), len_bytes, cudaHostAllocDefault), "length staging");
             h2d(m.context_len, lens.data(), len_bytes);  // start lengths for the append kernel
             cuda_check(cudaMemsetAsync(m.k_pool, 0, 2 * pool_bytes, s), "pool clear");
             void *ak = dk, *av = dv;
@@ -542,12 +660,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             throw_on(sfb_k_paged_kv_append(ak, av, m.k_pool, m.v_pool, m.block_table, m.context_len, c.batch, m.hkv,
                                            ctx, D, D, m.page_tokens, m.max_blocks, m.num_blocks, static_cast<sfb_dtype>(m.dtype), s));
             cuda_check(cudaStreamSynchronize(s), "paged cache build");
-            h2d(m.context_len, full.data(), len_bytes);
-            if (m.append_new) {
-                std::vector<int> plus(c.batch, ctx + 1);
-                h2d(m.context_len_attend, plus.data(), len_bytes);
-            }
-            m.splits = sfb_attention_decode_default_splits(c.batch, m.hkv, ctx + (m.append_new ? 1 : 0));
+            m.splits = sfb_attention_decode_default_splits(c.batch, m.hkv, m.kv_capacity);
             plan->attention_strategy = "split_kv_decode";
         } else {
             m.kv_pool.allocate(2 * cache_bytes + 1024);
@@ -600,7 +713,11 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     const bool piped = m.pipeline_chunks > 1;  // host copies overlap compute: I/O staging must not alias anything
     wp.add("input_f32", TH * 4, 0, (bf && !piped) ? 0 : 13);
     if (bf) wp.add("input", TH * e, 0, 13);
-    wp.add("normalized1", TH * e, 1, 2);
+    if (!m.fold1) wp.add("normalized1", TH * e, 1, 2);
+    // sums of squares per row for the folded norms; they live for the whole pass (the first one as long as the
+    // resident input, the second one keeps the zeros that a ragged column group never overwrites)
+    if (m.fold1) wp.add("ss1", static_cast<std::size_t>(T) * 4, 0, 13);
+    if (m.fold2) wp.add("ss2", static_cast<std::size_t>(T) * 4 * m.ss2_tiles, 0, 13);
     if (!fused) wp.add("fused_qkv", static_cast<std::size_t>(T) * m.qkv_l * e, 2, 3);
     wp.add("query", static_cast<std::size_t>(T) * m.hidden_l * e, 2, 4);
     // chunks that are part of a sequence attend to the keys and values of the chunks before them
@@ -613,10 +730,11 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     wp.add("attention", static_cast<std::size_t>(T) * m.hidden_l * e, 4, 5);
     if (!fused) wp.add("projected", TH * e, 5, 6);
     wp.add("attention_residual", TH * e, 5, 12);
-    wp.add("normalized2", TH * e, 7, 9);
+    if (!m.fold2) wp.add("normalized2", TH * e, 7, 9);
     if (!moe) {
         if (!fused) wp.add("gate_up", static_cast<std::size_t>(T) * 2 * I * e, 8, 9);
-        wp.add("activation", static_cast<std::size_t>(T) * I * e, 8, 10);
+        // the fused down projection reads it while it writes "output" (step 11): the two must not share bytes
+        wp.add("activation", static_cast<std::size_t>(T) * I * e, 8, fused ? 11 : 10);
         if (!fused) wp.add("down", TH * e, 10, 11);
     } else {
         const std::size_t A = static_cast<std::size_t>(T) * m.K;
@@ -646,6 +764,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     m.workspace.allocate(wp.total_bytes());
     if (m.has("gemm_partials"))
         cuda_check(cudaMemsetAsync(m.ws("gemm_partials"), 0, wp.bytes(wp.find("gemm_partials")), s), "scratch clear");
+    if (m.fold2) cuda_check(cudaMemsetAsync(m.ws("ss2"), 0, wp.bytes(wp.find("ss2")), s), "sums clear");
     plan->naive_bytes = wp.naive_bytes();
     plan->workspace_bytes = wp.total_bytes();
     (void)plan_start;
@@ -666,15 +785,22 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
 
 std::size_t DecoderExecutablePlan::peer_bytes() const {
     const auto& m = *impl_;
-    return m.size > 1 ? m.peer_flags_offset() + 2 * SFB_MAX_PEERS * sizeof(uint32_t) + 256 : 0;
+    return m.size > 1 ? m.peer_total_bytes() : 0;
 }
 
-void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* peer_bases) {
+void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* peer_bases, int mode) {
     auto& m = *impl_;
+    m.input_in_peer = false;
     if (!local_base) {  // back to the hook
         m.peer_local = nullptr;
+        m.peer_mode = 0;
         return;
     }
+    if (mode < 0 || mode > 2) throw std::invalid_argument("peer all-reduce: unknown mode");
+    const bool can_two_shot = m.T % std::max(1, m.size) == 0 && m.H % 8 == 0;
+    if (mode == 2 && !can_two_shot) throw std::invalid_argument("two-shot peer all-reduce needs rows divisible by the rank count");
+    // one-shot pushes (size - 1) x the tensor per rank: right for two ranks and for the small outputs of decode plans
+    if (mode == 0) mode = (can_two_shot && m.size > 2 && m.T > 128) ? 2 : 1;
     if (m.size < 2 || m.size > SFB_MAX_PEERS) throw std::invalid_argument("peer all-reduce needs a sharded plan of 2..8 ranks");
     if (m.dtype != SFB_BF16 || !policy.fuse_epilogues || policy.gemm_backend == SFB_GEMM_SIMT || m.H % 8 != 0 ||
         m.hidden_l % 8 != 0 || m.I_l % 8 != 0)
@@ -685,17 +811,24 @@ void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* pe
         m.peer_remote[s] = static_cast<char*>(peer_bases[s]);
     }
     m.peer_local = static_cast<char*>(local_base);
+    m.peer_mode = mode;
     m.peer_epoch[0] = m.peer_epoch[1] = 0;
+    m.gather_epoch[0] = m.gather_epoch[1] = m.gather_epoch[2] = 0;
 }
 
 void DecoderExecutablePlan::upload_input(const float* input) {
     if (!input) throw std::invalid_argument("decoder input is null");
     auto& m = *impl_;
+    m.input_in_peer = false;
     cuda_check(cudaMemcpyAsync(m.ws<float>("input_f32"), input, static_cast<std::size_t>(m.T) * m.H * 4,
                                cudaMemcpyHostToDevice, stream_), "input upload");
-    if (m.dtype == SFB_BF16)
-        throw_on(sfb_k_convert(m.ws("input_f32"), SFB_F32, m.ws("input"), SFB_BF16,
-                               static_cast<int64_t>(m.T) * m.H, stream_));
+    if (m.dtype == SFB_BF16) {
+        if (m.fold1)  // the conversion also leaves the sums of squares of the rounded rows for the folded first norm
+            throw_on(sfb_k_convert_rows_sumsq(m.ws<float>("input_f32"), m.ws("input"), m.ws<float>("ss1"), m.T, m.H, stream_));
+        else
+            throw_on(sfb_k_convert(m.ws("input_f32"), SFB_F32, m.ws("input"), SFB_BF16,
+                                   static_cast<int64_t>(m.T) * m.H, stream_));
+    }
     m.has_input = true;
 }
 
@@ -719,8 +852,13 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     const int T = m.T, H = m.H, I = m.I_l, D = m.D;
     int ev = 0;
     auto mark = [&] { if (stage_events) cuda_check(cudaEventRecord(m.events[ev++], s), "event"); };
+    // the rotary table advanced to the position of the (one) new token of an appending decode plan
+    const int position = m.append_new ? m.kv_length : 0;
+    const std::size_t rope_shift = static_cast<std::size_t>(position) * static_cast<std::size_t>(std::max(1, D / 2));
+    using Tweak = void (*)(sfb_gemm_args&, DecoderExecutablePlan::Impl&, int);
     auto gemm = [&](const void* a, const void* w, void* out, int mm, int n, int k, int epi, const void* res = nullptr,
-                    int sb = 0, const int* offsets = nullptr, int groups = 0, bool f32_out = false, int peer_set = -1) {
+                    int sb = 0, const int* offsets = nullptr, int groups = 0, bool f32_out = false, int peer_set = -1,
+                    Tweak tweak = nullptr) {
         if (!bf) {
             throw_on(sfb_k_gemm_f32(static_cast<const float*>(a), static_cast<const float*>(w),
                                     static_cast<float*>(out), mm, n, k, s));
@@ -731,9 +869,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb; g.out_f32 = f32_out ? 1 : 0;
         if (epi == SFB_EPI_ROPE_SPLIT) {
             g.q = m.ws("query"); g.key = m.ws("key"); g.value = m.ws("value");
-            g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
+            g.rope_cos = m.rope_cos + rope_shift; g.rope_sin = m.rope_sin + rope_shift;
             g.batch = c.batch; g.seq = c.sequence; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
         }
+        if (tweak) tweak(g, m, T);
         if (offsets) { g.group_offsets = offsets; g.groups = groups; g.tile_table = m.ws("tile_table"); }
         if (m.has("gemm_partials")) {
             g.split_workspace = m.ws("gemm_partials");
@@ -753,31 +892,59 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     const bool peer = m.size > 1 && m.peer_local != nullptr;
     auto peer_finish = [&](int peer_set, void* buffer, int64_t count) { throw_on(m.peer_finish(peer_set, buffer, 0, count, s)); };
 
+    // QKV GEMM with the first RMSNorm folded in (1/rms from the sums of squares the input conversion left) and, in an
+    // appending decode plan, the new token's K/V written into the paged cache by the same epilogue
+    const Tweak qkv_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int rows) {
+        if (im.fold1) {
+            g.row_ss = im.cur_ss1; g.row_ss_tiles = 1; g.row_ss_stride = rows; g.rms_epsilon = im.rms_eps;
+        }
+        if (im.kv_in_epilogue) {
+            g.kv_k_pool = im.k_pool; g.kv_v_pool = im.v_pool; g.kv_table = im.block_table;
+            g.kv_position = im.kv_length; g.kv_block_tokens = im.page_tokens; g.kv_max_blocks = im.max_blocks;
+            g.kv_num_blocks = im.num_blocks;
+        }
+    };
+    m.rms_eps = c.rms_epsilon;
+    const bool two = m.two_shot();
     mark();  // 0
     void* x = bf ? m.ws("input") : m.ws("input_f32");
-    throw_on(sfb_k_rms_norm(x, m.rms1, m.ws("normalized1"), T, H, c.rms_epsilon, dt, s));
+    if (two && m.input_in_peer) x = m.gathered(0);  // the rows every rank contributed, gathered by peer stores
+    m.cur_ss1 = m.fold1 ? (two && m.input_in_peer ? m.gathered_ss(0) : m.ws<float>("ss1")) : nullptr;
+    void* a1 = x;
+    if (!m.fold1) {
+        a1 = m.ws("normalized1");
+        throw_on(sfb_k_rms_norm(x, m.rms1, a1, T, H, c.rms_epsilon, dt, s));
+    }
     mark();  // 1: norm
     const bool rope_fused = fused && D % 2 == 0;
     if (rope_fused) {
-        gemm(m.ws("normalized1"), m.wqkv, nullptr, T, m.qkv_l, H, SFB_EPI_ROPE_SPLIT);
+        gemm(a1, m.wqkv, nullptr, T, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, nullptr, 0, false, -1, qkv_tweak);
         mark(); mark();  // 2: projection, 3: (rope inside)
     } else {
-        gemm(m.ws("normalized1"), m.wqkv, m.ws("fused_qkv"), T, m.qkv_l, H, SFB_EPI_STORE);
+        gemm(a1, m.wqkv, m.ws("fused_qkv"), T, m.qkv_l, H, SFB_EPI_STORE);
         mark();  // 2
-        throw_on(sfb_k_rope_split(m.ws("fused_qkv"), m.ws("query"), m.ws("key"), m.ws("value"), m.rope_cos, m.rope_sin,
-                                  c.batch, c.sequence, m.hq, m.hkv, D, dt, s));
+        throw_on(sfb_k_rope_split(m.ws("fused_qkv"), m.ws("query"), m.ws("key"), m.ws("value"), m.rope_cos + rope_shift,
+                                  m.rope_sin + rope_shift, c.batch, c.sequence, m.hq, m.hkv, D, dt, s));
         mark();  // 3
     }
     if (m.paged) {
-        if (m.append_new)  // the rotated key and the value of the new token go to position context_len of every sequence
+        if (m.append_new && !(m.kv_in_epilogue && rope_fused)) {
+            // the rotated key and the value of the new token go to position kv_length of every sequence
+            if (m.len_uploaded != m.kv_length) {
+                for (int b = 0; b < c.batch; ++b) m.len_pinned[b] = m.kv_length;
+                cuda_check(cudaMemcpyAsync(m.context_len, m.len_pinned, sizeof(int) * c.batch, cudaMemcpyHostToDevice, s), "lengths");
+                m.len_uploaded = m.kv_length;
+            }
             throw_on(sfb_k_paged_kv_append(m.ws("key"), m.ws("value"), m.k_pool, m.v_pool, m.block_table, m.context_len,
                                            c.batch, m.hkv, 1, D, D, m.page_tokens, m.max_blocks, m.num_blocks, dt, s));
+        }
         sfb_decode_args a{};
         a.q = m.ws("query"); a.k_pool = m.k_pool; a.v_pool = m.v_pool; a.block_table = m.block_table;
-        a.context_len = m.context_len_attend; a.out = m.ws("attention"); a.partials = m.ws("decode_partials");
+        a.context_len = nullptr; a.uniform_context = m.kv_length + (m.append_new ? 1 : 0);  // the batch decodes in lock step
+        a.out = m.ws("attention"); a.partials = m.ws("decode_partials");
         a.batch = c.batch; a.q_heads = m.hq; a.kv_heads = m.hkv; a.head_dim = D; a.head_dim_value = D;
         a.block_tokens = m.page_tokens; a.max_blocks = m.max_blocks; a.num_blocks = m.num_blocks;
-        a.max_context = c.context_sequence + (m.append_new ? 1 : 0); a.splits = m.splits; a.scale = 0.0F; a.dtype = m.dtype;
+        a.max_context = m.kv_capacity; a.splits = m.splits; a.scale = 0.0F; a.dtype = m.dtype;
         throw_on(sfb_k_attention_decode_paged(&a, s));
     } else {
         sfb_attention_args a{};
@@ -792,17 +959,39 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         throw_on(sfb_k_attention_prefill(&a, s));
     }
     mark();  // 4: attention
-    void* r1 = m.ws("attention_residual");
+    void* r1 = two ? m.gathered(1) : m.ws("attention_residual");
     const bool add_residual_here = m.rank == 0;  // under sharding the residual enters the sum once
+    const Tweak scatter_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int) { im.fill_scatter_out(g, im.scatter_set); };
+    const std::size_t own_rows_offset = two ? static_cast<std::size_t>(m.rank) * (T / m.size) * H * 2 : 0;
+    // second fold: a single shard collects the sums of squares of attention_residual in the O epilogue; a
+    // sharded plan sums the squares of the reduced rows after its all-reduce
+    const Tweak o_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int rows) {
+        if (im.fold2 && im.size == 1) { g.ss_out = im.ws<float>("ss2"); g.ss_out_stride = rows; }
+    };
+    m.cur_ss2 = m.fold2 ? (two ? m.gathered_ss(1) : m.ws<float>("ss2")) : nullptr;
+    m.cur_ss2_tiles = two ? 1 : m.ss2_tiles;
+    const Tweak gate_up_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int rows) {
+        if (im.fold2) {
+            g.row_ss = im.cur_ss2; g.row_ss_tiles = im.cur_ss2_tiles; g.row_ss_stride = rows; g.rms_epsilon = im.rms_eps;
+        }
+    };
     if (fused) {
-        if (peer) {
+        if (two) {
+            // every rank's partial rows go to their owners under the GEMM; the owner adds them up with its rows of the
+            // residual stream, takes the sums of squares and hands the finished rows to everybody
+            m.scatter_set = 0;
+            gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, SFB_EPI_STORE, nullptr, 0, nullptr, 0, false, -1, scatter_tweak);
+            throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s));
+        } else if (peer) {
             gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
                  nullptr, 0, false, 0);
             peer_finish(0, r1, static_cast<int64_t>(T) * H);
         } else {
-            gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x);
+            gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
+                 nullptr, 0, false, -1, o_tweak);
             allreduce(r1, static_cast<int64_t>(T) * H);
         }
+        if (m.fold2 && m.size > 1 && !two) throw_on(sfb_k_row_sumsq(r1, m.ws<float>("ss2"), T, H, s));
         mark(); mark();  // 5: projection, 6: (residual inside)
     } else {
         gemm(m.ws("attention"), m.wo, m.ws("projected"), T, H, m.hidden_l, SFB_EPI_STORE);
@@ -811,14 +1000,23 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         throw_on(sfb_k_add(m.ws("projected"), x, r1, static_cast<int64_t>(T) * H, dt, s));
         mark();  // 6
     }
-    throw_on(sfb_k_rms_norm(r1, m.rms2, m.ws("normalized2"), T, H, c.rms_epsilon, dt, s));
+    void* a2 = r1;
+    if (!m.fold2) {
+        a2 = m.ws("normalized2");
+        throw_on(sfb_k_rms_norm(r1, m.rms2, a2, T, H, c.rms_epsilon, dt, s));
+    }
     mark();  // 7: norm
-    void* out = m.ws("output");
+    void* out = two && !moe ? m.gathered(2) : m.ws("output");
     if (!moe) {
         if (fused) {
-            gemm(m.ws("normalized2"), m.wgu, m.ws("activation"), T, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block);
+            gemm(a2, m.wgu, m.ws("activation"), T, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, nullptr, 0, false, -1,
+                 gate_up_tweak);
             if (m.direct_f32_output) {
                 gemm(m.ws("activation"), m.wd, m.ws("output_f32"), T, H, I, SFB_EPI_RESIDUAL, r1, 0, nullptr, 0, true);
+            } else if (two) {
+                m.scatter_set = 1;
+                gemm(m.ws("activation"), m.wd, out, T, H, I, SFB_EPI_STORE, nullptr, 0, nullptr, 0, false, -1, scatter_tweak);
+                throw_on(m.reduce_gather(2, nullptr, nullptr, static_cast<const char*>(r1) + own_rows_offset, false, s));
             } else if (peer) {
                 gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0,
                      nullptr, 0, false, 1);
@@ -829,7 +1027,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             }
             mark(); mark();  // 8: ffn, 9: (residual inside)
         } else {
-            gemm(m.ws("normalized2"), m.wgu, m.ws("gate_up"), T, 2 * I, H, SFB_EPI_STORE);
+            gemm(a2, m.wgu, m.ws("gate_up"), T, 2 * I, H, SFB_EPI_STORE);
             throw_on(sfb_k_swiglu(m.ws("gate_up"), m.ws("activation"), T, I, dt, s));
             gemm(m.ws("activation"), m.wd, m.ws("down"), T, H, I, SFB_EPI_STORE);
             allreduce(m.ws("down"), static_cast<int64_t>(T) * H);
@@ -933,6 +1131,64 @@ void DecoderExecutablePlan::execute(const float* input, float* output, RoutingTr
     result->kernel_launches = sfb_launch_count() - launches_before;
 }
 
+void DecoderExecutablePlan::step(const float* input, float* output, sfb_decoder_result* result) {
+    auto& m = *impl_;
+    if (!m.paged || !m.append_new) throw std::invalid_argument("decoder step needs a decode plan compiled with append_new_token");
+    if (m.kv_length + 1 > m.kv_capacity) throw std::invalid_argument("paged KV capacity exceeded");
+    // append_paged_kv: a token that opens a new page takes it from the back of the free list; the device table
+    // already holds that entry (sync_table lays the free pages out in hand-out order)
+    const int last_page = m.kv_length / m.page_tokens;
+    std::vector<int> taken;
+    while (static_cast<int>(m.page_table.size()) <= last_page) {
+        if (m.free_pages.empty()) {
+            for (auto it = taken.rbegin(); it != taken.rend(); ++it) { m.free_pages.push_back(*it); m.page_table.pop_back(); }
+            throw std::runtime_error("paged KV page allocator exhausted");
+        }
+        taken.push_back(m.free_pages.back());
+        m.page_table.push_back(m.free_pages.back());
+        m.free_pages.pop_back();
+    }
+    execute(input, output, RoutingTraceView{}, result);  // appends at kv_length, attends over kv_length + 1
+    m.kv_length += 1;
+}
+
+void DecoderExecutablePlan::kv_info(int* info, int* page_table, int table_capacity, int* free_pages, int free_capacity) const {
+    const auto& m = *impl_;
+    if (!m.paged || !info) throw std::invalid_argument("plan has no paged KV cache");
+    info[0] = m.kv_length;
+    info[1] = static_cast<int>(m.page_table.size());
+    info[2] = static_cast<int>(m.free_pages.size());
+    info[3] = m.max_blocks;
+    for (int i = 0; page_table && i < info[1] && i < table_capacity; ++i) page_table[i] = m.page_table[i];
+    for (int i = 0; free_pages && i < info[2] && i < free_capacity; ++i) free_pages[i] = m.free_pages[i];
+}
+
+void DecoderExecutablePlan::kv_truncate(int new_length) {
+    auto& m = *impl_;
+    if (!m.paged) throw std::invalid_argument("plan has no paged KV cache");
+    if (new_length < 0 || new_length > m.kv_length) throw std::invalid_argument("invalid paged KV truncation length");
+    const int keep = new_length == 0 ? 0 : ceil_div(new_length, m.page_tokens);
+    while (static_cast<int>(m.page_table.size()) > keep) {
+        m.free_pages.push_back(m.page_table.back());
+        m.page_table.pop_back();
+    }
+    m.kv_length = new_length;
+    m.sync_table(config.batch, stream_);
+}
+
+void DecoderExecutablePlan::kv_release(const int* pages, int count) {
+    auto& m = *impl_;
+    if (!m.paged || (!pages && count > 0)) throw std::invalid_argument("plan has no paged KV cache");
+    for (int i = 0; i < count; ++i) {
+        const int page = pages[i];
+        if (page < 0 || page >= m.max_blocks) throw std::invalid_argument("invalid physical KV page");
+        if (std::find(m.page_table.begin(), m.page_table.end(), page) != m.page_table.end())
+            throw std::invalid_argument("cannot release an active paged KV page");
+        if (std::find(m.free_pages.begin(), m.free_pages.end(), page) == m.free_pages.end()) m.free_pages.push_back(page);
+    }
+    m.sync_table(config.batch, stream_);
+}
+
 // One pass of a sharded plan where every rank brings and takes only ITS rows over its own PCIe link:
 // the rows are uploaded into a zeroed input tensor, the sum all-reduce of the hook then acts as the
 // all-gather (every row is non-zero on exactly one rank, so the sum is exact), the layer runs on the
@@ -944,7 +1200,9 @@ void DecoderExecutablePlan::execute_rows(const float* input_rows, float* output_
     if (row_begin < 0 || row_count <= 0 || row_begin + row_count > m.T)
         throw std::invalid_argument("decoder row range lies outside the plan");
     const bool whole = row_begin == 0 && row_count == m.T;
-    if (!whole && (m.dtype != SFB_BF16 || !allreduce_))
+    // a two-shot plan gathers the rows with peer stores when every rank brings exactly the rows it owns
+    const bool peer_gather = !whole && m.two_shot() && row_count == m.T / m.size && row_begin == m.rank * row_count;
+    if (!whole && !peer_gather && (m.dtype != SFB_BF16 || !allreduce_))
         throw std::invalid_argument("a row range needs a bf16 plan with an all-reduce hook");
     cudaStream_t s = stream_;
     const uint64_t launches_before = sfb_launch_count();
@@ -952,11 +1210,23 @@ void DecoderExecutablePlan::execute_rows(const float* input_rows, float* output_
     cudaEvent_t h0 = m.events[12], h1 = m.events[13], d0 = m.events[14], d1 = m.events[15];
     cuda_check(cudaEventRecord(h0, s), "event");
     cuda_check(cudaMemcpyAsync(m.ws<float>("input_f32") + first, input_rows, count * 4, cudaMemcpyHostToDevice, s), "input upload");
-    if (m.dtype == SFB_BF16) {
+    m.input_in_peer = false;
+    if (peer_gather) {
+        // own rows -> bf16 (+ sums of squares) straight into this rank's gathered input, then out to every peer
+        char* mine = m.gathered<char>(0) + first * 2;
+        float* mine_ss = m.gathered_ss(0) + row_begin;
+        if (m.fold1)
+            throw_on(sfb_k_convert_rows_sumsq(m.ws<float>("input_f32") + first, mine, mine_ss, row_count, m.H, s));
+        else
+            throw_on(sfb_k_convert(m.ws<float>("input_f32") + first, SFB_F32, mine, SFB_BF16, static_cast<int64_t>(count), s));
+        throw_on(m.reduce_gather(0, mine, m.fold1 ? mine_ss : nullptr, nullptr, m.fold1, s));
+        m.input_in_peer = true;
+    } else if (m.dtype == SFB_BF16) {
         char* input = static_cast<char*>(m.ws("input"));
         if (!whole) cuda_check(cudaMemsetAsync(input, 0, static_cast<std::size_t>(m.T) * m.H * 2, s), "input clear");
         throw_on(sfb_k_convert(m.ws<float>("input_f32") + first, SFB_F32, input + first * 2, SFB_BF16, static_cast<int64_t>(count), s));
         if (!whole) allreduce_(allreduce_user_, input, static_cast<int64_t>(m.T) * m.H, SFB_BF16, s);
+        if (m.fold1) throw_on(sfb_k_row_sumsq(input, m.ws<float>("ss1"), m.T, m.H, s));
     }
     m.has_input = true;
     cuda_check(cudaEventRecord(h1, s), "event");
@@ -997,14 +1267,16 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     if (!input || !output) throw std::invalid_argument("decoder input or output is null");
     const DecoderConfig& c = config;
     cudaStream_t s = stream_;
+    m.input_in_peer = false;
     const int chunks = m.pipeline_chunks, S = c.sequence;
     int rows = 0;  // rows of the chunk at hand
     const int H = m.H, I = m.I_l, D = m.D;
     const std::size_t row_f32 = static_cast<std::size_t>(H) * 4, row_bf = static_cast<std::size_t>(H) * 2;
     auto at = [](void* base, std::size_t bytes) { return static_cast<void*>(static_cast<char*>(base) + bytes); };
     const bool peer = m.size > 1 && m.peer_local != nullptr;
+    // which folded-norm role a GEMM of the chunk plays: 1 = QKV (scaled by ss1), 2 = O (leaves ss2), 3 = gate/up (scaled by ss2)
     auto gemm = [&](const void* a, const void* w, void* out, int n, int k, int epi, const void* res, int sb, int g0,
-                    bool f32_out = false, int peer_set = -1) {
+                    bool f32_out = false, int peer_set = -1, int fold_role = 0) {
         sfb_gemm_args g{};
         g.a = a; g.bt = w; g.out = out; g.m = rows; g.n = n; g.k = k; g.epilogue = epi;
         g.backend = policy.gemm_backend; g.residual = res; g.swiglu_block = sb; g.out_f32 = f32_out ? 1 : 0;
@@ -1013,6 +1285,13 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             g.rope_cos = m.rope_cos; g.rope_sin = m.rope_sin;
             g.batch = c.batch; g.seq = S; g.q_heads = m.hq; g.kv_heads = m.hkv; g.head_dim = D;
             g.rope_row_offset = g0;
+        }
+        if (fold_role == 1 && m.fold1) {
+            g.row_ss = m.ws<float>("ss1") + g0; g.row_ss_tiles = 1; g.row_ss_stride = m.T; g.rms_epsilon = c.rms_epsilon;
+        } else if (fold_role == 2 && m.fold2 && m.size == 1) {
+            g.ss_out = m.ws<float>("ss2") + g0; g.ss_out_stride = m.T;
+        } else if (fold_role == 3 && m.fold2) {
+            g.row_ss = m.ws<float>("ss2") + g0; g.row_ss_tiles = m.ss2_tiles; g.row_ss_stride = m.T; g.rms_epsilon = c.rms_epsilon;
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
         if (const auto* quantized = m.int8(w)) {
@@ -1045,17 +1324,22 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         cuda_check(cudaEventRecord(ev[0], m.copy_in), "event");
         cuda_check(cudaStreamWaitEvent(s, ev[0], 0), "stream wait");
         void* x = at(m.ws("input"), r0 * row_bf);
-        void* n1 = at(m.ws("normalized1"), r0 * row_bf);
+        void* n1 = m.fold1 ? x : at(m.ws("normalized1"), r0 * row_bf);
         void* attn = at(m.ws("attention"), r0 * static_cast<std::size_t>(m.hidden_l) * 2);
         void* r1 = at(m.ws("attention_residual"), r0 * row_bf);
-        void* n2 = at(m.ws("normalized2"), r0 * row_bf);
+        void* n2 = m.fold2 ? r1 : at(m.ws("normalized2"), r0 * row_bf);
         void* act = at(m.ws("activation"), r0 * static_cast<std::size_t>(I) * 2);
         void* out = at(m.ws("output"), r0 * row_bf);
         void* out32 = at(m.ws("output_f32"), r0 * row_f32);
         cuda_check(cudaEventRecord(ev[2], s), "event");
-        throw_on(sfb_k_convert(at(m.ws("input_f32"), r0 * row_f32), SFB_F32, x, SFB_BF16, static_cast<int64_t>(rows) * H, s));
-        throw_on(sfb_k_rms_norm(x, m.rms1, n1, rows, H, c.rms_epsilon, SFB_BF16, s));
-        gemm(n1, m.wqkv, nullptr, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, g0);
+        if (m.fold1) {
+            throw_on(sfb_k_convert_rows_sumsq(static_cast<const float*>(at(m.ws("input_f32"), r0 * row_f32)), x,
+                                              m.ws<float>("ss1") + g0, rows, H, s));
+        } else {
+            throw_on(sfb_k_convert(at(m.ws("input_f32"), r0 * row_f32), SFB_F32, x, SFB_BF16, static_cast<int64_t>(rows) * H, s));
+            throw_on(sfb_k_rms_norm(x, m.rms1, n1, rows, H, c.rms_epsilon, SFB_BF16, s));
+        }
+        gemm(n1, m.wqkv, nullptr, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, g0, false, -1, 1);
         cuda_check(cudaEventRecord(ev[3], s), "event");
         sfb_attention_args a{};
         a.q = at(m.ws("query"), (static_cast<std::size_t>(b0) * m.hq * S + t0_in_sequence) * D * 2);
@@ -1070,11 +1354,12 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         a.dtype = SFB_BF16; a.backend = policy.attention_backend;
         throw_on(sfb_k_attention_prefill(&a, s));
         cuda_check(cudaEventRecord(ev[4], s), "event");
-        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, g0, false, peer ? 0 : -1);
+        gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, g0, false, peer ? 0 : -1, 2);
         reduce(0, r1, g0);
-        throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
+        if (!m.fold2) throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
+        else if (m.size > 1) throw_on(sfb_k_row_sumsq(r1, m.ws<float>("ss2") + g0, rows, H, s));
         cuda_check(cudaEventRecord(ev[5], s), "event");
-        gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, g0);
+        gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, g0, false, -1, 3);
         if (m.direct_f32_output) {
             gemm(act, m.wd, out32, H, I, SFB_EPI_RESIDUAL, r1, 0, g0, true);
             cuda_check(cudaEventRecord(ev[6], s), "event");
@@ -1123,7 +1408,7 @@ int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_
     const bool is_int = name == "expert_ids" || name == "counts" || name == "offsets" || name == "token_ids" ||
                         name == "route_slots" || name == "dest_of";
     const bool is_f32 = is_int || name == "expert_weights" || name == "routing_weights" || name == "input_f32" ||
-                        name == "output_f32" || name == "decode_partials" || m.dtype == SFB_F32;
+                        name == "output_f32" || name == "decode_partials" || name == "ss1" || name == "ss2" || m.dtype == SFB_F32;
     std::size_t bytes = m.planner.bytes(id);
     int64_t count;
     const int A = m.T * std::max(1, m.K);
@@ -1137,7 +1422,8 @@ int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_
     else if (name == "fused_qkv") count = static_cast<int64_t>(m.T) * m.qkv_l;
     else if (name == "dispatched" || name == "expert_output") count = static_cast<int64_t>(A) * m.H;
     else if (name == "expert_activation" || name == "expert_first" || name == "expert_gate") count = static_cast<int64_t>(A) * config.intermediate;
-    else if (name == "decode_partials" || name == "dispatch_scratch" || name == "tile_table" || name == "gemm_partials") count = static_cast<int64_t>(bytes / 4);
+    else if (name == "decode_partials" || name == "dispatch_scratch" || name == "tile_table" || name == "gemm_partials" ||
+             name == "ss1" || name == "ss2") count = static_cast<int64_t>(bytes / 4);
     else count = static_cast<int64_t>(m.T) * m.H;
     if (!host_out) return count;
     if (capacity < count) throw std::invalid_argument("read_tensor: buffer too small");
@@ -1174,7 +1460,8 @@ std::string DecoderExecutablePlan::dump() const {
         << "\ndecoder.shard rank=" << m.rank << " size=" << m.size << " dtype=" << (bf ? "bf16" : "f32")
         << "\nkernels {\n"
         << "  qkv {\n    " << gemm_kind << " m=" << m.T << " n=" << m.qkv_l << " k=" << m.H
-        << " epilogue=" << (policy.fuse_epilogues ? "rope_split" : "store") << "\n  }\n"
+        << " epilogue=" << (policy.fuse_epilogues ? "rope_split" : "store") << (m.fold1 ? " prologue=rms_norm_folded" : "")
+        << (m.kv_in_epilogue ? " kv_append=paged_cache" : "") << "\n  }\n"
         << "  attention {\n    strategy=" << attention_strategy << "\n"
         << "    attention.qk attention.scale attention.causal_mask reduce.max vector.exp reduce.sum\n"
         << "    attention.rescale attention.online_softmax attention.pv vector.div\n";
@@ -1184,7 +1471,7 @@ std::string DecoderExecutablePlan::dump() const {
         << " epilogue=" << (policy.fuse_epilogues ? "residual" : "store") << "\n  }\n";
     if (!moe) {
         out << "  gate_up {\n    " << gemm_kind << " m=" << m.T << " n=" << 2 * m.I_l << " k=" << m.H << " epilogue="
-            << (policy.fuse_epilogues ? "swiglu" : "store") << "\n  }\n"
+            << (policy.fuse_epilogues ? "swiglu" : "store") << (m.fold2 ? " prologue=rms_norm_folded" : "") << "\n  }\n"
             << "  down {\n    " << gemm_kind << " m=" << m.T << " n=" << m.H << " k=" << m.I_l << " epilogue="
             << (policy.fuse_epilogues ? "residual" : "store") << "\n  }\n";
     } else {

@@ -82,13 +82,23 @@ public:
     void execute(const float* input, float* output, RoutingTraceView trace, sfb_decoder_result* result);
     void execute_pipelined(const float* input, float* output, sfb_decoder_result* result);
     void execute_rows(const float* input_rows, float* output_rows, int row_begin, int row_count, sfb_decoder_result* result);
+    // Autoregressive decode loop on a plan compiled with append_new_token: one pass that appends the new token's
+    // K/V at the cache length, attends over length + 1 keys and then advances the length (taking a page from the
+    // back of the free list when the token opens one), plus the reference's page accounting calls
+    // (append_paged_kv / truncate_paged_kv / release_paged_kv_pages, src/next_milestones.cpp:486-550).
+    void step(const float* input, float* output, sfb_decoder_result* result);
+    void kv_info(int* info, int* page_table, int table_capacity, int* free_pages, int free_capacity) const;
+    void kv_truncate(int new_length);
+    void kv_release(const int* pages, int count);
     void upload_input(const float* input);
     void run(cudaStream_t stream, RoutingTraceView trace, bool stage_events);
     void download_output(float* output);
     void set_allreduce(sfb_allreduce_fn fn, void* user) { allreduce_ = fn; allreduce_user_ = user; }
     // Fused all-reduce over peer memory for the O and Down projections of a sharded plan.
     std::size_t peer_bytes() const;
-    void set_peer_allreduce(void* local_base, void* const* peer_bases);
+    // mode: 0 = pick, 1 = one-shot (every rank pushes its whole partial tensor to every peer), 2 = two-shot
+    // (reduce-scatter under the GEMM, sum + all-gather by the row owners)
+    void set_peer_allreduce(void* local_base, void* const* peer_bases, int mode = 1);
     std::string dump() const;
     // Copies the named intermediate to the host as float32; returns the element count.
     int64_t read_tensor(const std::string& name, float* host_out, int64_t capacity);

@@ -98,13 +98,14 @@ namespace {
 // 32x32 shared-memory tile transpose with fp32 -> bf16 conversion.
 __global__ void pack_weight_kernel(const float* __restrict__ src, int src_cols, int k_begin, int k_count,
                                    int c_begin, int c_count, __nv_bfloat16* __restrict__ dst, int block,
-                                   int block_stride, int block_offset) {
+                                   int block_stride, int block_offset, const float* __restrict__ k_scale) {
     __shared__ float tile[32][33];
     const int c0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
     for (int i = threadIdx.y; i < 32; i += blockDim.y) {
         const int k = k0 + i, c = c0 + threadIdx.x;
-        tile[i][threadIdx.x] = (k < k_count && c < c_count)
-            ? src[static_cast<size_t>(k_begin + k) * src_cols + c_begin + c] : 0.0F;
+        float v = (k < k_count && c < c_count) ? src[static_cast<size_t>(k_begin + k) * src_cols + c_begin + c] : 0.0F;
+        if (k_scale && k < k_count) v *= k_scale[k_begin + k];  // a per-input-feature factor (folded norm weight)
+        tile[i][threadIdx.x] = v;
     }
     __syncthreads();
     for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -120,11 +121,11 @@ __global__ void pack_weight_kernel(const float* __restrict__ src, int src_cols, 
 
 void pack_weight_transposed(const float* src_device, int src_cols, int k_begin, int k_count, int c_begin,
                             int c_count, void* dst_bf16, int block, int block_stride, int block_offset,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const float* k_scale_device) {
     dim3 grid((c_count + 31) / 32, (k_count + 31) / 32), threads(32, 8);
     pack_weight_kernel<<<grid, threads, 0, stream>>>(src_device, src_cols, k_begin, k_count, c_begin, c_count,
                                                      static_cast<__nv_bfloat16*>(dst_bf16), block, block_stride,
-                                                     block_offset);
+                                                     block_offset, k_scale_device);
     count_launch();
     cuda_check(cudaGetLastError(), "pack_weight");
 }

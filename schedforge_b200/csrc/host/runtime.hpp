@@ -89,7 +89,11 @@ void shard_rows(const float* src, int rows, int cols, int rank, int size, float*
 // (c / block) * block_stride + block_offset + c % block.
 void pack_weight_transposed(const float* src_device, int src_cols, int k_begin, int k_count, int c_begin,
                             int c_count, void* dst_bf16, int block, int block_stride, int block_offset,
-                            cudaStream_t stream);
+                            cudaStream_t stream, const float* k_scale_device = nullptr);
+
+// Whether the tensor-core GEMM takes these arguments (gemm_tcgen05.cu); the CUDA-core kernel covers the rest
+// but knows neither the folded RMSNorm nor the paged K/V append of the RoPE epilogue.
+bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& args);
 
 // first[i] *= silu(gate[i]) (fp32 MoE plan; defined in moe.cu).
 void moe_silu_mul_f32(float* first, const float* gate, int64_t count, cudaStream_t stream);

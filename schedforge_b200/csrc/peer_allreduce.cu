@@ -105,6 +105,128 @@ peer_allreduce_finish_kernel(const PeerParams p) {
     }
 }
 
+// ---- two-shot form: reduce-scatter by the GEMM epilogues, sum + all-gather by the row owners ---------
+// Rank r owns rows [r * rows_own, (r + 1) * rows_own) of the [T, width] tensor.  The producing GEMM of every
+// rank stores each finished output piece ONLY into its slot of the owner's receive buffer (sfb_gemm_args.
+// scatter_out), so a rank sends (size - 1) / size of the tensor instead of (size - 1) times the tensor.  The
+// kernel below runs on the owner: it (A) tells every peer that its partial sums have been delivered and waits
+// for the same from them, then one warp per owned row adds the `slots` partial rows in rank order (fp32), adds
+// the owner's rows of the residual stream, rounds to bf16, takes the row's sum of squares (the RMSNorm of the
+// next GEMM is folded into that GEMM and only needs 1/rms), stores the finished row into its own copy of the
+// full tensor and, with plain peer stores, into every other rank's copy (the all-gather), and (B) the block that
+// finishes last tells every peer that this rank's rows have arrived and waits for theirs.  With slots == 0 the
+// rows are taken from `source` as they are: an all-gather of rows each rank already holds (the layer input).
+// Both waits are bounded; when one gives up the status word is set and the kernel returns.
+struct GatherParams {
+    const bf16* recv;
+    long long slot_elems;
+    int slots;
+    const bf16* source;
+    const bf16* residual;
+    bf16* gathered[SFB_MAX_PEERS];
+    float* ss[SFB_MAX_PEERS];
+    const float* source_ss;
+    uint32_t* local_flags_a;
+    uint32_t* local_flags_b;
+    uint32_t* peer_flags_a[SFB_MAX_PEERS];
+    uint32_t* peer_flags_b[SFB_MAX_PEERS];
+    uint32_t* done_counter;
+    int rank, size;
+    uint32_t epoch;
+    int rows_own, width, gather;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ bool wait_peers(const uint32_t* flags, int rank, int size, uint32_t epoch, uint32_t* status) {
+    const long long start = clock64();
+    for (int s = 0; s < size; ++s) {
+        if (s == rank) continue;
+        uint32_t spins = 0;
+        while (static_cast<int>(load_acquire_sys(flags + s) - epoch) < 0) {
+            if ((++spins & 0xFFu) == 0 && clock64() - start > kPeerWaitCycles) {
+                atomicOr(status, kCodePeerWait);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__global__ void __launch_bounds__(256)
+peer_reduce_gather_kernel(const GatherParams p) {
+    __shared__ int proceed;
+    if (blockIdx.x == 0 && threadIdx.x < p.size && static_cast<int>(threadIdx.x) != p.rank) {
+        __threadfence_system();  // the partial sums pushed by the preceding GEMM come before the flag
+        store_release_sys(p.peer_flags_a[threadIdx.x], p.epoch);
+    }
+    if (threadIdx.x == 0) proceed = wait_peers(p.local_flags_a, p.rank, p.size, p.epoch, p.status) ? 1 : 0;
+    __syncthreads();
+    if (!proceed) return;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int pieces = p.width / 8;  // width % 8 == 0
+    for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < p.rows_own; row += warps) {
+        const size_t local = static_cast<size_t>(row) * p.width;
+        const size_t global = (static_cast<size_t>(p.rank) * p.rows_own + row) * p.width;
+        float sumsq = 0.0F;
+        for (int c = lane; c < pieces; c += 32) {
+            float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+            auto add = [&](const bf16* src) {
+                const uint4 packed = *reinterpret_cast<const uint4*>(src + c * 8);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 x = __bfloat1622float2(h[j]);
+                    acc[2 * j] += x.x;
+                    acc[2 * j + 1] += x.y;
+                }
+            };
+            if (p.slots == 0) add(p.source + local);
+            for (int s = 0; s < p.slots; ++s) add(p.recv + s * p.slot_elems + local);  // rank order: one arithmetic everywhere
+            if (p.residual) add(p.residual + local);
+            uint4 result;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                const float2 r = __bfloat1622float2(h[j]);
+                sumsq = fmaf(r.x, r.x, sumsq);
+                sumsq = fmaf(r.y, r.y, sumsq);
+            }
+            *reinterpret_cast<uint4*>(p.gathered[p.rank] + global + c * 8) = result;
+            if (p.gather)
+                for (int s = 0; s < p.size; ++s)
+                    if (s != p.rank) *reinterpret_cast<uint4*>(p.gathered[s] + global + c * 8) = result;  // peer stores over NVLink
+        }
+        if (p.ss[p.rank]) {
+            sumsq = p.source_ss ? p.source_ss[row] : warp_sum(sumsq);
+            if (lane == 0) {
+                const size_t at = static_cast<size_t>(p.rank) * p.rows_own + row;
+                p.ss[p.rank][at] = sumsq;
+                if (p.gather)
+                    for (int s = 0; s < p.size; ++s)
+                        if (s != p.rank) p.ss[s][at] = sumsq;
+            }
+        }
+    }
+    if (!p.gather) return;
+    // (B) the last block to finish announces this rank's rows and waits for the peers' rows
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(p.done_counter, 1u);
+        proceed = ticket == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!proceed) return;
+    if (threadIdx.x == 0) *p.done_counter = 0;
+    if (threadIdx.x < p.size && static_cast<int>(threadIdx.x) != p.rank) {
+        __threadfence_system();
+        store_release_sys(p.peer_flags_b[threadIdx.x], p.epoch);
+    }
+    if (threadIdx.x == 0) wait_peers(p.local_flags_b, p.rank, p.size, p.epoch, p.status);
+}
+
 }  // namespace
 }  // namespace sfb
 
@@ -138,6 +260,47 @@ sfb_status sfb_k_peer_allreduce_finish(const sfb_peer_allreduce_args* a, sfb_str
     const int grid = static_cast<int>(std::min<long long>((pieces + 255) / 256, static_cast<long long>(sm_count()) * 4));
     peer_allreduce_finish_kernel<<<grid, 256, 0, as_stream(stream)>>>(p);
     return check_launch("peer_allreduce_finish");
+}
+
+sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* a, sfb_stream stream) {
+    SFB_REQUIRE(a && a->local_flags && a->done_counter, "peer reduce-gather: null buffer");
+    SFB_REQUIRE(a->size >= 2 && a->size <= SFB_MAX_PEERS && a->rank >= 0 && a->rank < a->size && a->rows_own > 0 &&
+                    a->width > 0 && a->width % 8 == 0 && a->slots >= 0 && a->slots <= a->size,
+                "peer reduce-gather: invalid group or shape");
+    SFB_REQUIRE(a->slots == 0 ? a->source != nullptr : (a->recv != nullptr && a->slot_elems >= static_cast<int64_t>(a->rows_own) * a->width &&
+                                                        a->slot_elems % 8 == 0),
+                "peer reduce-gather: missing source rows or receive slots");
+    SFB_REQUIRE(a->gathered[a->rank], "peer reduce-gather: null destination");
+    GatherParams p{};
+    p.recv = static_cast<const bf16*>(a->recv);
+    p.slot_elems = a->slot_elems;
+    p.slots = a->slots;
+    p.source = static_cast<const bf16*>(a->source);
+    p.residual = static_cast<const bf16*>(a->residual);
+    p.source_ss = a->source_ss;
+    for (int s = 0; s < a->size; ++s) {
+        if (a->gather) SFB_REQUIRE(a->gathered[s] && (a->ss[a->rank] == nullptr || a->ss[s]), "peer reduce-gather: null peer destination");
+        SFB_REQUIRE(s == a->rank || a->peer_flags[s], "peer reduce-gather: null peer flag");
+        SFB_REQUIRE((reinterpret_cast<uintptr_t>(a->gathered[s]) & 15) == 0, "peer reduce-gather: buffers must be 16-byte aligned");
+        p.gathered[s] = static_cast<bf16*>(a->gathered[s]);
+        p.ss[s] = a->ss[s];
+        // two flags per peer and collective: [0] partial sums delivered, [1] finished rows delivered
+        p.peer_flags_a[s] = a->peer_flags[s];
+        p.peer_flags_b[s] = a->peer_flags[s] ? a->peer_flags[s] + SFB_MAX_PEERS : nullptr;
+    }
+    p.local_flags_a = a->local_flags;
+    p.local_flags_b = a->local_flags + SFB_MAX_PEERS;
+    p.done_counter = a->done_counter;
+    p.rank = a->rank;
+    p.size = a->size;
+    p.epoch = a->epoch;
+    p.rows_own = a->rows_own;
+    p.width = a->width;
+    p.gather = a->gather;
+    p.status = device_status_word();
+    const int blocks = std::min((a->rows_own + 7) / 8, sm_count() * 4);
+    peer_reduce_gather_kernel<<<blocks, 256, 0, as_stream(stream)>>>(p);
+    return check_launch("peer_reduce_gather");
 }
 
 // ---- peer-visible device memory (CUDA IPC) -----------------------------------------------------

@@ -28,7 +28,13 @@ class GemmArgs(C.Structure):
                 ("head_dim", C.c_int),
                 ("group_offsets", vp), ("groups", C.c_int), ("tile_table", vp),
                 ("split_workspace", vp), ("split_workspace_bytes", C.c_size_t), ("bt_tiled", C.c_int),
-                ("peer_out", vp * 7), ("peer_count", C.c_int), ("rope_row_offset", C.c_int), ("bt_scales", vp)]
+                ("peer_out", vp * 7), ("peer_count", C.c_int), ("scatter_out", vp * 8), ("scatter_rows", C.c_int),
+                ("rope_row_offset", C.c_int), ("bt_scales", vp),
+                ("row_ss", vp), ("row_ss_tiles", C.c_int), ("row_ss_stride", C.c_int), ("rms_epsilon", C.c_float),
+                ("ss_out", vp), ("ss_out_stride", C.c_int),
+                ("kv_k_pool", vp), ("kv_v_pool", vp), ("kv_table", vp),
+                ("kv_position", C.c_int), ("kv_block_tokens", C.c_int), ("kv_max_blocks", C.c_int),
+                ("kv_num_blocks", C.c_int)]
 
 
 class AttentionArgs(C.Structure):
@@ -44,7 +50,7 @@ class DecodeArgs(C.Structure):
                 ("out", vp), ("partials", vp)] + \
                [(n, C.c_int) for n in ("batch", "q_heads", "kv_heads", "head_dim", "head_dim_value",
                                        "block_tokens", "max_blocks", "num_blocks", "max_context", "splits")] + \
-               [("scale", C.c_float), ("dtype", C.c_int)]
+               [("scale", C.c_float), ("dtype", C.c_int), ("uniform_context", C.c_int)]
 
 
 class DecoderConfig(C.Structure):
@@ -67,7 +73,8 @@ class CompileOptions(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dtype", "token_major_attention", "fuse_epilogues",
                                        "gemm_backend", "attention_backend", "page_tokens", "tp_rank",
                                        "tp_size", "seed_block_table", "no_workspace_reuse", "no_pipeline",
-                                       "append_new_token", "weight_int8", "local_expert_weights")]
+                                       "append_new_token", "weight_int8", "kv_capacity", "no_norm_fusion",
+                                       "local_expert_weights")]
 
 
 class PlanCost(C.Structure):
@@ -132,14 +139,15 @@ ALLREDUCE_FN = C.CFUNCTYPE(None, vp, vp, C.c_int64, C.c_int, vp)
 # Every symbol include/schedforge_b200.h declares (checked by tests/test_abi.py).
 EXPORTS = (
     "sfb_last_error sfb_version sfb_launch_count sfb_device_status "
-    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 sfb_tiled_weight_elems sfb_k_tile_weight_bf16 sfb_k_quantize_weight_int8 sfb_k_dequantize_weight_int8 sfb_gemm_stream_workspace_bytes "
+    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 sfb_tiled_weight_elems sfb_k_tile_weight_bf16 sfb_k_quantize_weight_int8 sfb_k_dequantize_weight_int8 sfb_gemm_stream_workspace_bytes sfb_gemm_ss_tiles sfb_k_convert_rows_sumsq sfb_k_row_sumsq "
     "sfb_rope_table sfb_k_rope_split sfb_k_attention_prefill "
     "sfb_attention_decode_workspace sfb_attention_decode_default_splits sfb_k_attention_decode_paged "
     "sfb_k_paged_kv_append sfb_k_paged_kv_gather "
     "sfb_k_moe_route sfb_k_moe_dispatch sfb_moe_dispatch_scratch_bytes sfb_k_moe_dispatch_static sfb_k_moe_combine "
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
     "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_execute_rows sfb_decoder_upload_input "
-    "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
+    "sfb_decoder_step sfb_decoder_kv_info sfb_decoder_kv_truncate sfb_decoder_kv_release "
+    "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_k_peer_reduce_gather sfb_decoder_set_peer_collective sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
     "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
     "sfb_attention_execute sfb_attention_decode "
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "

@@ -81,50 +81,81 @@ def main():
             rows = t_rows // world
             x2d = data["input"].reshape(t_rows, oc.hidden)
             mine_rows, _ = plan.execute_rows(x2d[rank * rows:(rank + 1) * rows], rank * rows)
-            if not np.array_equal(mine_rows, out.reshape(t_rows, oc.hidden)[rank * rows:(rank + 1) * rows]):
-                failures.append(name + ":row-sharded execute differs")
-        # the same layer with the all-reduces after O and Down fused into the GEMMs over peer memory
-        # (the MoE combine keeps the hook); three passes reuse the slot sets
+            # (the sums of squares of the folded norm are taken over other row groups here: last-bit differences)
+            gap = float(np.max(np.abs(mine_rows - out.reshape(t_rows, oc.hidden)[rank * rows:(rank + 1) * rows])) / np.max(np.abs(out)))
+            if not gap < 1e-2:
+                failures.append(name + f":row-sharded execute differs by {gap:.3e}")
+        # the same layer with the all-reduces after O and Down fused into the GEMMs over peer memory, one-shot
+        # (every rank pushes its whole partial tensor) and two-shot (reduce-scatter under the GEMM, the row owners
+        # sum, add the residual and all-gather); the MoE combine keeps the hook; three passes reuse the buffers
         def exchange(handle):
             handles = [None] * world
             dist.all_gather_object(handles, handle)
             return handles
-        plan.enable_peer_allreduce(rank, world, exchange)
-        dist.barrier()
-        for _ in range(3):
-            fused, _ = plan.execute(data["input"])
-        word = C.c_uint32(0)
-        L.check(L.load().sfb_device_status(C.byref(word)))
-        if word.value != 0:
-            failures.append(f"{name}:device status {word.value:#x}")
-        if moe:
-            # With more than two ranks the two all-reduces add the partial sums in different orders, and a
-            # token whose router logits nearly tie may pick another expert: compare with the oracle routed
-            # like THIS run instead of with the NCCL run.
-            t = oc.batch * oc.sequence
-            trace = (plan.read_tensor("expert_ids", np.int32).reshape(t, oc.top_k),
-                     plan.read_tensor("expert_weights").reshape(t, oc.top_k), plan.read_tensor("counts", np.int32))
-            err = 0.0
-            if rank == 0:
-                want = port.decoder_layer(oc, data, native=True, trace=trace)
-                err = float(np.max(np.abs(fused - want)) / np.max(np.abs(want)))
-                print(f"{name}: fused peer all-reduce rel err {err:.3e}", flush=True)
-            if not err < 2e-2:
-                failures.append(name + ":fused differs")
-        else:
-            err = float(np.max(np.abs(fused - out)) / np.max(np.abs(out)))
-            if rank == 0:
-                print(f"{name}: fused peer all-reduce vs NCCL rel diff {err:.3e}", flush=True)
-            if not err < 1e-2:  # both are sums of the same bf16 partial sums, rounded in a different order
-                failures.append(name + ":fused differs")
-        mine = torch.from_numpy(fused).cuda()
-        ref = mine.clone()
-        dist.broadcast(ref, 0)
-        if not torch.equal(mine, ref):
-            failures.append(name + ":fused ranks differ")
-        torch.cuda.synchronize()
-        dist.barrier()
-        plan.disable_peer_allreduce()
+        nccl_trace = trace
+        modes = [("one-shot", 1)] + ([("two-shot", 2)] if t_rows % world == 0 and t_rows // world >= 1 else [])
+        for mode_name, mode in modes:
+            plan.enable_peer_allreduce(rank, world, exchange, mode)
+            dist.barrier()
+            for _ in range(3):
+                if mode == 2:  # the whole-tensor pass (the host-buffer call of a dense plan runs row chunks, one-shot)
+                    plan.upload_input(data["input"])
+                    plan.execute_resident()
+                    fused = plan.download_output()
+                else:
+                    fused, _ = plan.execute(data["input"])
+            word = C.c_uint32(0)
+            L.check(L.load().sfb_device_status(C.byref(word)))
+            if word.value != 0:
+                failures.append(f"{name}:{mode_name}:device status {word.value:#x}")
+            label = f"{name}: fused {mode_name} peer all-reduce"
+            if moe:
+                # The all-reduce forms add the partial sums in different orders, so a token whose router logits
+                # nearly tie may pick another expert: count those tokens, require them to be rare, and compare the
+                # output with the oracle routed like THIS run.
+                t = oc.batch * oc.sequence
+                ids = plan.read_tensor("expert_ids", np.int32).reshape(t, oc.top_k)
+                trace = (ids, plan.read_tensor("expert_weights").reshape(t, oc.top_k), plan.read_tensor("counts", np.int32))
+                flipped = int((np.sort(ids, axis=1) != np.sort(nccl_trace[0], axis=1)).any(axis=1).sum())
+                same = ~(np.sort(ids, axis=1) != np.sort(nccl_trace[0], axis=1)).any(axis=1)
+                if flipped > max(1, t // 200):
+                    failures.append(f"{name}:{mode_name}:{flipped} of {t} tokens changed experts")
+                rows_err = float(np.max(np.abs(fused.reshape(t, -1)[same] - out.reshape(t, -1)[same])) / np.max(np.abs(out)))
+                if not rows_err < 1e-2:
+                    failures.append(f"{name}:{mode_name}:rows with unchanged routes differ from the NCCL run")
+                err = 0.0
+                if rank == 0:
+                    want = port.decoder_layer(oc, data, native=True, trace=trace)
+                    err = float(np.max(np.abs(fused - want)) / np.max(np.abs(want)))
+                    print(f"{label} rel err {err:.3e}, {flipped} of {t} tokens changed experts against the NCCL run, "
+                          f"other rows differ by {rows_err:.3e}", flush=True)
+                if not err < 2e-2:
+                    failures.append(f"{name}:{mode_name} differs")
+            else:
+                err = float(np.max(np.abs(fused - out)) / np.max(np.abs(out)))
+                if rank == 0:
+                    want = port.decoder_layer(oc, data, native=True)
+                    oracle_err = float(np.max(np.abs(fused - want)) / np.max(np.abs(want)))
+                    print(f"{label} vs NCCL rel diff {err:.3e}, vs oracle {oracle_err:.3e}", flush=True)
+                    if not oracle_err < 2e-2:
+                        failures.append(f"{name}:{mode_name} differs from the oracle")
+                if not err < 1e-2:  # both are sums of the same bf16 partial sums, rounded in a different order
+                    failures.append(f"{name}:{mode_name} differs")
+                if mode == 2:  # every rank brings its rows: the input is gathered with peer stores too
+                    rows = t_rows // world
+                    x2d = data["input"].reshape(t_rows, oc.hidden)
+                    mine_rows, _ = plan.execute_rows(x2d[rank * rows:(rank + 1) * rows], rank * rows)
+                    row_err = float(np.max(np.abs(mine_rows - fused.reshape(t_rows, oc.hidden)[rank * rows:(rank + 1) * rows])) / np.max(np.abs(fused)))
+                    if not row_err < 1e-2:
+                        failures.append(f"{name}:two-shot row-sharded execute differs by {row_err:.3e}")
+            mine = torch.from_numpy(fused).cuda()
+            ref = mine.clone()
+            dist.broadcast(ref, 0)
+            if not torch.equal(mine, ref):
+                failures.append(f"{name}:{mode_name} ranks differ")
+            torch.cuda.synchronize()
+            dist.barrier()
+            plan.disable_peer_allreduce()
         plan.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -48,12 +48,12 @@ def test_struct_layouts_match_header(sfb):
     """ctypes mirrors: field counts and sizes follow the C structs (natural alignment)."""
     assert C.sizeof(sfb.DecoderConfig) == 14 * 4
     assert C.sizeof(sfb.DecoderData) == 16 * 8
-    assert C.sizeof(sfb.CompileOptions) == 14 * 4
+    assert C.sizeof(sfb.CompileOptions) == 16 * 4
     assert C.sizeof(sfb.AttentionConfig) == 9 * 4
     assert C.sizeof(sfb.MoeConfig) == 5 * 4
     assert C.sizeof(sfb.GraphSummary) == 7 * 4
     assert C.sizeof(sfb.DecoderResult) == 9 * 8 + 8
-    assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.bt_scales.offset == C.sizeof(sfb.GemmArgs) - 8
+    assert C.sizeof(sfb.GemmArgs) % 8 == 0 and sfb.GemmArgs.kv_num_blocks.offset == C.sizeof(sfb.GemmArgs) - 4
 
 
 def test_weight_layout_and_scratch_size_helpers_need_no_device(sfb):

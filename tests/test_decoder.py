@@ -257,8 +257,9 @@ def test_autoregressive_step_equals_last_token_of_the_prefill(port, dtype, head_
     out, _ = plan.execute(last)
     assert rel_err(out, want) < (F32_TOL if dtype == L.F32 else BF16_TOL)
     again, _ = plan.execute(last)  # the append overwrites the same position: the plan can be run again
-    # (bf16 plans sum the partial tiles of their few-row GEMMs with fp32 reductions at L2, whose order is not fixed)
-    assert rel_err(again, out) < 1e-5
+    # (bf16 plans sum the partial tiles of their few-row GEMMs with fp32 reductions at L2, whose order is not fixed:
+    # a last-bit difference in a sum can move a bf16 intermediate by one step, which the fp32 output then shows)
+    assert rel_err(again, out) < (1e-5 if dtype == L.F32 else BF16_TOL / 4)
     # without the flag the same plan input gives the reference's decode semantics, which differ
     legacy = api.DecoderCompiler.compile(c, step, "", api.compile_options(dtype=dtype))
     out_legacy, _ = legacy.execute(last)
@@ -401,3 +402,79 @@ def test_device_wait_that_runs_out_surfaces_as_device_timeout(port, dev):
     out, _ = plan.execute(data["input"])
     assert np.all(np.isfinite(out))
     plan.close()
+
+
+@pytest.mark.parametrize("dtype,head_dim", [(L.BF16, 128), (L.BF16, 64), (L.F32, 64)])
+def test_decode_loop_steps_across_a_page_boundary(port, dtype, head_dim):
+    """sfb_decoder_step: five successive steps from a cache of 13 tokens (16-token pages, so the fourth step
+    opens the second page) must reproduce the last five tokens of the oracle's causal prefill over 18 tokens,
+    and the page accounting after every step must equal the reference's PagedKVCache fed the same appends;
+    then truncate / release behave like truncate_paged_kv / release_paged_kv_pages."""
+    batch, hq, hkv, ctx, steps = 3, 4, 2, 13, 5
+    total = ctx + steps
+    kw = dict(batch=batch, sequence=total, hidden=hq * head_dim, intermediate=384, query_heads=hq, kv_heads=hkv,
+              head_dim=head_dim, rope_theta=10000.0)
+    oc, _, data = bf16_case(port, 71, **kw)
+    hidden, kvw = oc.hidden, hkv * head_dim
+    want = port.decoder_layer(oc, data, native=True).reshape(batch, total, hidden)
+    x = data["input"].reshape(batch * total, hidden)
+    normalized = port.rms_norm(x, data["rms1_weight"], oc.rms_epsilon)
+    wqkv = np.concatenate([data["query_weight"].reshape(hidden, hidden), data["key_weight"].reshape(hidden, kvw),
+                           data["value_weight"].reshape(hidden, kvw)], axis=1)
+    _, keys, values = port.split_qkv_rope(oc, port.matmul(normalized, wqkv, fma=True))
+    start = dict(weights_of(data))
+    start["cached_key"] = np.ascontiguousarray(keys[:, :, :ctx, :])
+    start["cached_value"] = np.ascontiguousarray(values[:, :, :ctx, :])
+    if dtype == L.BF16:
+        start["cached_key"], start["cached_value"] = port.round_bf16(start["cached_key"]), port.round_bf16(start["cached_value"])
+    capacity = 40                                    # three pages
+    c = api.decoder_config(**dict(kw, sequence=1, context_sequence=ctx))
+    plan = api.DecoderCompiler.compile(c, start, "", api.compile_options(dtype=dtype, append_new_token=True,
+                                                                         seed_block_table=9, kv_capacity=capacity))
+    if dtype == L.BF16:
+        assert "kv_append=paged_cache" in plan.dump() and "prologue=rms_norm_folded" in plan.dump()
+    mirror = port.paged_create(batch, hkv, head_dim, head_dim, 16, capacity)   # the reference's accounting
+    mirror.append(start["cached_key"], start["cached_value"], ctx)
+    tokens = data["input"].reshape(batch, total, hidden)
+    tol = F32_TOL if dtype == L.F32 else BF16_TOL
+    one = np.zeros((batch, hkv, 1, head_dim), np.float32)
+    for i in range(steps):
+        out, _ = plan.step(np.ascontiguousarray(tokens[:, ctx + i, :]))
+        assert rel_err(out, want[:, ctx + i, :]) < tol, i
+        mirror.append(one, one, 1)
+        got, ref_info = plan.kv_info(), mirror.info()
+        assert got["length"] == ref_info["length"] == ctx + i + 1
+        assert np.array_equal(got["page_table"], ref_info["page_table"])
+        assert np.array_equal(got["free_pages"], ref_info["free_pages"]) and got["pages"] == ref_info["pages"] == 3
+    assert len(plan.kv_info()["page_table"]) == 2
+    # execute() on the same plan runs the pass at the current length without advancing it
+    before = plan.kv_info()["length"]
+    plan.execute(np.ascontiguousarray(tokens[:, total - 1, :]))
+    assert plan.kv_info()["length"] == before
+    # truncate back into the first page: the second page returns to the free list; stepping again from there
+    # reproduces the prefill's token 15 and 16 (the page is handed out again at the boundary)
+    plan.kv_truncate(ctx + 2)
+    mirror.truncate(ctx + 2)
+    assert np.array_equal(plan.kv_info()["page_table"], mirror.info()["page_table"])
+    assert np.array_equal(plan.kv_info()["free_pages"], mirror.info()["free_pages"])
+    for i in (2, 3):
+        out, _ = plan.step(np.ascontiguousarray(tokens[:, ctx + i, :]))
+        assert rel_err(out, want[:, ctx + i, :]) < tol, i
+    with pytest.raises(L.InvalidArgument, match="cannot release an active paged KV page"):
+        plan.kv_release([int(plan.kv_info()["page_table"][0])])
+    with pytest.raises(L.InvalidArgument, match="invalid physical KV page"):
+        plan.kv_release([99])
+    with pytest.raises(L.InvalidArgument, match="invalid paged KV truncation length"):
+        plan.kv_truncate(100)
+    # fill the cache: the step after the last slot is refused
+    while plan.kv_info()["length"] < capacity:
+        plan.step(np.ascontiguousarray(tokens[:, total - 1, :]))
+    with pytest.raises(L.InvalidArgument, match="paged KV capacity exceeded"):
+        plan.step(np.ascontiguousarray(tokens[:, total - 1, :]))
+    mirror.close()
+    plan.close()
+    # a plan without the flag has no loop
+    legacy = api.DecoderCompiler.compile(c, start, "", api.compile_options(dtype=dtype))
+    with pytest.raises(L.InvalidArgument, match="append_new_token"):
+        legacy.step(np.ascontiguousarray(tokens[:, ctx, :]))
+    legacy.close()

@@ -345,3 +345,31 @@ def test_gemm_int8_weights_swiglu(sfb, dev, port):
     got = gemm_bf16(sfb, dev, dev.bf16(a), q, epilogue=sfb.EPI_SWIGLU, backend=2, swiglu_block=block,
                     scratch=_scratch(sfb, dev, 2 * inter), n=2 * inter, int8_scales=scales)
     assert rel_err(dev.np(got), want) < BF16_TOL
+
+
+def test_gemm_scatters_rows_to_their_owners(sfb, dev, port):
+    """Two-shot form, producer side: with scatter_rows the tcgen05 epilogue stores row r only into the buffer of
+    rank r / scatter_rows at row r % scatter_rows (here four buffers of one GPU stand in for four ranks)."""
+    rng = np.random.default_rng(17)
+    m, n, k, owners = 512, 384, 256, 4
+    a = port.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    w = port.round_bf16((rng.standard_normal((k, n)) * 0.05).astype(np.float32))
+    da, dbt = dev.bf16(a), dev.bf16(np.ascontiguousarray(w.T))
+    plain = dev.zeros((m, n), dev.torch.bfloat16)
+    slots = [dev.zeros((m // owners, n), dev.torch.bfloat16) for _ in range(owners)]
+    L = sfb
+    lib, s = L.load(), C.c_void_p(dev.stream())
+    g = L.GemmArgs()
+    g.a, g.bt, g.out, g.m, g.n, g.k = da.data_ptr(), dbt.data_ptr(), plain.data_ptr(), m, n, k
+    g.epilogue, g.backend = L.EPI_STORE, L.GEMM_TCGEN05
+    L.check(lib.sfb_k_gemm_bf16(C.byref(g), s))
+    want = dev.np(plain)
+    unused = dev.zeros((m, n), dev.torch.bfloat16)
+    g.out, g.scatter_rows = unused.data_ptr(), m // owners
+    for r in range(owners):
+        g.scatter_out[r] = slots[r].data_ptr()
+    L.check(lib.sfb_k_gemm_bf16(C.byref(g), s))
+    for r in range(owners):
+        assert np.array_equal(dev.np(slots[r]), want[r * (m // owners):(r + 1) * (m // owners)])
+    assert float(np.abs(dev.np(unused)).sum()) == 0.0
+    assert rel_err(want, a @ w) < 2e-2

@@ -70,3 +70,84 @@ def test_finish_rejects_bad_groups(dev, port):
     a.rank, a.size, a.count, a.slot_elems = 0, 1, 8, 8
     with pytest.raises(L.SfbError):
         L.check(L.load().sfb_k_peer_allreduce_finish(C.byref(a), C.c_void_p(dev.stream())))
+
+
+class GatherArgs(C.Structure):
+    _fields_ = [("recv", C.c_void_p), ("slot_elems", C.c_int64), ("slots", C.c_int), ("source", C.c_void_p),
+                ("source_ss", C.c_void_p), ("residual", C.c_void_p), ("gathered", C.c_void_p * 8), ("ss", C.c_void_p * 8),
+                ("local_flags", C.c_void_p), ("peer_flags", C.c_void_p * 8), ("done_counter", C.c_void_p),
+                ("rank", C.c_int), ("size", C.c_int), ("epoch", C.c_uint32), ("rows_own", C.c_int), ("width", C.c_int),
+                ("gather", C.c_int)]
+
+
+def _run_gather(dev, port, size, rank, rows_own, width, flag_a, flag_b, epoch, slots=None, with_residual=True):
+    """The owner's kernel of the two-shot form on ONE GPU: the slots the peers' GEMMs would have filled, the peers'
+    copies of the gathered tensor and both flag sets are plain tensors of this GPU prepared by the test."""
+    torch = dev.torch
+    rng = np.random.default_rng(size * 1000 + rank * 10 + rows_own)
+    slots = size if slots is None else slots
+    total = size * rows_own
+    parts = [port.round_bf16(rng.standard_normal((rows_own, width)).astype(np.float32)) for _ in range(max(slots, 1))]
+    residual = port.round_bf16(rng.standard_normal((rows_own, width)).astype(np.float32))
+    recv = dev.bf16(np.stack(parts))
+    res = dev.bf16(residual)
+    copies = [dev.zeros((total, width), torch.bfloat16) for _ in range(size)]      # every rank's full tensor
+    sums = [dev.zeros((total,), torch.float32) for _ in range(size)]
+    flags = torch.zeros((16,), dtype=torch.int32, device="cuda")
+    flags[:8] = flag_a
+    flags[8:] = flag_b
+    sink = torch.zeros((8, 16), dtype=torch.int32, device="cuda")                   # peers' flag arrays
+    counter = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    a = GatherArgs()
+    if slots > 0:
+        a.recv, a.slot_elems, a.slots = recv.data_ptr(), rows_own * width, slots
+    else:
+        a.source = recv.data_ptr()
+    a.residual = res.data_ptr() if with_residual else None
+    for s in range(size):
+        a.gathered[s] = copies[s].data_ptr()
+        a.ss[s] = sums[s].data_ptr()
+        a.peer_flags[s] = sink[s].data_ptr() + 4 * rank
+    a.local_flags, a.done_counter = flags.data_ptr(), counter.data_ptr()
+    a.rank, a.size, a.epoch, a.rows_own, a.width, a.gather = rank, size, epoch, rows_own, width, 1
+    lib = L.load()
+    L.check(lib.sfb_k_peer_reduce_gather(C.byref(a), C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    word = C.c_uint32(0)
+    L.check(lib.sfb_device_status(C.byref(word)))
+    acc = np.zeros((rows_own, width), np.float32)
+    for part in parts[:max(slots, 1)]:
+        acc = (acc + part).astype(np.float32)
+    if with_residual:
+        acc = (acc + residual).astype(np.float32)
+    want = port.round_bf16(acc)
+    return want, [dev.np(t) for t in copies], [dev.np(t) for t in sums], dev.np(sink.float()), int(counter.item()), word.value
+
+
+@pytest.mark.parametrize("size,rank,rows_own,width", [(2, 1, 64, 256), (4, 2, 37, 512), (8, 5, 128, 4096)])
+def test_two_shot_owner_sums_its_rows_and_hands_them_to_every_rank(dev, port, size, rank, rows_own, width):
+    want, copies, sums, sink, counter, status = _run_gather(dev, port, size, rank, rows_own, width, 3, 3, 3)
+    assert status == 0 and counter == 0
+    lo, hi = rank * rows_own, (rank + 1) * rows_own
+    for s in range(size):       # the finished rows and their sums of squares landed in every rank's copy, nowhere else
+        assert np.array_equal(copies[s][lo:hi], want)
+        assert float(np.abs(copies[s][:lo]).sum()) == 0.0 and float(np.abs(copies[s][hi:]).sum()) == 0.0
+        assert np.allclose(sums[s][lo:hi], (want.astype(np.float64) ** 2).sum(1), rtol=1e-5)
+    for s in range(size):       # both announcements reached every peer's flag array at this rank's entry
+        expect = 0 if s == rank else 3
+        assert sink[s][rank] == expect and sink[s][8 + rank] == expect
+
+
+def test_two_shot_all_gather_of_rows_a_rank_already_holds(dev, port):
+    want, copies, _, _, _, status = _run_gather(dev, port, 4, 1, 48, 256, 1, 1, 1, slots=0, with_residual=False)
+    assert status == 0
+    for s in range(4):
+        assert np.array_equal(copies[s][48:96], want)
+
+
+def test_two_shot_wait_that_runs_out_reports_and_leaves_the_rows_alone(dev, port):
+    # partial sums never announced: nothing is summed; rows announced late: the sum is done, the wait reports
+    _, copies, _, _, _, status = _run_gather(dev, port, 2, 0, 16, 256, 0, 0, 1)
+    assert status & 0x100 and float(np.abs(copies[0]).sum()) == 0.0
+    want, copies, _, _, counter, status = _run_gather(dev, port, 2, 0, 16, 256, 1, 0, 1)
+    assert status & 0x100 and np.array_equal(copies[1][:16], want) and counter == 0
