@@ -769,6 +769,32 @@ sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, i
 sfb_status sfb_make_routing_trace(const sfb_moe_config* config, int distribution, unsigned seed, int* expert_ids,
                                   float* expert_weights, int* counts);
 sfb_status sfb_make_decoder_input(const sfb_decoder_config* config, unsigned seed, float* input);
+/* The whole of make_decoder_data (src/decoder_compiler.cpp:483-514, with make_moe_data, src/moe_compiler.cpp:
+ * 393-406, for MoE layers): one std::mt19937(seed) stream, uniform in (-0.15, 0.15), drawn in the order input,
+ * Wq, Wk, Wv, Wo, Wgate, Wup, Wdown, then (decode) cached K and V; RMSNorm weights 1; MoE layers add a second
+ * stream std::mt19937(seed + 1), uniform in (-0.2, 0.2), in the order (unused input), router, W1, W3, W2.
+ * Bit-identical to the reference's generator, so a benchmark here and one of the reference see the same layer.
+ * Destinations are HOST float32 buffers of the DecoderData sizes; a NULL destination is skipped (its values are
+ * still drawn). */
+typedef struct sfb_decoder_data_buffers {
+    float* rms1_weight;
+    float* query_weight;
+    float* key_weight;
+    float* value_weight;
+    float* output_weight;
+    float* rms2_weight;
+    float* gate_weight;
+    float* up_weight;
+    float* down_weight;
+    float* router_weight;
+    float* w1;
+    float* w3;
+    float* w2;
+    float* cached_key;
+    float* cached_value;
+} sfb_decoder_data_buffers;
+sfb_status sfb_make_decoder_data(const sfb_decoder_config* config, unsigned seed, float* input,
+                                 const sfb_decoder_data_buffers* out);
 
 /* Column shard of a [rows, cols] row-major host matrix / row shard, used by the
  * tensor-parallel plan build and exposed for tests: copies shard `rank` of `size`. */

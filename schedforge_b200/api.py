@@ -415,6 +415,27 @@ def make_decoder_input(config, seed):
     return x
 
 
+def make_decoder_data(config, seed):
+    """make_decoder_data of the reference (same seeded streams): dict of float32 arrays incl. "input"."""
+    t, h, i = config.batch * config.sequence, config.hidden, config.intermediate
+    kv = config.kv_heads * config.head_dim
+    sizes = {"input": t * h, "rms1_weight": h, "rms2_weight": h, "query_weight": h * h, "key_weight": h * kv,
+             "value_weight": h * kv, "output_weight": h * h, "gate_weight": h * i, "up_weight": h * i, "down_weight": i * h}
+    if config.ffn_moe:
+        e = config.experts
+        sizes.update(router_weight=h * e, w1=e * h * i, w3=e * h * i, w2=e * i * h)
+    if config.context_sequence > 0:
+        n = config.batch * config.kv_heads * config.context_sequence * config.head_dim
+        sizes.update(cached_key=n, cached_value=n)
+    data = {k: np.zeros(n, np.float32) for k, n in sizes.items()}
+    buffers = L.DecoderDataBuffers()
+    for name in L.DATA_BUFFER_FIELDS:
+        if name in data:
+            setattr(buffers, name, _fp(data[name]))
+    L.check(L.load().sfb_make_decoder_data(C.byref(config), C.c_uint(seed), _fp(data["input"]), C.byref(buffers)))
+    return data
+
+
 def realistic_decoder_profiles():
     """realistic_decoder_profiles of the reference: 24 DecoderProfile records."""
     lib = L.load()

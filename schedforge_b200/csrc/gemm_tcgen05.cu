@@ -53,7 +53,8 @@ struct Tile {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBarrierBytes = 512;
-    static constexpr int kEpilogueStagingBytes = kEpilogueWarps * 32 * 32 * 4;  // per warp 32 rows x 32 fp32 columns
+    // per warp 32 rows x 32 fp32 columns, then per warp 32 row sums of squares
+    static constexpr int kEpilogueStagingBytes = kEpilogueWarps * 32 * 32 * 4 + kEpilogueWarps * 32 * 4;
     static constexpr int kSmemBytes =
         kStagesA * kABytes + kStagesB * kBBytes + kEpilogueStagingBytes + kBarrierBytes + 1024;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -278,6 +279,20 @@ __device__ __forceinline__ float sumsq_bf16x8(const float (&f)[8], int valid) {
     return ss;
 }
 
+// Decode step: the new token's key / value (8 elements of one head) also goes to slot kv_position + t of sequence b
+// in the paged cache.  A position past the table or a block outside the pool is skipped and flagged, never written.
+// Kept out of line: it runs for a handful of rows per step and must not cost the common epilogue its registers.
+__device__ __noinline__ void kv_append8(const TcParams& p, bf16* pool, int b, int t, int head, int d0, const float (&f)[8]) {
+    const int pos = p.kv_position + t, block = pos / p.kv_block_tokens;
+    int page = -1;
+    if (block < p.kv_max_blocks) page = p.kv_table[static_cast<size_t>(b) * p.kv_max_blocks + block];
+    if (page >= 0 && page < p.kv_num_blocks)
+        store8(pool, 0, ((static_cast<size_t>(page) * p.kv_heads + head) * p.kv_block_tokens + pos % p.kv_block_tokens) *
+                                p.head_dim + d0, f, 8);
+    else
+        atomicOr(p.status, 0x200u);
+}
+
 // Epilogue of output columns [col, col + 8) of `row` (not SwiGLU); col is a multiple of 8.  Returns the sum of
 // squares of the stored values when the kernel collects them for the RMSNorm of the next GEMM (else 0).
 __device__ __forceinline__ float emit8(const TcParams& p, int row, int col, float (&f)[8], bool residual_added = false) {
@@ -307,18 +322,7 @@ __device__ __forceinline__ float emit8(const TcParams& p, int row, int col, floa
             }
         }
         store8(dst, 0, ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d0, f, 8);
-        if (pool) {
-            // the new token's key / value also goes to slot kv_position + t of sequence b in the paged cache; a
-            // position past the table or a block outside the pool is skipped and flagged, never written
-            const int pos = p.kv_position + t, block = pos / p.kv_block_tokens;
-            int page = -1;
-            if (block < p.kv_max_blocks) page = p.kv_table[static_cast<size_t>(b) * p.kv_max_blocks + block];
-            if (page >= 0 && page < p.kv_num_blocks)
-                store8(pool, 0, ((static_cast<size_t>(page) * p.kv_heads + head) * p.kv_block_tokens + pos % p.kv_block_tokens) *
-                                        p.head_dim + d0, f, 8);
-            else
-                atomicOr(p.status, 0x200u);
-        }
+        if (pool) kv_append8(p, pool, b, t, head, d0, f);
         return 0.0F;
     }
     const size_t index = static_cast<size_t>(row) * p.n + col;
@@ -337,7 +341,7 @@ __device__ __forceinline__ float emit8(const TcParams& p, int row, int col, floa
 // phase 2 for one warp: the staged values are output columns [col0, col0 + 32) of rows
 // [row0, row0 + 32); `plain` = they are final (SwiGLU) and only need storing into [m, width].
 __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stage, int lane, int row0, int row_end,
-                                            int col0, bool plain, int width, float (&row_ss)[4]) {
+                                            int col0, bool plain, int width, float* row_sums) {
     // The residual rows come from DRAM: all four loads of this lane go out before the first is used
     // (one at a time, they made the epilogue of a tile as long as its main loop).
     const bool prefetch = !plain && p.epilogue == SFB_EPI_RESIDUAL && (p.n & 7) == 0 &&
@@ -356,7 +360,8 @@ __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stag
     for (int i = 0; i < 4; ++i) {
         const int r = i * 8 + (lane >> 2), first = (lane & 3) * 8;
         const int row = row0 + r, col = col0 + first;
-        if (row >= row_end || col >= width) continue;
+        const bool live = row < row_end && col < width;
+        if (!live && !row_sums) continue;
         float f[8];
         stage_read8(stage, r, first, f);
         if (prefetch) {
@@ -368,25 +373,28 @@ __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stag
                 f[2 * j + 1] += x.y;
             }
         }
-        if (plain) store8(p.out, p.out_f32, static_cast<size_t>(row) * width + col, f, width - col);
-        else row_ss[i] += emit8(p, row, col, f, prefetch);
+        if (plain) {
+            store8(p.out, p.out_f32, static_cast<size_t>(row) * width + col, f, width - col);
+        } else {
+            float v = live ? emit8(p, row, col, f, prefetch) : 0.0F;
+            if (row_sums) {  // the four lanes of a row add up; one of them keeps the row's running sum in shared memory
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if ((lane & 3) == 0) row_sums[r] += v;
+            }
+        }
     }
 }
 
-// Sums of squares collected by one warp over the chunks of one 128-column group: the four lanes of a row
-// are added and the row's slot (group, epilogue half `pass`) is written.
-__device__ __forceinline__ void flush_row_ss(const TcParams& p, float (&row_ss)[4], int lane, int row0, int row_end,
+// Sums of squares collected by one warp over the chunks of one 128-column group: lane r holds row r's sum in
+// shared memory; the row's slot (group, epilogue half `pass`) is written and the sum cleared.
+__device__ __forceinline__ void flush_row_ss(const TcParams& p, float* row_sums, int lane, int row0, int row_end,
                                              int col_group, int pass) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float v = row_ss[i];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        const int row = row0 + i * 8 + (lane >> 2);
-        if ((lane & 3) == 0 && row < row_end)
-            p.ss_out[static_cast<size_t>(col_group * 2 + pass) * p.ss_out_stride + row] = v;
-        row_ss[i] = 0.0F;
-    }
+    __syncwarp();
+    const float v = row_sums[lane];
+    row_sums[lane] = 0.0F;
+    if (row0 + lane < row_end) p.ss_out[static_cast<size_t>(col_group * 2 + pass) * p.ss_out_stride + row0 + lane] = v;
+    __syncwarp();
 }
 
 // Epilogue of one work item for an epilogue thread: `acc` is the tensor-memory address of the
@@ -395,7 +403,7 @@ template <int BN, bool SCALED>
 __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segment& sg, const TileCoord& c, int k_blocks,
                                                  uint32_t acc, uint32_t tmem_empty_bar, float* stage,
                                                  volatile uint32_t* last_flag, int quarter, int pass, int lane,
-                                                 bool leader, float row_inv) {
+                                                 bool leader, float row_inv, float* row_sums_area) {
     constexpr uint32_t kEpilogueThreads = 32 * kEpilogueWarps;
     const int row_in_tile = quarter * 32 + lane;
     const int row0 = c.row_start + quarter * 32;
@@ -464,8 +472,8 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
         if (out0 + pass * 32 < width) fetch(pass * 32, r0);
         fetch((pass + 2) * 32, r1);
     }
-    float row_ss[4] = {0.0F, 0.0F, 0.0F, 0.0F};
     const bool collect = p.ss_out != nullptr && !swiglu;
+    float* row_sums = collect ? row_sums_area : nullptr;
 #pragma unroll 1
     for (int ch = pass; ch < chunks; ch += 2) {
         const int col0 = out0 + ch * 32;
@@ -510,11 +518,11 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
         }
         stage_write(stage, lane, r0);
         __syncwarp();
-        emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width, row_ss);
+        emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width, row_sums);
         __syncwarp();
         // the chunks of this warp advance by 64 columns: the last one inside a 128-column group closes its slot
         if (collect && ((col0 + 64) / 128 != col0 / 128 || ch + 2 >= chunks || col0 + 64 >= width))
-            flush_row_ss(p, row_ss, lane, row0, c.row_end, col0 / 128, pass);
+            flush_row_ss(p, row_sums, lane, row0, c.row_end, col0 / 128, pass);
     }
 }
 
@@ -522,6 +530,7 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
 __device__ __forceinline__ float folded_row_inv(const TcParams& p, int row, bool row_ok) {
     if (!p.row_ss || !row_ok) return 1.0F;
     float ss = 0.0F;
+#pragma unroll 8
     for (int t = 0; t < p.row_ss_tiles; ++t) ss += __ldcg(p.row_ss + static_cast<size_t>(t) * p.row_ss_stride + row);
     return 1.0F / sqrtf(ss / static_cast<float>(p.k) + p.rms_eps);
 }
@@ -753,6 +762,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         const int pass = (warp - 2) >> 2;        // the two warps of a quarter alternate over the chunks
         const bool leader = threadIdx.x == 64;  // first epilogue thread
         float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
+        staging[kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32 + lane] = 0.0F;  // this warp's row sums of squares
+        __syncwarp();
         uint32_t count = 0;
         Segment sg;
         for (; walk.next(sg); ++count) {
@@ -768,7 +779,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             epilogue_segment<BN, false>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter, pass,
-                                 lane, leader, row_inv);
+                                 lane, leader, row_inv, staging + kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32);
         }
     }
 
@@ -798,7 +809,7 @@ struct W8 {
     static constexpr int kQBytes = BN * BK;       // weights, int8
     static constexpr int kCBytes = BN * BK * 2;   // converted weights, bf16
     static constexpr int SA = 4, SQ = 10, SC = 3;
-    static constexpr int kStagingBytes = kEpilogueWarps * 32 * 32 * 4;
+    static constexpr int kStagingBytes = kEpilogueWarps * 32 * 32 * 4 + kEpilogueWarps * 32 * 4;
     static constexpr int kBarrierBytes = 512;
     static constexpr int kSmemBytes = SA * kABytes + SQ * kQBytes + SC * kCBytes + kStagingBytes + kBarrierBytes + 1024;
     static constexpr int kTmemCols = 2 * BN;
@@ -983,6 +994,8 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         const int pass = (warp - 2) >> 2;
         const bool leader = threadIdx.x == 64;
         float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
+        staging[kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32 + lane] = 0.0F;  // this warp's row sums of squares
+        __syncwarp();
         // converting thread: the 64 K values of one of the 128 weight rows, in every second tile
         // (the other group of four warps converts the tiles in between, so two conversions overlap)
         const int row = (threadIdx.x - 64) & 127;
@@ -1040,7 +1053,8 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             epilogue_segment<BN, true>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter,
                                        pass, lane, leader,
-                                       folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end));
+                                       folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end),
+                                       staging + kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32);
         }
     }
 

@@ -220,6 +220,29 @@ sfb_status sfb_make_decoder_input(const sfb_decoder_config* config, unsigned see
     });
 }
 
+sfb_status sfb_make_decoder_data(const sfb_decoder_config* config, unsigned seed, float* input,
+                                 const sfb_decoder_data_buffers* out) {
+    return guarded([&] {
+        if (!config || !out || rows_of(*config) <= 0 || config->hidden <= 0 || config->intermediate <= 0 ||
+            config->kv_heads <= 0 || config->head_dim <= 0 || (config->ffn_moe && (config->experts <= 0 || config->top_k <= 0)))
+            throw std::invalid_argument("invalid decoder configuration");
+        // every tensor is drawn (the stream position of each one is part of the contract); a NULL destination only skips the copy
+        sfb_decoder_config c = *config;
+        const int top_k = c.top_k;
+        if (c.ffn_moe) c.top_k = std::min(std::max(top_k, 1), c.experts);  // only sizes the (unused) routing trace
+        const HostData d = make_data(c, seed, 0, 0);
+        auto put = [](float* dst, const std::vector<float>& src) {
+            if (dst && !src.empty()) std::memcpy(dst, src.data(), src.size() * sizeof(float));
+        };
+        put(input, d.input);
+        put(out->rms1_weight, d.rms1); put(out->rms2_weight, d.rms2);
+        put(out->query_weight, d.wq); put(out->key_weight, d.wk); put(out->value_weight, d.wv); put(out->output_weight, d.wo);
+        put(out->gate_weight, d.gate); put(out->up_weight, d.up); put(out->down_weight, d.down);
+        put(out->router_weight, d.router); put(out->w1, d.w1); put(out->w3, d.w3); put(out->w2, d.w2);
+        put(out->cached_key, d.cached_key); put(out->cached_value, d.cached_value);
+    });
+}
+
 int sfb_decoder_profile_count(void) { return static_cast<int>(profiles().size()); }
 
 sfb_status sfb_decoder_profile_get(int index, sfb_decoder_profile* out) {

@@ -69,6 +69,15 @@ class DecoderData(C.Structure):
     _fields_ = [(n, f32p) for n in DATA_FIELDS]
 
 
+DATA_BUFFER_FIELDS = ("rms1_weight", "query_weight", "key_weight", "value_weight", "output_weight", "rms2_weight",
+                      "gate_weight", "up_weight", "down_weight", "router_weight", "w1", "w3", "w2", "cached_key",
+                      "cached_value")
+
+
+class DecoderDataBuffers(C.Structure):
+    _fields_ = [(n, C.POINTER(C.c_float)) for n in DATA_BUFFER_FIELDS]
+
+
 class CompileOptions(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dtype", "token_major_attention", "fuse_epilogues",
                                        "gemm_backend", "attention_backend", "page_tokens", "tp_rank",
@@ -153,7 +162,7 @@ EXPORTS = (
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "
     "sfb_paged_release sfb_paged_info sfb_paged_gather sfb_paged_decode "
     "sfb_moe_route_topk sfb_moe_dispatch_tokens sfb_moe_execute sfb_moe_execute_quantized sfb_moe_plan_tasks "
-    "sfb_make_routing_trace sfb_make_decoder_input sfb_decoder_profile_count sfb_decoder_profile_get "
+    "sfb_make_routing_trace sfb_make_decoder_input sfb_make_decoder_data sfb_decoder_profile_count sfb_decoder_profile_get "
     "sfb_benchmark_decoder_profile sfb_write_decoder_benchmark_csv sfb_write_decoder_plan_candidates_csv "
     "sfb_decoder_compile_milliseconds "
     "sfb_shard_columns sfb_shard_rows"

@@ -205,3 +205,23 @@ def test_malformed_routing_trace_is_rejected_on_the_host(sfb):
                                          counts.ctypes.data_as(ip), 0, None, offsets.ctypes.data_as(ip),
                                          tokens.ctypes.data_as(ip), tokens.ctypes.data_as(ip), weights.ctypes.data_as(fp))
     assert status == sfb.SFB_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("name", ["decoder_dense", "decoder_moe", "decoder_decode", "decoder_moe_medium"])
+def test_make_decoder_data_equals_the_reference_generator(sfb, name):
+    """sfb_make_decoder_data against the tensors the reference's make_decoder_data produced for the same
+    configuration and seed (stored in the golden fixtures as in_*): every weight stream bit for bit."""
+    from schedforge_b200 import api
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    fields = [f for f, _ in sfb.DecoderConfig._fields_]
+    values = [float(v) if f in ("rms_epsilon", "rope_theta") else int(v) for f, v in zip(fields, z["config"])]
+    config = sfb.DecoderConfig(*values)
+    data = api.make_decoder_data(config, int(z["seed"]))
+    compared = 0
+    for key in z.files:
+        if not key.startswith("in_"):
+            continue
+        got = data[key[3:]]
+        assert got.shape == z[key].reshape(-1).shape and np.array_equal(got, z[key].reshape(-1)), key
+        compared += 1
+    assert compared >= 10
