@@ -163,21 +163,22 @@ typedef struct sfb_gemm_args {
     const float* bt_scales;
     /* RMSNorm folded into the GEMM (tcgen05 backend, dense mode).  The caller has multiplied the norm weight
      * into the weight (bt[n, k] *= norm_weight[k]) and passes A un-normalised; row r of the accumulator is
-     * multiplied by 1 / sqrt(sum_t row_ss[t * row_ss_stride + r] / k + rms_epsilon) before the epilogue, which
-     * is rms_norm (src/decoder_compiler.cpp:41-62) moved behind the product.  row_ss: device float32,
-     * row_ss_tiles partial sums of squares per row of A (one for a row written at once, several when the
-     * producing GEMM left one per column tile, see ss_out).  NULL = no scaling. */
-    const float* row_ss;
-    int row_ss_tiles;
-    int row_ss_stride;
+     * multiplied by 1 / sqrt(ss[r] / k + rms_epsilon) before the epilogue, which is rms_norm
+     * (src/decoder_compiler.cpp:41-62) moved behind the product.  row_ss: device memory, one sum of squares
+     * per row of A: float32, or with row_ss_fixed != 0 the unsigned 64-bit fixed-point sums (24 fraction
+     * bits) that ss_out of the producing GEMM left.  NULL = no scaling. */
+    const void* row_ss;
+    int row_ss_fixed;
     float rms_epsilon;
-    /* SFB_EPI_STORE / SFB_EPI_RESIDUAL with bf16 output (tcgen05): the kernel also leaves the sums of squares
-     * of the values it stored, per row and per (128 output columns, epilogue half):
-     * ss_out[(column / 128 * 2 + half) * ss_out_stride + row]; sfb_gemm_ss_tiles(n) slots in all, which the
-     * caller zero-fills once (a ragged last column group may leave a slot untouched).  The next GEMM takes
-     * them as row_ss.  NULL = not collected. */
-    float* ss_out;
-    int ss_out_stride;
+    /* SFB_EPI_STORE / SFB_EPI_RESIDUAL with bf16 output (tcgen05): the kernel also adds the squares of the values
+     * it stored to ss_out[row], unsigned 64-bit fixed point with 24 fraction bits (integer atomics: the total
+     * does not depend on the order in which the tiles finish).  The caller zero-fills it before the launch
+     * (or lets an earlier GEMM do it, see clear).  The next GEMM takes it as row_ss.  NULL = not collected. */
+    void* ss_out;
+    /* clear != NULL: this launch zero-fills clear_bytes bytes (8-byte aligned, a multiple of 8) after it has
+     * waited for the kernels before it: how a chain of launches resets the sums a later GEMM adds to. */
+    void* clear;
+    size_t clear_bytes;
     /* SFB_EPI_ROPE_SPLIT of a decode step (tcgen05): kv_k_pool != NULL also writes the rotated key and the
      * value of token t of sequence b into the paged cache at position kv_position + t (block
      * kv_table[b * kv_max_blocks + position / kv_block_tokens], pool layout of sfb_decode_args).  A position
@@ -192,8 +193,6 @@ typedef struct sfb_gemm_args {
 
 sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream);
 size_t sfb_gemm_stream_workspace_bytes(int n);
-/* Number of per-row slots sfb_gemm_args.ss_out receives for n output columns. */
-int sfb_gemm_ss_tiles(int n);
 
 /* dst[r, :] = bf16(src[r, :]) and ss[r] = sum of squares of the rounded row: the float32 -> bf16 conversion of
  * the layer input that also prepares the folded RMSNorm of the first GEMM (row_ss with one slot per row).

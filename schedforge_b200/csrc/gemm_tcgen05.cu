@@ -83,13 +83,17 @@ struct TcParams {
     int* tile_counters;
     int shared_tiles;       // trailing tiles whose K blocks are cut into equal ranges (0 = none)
     uint32_t* status;
-    // RMSNorm folded into this GEMM: accumulator row r is multiplied by 1/sqrt(sum_t row_ss[t][r] / k + eps)
-    const float* row_ss;
-    int row_ss_tiles, row_ss_stride;
+    // RMSNorm folded into this GEMM: accumulator row r is multiplied by 1/sqrt(ss[r] / k + eps); ss[r] is a float, or
+    // (row_ss_fixed) an unsigned 64-bit fixed-point sum with 24 fraction bits as ss_out leaves it
+    const void* row_ss;
+    int row_ss_fixed;
     float rms_eps;
-    // per-row sums of squares of the stored bf16 outputs, one slot per (128 output columns, epilogue half)
-    float* ss_out;
-    int ss_out_stride;
+    // per-row sums of squares of the stored bf16 outputs: every (warp, 128-column group) adds its share to the row's
+    // 64-bit fixed-point sum with an integer atomic, so the total does not depend on the order of arrival
+    unsigned long long* ss_out;
+    // zero-filled by this kernel after its dependency wait (the sums the NEXT kernels will add to)
+    unsigned long long* clear;
+    unsigned clear_pieces;  // 8-byte words
     // RoPE epilogue of a decode step: the paged cache that receives K and V
     bf16 *kv_k_pool, *kv_v_pool;
     const int* kv_table;
@@ -295,6 +299,9 @@ __device__ __noinline__ void kv_append8(const TcParams& p, bf16* pool, int b, in
 
 // Epilogue of output columns [col, col + 8) of `row` (not SwiGLU); col is a multiple of 8.  Returns the sum of
 // squares of the stored values when the kernel collects them for the RMSNorm of the next GEMM (else 0).
+// EXTRA = the launch uses one of the rarer epilogue features (paged K/V append, scatter to row owners, sums of squares):
+// kernels without them are compiled without that code, which the hot prefill epilogue would otherwise pay for.
+template <bool EXTRA>
 __device__ __forceinline__ float emit8(const TcParams& p, int row, int col, float (&f)[8], bool residual_added = false) {
     if (col >= p.n) return 0.0F;
     if (p.epilogue == SFB_EPI_ROPE_SPLIT) {  // head_dim % 32 == 0: the 8 columns lie in one head
@@ -322,24 +329,30 @@ __device__ __forceinline__ float emit8(const TcParams& p, int row, int col, floa
             }
         }
         store8(dst, 0, ((static_cast<size_t>(b) * heads + head) * p.seq + t) * p.head_dim + d0, f, 8);
-        if (pool) kv_append8(p, pool, b, t, head, d0, f);
+        if constexpr (EXTRA) {
+            if (pool) kv_append8(p, pool, b, t, head, d0, f);
+        }
         return 0.0F;
     }
     const size_t index = static_cast<size_t>(row) * p.n + col;
     const int valid = p.n - col;
     if (p.epilogue == SFB_EPI_RESIDUAL && !residual_added) add_bf16x8(p.residual + index, f, valid);
-    if (p.scatter_rows > 0) {  // reduce-scatter: the piece goes to the owner of its row only (a peer store unless that is this rank)
-        const int owner = row / p.scatter_rows;
-        store8(p.scatter_out[owner], 0, static_cast<size_t>(row - owner * p.scatter_rows) * p.n + col, f, valid);
-        return 0.0F;
+    if constexpr (EXTRA) {
+        if (p.scatter_rows > 0) {  // reduce-scatter: the piece goes to the owner of its row only (a peer store unless that is this rank)
+            const int owner = row / p.scatter_rows;
+            store8(p.scatter_out[owner], 0, static_cast<size_t>(row - owner * p.scatter_rows) * p.n + col, f, valid);
+            return 0.0F;
+        }
     }
     store8(p.out, p.out_f32, index, f, valid);
     for (int i = 0; i < p.peer_count; ++i) store8(p.peer_out[i], 0, index, f, valid);  // peer stores over NVLink
-    return p.ss_out ? sumsq_bf16x8(f, valid) : 0.0F;
+    if constexpr (EXTRA) return p.ss_out ? sumsq_bf16x8(f, valid) : 0.0F;
+    return 0.0F;
 }
 
 // phase 2 for one warp: the staged values are output columns [col0, col0 + 32) of rows
 // [row0, row0 + 32); `plain` = they are final (SwiGLU) and only need storing into [m, width].
+template <bool EXTRA>
 __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stage, int lane, int row0, int row_end,
                                             int col0, bool plain, int width, float* row_sums) {
     // The residual rows come from DRAM: all four loads of this lane go out before the first is used
@@ -361,7 +374,7 @@ __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stag
         const int r = i * 8 + (lane >> 2), first = (lane & 3) * 8;
         const int row = row0 + r, col = col0 + first;
         const bool live = row < row_end && col < width;
-        if (!live && !row_sums) continue;
+        if (!live && (!EXTRA || !row_sums)) continue;
         float f[8];
         stage_read8(stage, r, first, f);
         if (prefetch) {
@@ -376,30 +389,33 @@ __device__ __forceinline__ void emit_staged(const TcParams& p, const float* stag
         if (plain) {
             store8(p.out, p.out_f32, static_cast<size_t>(row) * width + col, f, width - col);
         } else {
-            float v = live ? emit8(p, row, col, f, prefetch) : 0.0F;
-            if (row_sums) {  // the four lanes of a row add up; one of them keeps the row's running sum in shared memory
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                if ((lane & 3) == 0) row_sums[r] += v;
+            float v = live ? emit8<EXTRA>(p, row, col, f, prefetch) : 0.0F;
+            if constexpr (EXTRA) {
+                if (row_sums) {  // the four lanes of a row add up; one of them keeps the row's running sum in shared memory
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    if ((lane & 3) == 0) row_sums[r] += v;
+                }
             }
         }
     }
 }
 
+constexpr float kSumFixedScale = 16777216.0F;  // 2^24
+
 // Sums of squares collected by one warp over the chunks of one 128-column group: lane r holds row r's sum in
-// shared memory; the row's slot (group, epilogue half `pass`) is written and the sum cleared.
-__device__ __forceinline__ void flush_row_ss(const TcParams& p, float* row_sums, int lane, int row0, int row_end,
-                                             int col_group, int pass) {
+// shared memory; it is added to the row's fixed-point total and cleared.
+__device__ __forceinline__ void flush_row_ss(const TcParams& p, float* row_sums, int lane, int row0, int row_end) {
     __syncwarp();
     const float v = row_sums[lane];
     row_sums[lane] = 0.0F;
-    if (row0 + lane < row_end) p.ss_out[static_cast<size_t>(col_group * 2 + pass) * p.ss_out_stride + row0 + lane] = v;
+    if (row0 + lane < row_end) atomicAdd(p.ss_out + row0 + lane, __float2ull_rn(v * kSumFixedScale));
     __syncwarp();
 }
 
 // Epilogue of one work item for an epilogue thread: `acc` is the tensor-memory address of the
 // accumulator (lane quarter and buffer included), `tmem_empty_bar` the barrier that hands it back.
-template <int BN, bool SCALED>
+template <int BN, bool SCALED, bool EXTRA>
 __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segment& sg, const TileCoord& c, int k_blocks,
                                                  uint32_t acc, uint32_t tmem_empty_bar, float* stage,
                                                  volatile uint32_t* last_flag, int quarter, int pass, int lane,
@@ -472,7 +488,7 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
         if (out0 + pass * 32 < width) fetch(pass * 32, r0);
         fetch((pass + 2) * 32, r1);
     }
-    const bool collect = p.ss_out != nullptr && !swiglu;
+    const bool collect = EXTRA && p.ss_out != nullptr && !swiglu;
     float* row_sums = collect ? row_sums_area : nullptr;
 #pragma unroll 1
     for (int ch = pass; ch < chunks; ch += 2) {
@@ -502,7 +518,7 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
                 if (swiglu) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * __ldg(scale1 + i));
             }
         }
-        if (p.row_ss) {  // folded RMSNorm: the whole accumulator row carries the factor 1/rms(row of A)
+        if (EXTRA && p.row_ss) {  // folded RMSNorm: the whole accumulator row carries the factor 1/rms(row of A)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 r0[i] = __float_as_uint(__uint_as_float(r0[i]) * row_inv);
@@ -518,24 +534,24 @@ __device__ __forceinline__ void epilogue_segment(const TcParams& p, const Segmen
         }
         stage_write(stage, lane, r0);
         __syncwarp();
-        emit_staged(p, stage, lane, row0, c.row_end, col0, swiglu, width, row_sums);
+        emit_staged<EXTRA>(p, stage, lane, row0, c.row_end, col0, swiglu, width, row_sums);
         __syncwarp();
         // the chunks of this warp advance by 64 columns: the last one inside a 128-column group closes its slot
         if (collect && ((col0 + 64) / 128 != col0 / 128 || ch + 2 >= chunks || col0 + 64 >= width))
-            flush_row_ss(p, row_sums, lane, row0, c.row_end, col0 / 128, pass);
+            flush_row_ss(p, row_sums, lane, row0, c.row_end);
     }
 }
 
-// 1 / rms of row `row` of A from the partial sums of squares its producer left (see TcParams::row_ss).
+// 1 / rms of row `row` of A from the sum of squares its producer left (see TcParams::row_ss).
 __device__ __forceinline__ float folded_row_inv(const TcParams& p, int row, bool row_ok) {
     if (!p.row_ss || !row_ok) return 1.0F;
-    float ss = 0.0F;
-#pragma unroll 8
-    for (int t = 0; t < p.row_ss_tiles; ++t) ss += __ldcg(p.row_ss + static_cast<size_t>(t) * p.row_ss_stride + row);
+    const float ss = p.row_ss_fixed
+        ? static_cast<float>(__ldcg(static_cast<const unsigned long long*>(p.row_ss) + row)) * (1.0F / kSumFixedScale)
+        : __ldcg(static_cast<const float*>(p.row_ss) + row);
     return 1.0F / sqrtf(ss / static_cast<float>(p.k) + p.rms_eps);
 }
 
-template <int BN, bool STREAM>
+template <int BN, bool STREAM, bool EXTRA>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ TcParams p) {
@@ -764,13 +780,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         float* stage = staging + (warp - 2) * kStageFloatsPerWarp;
         staging[kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32 + lane] = 0.0F;  // this warp's row sums of squares
         __syncwarp();
+        if constexpr (EXTRA) {
+            // nothing that ran before this kernel still reads `clear`, nothing before the next kernel writes it
+            for (unsigned i = blockIdx.x * (32 * kEpilogueWarps) + (threadIdx.x - 64); i < p.clear_pieces;
+                 i += gridDim.x * (32 * kEpilogueWarps))
+                p.clear[i] = 0ull;
+        }
         uint32_t count = 0;
         Segment sg;
         for (; walk.next(sg); ++count) {
             const TileCoord c = tile_coord(p, sg.tile, m_tiles);
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
             // read while the tile's main loop is still running
-            const float row_inv = folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end);
+            const float row_inv = EXTRA ? folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end) : 1.0F;
             bool go = ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue);
             // With cut-up tiles the epilogue threads meet at barriers that have no time limit, so they must all
             // take the same decision here: one thread that saw the abort flag takes the whole group out.
@@ -778,7 +800,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             if (!go) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            epilogue_segment<BN, false>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter, pass,
+            epilogue_segment<BN, false, EXTRA>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter, pass,
                                  lane, leader, row_inv, staging + kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32);
         }
     }
@@ -1051,7 +1073,7 @@ gemm_w8_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             if (!go) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            epilogue_segment<BN, true>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter,
+            epilogue_segment<BN, true, true>(p, sg, c, k_blocks, acc, ptx::smem_u32(&tmem_empty[buf]), stage, last_flag, quarter,
                                        pass, lane, leader,
                                        folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end),
                                        staging + kEpilogueWarps * kStageFloatsPerWarp + (warp - 2) * 32);
@@ -1095,13 +1117,13 @@ bool stream_shape(const sfb_gemm_args& g) { return g.m <= BM && !g.group_offsets
 // folded RMSNorm, sums of squares of the output, decode-step RoPE position and paged K/V append
 void fill_fold_params(TcParams& p, const sfb_gemm_args& g) {
     p.row_ss = g.row_ss;
-    p.row_ss_tiles = g.row_ss_tiles;
-    p.row_ss_stride = g.row_ss_stride;
+    p.row_ss_fixed = g.row_ss_fixed;
     p.rms_eps = g.rms_epsilon;
+    p.clear = static_cast<unsigned long long*>(g.clear);
+    p.clear_pieces = static_cast<unsigned>(g.clear_bytes / 8);
     p.scatter_rows = g.scatter_rows;
     for (int i = 0; i < SFB_MAX_PEERS; ++i) p.scatter_out[i] = static_cast<bf16*>(g.scatter_out[i]);
-    p.ss_out = g.out_f32 || g.scatter_rows > 0 ? nullptr : g.ss_out;
-    p.ss_out_stride = g.ss_out_stride;
+    p.ss_out = g.out_f32 || g.scatter_rows > 0 ? nullptr : static_cast<unsigned long long*>(g.ss_out);
     p.kv_k_pool = static_cast<bf16*>(g.kv_k_pool);
     p.kv_v_pool = static_cast<bf16*>(g.kv_v_pool);
     p.kv_table = g.kv_table;
@@ -1111,12 +1133,12 @@ void fill_fold_params(TcParams& p, const sfb_gemm_args& g) {
     p.kv_num_blocks = g.kv_num_blocks;
 }
 
-template <int BN, bool STREAM>
+template <int BN, bool STREAM, bool EXTRA>
 sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
     using T = Tile<BN, STREAM>;
     static bool configured = false;
     if (!configured) {
-        SFB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STREAM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        SFB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STREAM, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       T::kSmemBytes));
         configured = true;
     }
@@ -1178,7 +1200,7 @@ sfb_status launch(const sfb_gemm_args& g, cudaStream_t stream) {
             grid = static_cast<int>(tiles >= sm_count() || units >= sm_count() ? sm_count() : units);
         }
     }
-    SFB_CUDA(launch_dependent(gemm_tcgen05_kernel<BN, STREAM>, dim3(grid), dim3(kThreads), T::kSmemBytes, stream, map_a,
+    SFB_CUDA(launch_dependent(gemm_tcgen05_kernel<BN, STREAM, EXTRA>, dim3(grid), dim3(kThreads), T::kSmemBytes, stream, map_a,
                               map_b, p));
     return check_launch("gemm_tcgen05");
 }
@@ -1262,10 +1284,11 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
         for (int i = 0; i < ceil_div(g.m, g.scatter_rows); ++i)
             if (!g.scatter_out[i]) return false;
     }
-    if (g.row_ss && (g.group_offsets || g.row_ss_tiles <= 0 || g.row_ss_stride < g.m)) return false;
-    if (g.ss_out && (g.group_offsets || g.ss_out_stride < g.m ||
+    if (g.row_ss && g.group_offsets) return false;
+    if (g.ss_out && (g.group_offsets || (reinterpret_cast<uintptr_t>(g.ss_out) & 7) ||
                      (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL)))
         return false;
+    if (g.clear && ((reinterpret_cast<uintptr_t>(g.clear) & 7) || g.clear_bytes % 8 != 0)) return false;
     if (g.kv_k_pool && (g.epilogue != SFB_EPI_ROPE_SPLIT || !g.kv_v_pool || !g.kv_table || g.kv_block_tokens <= 0 ||
                         g.kv_max_blocks <= 0 || g.kv_position < 0))
         return false;
@@ -1274,14 +1297,13 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
 
 sfb_status gemm_bf16_tcgen05(const sfb_gemm_args& g, cudaStream_t stream) {
     if (g.bt_scales) return launch_w8(g, stream);
-    if (pick_bn(g) == 256) return launch<256, false>(g, stream);
-    if (stream_shape(g)) return launch<128, true>(g, stream);
-    return launch<128, false>(g, stream);
+    const bool extra = g.row_ss || g.ss_out || g.scatter_rows > 0 || g.kv_k_pool || g.clear;
+    if (pick_bn(g) == 256) return extra ? launch<256, false, true>(g, stream) : launch<256, false, false>(g, stream);
+    if (stream_shape(g)) return extra ? launch<128, true, true>(g, stream) : launch<128, true, false>(g, stream);
+    return extra ? launch<128, false, true>(g, stream) : launch<128, false, false>(g, stream);
 }
 
 }  // namespace sfb
-
-extern "C" int sfb_gemm_ss_tiles(int n) { return n > 0 ? 2 * sfb::ceil_div(n, 128) : 0; }
 
 extern "C" size_t sfb_gemm_stream_workspace_bytes(int n) {
     if (n <= 0) return 0;

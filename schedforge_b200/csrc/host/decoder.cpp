@@ -112,10 +112,9 @@ struct DecoderExecutablePlan::Impl {
     float rms_eps = 1.0e-5F;
     // where the sums of squares of the current pass live (workspace, or the gathered copies of a two-shot plan)
     const float* cur_ss1 = nullptr;
-    const float* cur_ss2 = nullptr;
-    int cur_ss2_tiles = 1;
+    const void* cur_ss2 = nullptr;
+    bool cur_ss2_fixed = false;     // 64-bit fixed-point sums left by the O projection's epilogue (single shard)
     int scatter_set = -1;           // >= 0: the GEMM being set up scatters its rows to their owners (two-shot form)
-    int ss2_tiles = 1;              // partial sums of squares per row of attention_residual that feed the second fold
     bool kv_in_epilogue = false;    // the QKV epilogue writes the new token's K/V into the paged cache itself
     // Paged cache accounting of a decode plan, kept like the reference's PagedKVCache (one page table and one
     // length for the whole batch, pages taken from the back of the free list; src/next_milestones.cpp:486-550).
@@ -387,7 +386,6 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         m.fold1 = eligible && on_tensor_cores(SFB_EPI_ROPE_SPLIT, m.qkv_l, H, 0);
         m.fold2 = eligible && !moe && on_tensor_cores(SFB_EPI_SWIGLU, 2 * I, H, m.swiglu_block) &&
                   on_tensor_cores(SFB_EPI_RESIDUAL, H, m.hidden_l, 0);
-        m.ss2_tiles = G == 1 ? sfb_gemm_ss_tiles(H) : 1;  // a sharded plan sums the squares after its all-reduce
         m.kv_in_epilogue = m.append_new && bf && fused && opt.gemm_backend != SFB_GEMM_SIMT && D % 2 == 0 &&
                            on_tensor_cores(SFB_EPI_ROPE_SPLIT, m.qkv_l, H, 0);
     }
@@ -717,7 +715,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     // sums of squares per row for the folded norms; they live for the whole pass (the first one as long as the
     // resident input, the second one keeps the zeros that a ragged column group never overwrites)
     if (m.fold1) wp.add("ss1", static_cast<std::size_t>(T) * 4, 0, 13);
-    if (m.fold2) wp.add("ss2", static_cast<std::size_t>(T) * 4 * m.ss2_tiles, 0, 13);
+    if (m.fold2) wp.add("ss2", static_cast<std::size_t>(T) * 8, 0, 13);  // 64-bit fixed point (one shard) or float (sharded)
     if (!fused) wp.add("fused_qkv", static_cast<std::size_t>(T) * m.qkv_l * e, 2, 3);
     wp.add("query", static_cast<std::size_t>(T) * m.hidden_l * e, 2, 4);
     // chunks that are part of a sequence attend to the keys and values of the chunks before them
@@ -896,7 +894,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     // appending decode plan, the new token's K/V written into the paged cache by the same epilogue
     const Tweak qkv_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int rows) {
         if (im.fold1) {
-            g.row_ss = im.cur_ss1; g.row_ss_tiles = 1; g.row_ss_stride = rows; g.rms_epsilon = im.rms_eps;
+            g.row_ss = im.cur_ss1; g.rms_epsilon = im.rms_eps;
+        }
+        if (im.fold2 && im.size == 1) {  // the sums the O projection of this pass will add to start at zero
+            g.clear = im.ws("ss2"); g.clear_bytes = static_cast<std::size_t>(rows) * 8;
         }
         if (im.kv_in_epilogue) {
             g.kv_k_pool = im.k_pool; g.kv_v_pool = im.v_pool; g.kv_table = im.block_table;
@@ -966,13 +967,13 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     // second fold: a single shard collects the sums of squares of attention_residual in the O epilogue; a
     // sharded plan sums the squares of the reduced rows after its all-reduce
     const Tweak o_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int rows) {
-        if (im.fold2 && im.size == 1) { g.ss_out = im.ws<float>("ss2"); g.ss_out_stride = rows; }
+        if (im.fold2 && im.size == 1) g.ss_out = im.ws("ss2");
     };
-    m.cur_ss2 = m.fold2 ? (two ? m.gathered_ss(1) : m.ws<float>("ss2")) : nullptr;
-    m.cur_ss2_tiles = two ? 1 : m.ss2_tiles;
+    m.cur_ss2 = m.fold2 ? (two ? static_cast<const void*>(m.gathered_ss(1)) : m.ws("ss2")) : nullptr;
+    m.cur_ss2_fixed = m.size == 1;
     const Tweak gate_up_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int rows) {
         if (im.fold2) {
-            g.row_ss = im.cur_ss2; g.row_ss_tiles = im.cur_ss2_tiles; g.row_ss_stride = rows; g.rms_epsilon = im.rms_eps;
+            g.row_ss = im.cur_ss2; g.row_ss_fixed = im.cur_ss2_fixed ? 1 : 0; g.rms_epsilon = im.rms_eps;
         }
     };
     if (fused) {
@@ -1287,11 +1288,16 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             g.rope_row_offset = g0;
         }
         if (fold_role == 1 && m.fold1) {
-            g.row_ss = m.ws<float>("ss1") + g0; g.row_ss_tiles = 1; g.row_ss_stride = m.T; g.rms_epsilon = c.rms_epsilon;
+            g.row_ss = m.ws<float>("ss1") + g0; g.rms_epsilon = c.rms_epsilon;
         } else if (fold_role == 2 && m.fold2 && m.size == 1) {
-            g.ss_out = m.ws<float>("ss2") + g0; g.ss_out_stride = m.T;
-        } else if (fold_role == 3 && m.fold2) {
-            g.row_ss = m.ws<float>("ss2") + g0; g.row_ss_tiles = m.ss2_tiles; g.row_ss_stride = m.T; g.rms_epsilon = c.rms_epsilon;
+            g.ss_out = m.ws<unsigned long long>("ss2") + g0;
+        } else if (fold_role == 3 && m.fold2) {  // 64-bit fixed-point sums from the O epilogue, or floats summed after the all-reduce
+            g.row_ss = m.size == 1 ? static_cast<const void*>(m.ws<unsigned long long>("ss2") + g0)
+                                   : static_cast<const void*>(m.ws<float>("ss2") + g0);
+            g.row_ss_fixed = m.size == 1 ? 1 : 0; g.rms_epsilon = c.rms_epsilon;
+        }
+        if (fold_role == 1 && m.fold2 && m.size == 1) {  // this chunk's sums start at zero
+            g.clear = m.ws<unsigned long long>("ss2") + g0; g.clear_bytes = static_cast<std::size_t>(rows) * 8;
         }
         g.bt_tiled = m.blocked(w) ? 1 : 0;
         if (const auto* quantized = m.int8(w)) {

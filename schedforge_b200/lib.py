@@ -30,8 +30,8 @@ class GemmArgs(C.Structure):
                 ("split_workspace", vp), ("split_workspace_bytes", C.c_size_t), ("bt_tiled", C.c_int),
                 ("peer_out", vp * 7), ("peer_count", C.c_int), ("scatter_out", vp * 8), ("scatter_rows", C.c_int),
                 ("rope_row_offset", C.c_int), ("bt_scales", vp),
-                ("row_ss", vp), ("row_ss_tiles", C.c_int), ("row_ss_stride", C.c_int), ("rms_epsilon", C.c_float),
-                ("ss_out", vp), ("ss_out_stride", C.c_int),
+                ("row_ss", vp), ("row_ss_fixed", C.c_int), ("rms_epsilon", C.c_float),
+                ("ss_out", vp), ("clear", vp), ("clear_bytes", C.c_size_t),
                 ("kv_k_pool", vp), ("kv_v_pool", vp), ("kv_table", vp),
                 ("kv_position", C.c_int), ("kv_block_tokens", C.c_int), ("kv_max_blocks", C.c_int),
                 ("kv_num_blocks", C.c_int)]
@@ -148,7 +148,7 @@ ALLREDUCE_FN = C.CFUNCTYPE(None, vp, vp, C.c_int64, C.c_int, vp)
 # Every symbol include/schedforge_b200.h declares (checked by tests/test_abi.py).
 EXPORTS = (
     "sfb_last_error sfb_version sfb_launch_count sfb_device_status "
-    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 sfb_tiled_weight_elems sfb_k_tile_weight_bf16 sfb_k_quantize_weight_int8 sfb_k_dequantize_weight_int8 sfb_gemm_stream_workspace_bytes sfb_gemm_ss_tiles sfb_k_convert_rows_sumsq sfb_k_row_sumsq "
+    "sfb_k_rms_norm sfb_k_add sfb_k_swiglu sfb_k_convert sfb_k_gemm_f32 sfb_k_gemm_bf16 sfb_tiled_weight_elems sfb_k_tile_weight_bf16 sfb_k_quantize_weight_int8 sfb_k_dequantize_weight_int8 sfb_gemm_stream_workspace_bytes sfb_k_convert_rows_sumsq sfb_k_row_sumsq "
     "sfb_rope_table sfb_k_rope_split sfb_k_attention_prefill "
     "sfb_attention_decode_workspace sfb_attention_decode_default_splits sfb_k_attention_decode_paged "
     "sfb_k_paged_kv_append sfb_k_paged_kv_gather "
