@@ -358,7 +358,8 @@ class Layer:
         c = api.decoder_config(**cfg)
         self.plan = api.DecoderCompiler.compile(c, data, "", api.compile_options(
             tp_rank=rank, tp_size=world, seed_block_table=1 if workload == "decode" else 0,
-            weight_int8=args.weights == "int8", local_expert_weights=workload == "moe"))
+            weight_int8=args.weights == "int8", local_expert_weights=workload == "moe",
+            norm_fusion=args.norm_fusion))
         self.stream = torch.cuda.ExternalStream(self.plan.stream)
         self.collective = "none"
         views = {}
@@ -613,6 +614,8 @@ def main():
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="headline only: skip the decode / moe / kernel sub-records")
+    ap.add_argument("--norm-fusion", action="store_true",
+                    help="fold the RMSNorms into the QKV and gate/up GEMMs instead of stand-alone norm kernels (for A/B runs)")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "int8"],
                     help="int8: per-output-channel weight-only INT8 (the reference's quantized layer); not the default")
     ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer", "two-shot"],

@@ -382,7 +382,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             return gemm_bf16_tcgen05_supported(g);
         };
         const bool eligible = bf && fused && opt.gemm_backend != SFB_GEMM_SIMT && opt.weight_int8 == 0 &&
-                              opt.no_norm_fusion == 0 && D % 2 == 0;
+                              opt.norm_fusion != 0 && D % 2 == 0;
         m.fold1 = eligible && on_tensor_cores(SFB_EPI_ROPE_SPLIT, m.qkv_l, H, 0);
         m.fold2 = eligible && !moe && on_tensor_cores(SFB_EPI_SWIGLU, 2 * I, H, m.swiglu_block) &&
                   on_tensor_cores(SFB_EPI_RESIDUAL, H, m.hidden_l, 0);

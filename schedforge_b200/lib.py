@@ -82,7 +82,7 @@ class CompileOptions(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dtype", "token_major_attention", "fuse_epilogues",
                                        "gemm_backend", "attention_backend", "page_tokens", "tp_rank",
                                        "tp_size", "seed_block_table", "no_workspace_reuse", "no_pipeline",
-                                       "append_new_token", "weight_int8", "kv_capacity", "no_norm_fusion",
+                                       "append_new_token", "weight_int8", "kv_capacity", "norm_fusion",
                                        "local_expert_weights")]
 
 

@@ -62,14 +62,17 @@ def test_llama_layer_prefill_pipelined_row_chunks(llama_prefill_b2_s1024, llama_
     plan.close()
 
 
-def test_llama_layer_prefill_one_shot(port, llama_weights):
-    """One sequence of 384 tokens through the unchunked path (the sample the CPU baseline of bench.py times)."""
+@pytest.mark.parametrize("norm_fusion", [False, True])
+def test_llama_layer_prefill_one_shot(port, llama_weights, norm_fusion):
+    """One sequence of 384 tokens through the unchunked path (the sample the CPU baseline of bench.py times), with
+    stand-alone RMSNorm kernels and with both norms folded into the QKV and gate/up GEMMs."""
     kw = dict(LLAMA, batch=1, sequence=384)
     data = dict(llama_weights, input=_normal((384, 4096), 1.0, 2))
     want = port.decoder_layer(ob.decoder_config(**kw), data, native=True)
-    plan = api.DecoderCompiler.compile(api.decoder_config(**kw), llama_weights)
+    plan = api.DecoderCompiler.compile(api.decoder_config(**kw), llama_weights, "", api.compile_options(norm_fusion=norm_fusion))
     out, _ = plan.execute(data["input"])
     assert rel_err(out, want) < BF16_TOL
+    assert ("prologue=rms_norm_folded" in plan.dump()) == norm_fusion
     plan.close()
 
 
@@ -104,7 +107,8 @@ def test_llama_layer_autoregressive_step_equals_last_prefill_token(port, llama_p
     step["cached_key"] = port.round_bf16(np.ascontiguousarray(keys[:, :, :ctx, :]))
     step["cached_value"] = port.round_bf16(np.ascontiguousarray(values[:, :, :ctx, :]))
     c = api.decoder_config(**dict(kw, sequence=1, context_sequence=ctx))
-    plan = api.DecoderCompiler.compile(c, step, "", api.compile_options(append_new_token=True, seed_block_table=5))
+    plan = api.DecoderCompiler.compile(c, step, "", api.compile_options(append_new_token=True, seed_block_table=5,
+                                                                        norm_fusion=True))
     last = np.ascontiguousarray(x.reshape(2, ctx + 1, hidden)[:, ctx, :])
     out, _ = plan.execute(last)
     want = want_all.reshape(2, ctx + 1, hidden)[:, ctx, :]

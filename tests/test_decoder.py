@@ -430,9 +430,11 @@ def test_decode_loop_steps_across_a_page_boundary(port, dtype, head_dim):
     capacity = 40                                    # three pages
     c = api.decoder_config(**dict(kw, sequence=1, context_sequence=ctx))
     plan = api.DecoderCompiler.compile(c, start, "", api.compile_options(dtype=dtype, append_new_token=True,
-                                                                         seed_block_table=9, kv_capacity=capacity))
+                                                                         seed_block_table=9, kv_capacity=capacity,
+                                                                         norm_fusion=head_dim == 128))
     if dtype == L.BF16:
-        assert "kv_append=paged_cache" in plan.dump() and "prologue=rms_norm_folded" in plan.dump()
+        assert "kv_append=paged_cache" in plan.dump()
+        assert ("prologue=rms_norm_folded" in plan.dump()) == (head_dim == 128)
     mirror = port.paged_create(batch, hkv, head_dim, head_dim, 16, capacity)   # the reference's accounting
     mirror.append(start["cached_key"], start["cached_value"], ctx)
     tokens = data["input"].reshape(batch, total, hidden)
@@ -478,3 +480,31 @@ def test_decode_loop_steps_across_a_page_boundary(port, dtype, head_dim):
     with pytest.raises(L.InvalidArgument, match="append_new_token"):
         legacy.step(np.ascontiguousarray(tokens[:, ctx, :]))
     legacy.close()
+
+
+@pytest.mark.parametrize("kw", [
+    dict(batch=2, sequence=192, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64, rope_theta=500000.0),
+    dict(batch=1, sequence=300, hidden=1024, intermediate=2752, query_heads=8, kv_heads=8, head_dim=128),
+    dict(batch=5, sequence=1, hidden=1024, intermediate=512, query_heads=8, kv_heads=2, head_dim=128, context_sequence=300),
+])
+def test_rms_norm_folded_into_the_gemms(port, kw):
+    """norm_fusion: both RMSNorms disappear as kernels; the norm weights are multiplied into the packed QKV and
+    gate/up weights, the QKV / gate-up epilogues scale their accumulator rows by 1/rms (sums of squares from the
+    input conversion and from the O projection's epilogue).  Same oracle, same bar; fewer launches."""
+    oc, c, data = bf16_case(port, 81, **kw)
+    want = port.decoder_layer(oc, data, native=True)
+    plain = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(no_pipeline=True))
+    folded = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(no_pipeline=True, norm_fusion=True))
+    out_plain, r_plain = plain.execute(data["input"])
+    out, r = folded.execute(data["input"])
+    assert rel_err(out, want) < BF16_TOL and rel_err(out_plain, want) < BF16_TOL
+    assert r.kernel_launches == r_plain.kernel_launches - 2
+    dump = folded.dump()
+    assert dump.count("prologue=rms_norm_folded") == 2 and "_rms_folded" in dump
+    assert "rms_norm_folded" not in plain.dump()
+    if kw["batch"] == 2:   # the row-chunk pipeline takes the sums of squares per chunk
+        piped = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(norm_fusion=True))
+        assert rel_err(piped.execute(data["input"])[0], want) < BF16_TOL
+        piped.close()
+    plain.close()
+    folded.close()
