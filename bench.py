@@ -359,7 +359,7 @@ class Layer:
         self.plan = api.DecoderCompiler.compile(c, data, "", api.compile_options(
             tp_rank=rank, tp_size=world, seed_block_table=1 if workload == "decode" else 0,
             weight_int8=args.weights == "int8", local_expert_weights=workload == "moe",
-            norm_fusion=args.norm_fusion))
+            norm_fusion=True if args.norm_fusion else None))
         self.stream = torch.cuda.ExternalStream(self.plan.stream)
         self.collective = "none"
         views = {}

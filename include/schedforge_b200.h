@@ -433,10 +433,12 @@ typedef struct sfb_compile_options {
                              bf16-rounded weights. */
     int kv_capacity;      /* decode plans with append_new_token: tokens the paged cache can hold (0 -> context_sequence
                              + 1); sfb_decoder_step appends one token per call until the cache is full */
-    int norm_fusion;      /* != 0: bf16 plans with fused epilogues fold both RMSNorms into the GEMM that follows (norm
+    int norm_fusion;      /* > 0: bf16 plans with fused epilogues fold both RMSNorms into the GEMM that follows (norm
                              weight multiplied into the packed weight, 1/rms applied to the accumulator rows, sums of
-                             squares taken where the rows are produced); 0: stand-alone RMSNorm kernels, which
-                             measured faster on B200 for both the prefill and the decode shape */
+                             squares taken where the rows are produced); < 0: stand-alone RMSNorm kernels; 0: folded
+                             for sharded plans (tp_size > 1), where the stand-alone norms are replicated work that
+                             does not shrink with the rank count, stand-alone for a single shard, where they measured
+                             faster on B200 */
     int local_expert_weights; /* MoE plans with tp_size > 1: != 0 says that w1 / w3 / w2 of sfb_decoder_data hold
                              only this rank's experts/tp_size experts (expert tp_rank * experts/tp_size first), so
                              that a rank never has to materialise the other ranks' expert weights on its host;
@@ -621,9 +623,9 @@ sfb_status sfb_k_peer_allreduce_finish(const sfb_peer_allreduce_args* args, sfb_
 
 /* Two-shot form of the same all-reduce for large outputs on several ranks (no counterpart in the reference):
  * rank r owns rows [r * rows_own, (r + 1) * rows_own) of a [size * rows_own, width] bf16 tensor.
- *   1. reduce-scatter under the GEMM: with sfb_gemm_args.scatter_rows = rows_own the O / Down projection stores
- *      each output piece only to scatter_out[owner of the row] (this rank's slot in the owner's receive buffer,
- *      row-local layout [rows_own, width]), so a rank sends (size - 1) / size of the tensor;
+ *   1. reduce-scatter: either under the GEMM (with sfb_gemm_args.scatter_rows = rows_own the O / Down projection stores
+ *      each output piece only to scatter_out[owner of the row], this rank's slot in the owner's receive buffer, row-local
+ *      layout [rows_own, width]) or by the owners themselves (pull, below); a rank moves (size - 1) / size of the tensor;
  *   2. this kernel on the owner: waits (bounded) until every peer has delivered, adds the `slots` partial rows in
  *      rank order in fp32 (+ the owner's rows of `residual`), rounds to bf16, writes the finished rows into
  *      gathered[rank] (its own full tensor) and, when gather != 0, into gathered[s] of every peer with plain peer
@@ -638,6 +640,11 @@ typedef struct sfb_peer_gather_args {
     const void* recv;
     int64_t slot_elems;
     int slots;
+    /* pull[0] != NULL: the partial rows of rank s are READ from pull[s] ([rows_own, width], this owner's row range inside
+     * rank s's partial tensor, mapped into this process; pull[rank] is local) instead of from recv.  The producing GEMM
+     * then stores its whole partial tensor locally with its ordinary epilogue and the owners fetch their rows with wide
+     * peer loads: small peer stores from a GEMM epilogue use NVLink poorly. */
+    const void* pull[SFB_MAX_PEERS];
     const void* source;
     const float* source_ss;
     const void* residual;

@@ -1258,9 +1258,15 @@ sfb_status launch_w8(const sfb_gemm_args& g, cudaStream_t stream) {
 int pick_bn(const sfb_gemm_args& g) {
     if (g.epilogue == SFB_EPI_SWIGLU) return 2 * g.swiglu_block;
     if (g.bt_tiled || stream_shape(g)) return 128;
-    // A narrow output or few tiles: more, smaller tiles keep more SMs busy.
-    const long long wide_tiles = static_cast<long long>(ceil_div(g.m, BM)) * ceil_div(g.n, 256);
-    return (g.n < 256 || wide_tiles < sm_count()) ? 128 : 256;
+    if (g.n < 256) return 128;
+    // Wave quantisation: the tiles run in rounds of one per SM, so the time is about rounds x tile cost.  A 128-column
+    // tile costs a little more than half a 256-column one (the A tile is re-read for half the work), but a narrow or
+    // short output can need fewer, better filled rounds with it (a sharded QKV projection: 192 wide tiles = 2 rounds,
+    // 384 narrow ones = 3 rounds of half the length).
+    const long long m_tiles = ceil_div(g.m, BM);
+    const long long rounds_wide = ceil_div64(m_tiles * ceil_div(g.n, 256), sm_count());
+    const long long rounds_narrow = ceil_div64(m_tiles * ceil_div(g.n, 128), sm_count());
+    return rounds_narrow * 115 < rounds_wide * 200 ? 128 : 256;
 }
 
 }  // namespace

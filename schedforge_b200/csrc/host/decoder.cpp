@@ -114,7 +114,6 @@ struct DecoderExecutablePlan::Impl {
     const float* cur_ss1 = nullptr;
     const void* cur_ss2 = nullptr;
     bool cur_ss2_fixed = false;     // 64-bit fixed-point sums left by the O projection's epilogue (single shard)
-    int scatter_set = -1;           // >= 0: the GEMM being set up scatters its rows to their owners (two-shot form)
     bool kv_in_epilogue = false;    // the QKV epilogue writes the new token's K/V into the paged cache itself
     // Paged cache accounting of a decode plan, kept like the reference's PagedKVCache (one page table and one
     // length for the whole batch, pages taken from the back of the free list; src/next_milestones.cpp:486-550).
@@ -153,6 +152,16 @@ struct DecoderExecutablePlan::Impl {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
+    void* output_bf16 = nullptr;    // where the last pass left the bf16 output
+    bool output_f32_valid = true;   // false: "output_f32" has to be converted from output_bf16 before the host reads it
+    // fp32 copy of output rows [first, first + rows) for a host read (no-op when the pass already produced it)
+    void materialize_output(int first, int rows, cudaStream_t s) {
+        if (output_f32_valid || !output_bf16) return;
+        const std::size_t at = static_cast<std::size_t>(first) * H;
+        throw_on(sfb_k_convert(static_cast<char*>(output_bf16) + at * 2, SFB_BF16, ws<float>("output_f32") + at, SFB_F32,
+                               static_cast<int64_t>(rows) * H, s));
+        if (first == 0 && rows == T) output_f32_valid = true;
+    }
     // Device status word (bounded waits that gave up) of the plan's device and a pinned host copy that every
     // host-synchronising call refreshes in stream order, so a timed-out wait surfaces as SFB_DEVICE_TIMEOUT.
     uint32_t* status_device = nullptr;
@@ -194,39 +203,36 @@ struct DecoderExecutablePlan::Impl {
                     peer_remote[r] + (static_cast<std::size_t>(set) * size + rank) * peer_slot_bytes() + offset * 2;
     }
     // ---- two-shot form (reduce-scatter under the GEMM, sum + all-gather by the row owners), see peer_allreduce.cu.
-    // Behind the one-shot slots and their flags the peer buffer holds: two-shot flags and counters, the receive
-    // slots [2 sets][size][T / size rows], three gathered tensors (layer input, attention_residual, output) that
-    // every rank's finish kernel fills on every rank, and the gathered sums of squares of the first two.
+    // Behind the one-shot slots and their flags the peer buffer holds: two-shot flags and counters, this rank's
+    // partial tensors [2 sets][T rows] (written by its own O / Down GEMM with the ordinary epilogue; every owner
+    // fetches its rows from them with wide peer loads, which use NVLink far better than 64-byte stores out of a
+    // GEMM epilogue), three gathered tensors (layer input, attention_residual, output) that every rank's finish
+    // kernel fills on every rank, and the gathered sums of squares of the first two.
     int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot
     bool input_in_peer = false;    // the resident input is the gathered copy (sfb_decoder_execute_rows on a two-shot plan)
     uint32_t gather_epoch[3] = {0, 0, 0};
     std::size_t th_bytes() const { return (static_cast<std::size_t>(T) * H * 2 + 1023) / 1024 * 1024; }
-    std::size_t slot2_bytes() const { return (static_cast<std::size_t>(T / size) * H * 2 + 255) / 256 * 256; }
     std::size_t flags2_offset() const { return peer_flags_offset() + 256; }
     std::size_t counters_offset() const { return peer_flags_offset() + 1024; }
     std::size_t recv2_offset() const { return peer_flags_offset() + 2048; }
-    std::size_t gathered_offset(int which) const { return recv2_offset() + 2 * size * slot2_bytes() + which * th_bytes(); }
+    std::size_t partial_offset(int set) const { return recv2_offset() + set * th_bytes(); }
+    std::size_t gathered_offset(int which) const { return recv2_offset() + 2 * th_bytes() + which * th_bytes(); }
     std::size_t ss_offset(int which) const { return gathered_offset(3) + which * ((static_cast<std::size_t>(T) * 4 + 255) / 256 * 256); }
     std::size_t peer_total_bytes() const { return ss_offset(2) + 256; }
     char* peer_base(int r) const { return r == rank ? peer_local : peer_remote[r]; }
     template <class P = void> P* gathered(int which) const { return reinterpret_cast<P*>(peer_local + gathered_offset(which)); }
     float* gathered_ss(int which) const { return reinterpret_cast<float*>(peer_local + ss_offset(which)); }
     bool two_shot() const { return size > 1 && peer_local != nullptr && peer_mode == 2; }
-    // this rank's slot of slot set `set` in the receive buffer of every row owner
-    void fill_scatter_out(sfb_gemm_args& g, int set) const {
-        g.scatter_rows = T / size;
-        for (int r = 0; r < size; ++r)
-            g.scatter_out[r] = peer_base(r) + recv2_offset() + (static_cast<std::size_t>(set) * size + rank) * slot2_bytes();
-    }
+    void* partial(int set) const { return peer_local + partial_offset(set); }
     // Owner side of collective `coll` (0 = all-gather of the input rows, 1 = after O, 2 = after Down): sums the slots of
     // set coll - 1 (+ residual rows), writes gathered tensor `coll` and optionally its sums of squares on every rank.
     sfb_status reduce_gather(int coll, const void* source, const float* source_ss, const void* residual, bool with_ss, cudaStream_t s) {
         sfb_peer_gather_args a{};
         const int rows_own = T / size;
-        if (coll > 0) {
-            a.recv = peer_local + recv2_offset() + static_cast<std::size_t>(coll - 1) * size * slot2_bytes();
-            a.slot_elems = static_cast<int64_t>(slot2_bytes() / 2);
+        if (coll > 0) {  // this owner's rows inside every rank's partial tensor of set coll - 1
             a.slots = size;
+            for (int r = 0; r < size; ++r)
+                a.pull[r] = peer_base(r) + partial_offset(coll - 1) + static_cast<std::size_t>(rank) * rows_own * H * 2;
         }
         a.source = source; a.source_ss = source_ss; a.residual = residual;
         for (int r = 0; r < size; ++r) {
@@ -382,7 +388,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
             return gemm_bf16_tcgen05_supported(g);
         };
         const bool eligible = bf && fused && opt.gemm_backend != SFB_GEMM_SIMT && opt.weight_int8 == 0 &&
-                              opt.norm_fusion != 0 && D % 2 == 0;
+                              D % 2 == 0 && (opt.norm_fusion > 0 || (opt.norm_fusion == 0 && G > 1));
         m.fold1 = eligible && on_tensor_cores(SFB_EPI_ROPE_SPLIT, m.qkv_l, H, 0);
         m.fold2 = eligible && !moe && on_tensor_cores(SFB_EPI_SWIGLU, 2 * I, H, m.swiglu_block) &&
                   on_tensor_cores(SFB_EPI_RESIDUAL, H, m.hidden_l, 0);
@@ -834,6 +840,7 @@ void DecoderExecutablePlan::download_output(float* output) {
     if (!output) throw std::invalid_argument("decoder output is null");
     auto& m = *impl_;
     const float* src = m.dtype == SFB_BF16 ? m.ws<float>("output_f32") : m.ws<float>("output");
+    m.materialize_output(0, m.T, stream_);
     m.queue_status_read(stream_);
     cuda_check(cudaMemcpyAsync(output, src, static_cast<std::size_t>(m.T) * m.H * 4, cudaMemcpyDeviceToHost, stream_),
                "output download");
@@ -962,7 +969,6 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     mark();  // 4: attention
     void* r1 = two ? m.gathered(1) : m.ws("attention_residual");
     const bool add_residual_here = m.rank == 0;  // under sharding the residual enters the sum once
-    const Tweak scatter_tweak = [](sfb_gemm_args& g, DecoderExecutablePlan::Impl& im, int) { im.fill_scatter_out(g, im.scatter_set); };
     const std::size_t own_rows_offset = two ? static_cast<std::size_t>(m.rank) * (T / m.size) * H * 2 : 0;
     // second fold: a single shard collects the sums of squares of attention_residual in the O epilogue; a
     // sharded plan sums the squares of the reduced rows after its all-reduce
@@ -978,10 +984,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     };
     if (fused) {
         if (two) {
-            // every rank's partial rows go to their owners under the GEMM; the owner adds them up with its rows of the
-            // residual stream, takes the sums of squares and hands the finished rows to everybody
-            m.scatter_set = 0;
-            gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, SFB_EPI_STORE, nullptr, 0, nullptr, 0, false, -1, scatter_tweak);
+            // the partial tensor stays in this rank's peer-visible memory; every owner fetches its rows from all ranks,
+            // adds them up with its rows of the residual stream, takes the sums of squares and hands the finished
+            // rows to everybody
+            gemm(m.ws("attention"), m.wo, m.partial(0), T, H, m.hidden_l, SFB_EPI_STORE);
             throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s));
         } else if (peer) {
             gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
@@ -1015,8 +1021,7 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             if (m.direct_f32_output) {
                 gemm(m.ws("activation"), m.wd, m.ws("output_f32"), T, H, I, SFB_EPI_RESIDUAL, r1, 0, nullptr, 0, true);
             } else if (two) {
-                m.scatter_set = 1;
-                gemm(m.ws("activation"), m.wd, out, T, H, I, SFB_EPI_STORE, nullptr, 0, nullptr, 0, false, -1, scatter_tweak);
+                gemm(m.ws("activation"), m.wd, m.partial(1), T, H, I, SFB_EPI_STORE);
                 throw_on(m.reduce_gather(2, nullptr, nullptr, static_cast<const char*>(r1) + own_rows_offset, false, s));
             } else if (peer) {
                 gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0,
@@ -1088,7 +1093,12 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         allreduce(out, static_cast<int64_t>(T) * H);
         mark(); mark();  // 8: ffn, 9
     }
-    if (bf && !m.direct_f32_output)
+    // The layer's product on the device is the bf16 output (what a next layer would read).  A single shard also
+    // leaves the fp32 copy the host calls hand out; a sharded plan converts only the rows a host call asks for,
+    // instead of every rank converting the whole replicated tensor on every pass.
+    m.output_bf16 = out;
+    m.output_f32_valid = !bf || m.direct_f32_output || m.size == 1;
+    if (bf && !m.direct_f32_output && m.size == 1)
         throw_on(sfb_k_convert(out, SFB_BF16, m.ws("output_f32"), SFB_F32, static_cast<int64_t>(T) * H, s));
     mark();  // 10
 }
@@ -1234,6 +1244,7 @@ void DecoderExecutablePlan::execute_rows(const float* input_rows, float* output_
     run(s, RoutingTraceView{}, true);
     cuda_check(cudaEventRecord(d0, s), "event");
     const float* src = m.dtype == SFB_BF16 ? m.ws<float>("output_f32") : m.ws<float>("output");
+    m.materialize_output(row_begin, row_count, s);
     m.queue_status_read(s);
     cuda_check(cudaMemcpyAsync(output_rows, src + first, count * 4, cudaMemcpyDeviceToHost, s), "output download");
     cuda_check(cudaEventRecord(d1, s), "event");
@@ -1408,6 +1419,18 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
 int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_out, int64_t capacity) {
     auto& m = *impl_;
     if (name == "output" && m.direct_f32_output) return read_tensor("output_f32", host_out, capacity);
+    if (name == "output_f32") m.materialize_output(0, m.T, stream_);
+    if (m.two_shot() && host_out && (name == "output" || name == "attention_residual")) {
+        // a two-shot plan keeps these two in its peer-visible buffer (every rank's owners fill them on every rank)
+        const int64_t n = static_cast<int64_t>(m.T) * m.H;
+        if (capacity < n) throw std::invalid_argument("read_tensor: buffer too small");
+        DeviceBuffer tmp(static_cast<std::size_t>(n) * 4);
+        const void* src = name == "output" ? (m.output_bf16 ? m.output_bf16 : m.ws("output")) : m.gathered(1);
+        throw_on(sfb_k_convert(src, SFB_BF16, tmp.get(), SFB_F32, n, stream_));
+        cuda_check(cudaStreamSynchronize(stream_), "sync");
+        cuda_check(cudaMemcpy(host_out, tmp.get(), static_cast<std::size_t>(n) * 4, cudaMemcpyDeviceToHost), "read tensor");
+        return n;
+    }
     const int id = m.planner.find(name);
     if (id < 0) throw std::invalid_argument("unknown decoder tensor: " + name);
     cuda_check(cudaStreamSynchronize(stream_), "sync");

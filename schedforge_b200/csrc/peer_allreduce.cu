@@ -118,8 +118,7 @@ peer_allreduce_finish_kernel(const PeerParams p) {
 // rows are taken from `source` as they are: an all-gather of rows each rank already holds (the layer input).
 // Both waits are bounded; when one gives up the status word is set and the kernel returns.
 struct GatherParams {
-    const bf16* recv;
-    long long slot_elems;
+    const bf16* slot[SFB_MAX_PEERS];  // partial rows of rank s for this owner's row range (local slots, or peers' buffers)
     int slots;
     const bf16* source;
     const bf16* residual;
@@ -182,7 +181,24 @@ peer_reduce_gather_kernel(const GatherParams p) {
                 }
             };
             if (p.slots == 0) add(p.source + local);
-            for (int s = 0; s < p.slots; ++s) add(p.recv + s * p.slot_elems + local);  // rank order: one arithmetic everywhere
+            {   // all partial rows are requested before the first is used (peer loads take microseconds); they are
+                // added in rank order: one arithmetic everywhere
+                uint4 packed[SFB_MAX_PEERS];
+#pragma unroll
+                for (int s = 0; s < SFB_MAX_PEERS; ++s)
+                    if (s < p.slots) packed[s] = *reinterpret_cast<const uint4*>(p.slot[s] + local + c * 8);
+#pragma unroll
+                for (int s = 0; s < SFB_MAX_PEERS; ++s) {
+                    if (s >= p.slots) break;
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed[s]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 x = __bfloat1622float2(h[j]);
+                        acc[2 * j] += x.x;
+                        acc[2 * j + 1] += x.y;
+                    }
+                }
+            }
             if (p.residual) add(p.residual + local);
             uint4 result;
             __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&result);
@@ -267,14 +283,17 @@ sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* a, sfb_stream st
     SFB_REQUIRE(a->size >= 2 && a->size <= SFB_MAX_PEERS && a->rank >= 0 && a->rank < a->size && a->rows_own > 0 &&
                     a->width > 0 && a->width % 8 == 0 && a->slots >= 0 && a->slots <= a->size,
                 "peer reduce-gather: invalid group or shape");
-    SFB_REQUIRE(a->slots == 0 ? a->source != nullptr : (a->recv != nullptr && a->slot_elems >= static_cast<int64_t>(a->rows_own) * a->width &&
-                                                        a->slot_elems % 8 == 0),
+    SFB_REQUIRE(a->slots == 0 ? a->source != nullptr
+                              : (a->pull[0] != nullptr || (a->recv != nullptr && a->slot_elems >= static_cast<int64_t>(a->rows_own) * a->width &&
+                                                           a->slot_elems % 8 == 0)),
                 "peer reduce-gather: missing source rows or receive slots");
     SFB_REQUIRE(a->gathered[a->rank], "peer reduce-gather: null destination");
     GatherParams p{};
-    p.recv = static_cast<const bf16*>(a->recv);
-    p.slot_elems = a->slot_elems;
     p.slots = a->slots;
+    for (int s = 0; s < a->slots; ++s) {
+        p.slot[s] = a->pull[0] ? static_cast<const bf16*>(a->pull[s]) : static_cast<const bf16*>(a->recv) + s * a->slot_elems;
+        SFB_REQUIRE(p.slot[s] && (reinterpret_cast<uintptr_t>(p.slot[s]) & 15) == 0, "peer reduce-gather: null or misaligned partial rows");
+    }
     p.source = static_cast<const bf16*>(a->source);
     p.residual = static_cast<const bf16*>(a->residual);
     p.source_ss = a->source_ss;

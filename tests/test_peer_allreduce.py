@@ -73,14 +73,15 @@ def test_finish_rejects_bad_groups(dev, port):
 
 
 class GatherArgs(C.Structure):
-    _fields_ = [("recv", C.c_void_p), ("slot_elems", C.c_int64), ("slots", C.c_int), ("source", C.c_void_p),
+    _fields_ = [("recv", C.c_void_p), ("slot_elems", C.c_int64), ("slots", C.c_int), ("pull", C.c_void_p * 8),
+                ("source", C.c_void_p),
                 ("source_ss", C.c_void_p), ("residual", C.c_void_p), ("gathered", C.c_void_p * 8), ("ss", C.c_void_p * 8),
                 ("local_flags", C.c_void_p), ("peer_flags", C.c_void_p * 8), ("done_counter", C.c_void_p),
                 ("rank", C.c_int), ("size", C.c_int), ("epoch", C.c_uint32), ("rows_own", C.c_int), ("width", C.c_int),
                 ("gather", C.c_int)]
 
 
-def _run_gather(dev, port, size, rank, rows_own, width, flag_a, flag_b, epoch, slots=None, with_residual=True):
+def _run_gather(dev, port, size, rank, rows_own, width, flag_a, flag_b, epoch, slots=None, with_residual=True, pull=False):
     """The owner's kernel of the two-shot form on ONE GPU: the slots the peers' GEMMs would have filled, the peers'
     copies of the gathered tensor and both flag sets are plain tensors of this GPU prepared by the test."""
     torch = dev.torch
@@ -99,7 +100,12 @@ def _run_gather(dev, port, size, rank, rows_own, width, flag_a, flag_b, epoch, s
     sink = torch.zeros((8, 16), dtype=torch.int32, device="cuda")                   # peers' flag arrays
     counter = torch.zeros((1,), dtype=torch.int32, device="cuda")
     a = GatherArgs()
-    if slots > 0:
+    if slots > 0 and pull:   # every rank's partial rows sit in a tensor of their own (here: of this GPU)
+        a.slots = slots
+        singles = [recv[s].clone() for s in range(slots)]
+        for s in range(slots):
+            a.pull[s] = singles[s].data_ptr()
+    elif slots > 0:
         a.recv, a.slot_elems, a.slots = recv.data_ptr(), rows_own * width, slots
     else:
         a.source = recv.data_ptr()
@@ -124,9 +130,10 @@ def _run_gather(dev, port, size, rank, rows_own, width, flag_a, flag_b, epoch, s
     return want, [dev.np(t) for t in copies], [dev.np(t) for t in sums], dev.np(sink.float()), int(counter.item()), word.value
 
 
+@pytest.mark.parametrize("pull", [False, True])
 @pytest.mark.parametrize("size,rank,rows_own,width", [(2, 1, 64, 256), (4, 2, 37, 512), (8, 5, 128, 4096)])
-def test_two_shot_owner_sums_its_rows_and_hands_them_to_every_rank(dev, port, size, rank, rows_own, width):
-    want, copies, sums, sink, counter, status = _run_gather(dev, port, size, rank, rows_own, width, 3, 3, 3)
+def test_two_shot_owner_sums_its_rows_and_hands_them_to_every_rank(dev, port, size, rank, rows_own, width, pull):
+    want, copies, sums, sink, counter, status = _run_gather(dev, port, size, rank, rows_own, width, 3, 3, 3, pull=pull)
     assert status == 0 and counter == 0
     lo, hi = rank * rows_own, (rank + 1) * rows_own
     for s in range(size):       # the finished rows and their sums of squares landed in every rank's copy, nowhere else
