@@ -660,6 +660,64 @@ typedef struct sfb_peer_gather_args {
 } sfb_peer_gather_args;
 sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* args, sfb_stream stream);
 
+/* ---- token-sharded expert parallelism: all-to-all dispatch and combine over peer stores --------------------
+ * No counterpart in the reference (a single-process library); what must be preserved is the order of its
+ * dispatch_tokens (src/moe_compiler.cpp:496-528: per expert, rows in (token, slot) order) and of its weighted
+ * combine (:219-226).  Rank r owns tokens [r * rows_own, (r + 1) * rows_own) and experts [r * E / size, ...).
+ * Every rank routes and dispatches its own tokens (sfb_k_moe_route, sfb_k_moe_dispatch with values = NULL), then
+ *   sfb_k_moe_ep_plan    exchanges the per-expert histograms and derives send_base[E] (first row, on the expert's
+ *                        owner, of this rank's rows of that expert), recv_offsets[E / size + 1] (segment starts of
+ *                        this rank's experts = group_offsets of the grouped GEMMs) and return_table
+ *                        [E / size * size][4] = (receive start, rows, source rank, first row at the source);
+ *   sfb_k_moe_ep_send    copies every locally dispatched token row to its final position in the owner's receive
+ *                        buffer (a segment holds rank 0's rows, then rank 1's, ...: the reference's order), with
+ *                        the global token id and the route slot;
+ *   sfb_k_moe_ep_return  copies every expert output row back to the source rank, to the row's position in that
+ *                        rank's local dispatched order, where sfb_k_moe_combine of that rank reads it.
+ * Each call ends with an announcement to every peer and a bounded wait for theirs (sfb_ep_sync: local_flags[s] is
+ * written by rank s, peer_flags[s] is the address of entry [rank] of rank s's local_flags, done_counter one
+ * zeroed word, epoch grows by one per use); a wait that gives up sets bit 0x100 of sfb_device_status. */
+typedef struct sfb_ep_sync {
+    uint32_t* local_flags;
+    uint32_t* peer_flags[SFB_MAX_PEERS];
+    uint32_t* done_counter;
+    uint32_t epoch;
+    int rank, size;
+} sfb_ep_sync;
+typedef struct sfb_moe_ep_plan_args {
+    const int* counts;                 /* this rank's histogram [experts] (sfb_k_moe_route on its tokens) */
+    int* counts_all[SFB_MAX_PEERS];    /* every rank's table [size][experts]; entry [rank] is local */
+    int experts;
+    int* send_base;
+    int* recv_offsets;
+    int* return_table;
+    sfb_ep_sync sync;
+} sfb_moe_ep_plan_args;
+typedef struct sfb_moe_ep_send_args {
+    const void* rows;                  /* this rank's token rows [rows_own, hidden] bf16 */
+    const int* offsets;                /* local dispatch: segment starts [experts + 1] */
+    const int* token_ids;              /* local dispatch: token of every dispatched row */
+    const int* route_slots;
+    const int* send_base;
+    void* recv_rows[SFB_MAX_PEERS];    /* every rank's receive buffer [capacity, hidden] bf16 */
+    int* recv_tokens[SFB_MAX_PEERS];   /* ... and the global token id / route slot of every received row */
+    int* recv_slots[SFB_MAX_PEERS];
+    int assignments, hidden, experts, first_token;
+    sfb_ep_sync sync;
+} sfb_moe_ep_send_args;
+typedef struct sfb_moe_ep_return_args {
+    const void* rows;                  /* expert outputs in receive order [received, hidden] bf16 */
+    const int* recv_offsets;
+    const int* return_table;
+    void* back[SFB_MAX_PEERS];         /* every rank's [rows_own * top_k, hidden] buffer in its local dispatched order */
+    int hidden, experts_local;
+    int max_rows;                      /* upper bound of the received rows (sizes the launch) */
+    sfb_ep_sync sync;
+} sfb_moe_ep_return_args;
+sfb_status sfb_k_moe_ep_plan(const sfb_moe_ep_plan_args* args, sfb_stream stream);
+sfb_status sfb_k_moe_ep_send(const sfb_moe_ep_send_args* args, sfb_stream stream);
+sfb_status sfb_k_moe_ep_return(const sfb_moe_ep_return_args* args, sfb_stream stream);
+
 /* Device memory that other processes of this node can map (CUDA IPC): allocate + export a 64-byte
  * handle, map a peer's handle, unmap, free. */
 sfb_status sfb_peer_alloc(size_t bytes, void** ptr, void* handle64);

@@ -120,6 +120,7 @@ struct DecoderExecutablePlan::Impl {
     // Page p of sequence b is physical block block_ids[p * batch + b] of the pool.
     int kv_length = 0, kv_capacity = 0;
     std::vector<int> page_table, free_pages, block_ids;
+    std::vector<int> trace_counts;  // expert-parallel plan with a caller's trace: this rank's histogram of it
     int* len_pinned = nullptr;      // start lengths for the stand-alone append kernel (plans without the fused append)
     int len_uploaded = -1;
     // Device block table for ALL logical blocks: the pages in use, then the free pages in the order they will be
@@ -210,7 +211,7 @@ struct DecoderExecutablePlan::Impl {
     // kernel fills on every rank, and the gathered sums of squares of the first two.
     int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot
     bool input_in_peer = false;    // the resident input is the gathered copy (sfb_decoder_execute_rows on a two-shot plan)
-    uint32_t gather_epoch[3] = {0, 0, 0};
+    uint32_t gather_epoch[6] = {0, 0, 0, 0, 0, 0};  // collectives 0-2: gathers; 3-5: expert-parallel plan / send / return
     std::size_t th_bytes() const { return (static_cast<std::size_t>(T) * H * 2 + 1023) / 1024 * 1024; }
     std::size_t flags2_offset() const { return peer_flags_offset() + 256; }
     std::size_t counters_offset() const { return peer_flags_offset() + 1024; }
@@ -218,7 +219,28 @@ struct DecoderExecutablePlan::Impl {
     std::size_t partial_offset(int set) const { return recv2_offset() + set * th_bytes(); }
     std::size_t gathered_offset(int which) const { return recv2_offset() + 2 * th_bytes() + which * th_bytes(); }
     std::size_t ss_offset(int which) const { return gathered_offset(3) + which * ((static_cast<std::size_t>(T) * 4 + 255) / 256 * 256); }
-    std::size_t peer_total_bytes() const { return ss_offset(2) + 256; }
+    // expert-parallel MoE plans add: the table of every rank's per-expert histogram, the receive buffer for dispatched
+    // rows (any split of the T * top_k assignments may land here) with their token ids and slots, and the buffer the
+    // experts' owners return this rank's rows to (its local dispatched order)
+    std::size_t ep_counts_offset() const { return ss_offset(2); }
+    std::size_t ep_recv_rows_offset() const { return ep_counts_offset() + 4096; }
+    std::size_t ep_capacity() const { return static_cast<std::size_t>(T) * std::max(1, K); }
+    std::size_t ep_recv_tokens_offset() const { return ep_recv_rows_offset() + (ep_capacity() * H * 2 + 1023) / 1024 * 1024; }
+    std::size_t ep_recv_slots_offset() const { return ep_recv_tokens_offset() + (ep_capacity() * 4 + 1023) / 1024 * 1024; }
+    std::size_t ep_back_offset() const { return ep_recv_slots_offset() + (ep_capacity() * 4 + 1023) / 1024 * 1024; }
+    std::size_t ep_end_offset() const { return ep_back_offset() + (ep_capacity() / size * H * 2 + 1023) / 1024 * 1024; }
+    std::size_t peer_total_bytes() const { return (E > 0 ? ep_end_offset() : ss_offset(2)) + 256; }
+    sfb_ep_sync ep_sync(int coll) {
+        sfb_ep_sync y{};
+        y.local_flags = reinterpret_cast<uint32_t*>(peer_local + flags2_offset()) + coll * 2 * SFB_MAX_PEERS;
+        for (int r = 0; r < size; ++r)
+            if (r != rank)
+                y.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_remote[r] + flags2_offset()) + coll * 2 * SFB_MAX_PEERS + rank;
+        y.done_counter = reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + coll;
+        y.epoch = ++gather_epoch[coll];
+        y.rank = rank; y.size = size;
+        return y;
+    }
     char* peer_base(int r) const { return r == rank ? peer_local : peer_remote[r]; }
     template <class P = void> P* gathered(int which) const { return reinterpret_cast<P*>(peer_local + gathered_offset(which)); }
     float* gathered_ss(int which) const { return reinterpret_cast<float*>(peer_local + ss_offset(which)); }
@@ -226,10 +248,11 @@ struct DecoderExecutablePlan::Impl {
     void* partial(int set) const { return peer_local + partial_offset(set); }
     // Owner side of collective `coll` (0 = all-gather of the input rows, 1 = after O, 2 = after Down): sums the slots of
     // set coll - 1 (+ residual rows), writes gathered tensor `coll` and optionally its sums of squares on every rank.
-    sfb_status reduce_gather(int coll, const void* source, const float* source_ss, const void* residual, bool with_ss, cudaStream_t s) {
+    sfb_status reduce_gather(int coll, const void* source, const float* source_ss, const void* residual, bool with_ss, cudaStream_t s,
+                             int gather = 1) {
         sfb_peer_gather_args a{};
         const int rows_own = T / size;
-        if (coll > 0) {  // this owner's rows inside every rank's partial tensor of set coll - 1
+        if (coll > 0 && !source) {  // this owner's rows inside every rank's partial tensor of set coll - 1
             a.slots = size;
             for (int r = 0; r < size; ++r)
                 a.pull[r] = peer_base(r) + partial_offset(coll - 1) + static_cast<std::size_t>(rank) * rows_own * H * 2;
@@ -244,7 +267,7 @@ struct DecoderExecutablePlan::Impl {
         a.local_flags = reinterpret_cast<uint32_t*>(peer_local + flags2_offset()) + coll * 2 * SFB_MAX_PEERS;
         a.done_counter = reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + coll;
         a.rank = rank; a.size = size; a.epoch = ++gather_epoch[coll];
-        a.rows_own = rows_own; a.width = H; a.gather = 1;
+        a.rows_own = rows_own; a.width = H; a.gather = gather;
         return sfb_k_peer_reduce_gather(&a, s);
     }
     // completes the all-reduce whose data the preceding GEMM pushed: `count` elements starting `offset` elements in
@@ -751,6 +774,11 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         wp.add("routing_weights", A * 4, 8, 12);
         wp.add("dest_of", A * 4, 8, 12);
         wp.add("dispatch_scratch", sfb_moe_dispatch_scratch_bytes(T, m.E, m.K), 8, 9);
+        if (G > 1) {  // expert-parallel tables (see moe_ep.cu)
+            wp.add("ep_send_base", static_cast<std::size_t>(m.E) * 4, 8, 12);
+            wp.add("ep_recv_offsets", static_cast<std::size_t>(m.E_l + 1) * 4, 8, 12);
+            wp.add("ep_return_table", static_cast<std::size_t>(m.E_l) * G * 16, 8, 12);
+        }
         wp.add("tile_table", sizeof(int) * 4 * (A / 128 + m.E + 2), 9, 11);
         wp.add("dispatched", A * H * e, 8, 10);
         if (bf) {
@@ -817,7 +845,7 @@ void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* pe
     m.peer_local = static_cast<char*>(local_base);
     m.peer_mode = mode;
     m.peer_epoch[0] = m.peer_epoch[1] = 0;
-    m.gather_epoch[0] = m.gather_epoch[1] = m.gather_epoch[2] = 0;
+    for (auto& epoch : m.gather_epoch) epoch = 0;
 }
 
 void DecoderExecutablePlan::upload_input(const float* input) {
@@ -988,7 +1016,8 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             // adds them up with its rows of the residual stream, takes the sums of squares and hands the finished
             // rows to everybody
             gemm(m.ws("attention"), m.wo, m.partial(0), T, H, m.hidden_l, SFB_EPI_STORE);
-            throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s));
+            // (an expert-parallel MoE layer keeps the reduced rows with their owner: its FFN half is token sharded)
+            throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s, moe ? 0 : 1));
         } else if (peer) {
             gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
                  nullptr, 0, false, 0);
@@ -1007,13 +1036,14 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         throw_on(sfb_k_add(m.ws("projected"), x, r1, static_cast<int64_t>(T) * H, dt, s));
         mark();  // 6
     }
+    const bool ep = two && moe;   // token-sharded expert parallelism (all-to-all dispatch / combine over peer stores)
     void* a2 = r1;
-    if (!m.fold2) {
+    if (!m.fold2 && !ep) {
         a2 = m.ws("normalized2");
         throw_on(sfb_k_rms_norm(r1, m.rms2, a2, T, H, c.rms_epsilon, dt, s));
     }
     mark();  // 7: norm
-    void* out = two && !moe ? m.gathered(2) : m.ws("output");
+    void* out = two ? m.gathered(2) : m.ws("output");
     if (!moe) {
         if (fused) {
             gemm(a2, m.wgu, m.ws("activation"), T, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, nullptr, 0, false, -1,
@@ -1041,6 +1071,70 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             throw_on(sfb_k_add(r1, m.ws("down"), out, static_cast<int64_t>(T) * H, dt, s));
             mark();  // 9
         }
+    } else if (ep) {
+        // This rank's tokens only: norm, router, stable local dispatch; the histograms go round, every dispatched row
+        // travels to the owner of its expert, the grouped GEMMs run on what arrived, the outputs travel back, the
+        // owner of the token combines them with the residual, and the finished rows are gathered on every rank.
+        const int rows_own = T / m.size, A_own = rows_own * m.K, Ifull = c.intermediate;
+        const int capacity = static_cast<int>(m.ep_capacity());
+        char* r1_own = static_cast<char*>(r1) + own_rows_offset;
+        char* n2_own = static_cast<char*>(m.ws("normalized2")) + own_rows_offset;
+        throw_on(sfb_k_rms_norm(r1_own, m.rms2, n2_own, rows_own, H, c.rms_epsilon, dt, s));
+        int* ids = m.ws<int>("expert_ids");
+        float* wts = m.ws<float>("expert_weights");
+        int* counts = m.ws<int>("counts");
+        if (trace) {  // the caller's trace covers all tokens: this rank takes its rows of it
+            validate_routing_trace(T, m.K, m.E, trace.expert_ids, trace.expert_weights, trace.counts);
+            const std::size_t first = static_cast<std::size_t>(m.rank) * A_own;
+            m.trace_counts.assign(static_cast<std::size_t>(m.E), 0);
+            for (int i = 0; i < A_own; ++i) ++m.trace_counts[static_cast<std::size_t>(trace.expert_ids[first + i])];
+            cuda_check(cudaMemcpyAsync(ids, trace.expert_ids + first, sizeof(int) * A_own, cudaMemcpyHostToDevice, s), "trace upload");
+            cuda_check(cudaMemcpyAsync(wts, trace.expert_weights + first, sizeof(float) * A_own, cudaMemcpyHostToDevice, s), "trace upload");
+            cuda_check(cudaMemcpyAsync(counts, m.trace_counts.data(), sizeof(int) * m.E, cudaMemcpyHostToDevice, s), "trace upload");
+            cuda_check(cudaStreamSynchronize(s), "trace upload sync");  // the host vector is reused by the next pass
+        } else {
+            throw_on(sfb_k_moe_route(n2_own, dt, m.router, m.router_bias, rows_own, H, m.E, m.K, ids, wts, counts, s));
+        }
+        int* offsets = m.ws<int>("offsets");
+        throw_on(sfb_k_moe_dispatch(nullptr, dt, ids, wts, counts, rows_own, H, m.E, m.K, nullptr, offsets,
+                                    m.ws<int>("token_ids"), m.ws<int>("route_slots"), m.ws<float>("routing_weights"),
+                                    m.ws<int>("dest_of"), m.ws<int>("dispatch_scratch"), s));
+        sfb_moe_ep_plan_args plan_args{};
+        plan_args.counts = counts;
+        for (int r = 0; r < m.size; ++r) plan_args.counts_all[r] = reinterpret_cast<int*>(m.peer_base(r) + m.ep_counts_offset());
+        plan_args.experts = m.E;
+        plan_args.send_base = m.ws<int>("ep_send_base");
+        plan_args.recv_offsets = m.ws<int>("ep_recv_offsets");
+        plan_args.return_table = m.ws<int>("ep_return_table");
+        plan_args.sync = m.ep_sync(3);
+        throw_on(sfb_k_moe_ep_plan(&plan_args, s));
+        sfb_moe_ep_send_args send{};
+        send.rows = n2_own; send.offsets = offsets; send.token_ids = m.ws<int>("token_ids"); send.route_slots = m.ws<int>("route_slots");
+        send.send_base = plan_args.send_base;
+        for (int r = 0; r < m.size; ++r) {
+            send.recv_rows[r] = m.peer_base(r) + m.ep_recv_rows_offset();
+            send.recv_tokens[r] = reinterpret_cast<int*>(m.peer_base(r) + m.ep_recv_tokens_offset());
+            send.recv_slots[r] = reinterpret_cast<int*>(m.peer_base(r) + m.ep_recv_slots_offset());
+        }
+        send.assignments = A_own; send.hidden = H; send.experts = m.E; send.first_token = m.rank * rows_own;
+        send.sync = m.ep_sync(4);
+        throw_on(sfb_k_moe_ep_send(&send, s));
+        void* received = m.peer_local + m.ep_recv_rows_offset();
+        void* y = m.ws("expert_output");
+        gemm(received, m.w13, m.ws("expert_activation"), capacity, 2 * Ifull, H, SFB_EPI_SWIGLU, nullptr, m.moe_swiglu_block,
+             plan_args.recv_offsets, m.E_l);
+        gemm(m.ws("expert_activation"), m.w2, y, capacity, H, Ifull, SFB_EPI_STORE, nullptr, 0, plan_args.recv_offsets, m.E_l);
+        sfb_moe_ep_return_args back{};
+        back.rows = y; back.recv_offsets = plan_args.recv_offsets; back.return_table = plan_args.return_table;
+        for (int r = 0; r < m.size; ++r) back.back[r] = m.peer_base(r) + m.ep_back_offset();
+        back.hidden = H; back.experts_local = m.E_l; back.max_rows = capacity;
+        back.sync = m.ep_sync(5);
+        throw_on(sfb_k_moe_ep_return(&back, s));
+        char* out_own = static_cast<char*>(out) + own_rows_offset;
+        throw_on(sfb_k_moe_combine(m.peer_local + m.ep_back_offset(), m.ws<int>("dest_of"), m.ws<float>("routing_weights"), r1_own,
+                                   out_own, rows_own, H, m.K, dt, s));
+        throw_on(m.reduce_gather(2, out_own, nullptr, nullptr, false, s));  // all-gather of the finished rows
+        mark(); mark();  // 8: ffn, 9
     } else {
         const int A = T * m.K, Ifull = c.intermediate;
         int* ids = m.ws<int>("expert_ids");
@@ -1420,6 +1514,16 @@ int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_
     auto& m = *impl_;
     if (name == "output" && m.direct_f32_output) return read_tensor("output_f32", host_out, capacity);
     if (name == "output_f32") m.materialize_output(0, m.T, stream_);
+    if (name == "ep_recv_tokens" || name == "ep_recv_slots") {  // expert-parallel receive side (peer-visible buffer), int32
+        if (!m.two_shot() || m.E == 0) throw std::invalid_argument("unknown decoder tensor: " + name);
+        const int64_t n = static_cast<int64_t>(m.ep_capacity());
+        if (!host_out) return n;
+        if (capacity < n) throw std::invalid_argument("read_tensor: buffer too small");
+        cuda_check(cudaStreamSynchronize(stream_), "sync");
+        const char* src = m.peer_local + (name == "ep_recv_tokens" ? m.ep_recv_tokens_offset() : m.ep_recv_slots_offset());
+        cuda_check(cudaMemcpy(host_out, src, static_cast<std::size_t>(n) * 4, cudaMemcpyDeviceToHost), "read tensor");
+        return n;
+    }
     if (m.two_shot() && host_out && (name == "output" || name == "attention_residual")) {
         // a two-shot plan keeps these two in its peer-visible buffer (every rank's owners fill them on every rank)
         const int64_t n = static_cast<int64_t>(m.T) * m.H;
@@ -1435,7 +1539,8 @@ int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_
     if (id < 0) throw std::invalid_argument("unknown decoder tensor: " + name);
     cuda_check(cudaStreamSynchronize(stream_), "sync");
     const bool is_int = name == "expert_ids" || name == "counts" || name == "offsets" || name == "token_ids" ||
-                        name == "route_slots" || name == "dest_of";
+                        name == "route_slots" || name == "dest_of" || name == "ep_send_base" || name == "ep_recv_offsets" ||
+                        name == "ep_return_table";
     const bool is_f32 = is_int || name == "expert_weights" || name == "routing_weights" || name == "input_f32" ||
                         name == "output_f32" || name == "decode_partials" || name == "ss1" || name == "ss2" || m.dtype == SFB_F32;
     std::size_t bytes = m.planner.bytes(id);
@@ -1443,6 +1548,9 @@ int64_t DecoderExecutablePlan::read_tensor(const std::string& name, float* host_
     const int A = m.T * std::max(1, m.K);
     if (name == "counts") count = m.E;
     else if (name == "offsets") count = m.E + 1;
+    else if (name == "ep_send_base") count = m.E;
+    else if (name == "ep_recv_offsets") count = m.E_l + 1;
+    else if (name == "ep_return_table") count = static_cast<int64_t>(m.E_l) * m.size * 4;
     else if (is_int || name == "expert_weights" || name == "routing_weights") count = A;
     else if (name == "query" || name == "attention") count = static_cast<int64_t>(m.T) * m.hidden_l;
     else if (name == "key" || name == "value") count = static_cast<int64_t>(m.T) * m.kvw_l;

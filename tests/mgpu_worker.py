@@ -109,7 +109,46 @@ def main():
             if word.value != 0:
                 failures.append(f"{name}:{mode_name}:device status {word.value:#x}")
             label = f"{name}: fused {mode_name} peer all-reduce"
-            if moe:
+            if moe and mode == 2:
+                # Token-sharded expert parallelism: every rank routed and dispatched its own rows and the rows went to
+                # the experts' owners and back.  Rebuild the global picture from the ranks and compare it with the
+                # single-process oracle: expert ids, histogram, segment offsets, token ids and route slots bit for bit.
+                t, k, rows = oc.batch * oc.sequence, oc.top_k, t_rows // world
+                mine = {"ids": plan.read_tensor("expert_ids", np.int32)[:rows * k].reshape(rows, k),
+                        "weights": plan.read_tensor("expert_weights")[:rows * k].reshape(rows, k),
+                        "n2": plan.read_tensor("normalized2").reshape(t, oc.hidden)[rank * rows:(rank + 1) * rows],
+                        "recv_offsets": plan.read_tensor("ep_recv_offsets", np.int32)}
+                received = int(mine["recv_offsets"][-1])
+                mine["recv_tokens"] = plan.read_tensor("ep_recv_tokens", np.int32)[:received]
+                mine["recv_slots"] = plan.read_tensor("ep_recv_slots", np.int32)[:received]
+                parts = [None] * world
+                dist.all_gather_object(parts, mine)
+                if rank == 0:
+                    ids = np.concatenate([p["ids"] for p in parts])
+                    weights = np.concatenate([p["weights"] for p in parts])
+                    n2 = np.concatenate([p["n2"] for p in parts])
+                    mc = ob.MoeConfig(t, oc.hidden, oc.intermediate, oc.experts, k)
+                    want_ids, want_w, want_counts = port.route_topk(mc, n2, data["router_weight"].reshape(oc.hidden, oc.experts))
+                    _, want_offsets, want_tokens, want_slots, _ = port.dispatch_tokens(mc, n2, want_ids, want_w, want_counts,
+                                                                                       copy_values=False)
+                    offsets, base = [0], 0
+                    for p in parts:   # rank r holds the segments of experts [r * E / world, ...), in expert order
+                        offsets += [base + int(v) for v in p["recv_offsets"][1:]]
+                        base += int(p["recv_offsets"][-1])
+                    tokens = np.concatenate([p["recv_tokens"] for p in parts])
+                    slots = np.concatenate([p["recv_slots"] for p in parts])
+                    exact = (np.array_equal(ids, want_ids) and np.array_equal(np.array(offsets, np.int32), want_offsets)
+                             and np.array_equal(tokens, want_tokens) and np.array_equal(slots, want_slots)
+                             and np.array_equal(np.bincount(ids.ravel(), minlength=oc.experts), want_counts))
+                    want = port.decoder_layer(oc, data, native=True, trace=(ids, weights, want_counts))
+                    err = float(np.max(np.abs(fused - want)) / np.max(np.abs(want)))
+                    print(f"{name}: expert parallel (all-to-all over peer stores) rel err {err:.3e}; global expert ids, offsets, "
+                          f"token ids and route slots equal to single-process dispatch_tokens: {exact}", flush=True)
+                    if not exact:
+                        failures.append(f"{name}:expert-parallel dispatch order differs from dispatch_tokens")
+                    if not err < 2e-2:
+                        failures.append(f"{name}:expert-parallel output differs")
+            elif moe:
                 # The all-reduce forms add the partial sums in different orders, so a token whose router logits
                 # nearly tie may pick another expert: count those tokens, require them to be rare, and compare the
                 # output with the oracle routed like THIS run.
