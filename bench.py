@@ -381,7 +381,7 @@ class Layer:
                 # one-shot pushes cost (N-1) x bytes per rank: two ranks, or the small decode outputs; more ranks with
                 # large outputs scatter the rows to their owners and gather the sums (two-shot)
                 if workload == "moe":
-                    collective = "nccl"
+                    collective = "two-shot"   # token-sharded expert parallelism needs the row ownership of this form
                 elif world == 2 or workload == "decode":
                     collective = "peer"
                 else:
@@ -696,7 +696,9 @@ def main():
             sub_layer.close()
             record["roofline"] = layer_roofline(name, sub_layer.cfg, world, sub_result, record["ms_per_step"])
             record["parallelism"] = (f"tp{world}" if name == "decode" else
-                                     f"attention tp{world}, experts sharded {world} ways on replicated tokens")
+                                     f"attention tp{world}; FFN token-sharded expert parallel ep{world}: local route + dispatch, "
+                                     f"all-to-all dispatch and combine over NVLink peer stores" if sub_layer.collective == "two-shot"
+                                     else f"attention tp{world}, experts sharded {world} ways on replicated tokens")
             subs[name] = record
         if world == 1:
             kernels = {}

@@ -715,6 +715,10 @@ typedef struct sfb_moe_ep_return_args {
     sfb_ep_sync sync;
 } sfb_moe_ep_return_args;
 sfb_status sfb_k_moe_ep_plan(const sfb_moe_ep_plan_args* args, sfb_stream stream);
+/* The table arithmetic of sfb_k_moe_ep_plan on the HOST (no device needed), from the complete histogram table
+ * counts_all[size][experts]: the same send_base, recv_offsets and return_table for rank `rank`. */
+sfb_status sfb_moe_ep_tables(const int* counts_all, int size, int experts, int rank, int* send_base, int* recv_offsets,
+                             int* return_table);
 sfb_status sfb_k_moe_ep_send(const sfb_moe_ep_send_args* args, sfb_stream stream);
 sfb_status sfb_k_moe_ep_return(const sfb_moe_ep_return_args* args, sfb_stream stream);
 

@@ -77,6 +77,46 @@ __device__ void announce_and_wait(const Sync& y) {
     }
 }
 
+// The three tables of rank `rank` from the complete histogram table all[size][experts] (host and device).
+//   send_base[e]       first row, in the receive buffer of expert e's owner, of THIS rank's rows of expert e: inside
+//                      owner d the experts of d follow one another in ascending order, each holding the ranks' rows
+//                      in ascending rank order;
+//   recv_offsets[el]   segment starts of this rank's experts (the last entry is the number of received rows);
+//   return_table       per (own expert, source rank): receive start, rows, source rank, first row of that expert's
+//                      segment in the SOURCE's local dispatched order.
+__host__ __device__ inline void ep_tables(const int* all, int size, int experts, int rank, int* send_base, int* recv_offsets,
+                                          int* return_table) {
+    const int local = experts / size;
+    for (int d = 0; d < size; ++d) {
+        int segment = 0;
+        for (int e = d * local; e < (d + 1) * local; ++e) {
+            int before = 0, total = 0;
+            for (int s = 0; s < size; ++s) {
+                if (s < rank) before += all[s * experts + e];
+                total += all[s * experts + e];
+            }
+            send_base[e] = segment + before;
+            segment += total;
+        }
+    }
+    int start = 0, entry = 0;
+    for (int el = 0; el < local; ++el) {
+        const int e = rank * local + el;
+        recv_offsets[el] = start;
+        for (int s = 0; s < size; ++s) {
+            int at_source = 0;
+            for (int before = 0; before < e; ++before) at_source += all[s * experts + before];
+            int* row = return_table + 4 * entry++;
+            row[0] = start;
+            row[1] = all[s * experts + e];
+            row[2] = s;
+            row[3] = at_source;
+            start += all[s * experts + e];
+        }
+    }
+    recv_offsets[local] = start;
+}
+
 struct PlanParams {
     const int* counts;                      // this rank's histogram [experts]
     int* counts_all[SFB_MAX_PEERS];         // every rank's table [size][experts] (index = rank that holds the table)
@@ -98,39 +138,7 @@ ep_plan_kernel(const PlanParams p) {
     announce_and_wait(p.sync);   // one block: it is the last one
     __syncthreads();
     if (threadIdx.x != 0) return;
-    const int* all = p.counts_all[rank];  // [size][E], complete now
-    // destinations of this rank's rows: inside the owner d of expert e, the experts of d in ascending order, each
-    // holding the ranks' rows in ascending rank order
-    for (int d = 0; d < size; ++d) {
-        int segment = 0;
-        for (int e = d * El; e < (d + 1) * El; ++e) {
-            int before = 0, total = 0;
-            for (int s = 0; s < size; ++s) {
-                if (s < rank) before += all[s * E + e];
-                total += all[s * E + e];
-            }
-            p.send_base[e] = segment + before;
-            segment += total;
-        }
-    }
-    // what this rank receives: segment starts of its experts, and for the way back, per (expert, source) the run of
-    // received rows and the first row of that expert's segment in the SOURCE's local dispatched order
-    int start = 0, entry = 0;
-    for (int el = 0; el < El; ++el) {
-        const int e = rank * El + el;
-        p.recv_offsets[el] = start;
-        for (int s = 0; s < size; ++s) {
-            int at_source = 0;
-            for (int before = 0; before < e; ++before) at_source += all[s * E + before];
-            int* row = p.return_table + 4 * entry++;
-            row[0] = start;
-            row[1] = all[s * E + e];
-            row[2] = s;
-            row[3] = at_source;
-            start += all[s * E + e];
-        }
-    }
-    p.recv_offsets[El] = start;
+    ep_tables(p.counts_all[rank], size, E, rank, p.send_base, p.recv_offsets, p.return_table);
 }
 
 struct SendParams {
@@ -247,6 +255,15 @@ sfb_status sfb_k_moe_ep_plan(const sfb_moe_ep_plan_args* a, sfb_stream stream) {
     p.sync = make_sync(a->sync, device_status_word());
     ep_plan_kernel<<<1, kMaxExperts, 0, as_stream(stream)>>>(p);
     return check_launch("moe_ep_plan");
+}
+
+sfb_status sfb_moe_ep_tables(const int* counts_all, int size, int experts, int rank, int* send_base, int* recv_offsets,
+                             int* return_table) {
+    SFB_REQUIRE(counts_all && send_base && recv_offsets && return_table, "expert-parallel tables: null buffer");
+    SFB_REQUIRE(size >= 1 && size <= SFB_MAX_PEERS && rank >= 0 && rank < size && experts > 0 && experts % size == 0,
+                "expert-parallel tables: the experts must divide over the ranks");
+    ep_tables(counts_all, size, experts, rank, send_base, recv_offsets, return_table);
+    return SFB_OK;
 }
 
 sfb_status sfb_k_moe_ep_send(const sfb_moe_ep_send_args* a, sfb_stream stream) {
