@@ -456,7 +456,7 @@ def time_layer(layer, args, sampler):
     # e2e: host buffers through the plan call.  With several ranks every rank brings and takes its own rows
     # (sfb_decoder_execute_rows): the whole job still moves the full input and output between host and device
     # each step, 1/N of it per PCIe link.
-    sharded_io = world > 1 and tokens % world == 0 and layer.workload != "moe"
+    sharded_io = world > 1 and tokens % world == 0 and (layer.workload != "moe" or layer.collective == "two-shot")
     if sharded_io:
         rows = tokens // world
         row0 = rank * rows

@@ -168,51 +168,55 @@ peer_reduce_gather_kernel(const GatherParams p) {
         const size_t local = static_cast<size_t>(row) * p.width;
         const size_t global = (static_cast<size_t>(p.rank) * p.rows_own + row) * p.width;
         float sumsq = 0.0F;
-        for (int c = lane; c < pieces; c += 32) {
-            float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
-            auto add = [&](const bf16* src) {
-                const uint4 packed = *reinterpret_cast<const uint4*>(src + c * 8);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+        // Two 16-byte pieces per lane and pass, and every load of a pass is issued before the first value is used:
+        // a peer load takes microseconds, so the bytes in flight per warp decide the NVLink rate.
+        for (int c0 = lane; c0 < pieces; c0 += 64) {
+            const int piece[2] = {c0, c0 + 32};
+            const int live = piece[1] < pieces ? 2 : 1;
+            uint4 packed[2][SFB_MAX_PEERS], extra[2], base[2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 x = __bfloat1622float2(h[j]);
-                    acc[2 * j] += x.x;
-                    acc[2 * j + 1] += x.y;
-                }
-            };
-            if (p.slots == 0) add(p.source + local);
-            {   // all partial rows are requested before the first is used (peer loads take microseconds); they are
-                // added in rank order: one arithmetic everywhere
-                uint4 packed[SFB_MAX_PEERS];
+            for (int u = 0; u < 2; ++u) {
+                if (u >= live) break;
+                if (p.slots == 0) base[u] = *reinterpret_cast<const uint4*>(p.source + local + piece[u] * 8);
 #pragma unroll
                 for (int s = 0; s < SFB_MAX_PEERS; ++s)
-                    if (s < p.slots) packed[s] = *reinterpret_cast<const uint4*>(p.slot[s] + local + c * 8);
+                    if (s < p.slots) packed[u][s] = *reinterpret_cast<const uint4*>(p.slot[s] + local + piece[u] * 8);
+                if (p.residual) extra[u] = *reinterpret_cast<const uint4*>(p.residual + local + piece[u] * 8);
+            }
 #pragma unroll
-                for (int s = 0; s < SFB_MAX_PEERS; ++s) {
-                    if (s >= p.slots) break;
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed[s]);
+            for (int u = 0; u < 2; ++u) {
+                if (u >= live) break;
+                float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+                auto add = [&](const uint4& value) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&value);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float2 x = __bfloat1622float2(h[j]);
                         acc[2 * j] += x.x;
                         acc[2 * j + 1] += x.y;
                     }
-                }
-            }
-            if (p.residual) add(p.residual + local);
-            uint4 result;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&result);
+                };
+                if (p.slots == 0) add(base[u]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-                const float2 r = __bfloat1622float2(h[j]);
-                sumsq = fmaf(r.x, r.x, sumsq);
-                sumsq = fmaf(r.y, r.y, sumsq);
+                for (int s = 0; s < SFB_MAX_PEERS; ++s) {  // rank order: one arithmetic everywhere
+                    if (s >= p.slots) break;
+                    add(packed[u][s]);
+                }
+                if (p.residual) add(extra[u]);
+                uint4 result;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                    const float2 r = __bfloat1622float2(h[j]);
+                    sumsq = fmaf(r.x, r.x, sumsq);
+                    sumsq = fmaf(r.y, r.y, sumsq);
+                }
+                *reinterpret_cast<uint4*>(p.gathered[p.rank] + global + piece[u] * 8) = result;
+                if (p.gather)
+                    for (int s = 0; s < p.size; ++s)
+                        if (s != p.rank) *reinterpret_cast<uint4*>(p.gathered[s] + global + piece[u] * 8) = result;  // peer stores over NVLink
             }
-            *reinterpret_cast<uint4*>(p.gathered[p.rank] + global + c * 8) = result;
-            if (p.gather)
-                for (int s = 0; s < p.size; ++s)
-                    if (s != p.rank) *reinterpret_cast<uint4*>(p.gathered[s] + global + c * 8) = result;  // peer stores over NVLink
         }
         if (p.ss[p.rank]) {
             sumsq = p.source_ss ? p.source_ss[row] : warp_sum(sumsq);
