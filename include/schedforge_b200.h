@@ -829,6 +829,21 @@ sfb_status sfb_moe_execute_quantized(const sfb_moe_config* config, const float* 
                                      const float* w1, const float* w3, const float* w2,
                                      const int* expert_ids, const float* expert_weights, const int* counts,
                                      int per_channel, int gemm_backend, float* out, double* milliseconds);
+/* MoeCompiler::compile + execute_moe on a compiled plan (include/schedforge/moe_compiler.h:181-212,
+ * src/moe_compiler.cpp:684-818): the expert weights (w1, w3 [E,H,I]; w2 [E,I,H]) are packed and uploaded ONCE and stay
+ * on the device with every buffer a pass needs; sfb_moe_plan_execute then only moves the tokens.  With a routing
+ * trace (all three arrays) the router is skipped; with none the plan routes with router_weight [H,E] (+ optional
+ * router_bias [E], which the reference does not have) and the time includes the routing, like the reference's
+ * untraced overload.  Guard: tokens <= config.tokens ("runtime token count exceeds compiled MoE guard").
+ * weight_int8 != 0: the experts of quantize_moe_weights (bf16 plans).  sfb_moe_execute above builds such a plan for
+ * one call. */
+typedef struct sfb_moe_plan sfb_moe_plan;
+sfb_status sfb_moe_compile(const sfb_moe_config* config, const float* w1, const float* w3, const float* w2,
+                           const float* router_weight, const float* router_bias, int dtype, int gemm_backend,
+                           int weight_int8, sfb_moe_plan** plan);
+void sfb_moe_destroy(sfb_moe_plan* plan);
+sfb_status sfb_moe_plan_execute(sfb_moe_plan* plan, const float* input, int tokens, const int* expert_ids,
+                                const float* expert_weights, const int* counts, float* out, double* milliseconds);
 /* plan_moe_tasks, src/moe_compiler.cpp:530-558: rows (expert, begin, end, bucket). */
 sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, int split_threshold,
                               int* tasks, int capacity, int* task_count);

@@ -377,6 +377,43 @@ def execute_moe(config, x, w1, w3, w2, ids, weights, counts, dtype=L.F32, gemm_b
     return out, ms.value
 
 
+class MoeExecutablePlan:
+    """MoeCompiler.compile + execute_moe on a plan that keeps the packed expert weights on the device."""
+
+    def __init__(self, config, w1, w3, w2, router_weight=None, router_bias=None, dtype=L.BF16, gemm_backend=L.GEMM_AUTO,
+                 weight_int8=False):
+        self.config = config
+        self._h = C.c_void_p()
+        w1, w3, w2 = _f32(w1), _f32(w3), _f32(w2)
+        rw = _f32(router_weight) if router_weight is not None else None
+        rb = _f32(router_bias) if router_bias is not None else None
+        L.check(L.load().sfb_moe_compile(C.byref(config), _fp(w1), _fp(w3), _fp(w2), _fp(rw), _fp(rb), dtype, gemm_backend,
+                                         int(weight_int8), C.byref(self._h)))
+
+    def execute(self, x, trace=None):
+        """One pass: with trace = (ids, weights, counts) the router is skipped, else the plan routes itself."""
+        x = _f32(x)
+        out = np.empty((x.shape[0], self.config.hidden), np.float32)
+        ms = C.c_double(0)
+        ids = weights = counts = None
+        if trace is not None:
+            ids, weights, counts = _i32(trace[0]), _f32(trace[1]), _i32(trace[2])
+        L.check(L.load().sfb_moe_plan_execute(self._h, _fp(x), x.shape[0], _ip(ids), _fp(weights), _ip(counts), _fp(out),
+                                              C.byref(ms)))
+        return out, ms.value
+
+    def close(self):
+        if self._h:
+            L.load().sfb_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def execute_quantized_moe(config, x, w1, w3, w2, ids, weights, counts, per_channel=True, gemm_backend=L.GEMM_AUTO):
     """quantize_moe_weights + execute_quantized_moe of the reference (src/next_milestones.cpp:699-738):
     the experts multiply by the INT8 round trip of their weights."""

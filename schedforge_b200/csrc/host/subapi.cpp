@@ -410,7 +410,149 @@ sfb_status sfb_moe_execute_quantized(const sfb_moe_config* config, const float* 
                        out, milliseconds);
 }
 
+// The compiled MoE block: expert weights packed once and kept on the device together with every buffer a pass needs
+// (MoeExecutablePlan, include/schedforge/moe_compiler.h:205-212; the reference's plan holds kernels and reads the
+// weights from MoeData at execute time, a device plan keeps them resident instead).
+struct sfb_moe_plan {
+    sfb_moe_config config{};
+    int dtype = SFB_BF16, gemm_backend = SFB_GEMM_AUTO, block = 0;
+    bool has_router = false, has_bias = false;
+    DeviceBuffer w13, w2t;            // bf16: [E][2I][H] (W3 | W1 interleaved in blocks), [E][H][I]
+    DeviceBuffer w1f, w3f, w2f;       // fp32: the reference's layouts
+    DeviceBuffer router, bias;        // fp32 [H, E], [E]
+    DeviceBuffer x, ids, wts, cnt, off, tok, slot, rw, dest, scratch, xs, act, gate, y, result, table, stage_f32;
+};
+
 namespace {
+
+void moe_plan_build(sfb_moe_plan& p, const sfb_moe_config& c, const float* w1, const float* w3, const float* w2,
+                    const float* router_weight, const float* router_bias, int dtype, int gemm_backend, bool int8) {
+    validate_moe(c);
+    if (!w1 || !w3 || !w2) throw std::invalid_argument("MoE plan has no expert kernels");
+    if (dtype != SFB_F32 && dtype != SFB_BF16) throw std::invalid_argument("unknown MoE plan dtype");
+    if (int8 && dtype != SFB_BF16) throw std::invalid_argument("quantized MoE needs a bf16 plan");
+    p.config = c; p.dtype = dtype; p.gemm_backend = gemm_backend;
+    cudaStream_t s = nullptr;
+    const int H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k, T = c.tokens;
+    const size_t A = static_cast<size_t>(T) * K, ee = static_cast<size_t>(H) * I, esz = dtype_size(dtype);
+    if (dtype == SFB_BF16) {
+        p.block = I % 128 == 0 && T * K > 128 ? 128 : (I % 64 == 0 ? 64 : I);
+        p.w13.allocate(static_cast<size_t>(E) * 2 * ee * 2);
+        p.w2t.allocate(static_cast<size_t>(E) * ee * 2);
+        DeviceBuffer stage(ee * 4);
+        for (int e = 0; e < E; ++e) {
+            char* d13 = p.w13.as<char>() + static_cast<size_t>(e) * 2 * ee * 2;
+            cuda_check(cudaMemcpyAsync(stage.get(), w3 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
+            pack_weight_transposed(stage.as<float>(), I, 0, H, 0, I, d13, p.block, 2 * p.block, 0, s);
+            cuda_check(cudaMemcpyAsync(stage.get(), w1 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
+            pack_weight_transposed(stage.as<float>(), I, 0, H, 0, I, d13, p.block, 2 * p.block, p.block, s);
+            cuda_check(cudaMemcpyAsync(stage.get(), w2 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
+            pack_weight_transposed(stage.as<float>(), H, 0, I, 0, H, p.w2t.as<char>() + static_cast<size_t>(e) * ee * 2, 1 << 30, 0, 0, s);
+        }
+        if (int8) {  // every row of the packed slabs is one output channel of one expert matrix
+            int8_round_trip(p.w13.get(), static_cast<long long>(E) * 2 * I, H, s);
+            int8_round_trip(p.w2t.get(), static_cast<long long>(E) * H, I, s);
+        }
+        cuda_check(cudaStreamSynchronize(s), "weight pack");
+        p.act.allocate(A * I * 2);
+        p.table.allocate(sizeof(int) * 4 * (A / 128 + E + 2));
+    } else {
+        for (auto [dst, src] : {std::pair<DeviceBuffer*, const float*>{&p.w1f, w1}, {&p.w3f, w3}, {&p.w2f, w2}}) {
+            dst->allocate(static_cast<size_t>(E) * ee * 4);
+            cuda_check(cudaMemcpyAsync(dst->get(), src, static_cast<size_t>(E) * ee * 4, cudaMemcpyHostToDevice, s), "upload");
+        }
+        cuda_check(cudaStreamSynchronize(s), "weight upload");
+        p.act.allocate(A * I * 4);
+        p.gate.allocate(A * I * 4);
+    }
+    if (router_weight) {
+        p.router.allocate(static_cast<size_t>(H) * E * 4);
+        cuda_check(cudaMemcpy(p.router.get(), router_weight, static_cast<size_t>(H) * E * 4, cudaMemcpyHostToDevice), "upload");
+        p.has_router = true;
+        if (router_bias) {
+            p.bias.allocate(static_cast<size_t>(E) * 4);
+            cuda_check(cudaMemcpy(p.bias.get(), router_bias, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice), "upload");
+            p.has_bias = true;
+        }
+    }
+    p.stage_f32.allocate(static_cast<size_t>(T) * H * 4);
+    p.x.allocate(static_cast<size_t>(T) * H * esz);
+    p.ids.allocate(A * 4); p.wts.allocate(A * 4); p.cnt.allocate(static_cast<size_t>(E) * 4);
+    p.off.allocate(static_cast<size_t>(E + 1) * 4); p.tok.allocate(A * 4); p.slot.allocate(A * 4); p.rw.allocate(A * 4);
+    p.dest.allocate(A * 4); p.scratch.allocate(sfb_moe_dispatch_scratch_bytes(T, E, K));
+    p.xs.allocate(A * H * esz); p.y.allocate(A * H * esz); p.result.allocate(static_cast<size_t>(T) * H * esz);
+}
+
+// One pass (execute_moe, src/moe_compiler.cpp:684-758): with a trace the router is skipped, without one route_topk
+// runs first and its time is part of the result (:734-740).  Guard: tokens <= plan.config.tokens (:696-697).
+void moe_plan_run(sfb_moe_plan& p, const float* input, int tokens, const int* expert_ids, const float* expert_weights,
+                  const int* counts, float* out, double* milliseconds) {
+    const auto& c = p.config;
+    if (!input || !out) throw std::invalid_argument("MoE input is smaller than routing trace");
+    if (tokens <= 0 || tokens > c.tokens) throw std::invalid_argument("runtime token count exceeds compiled MoE guard");
+    const bool traced = expert_ids || expert_weights || counts;
+    if (traced) validate_routing_trace(tokens, c.top_k, c.experts, expert_ids, expert_weights, counts);
+    else if (!p.has_router) throw std::invalid_argument("MoE plan has no router weights and no routing trace was given");
+    cudaStream_t s = nullptr;
+    const int H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;
+    const size_t A = static_cast<size_t>(tokens) * K, ee = static_cast<size_t>(H) * I;
+    const auto dt = static_cast<sfb_dtype>(p.dtype);
+    if (p.dtype == SFB_F32) {
+        cuda_check(cudaMemcpyAsync(p.x.get(), input, static_cast<size_t>(tokens) * H * 4, cudaMemcpyHostToDevice, s), "upload");
+    } else {
+        cuda_check(cudaMemcpyAsync(p.stage_f32.get(), input, static_cast<size_t>(tokens) * H * 4, cudaMemcpyHostToDevice, s), "upload");
+        throw_on(sfb_k_convert(p.stage_f32.get(), SFB_F32, p.x.get(), SFB_BF16, static_cast<int64_t>(tokens) * H, s));
+    }
+    if (traced) {
+        cuda_check(cudaMemcpyAsync(p.ids.get(), expert_ids, A * 4, cudaMemcpyHostToDevice, s), "upload");
+        cuda_check(cudaMemcpyAsync(p.wts.get(), expert_weights, A * 4, cudaMemcpyHostToDevice, s), "upload");
+        cuda_check(cudaMemcpyAsync(p.cnt.get(), counts, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice, s), "upload");
+    }
+    Timer timer;
+    timer.start(s);
+    if (!traced)
+        throw_on(sfb_k_moe_route(p.x.get(), dt, p.router.as<float>(), p.has_bias ? p.bias.as<float>() : nullptr, tokens, H, E, K,
+                                 p.ids.as<int>(), p.wts.as<float>(), p.cnt.as<int>(), s));
+    throw_on(sfb_k_moe_dispatch(p.x.get(), dt, p.ids.as<int>(), p.wts.as<float>(), p.cnt.as<int>(), tokens, H, E, K, p.xs.get(),
+                                p.off.as<int>(), p.tok.as<int>(), p.slot.as<int>(), p.rw.as<float>(), p.dest.as<int>(),
+                                p.scratch.as<int>(), s));
+    if (p.dtype == SFB_BF16) {
+        sfb_gemm_args g{};
+        g.a = p.xs.get(); g.bt = p.w13.get(); g.out = p.act.get(); g.m = static_cast<int>(A); g.n = 2 * I; g.k = H;
+        g.epilogue = SFB_EPI_SWIGLU; g.backend = p.gemm_backend; g.swiglu_block = p.block;
+        g.group_offsets = p.off.as<int>(); g.groups = E; g.tile_table = p.table.get();
+        throw_on(sfb_k_gemm_bf16(&g, s));
+        sfb_gemm_args g2{};
+        g2.a = p.act.get(); g2.bt = p.w2t.get(); g2.out = p.y.get(); g2.m = static_cast<int>(A); g2.n = H; g2.k = I;
+        g2.epilogue = SFB_EPI_STORE; g2.backend = p.gemm_backend;
+        g2.group_offsets = p.off.as<int>(); g2.groups = E; g2.tile_table = p.table.get();
+        throw_on(sfb_k_gemm_bf16(&g2, s));
+    } else {
+        std::vector<int> ho(E + 1);
+        cuda_check(cudaMemcpyAsync(ho.data(), p.off.get(), sizeof(int) * (E + 1), cudaMemcpyDeviceToHost, s), "offsets");
+        cuda_check(cudaStreamSynchronize(s), "offsets sync");
+        float *xs = p.xs.as<float>(), *first = p.act.as<float>(), *gate = p.gate.as<float>();
+        for (int e = 0; e < E; ++e) {
+            const int lo = ho[e], rows = ho[e + 1] - lo;
+            if (rows <= 0) continue;
+            throw_on(sfb_k_gemm_f32(xs + static_cast<size_t>(lo) * H, p.w1f.as<float>() + e * ee, first + static_cast<size_t>(lo) * I, rows, I, H, s));
+            throw_on(sfb_k_gemm_f32(xs + static_cast<size_t>(lo) * H, p.w3f.as<float>() + e * ee, gate + static_cast<size_t>(lo) * I, rows, I, H, s));
+        }
+        moe_silu_mul_f32(first, gate, static_cast<int64_t>(A) * I, s);
+        for (int e = 0; e < E; ++e) {
+            const int lo = ho[e], rows = ho[e + 1] - lo;
+            if (rows <= 0) continue;
+            throw_on(sfb_k_gemm_f32(first + static_cast<size_t>(lo) * I, p.w2f.as<float>() + e * ee,
+                                    p.y.as<float>() + static_cast<size_t>(lo) * H, rows, H, I, s));
+        }
+    }
+    throw_on(sfb_k_moe_combine(p.y.get(), p.dest.as<int>(), p.rw.as<float>(), nullptr, p.result.get(), tokens, H, K, dt, s));
+    const double ms = timer.stop(s);
+    if (milliseconds) *milliseconds = ms;
+    fetch(p.result.get(), static_cast<size_t>(tokens) * H, p.dtype, out, s);
+}
+
+// The one-call forms: a plan for this call only (weights uploaded and packed every time: a parity harness).
 sfb_status moe_execute(const sfb_moe_config* config, const float* input, int tokens, const float* w1,
                        const float* w3, const float* w2, const int* expert_ids, const float* expert_weights,
                        const int* counts, int dtype, int gemm_backend, bool int8, float* out, double* milliseconds) {
@@ -418,89 +560,38 @@ sfb_status moe_execute(const sfb_moe_config* config, const float* input, int tok
         if (!config || !input || !w1 || !w3 || !w2 || !expert_ids || !expert_weights || !counts || !out)
             throw std::invalid_argument("MoE plan has no expert kernels");
         validate_moe(*config);
-        const auto& c = *config;
-        if (tokens <= 0 || tokens > c.tokens) throw std::invalid_argument("runtime token count exceeds compiled MoE guard");
-        validate_routing_trace(tokens, c.top_k, c.experts, expert_ids, expert_weights, counts);
-        cudaStream_t s = nullptr;
-        const int H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;
-        const size_t A = static_cast<size_t>(tokens) * K, ee = static_cast<size_t>(H) * I;
-        const auto dt = static_cast<sfb_dtype>(dtype);
-        Staged x(input, static_cast<size_t>(tokens) * H, dtype, s);
-        DeviceBuffer ids(A * 4), wts(A * 4), cnt(static_cast<size_t>(E) * 4), off(static_cast<size_t>(E + 1) * 4), tok(A * 4),
-            slot(A * 4), rw(A * 4), dest(A * 4), scratch(sfb_moe_dispatch_scratch_bytes(tokens, E, K)),
-            xs(A * H * dtype_size(dtype)), y(A * H * dtype_size(dtype)), result(static_cast<size_t>(tokens) * H * dtype_size(dtype));
-        cuda_check(cudaMemcpyAsync(ids.get(), expert_ids, A * 4, cudaMemcpyHostToDevice, s), "upload");
-        cuda_check(cudaMemcpyAsync(wts.get(), expert_weights, A * 4, cudaMemcpyHostToDevice, s), "upload");
-        cuda_check(cudaMemcpyAsync(cnt.get(), counts, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice, s), "upload");
-        Timer timer;
-        double ms = 0.0;
-        if (dtype == SFB_BF16) {
-            const int block = I % 128 == 0 && tokens * K > 128 ? 128 : (I % 64 == 0 ? 64 : I);
-            DeviceBuffer w13(static_cast<size_t>(E) * 2 * ee * 2), w2t(static_cast<size_t>(E) * ee * 2), stage(ee * 4),
-                act(A * I * 2), table(sizeof(int) * 4 * (A / 128 + E + 2));
-            for (int e = 0; e < E; ++e) {
-                char* d13 = w13.as<char>() + static_cast<size_t>(e) * 2 * ee * 2;
-                cuda_check(cudaMemcpyAsync(stage.get(), w3 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
-                pack_weight_transposed(stage.as<float>(), I, 0, H, 0, I, d13, block, 2 * block, 0, s);
-                cuda_check(cudaMemcpyAsync(stage.get(), w1 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
-                pack_weight_transposed(stage.as<float>(), I, 0, H, 0, I, d13, block, 2 * block, block, s);
-                cuda_check(cudaMemcpyAsync(stage.get(), w2 + e * ee, ee * 4, cudaMemcpyHostToDevice, s), "upload");
-                pack_weight_transposed(stage.as<float>(), H, 0, I, 0, H, w2t.as<char>() + static_cast<size_t>(e) * ee * 2, 1 << 30, 0, 0, s);
-            }
-            if (int8) {  // every row of the packed slabs is one output channel of one expert matrix
-                int8_round_trip(w13.get(), static_cast<long long>(E) * 2 * I, H, s);
-                int8_round_trip(w2t.get(), static_cast<long long>(E) * H, I, s);
-            }
-            timer.start(s);
-            throw_on(sfb_k_moe_dispatch(x.get(), dt, ids.as<int>(), wts.as<float>(), cnt.as<int>(), tokens, H, E, K, xs.get(),
-                                        off.as<int>(), tok.as<int>(), slot.as<int>(), rw.as<float>(), dest.as<int>(),
-                                        scratch.as<int>(), s));
-            sfb_gemm_args g{};
-            g.a = xs.get(); g.bt = w13.get(); g.out = act.get(); g.m = static_cast<int>(A); g.n = 2 * I; g.k = H;
-            g.epilogue = SFB_EPI_SWIGLU; g.backend = gemm_backend; g.swiglu_block = block;
-            g.group_offsets = off.as<int>(); g.groups = E; g.tile_table = table.get();
-            throw_on(sfb_k_gemm_bf16(&g, s));
-            sfb_gemm_args g2{};
-            g2.a = act.get(); g2.bt = w2t.get(); g2.out = y.get(); g2.m = static_cast<int>(A); g2.n = H; g2.k = I;
-            g2.epilogue = SFB_EPI_STORE; g2.backend = gemm_backend;
-            g2.group_offsets = off.as<int>(); g2.groups = E; g2.tile_table = table.get();
-            throw_on(sfb_k_gemm_bf16(&g2, s));
-            throw_on(sfb_k_moe_combine(y.get(), dest.as<int>(), rw.as<float>(), nullptr, result.get(), tokens, H, K, dt, s));
-            ms = timer.stop(s);
-        } else {
-            Staged d1(w1, static_cast<size_t>(E) * ee, SFB_F32, s), d3(w3, static_cast<size_t>(E) * ee, SFB_F32, s),
-                d2(w2, static_cast<size_t>(E) * ee, SFB_F32, s);
-            DeviceBuffer first(A * I * 4), gate(A * I * 4);
-            timer.start(s);
-            throw_on(sfb_k_moe_dispatch(x.get(), dt, ids.as<int>(), wts.as<float>(), cnt.as<int>(), tokens, H, E, K, xs.get(),
-                                        off.as<int>(), tok.as<int>(), slot.as<int>(), rw.as<float>(), dest.as<int>(),
-                                        scratch.as<int>(), s));
-            std::vector<int> ho(E + 1);
-            cuda_check(cudaMemcpyAsync(ho.data(), off.get(), sizeof(int) * (E + 1), cudaMemcpyDeviceToHost, s), "offsets");
-            cuda_check(cudaStreamSynchronize(s), "offsets sync");
-            for (int e = 0; e < E; ++e) {
-                const int lo = ho[e], rows = ho[e + 1] - lo;
-                if (rows <= 0) continue;
-                throw_on(sfb_k_gemm_f32(xs.as<float>() + static_cast<size_t>(lo) * H, static_cast<const float*>(d1.get()) + e * ee,
-                                        first.as<float>() + static_cast<size_t>(lo) * I, rows, I, H, s));
-                throw_on(sfb_k_gemm_f32(xs.as<float>() + static_cast<size_t>(lo) * H, static_cast<const float*>(d3.get()) + e * ee,
-                                        gate.as<float>() + static_cast<size_t>(lo) * I, rows, I, H, s));
-            }
-            moe_silu_mul_f32(first.as<float>(), gate.as<float>(), static_cast<int64_t>(A) * I, s);
-            for (int e = 0; e < E; ++e) {
-                const int lo = ho[e], rows = ho[e + 1] - lo;
-                if (rows <= 0) continue;
-                throw_on(sfb_k_gemm_f32(first.as<float>() + static_cast<size_t>(lo) * I, static_cast<const float*>(d2.get()) + e * ee,
-                                        y.as<float>() + static_cast<size_t>(lo) * H, rows, H, I, s));
-            }
-            throw_on(sfb_k_moe_combine(y.get(), dest.as<int>(), rw.as<float>(), nullptr, result.get(), tokens, H, K, dt, s));
-            ms = timer.stop(s);
-        }
-        if (milliseconds) *milliseconds = ms;
-        fetch(result.get(), static_cast<size_t>(tokens) * H, dtype, out, s);
+        if (tokens <= 0 || tokens > config->tokens) throw std::invalid_argument("runtime token count exceeds compiled MoE guard");
+        validate_routing_trace(tokens, config->top_k, config->experts, expert_ids, expert_weights, counts);
+        sfb_moe_config sized = *config;
+        sized.tokens = tokens;  // buffers for this call's rows
+        sfb_moe_plan plan;
+        moe_plan_build(plan, sized, w1, w3, w2, nullptr, nullptr, dtype, gemm_backend, int8);
+        moe_plan_run(plan, input, tokens, expert_ids, expert_weights, counts, out, milliseconds);
     });
 }
 }  // namespace
+
+sfb_status sfb_moe_compile(const sfb_moe_config* config, const float* w1, const float* w3, const float* w2,
+                           const float* router_weight, const float* router_bias, int dtype, int gemm_backend,
+                           int weight_int8, sfb_moe_plan** plan) {
+    return guarded([&] {
+        if (!config || !plan) throw std::invalid_argument("invalid MoE configuration");
+        *plan = nullptr;
+        auto owned = std::make_unique<sfb_moe_plan>();
+        moe_plan_build(*owned, *config, w1, w3, w2, router_weight, router_bias, dtype, gemm_backend, weight_int8 != 0);
+        *plan = owned.release();
+    });
+}
+
+void sfb_moe_destroy(sfb_moe_plan* plan) { delete plan; }
+
+sfb_status sfb_moe_plan_execute(sfb_moe_plan* plan, const float* input, int tokens, const int* expert_ids,
+                                const float* expert_weights, const int* counts, float* out, double* milliseconds) {
+    return guarded([&] {
+        if (!plan) throw std::invalid_argument("MoE plan has no expert kernels");
+        moe_plan_run(*plan, input, tokens, expert_ids, expert_weights, counts, out, milliseconds);
+    });
+}
 
 sfb_status sfb_moe_plan_tasks(const sfb_moe_config* config, const int* counts, int split_threshold, int* tasks,
                               int capacity, int* task_count) {

@@ -162,6 +162,7 @@ EXPORTS = (
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "
     "sfb_paged_release sfb_paged_info sfb_paged_gather sfb_paged_decode "
     "sfb_moe_route_topk sfb_moe_dispatch_tokens sfb_moe_execute sfb_moe_execute_quantized sfb_moe_plan_tasks "
+    "sfb_moe_compile sfb_moe_destroy sfb_moe_plan_execute "
     "sfb_make_routing_trace sfb_make_decoder_input sfb_make_decoder_data sfb_decoder_profile_count sfb_decoder_profile_get "
     "sfb_benchmark_decoder_profile sfb_write_decoder_benchmark_csv sfb_write_decoder_plan_candidates_csv "
     "sfb_decoder_compile_milliseconds "

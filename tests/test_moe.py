@@ -111,3 +111,43 @@ def test_expert_ffn_bf16_grouped_gemm(port, backend):
     out, _ = api.execute_moe(api.moe_config(tokens, hidden, inter, experts, top_k), x, w1, w3, w2, ids, weights,
                              counts, dtype=L.BF16, gemm_backend=backend)
     assert rel_err(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+def test_compiled_moe_plan_keeps_its_weights_and_runs_repeatedly(port, dtype):
+    """sfb_moe_compile / sfb_moe_plan_execute: the expert weights are packed and uploaded once; passes with a
+    routing trace, passes that route themselves (router bias included), a shorter token count and the reference's
+    guard for a longer one.  Results equal the one-call form and the oracle."""
+    rng = np.random.default_rng(12)
+    t, h, i, e, k = 192, 128, 256, 8, 2
+    c, oc = api.moe_config(t, h, i, e, k), ob.MoeConfig(t, h, i, e, k)
+    x = port.round_bf16(rng.standard_normal((t, h)).astype(np.float32))
+    w1 = port.round_bf16((rng.standard_normal((e, h, i)) * 0.05).astype(np.float32))
+    w3 = port.round_bf16((rng.standard_normal((e, h, i)) * 0.05).astype(np.float32))
+    w2 = port.round_bf16((rng.standard_normal((e, i, h)) * 0.05).astype(np.float32))
+    router = port.round_bf16((rng.standard_normal((h, e)) * 0.1).astype(np.float32))
+    bias = rng.standard_normal(e).astype(np.float32)
+    tol = 1e-4 if dtype == L.F32 else 2e-2
+    plan = api.MoeExecutablePlan(c, w1, w3, w2, router, bias, dtype=dtype)
+    ids, weights, counts = port.route_topk(oc, x, router, bias)
+    want = port.moe_grouped(oc, x, w1, w3, w2, ids, weights, counts)
+    routed, ms = plan.execute(x)                                  # the plan routes itself
+    assert rel_err(routed, want) < tol and ms > 0
+    traced, _ = plan.execute(x, trace=(ids, weights, counts))     # DecoderData::routing_trace style
+    assert rel_err(traced, want) < tol
+    one_call, _ = api.execute_moe(c, x, w1, w3, w2, ids, weights, counts, dtype=dtype)
+    assert np.array_equal(traced, one_call)
+    # fewer tokens than compiled: allowed; more: the reference's guard
+    half = t // 2
+    ids_h, weights_h, counts_h = port.route_topk(ob.MoeConfig(half, h, i, e, k), x[:half], router, bias)
+    short, _ = plan.execute(x[:half], trace=(ids_h, weights_h, counts_h))
+    assert rel_err(short, port.moe_grouped(ob.MoeConfig(half, h, i, e, k), x[:half], w1, w3, w2, ids_h, weights_h, counts_h)) < tol
+    again, _ = plan.execute(x)
+    assert np.array_equal(again, routed)
+    with pytest.raises(L.InvalidArgument, match="runtime token count exceeds compiled MoE guard"):
+        plan.execute(np.concatenate([x, x]))
+    plan.close()
+    unrouted = api.MoeExecutablePlan(c, w1, w3, w2, dtype=dtype)
+    with pytest.raises(L.InvalidArgument, match="no router weights"):
+        unrouted.execute(x)
+    unrouted.close()
