@@ -179,6 +179,14 @@ typedef struct sfb_gemm_args {
      * waited for the kernels before it: how a chain of launches resets the sums a later GEMM adds to. */
     void* clear;
     size_t clear_bytes;
+    /* owner_flags != NULL (tcgen05, dense, more than 128 rows): A is being all-gathered while the GEMM runs.  Rows
+     * [o * owner_rows, (o + 1) * owner_rows) (owner_rows a multiple of 128) may be read once owner_flags[o] has reached
+     * owner_epoch (device words that another GPU or a copy engine writes after the rows, and after their row_ss
+     * entries); the rows of owner_self are complete at launch and their tiles are visited first.  The wait is
+     * bounded; when it gives up bit 0x100 of sfb_device_status is set and the kernel drains. */
+    const uint32_t* owner_flags;
+    uint32_t owner_epoch;
+    int owner_rows, owner_self;
     /* SFB_EPI_ROPE_SPLIT of a decode step (tcgen05): kv_k_pool != NULL also writes the rotated key and the
      * value of token t of sequence b into the paged cache at position kv_position + t (block
      * kv_table[b * kv_max_blocks + position / kv_block_tokens], pool layout of sfb_decode_args).  A position
@@ -657,8 +665,14 @@ typedef struct sfb_peer_gather_args {
     uint32_t epoch;
     int rows_own, width;
     int gather;
+    uint32_t* epoch_out;   /* gather == 0: optional device word that receives `epoch` when the rows are done; a caller
+                              that moves the rows to the peers with copy engines copies this word into the peers' flag
+                              arrays after the rows ("rows sent") */
 } sfb_peer_gather_args;
 sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* args, sfb_stream stream);
+/* Bounded wait (one thread) until local_flags[s] has reached epoch for every peer s: closes an all-gather whose rows
+ * travel by copy engine while other kernels run.  Bit 0x100 of sfb_device_status when it gives up. */
+sfb_status sfb_k_peer_wait(const uint32_t* local_flags, int rank, int size, uint32_t epoch, sfb_stream stream);
 
 /* ---- token-sharded expert parallelism: all-to-all dispatch and combine over peer stores --------------------
  * No counterpart in the reference (a single-process library); what must be preserved is the order of its
@@ -739,8 +753,10 @@ sfb_status sfb_decoder_set_peer_allreduce(sfb_decoder_plan* plan, void* local_ba
 /* The same with the form chosen: mode 1 = the one-shot form above (each rank pushes its whole partial tensor to
  * every peer: two ranks, or the small outputs of decode plans), mode 2 = the two-shot form (sfb_k_peer_reduce_gather:
  * reduce-scatter under the GEMM, then the row owners add the residual, sum, take the sums of squares for the folded
- * RMSNorm and all-gather the finished rows with peer stores; needs rows % tp_size == 0), mode 0 = two-shot for more
- * than two ranks and more than 128 rows, else one-shot.  With the two-shot form sfb_decoder_execute_rows gathers
+ * RMSNorm and all-gather the finished rows with peer stores; needs rows % tp_size == 0), mode 3 = the two-shot form
+ * with the all-gather moved to copy engines (peer-to-peer copies on a side stream of the plan) so that it runs UNDER
+ * the next GEMM, which waits per owner for the rows it has not got yet (sfb_gemm_args.owner_flags; dense plans with
+ * 128-row multiples per rank), mode 0 = mode 3 or 2 for more than two ranks and more than 128 rows, else one-shot.  With the two-shot form sfb_decoder_execute_rows gathers
  * the input rows with peer stores as well instead of going through the hook. */
 sfb_status sfb_decoder_set_peer_collective(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases, int mode);
 

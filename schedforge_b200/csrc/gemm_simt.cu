@@ -366,7 +366,7 @@ sfb_status sfb_k_gemm_bf16(const sfb_gemm_args* args, sfb_stream stream) {
                 "gemm: the blocked weight layout needs the dense tcgen05 kernel");
     int backend = args->backend;
     if (args->bt_tiled || args->peer_count != 0 || args->scatter_rows != 0 || args->bt_scales || args->row_ss || args->ss_out ||
-        args->kv_k_pool || args->clear)
+        args->kv_k_pool || args->clear || args->owner_flags)
         backend = SFB_GEMM_TCGEN05;  // only that kernel knows these
     if (backend == SFB_GEMM_AUTO)
         backend = gemm_bf16_tcgen05_supported(*args) ? SFB_GEMM_TCGEN05 : SFB_GEMM_SIMT;

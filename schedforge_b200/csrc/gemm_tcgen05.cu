@@ -91,6 +91,12 @@ struct TcParams {
     // per-row sums of squares of the stored bf16 outputs: every (warp, 128-column group) adds its share to the row's
     // 64-bit fixed-point sum with an integer atomic, so the total does not depend on the order of arrival
     unsigned long long* ss_out;
+    // A arrives from other ranks while the kernel runs (all-gather by copy engines): rows [o * owner_rows, ...) are
+    // complete once owner_flags[o] has reached owner_epoch; this rank's own rows (owner_self) are there from the start
+    // and the tiles are visited starting with them (m_rotate M-tiles further on)
+    const uint32_t* owner_flags;
+    uint32_t owner_epoch;
+    int owner_rows, owner_self, m_rotate;
     // zero-filled by this kernel after its dependency wait (the sums the NEXT kernels will add to)
     unsigned long long* clear;
     unsigned clear_pieces;  // 8-byte words
@@ -184,7 +190,8 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile, int
     const int first_m = band * GROUP_M;
     const int band_m = min(GROUP_M, m_tiles - first_m);
     const int local = tile - band * band_tiles;
-    const int m_index = first_m + local % band_m;
+    int m_index = first_m + local % band_m;
+    if (p.m_rotate > 0) m_index = (m_index + p.m_rotate) % m_tiles;
     TileCoord c;
     c.n_index = local / band_m;
     if (p.tile_table) {
@@ -649,8 +656,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     }
                     grid_dependency_wait();
                 }
+                uint32_t arrived = 0;  // owners whose rows this CTA has seen complete
                 while (ok && walk.next(sg)) {
                     const TileCoord c = tile_coord(p, sg.tile, m_tiles);
+                    if constexpr (EXTRA) {
+                        if (p.owner_flags) {
+                            const int owner = c.row_start / p.owner_rows;
+                            if (owner != p.owner_self && !((arrived >> owner) & 1u)) {
+                                const long long start = clock64();
+                                uint32_t spins = 0;
+                                while (static_cast<int>(ptx::load_acquire_sys_u32(p.owner_flags + owner) - p.owner_epoch) < 0) {
+                                    if ((++spins & 0xFFu) == 0 && (*abort_flag || clock64() - start > 2 * ptx::kWaitCycles)) {
+                                        *abort_flag = 1;
+                                        atomicOr(p.status, 0x100u);
+                                        ok = false;
+                                        break;
+                                    }
+                                }
+                                if (!ok) break;
+                                arrived |= 1u << owner;
+                            }
+                        }
+                    }
                     for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                         const uint32_t s = it % SB, ph = (it / SB) & 1;
                         const uint32_t full = ptx::smem_u32(&full_b[s]);
@@ -792,8 +819,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const TileCoord c = tile_coord(p, sg.tile, m_tiles);
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
             // read while the tile's main loop is still running
-            const float row_inv = EXTRA ? folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end) : 1.0F;
+            float row_inv = EXTRA && !p.owner_flags
+                ? folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end) : 1.0F;
             bool go = ptx::mbar_wait(ptx::smem_u32(&tmem_full[buf]), tph, abort_flag, p.status, kCodeEpilogue);
+            if constexpr (EXTRA) {  // rows (and their sums of squares) that arrive during the kernel are complete once the tile's
+                                    // products exist: the producer saw the owner's flag before it loaded them
+                if (p.owner_flags) row_inv = folded_row_inv(p, c.row_start + quarter * 32 + lane, c.row_start + quarter * 32 + lane < c.row_end);
+            }
             // With cut-up tiles the epilogue threads meet at barriers that have no time limit, so they must all
             // take the same decision here: one thread that saw the abort flag takes the whole group out.
             if (p.shared_tiles > 0) go = ptx::named_barrier_all(2, 32 * kEpilogueWarps, go);
@@ -1119,6 +1151,11 @@ void fill_fold_params(TcParams& p, const sfb_gemm_args& g) {
     p.row_ss = g.row_ss;
     p.row_ss_fixed = g.row_ss_fixed;
     p.rms_eps = g.rms_epsilon;
+    p.owner_flags = g.owner_flags;
+    p.owner_epoch = g.owner_epoch;
+    p.owner_rows = g.owner_rows;
+    p.owner_self = g.owner_self;
+    p.m_rotate = g.owner_flags && g.owner_rows > 0 ? (g.owner_self * g.owner_rows / BM) % std::max(1, ceil_div(g.m, BM)) : 0;
     p.clear = static_cast<unsigned long long*>(g.clear);
     p.clear_pieces = static_cast<unsigned>(g.clear_bytes / 8);
     p.scatter_rows = g.scatter_rows;
@@ -1295,6 +1332,10 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
                      (g.epilogue != SFB_EPI_STORE && g.epilogue != SFB_EPI_RESIDUAL)))
         return false;
     if (g.clear && ((reinterpret_cast<uintptr_t>(g.clear) & 7) || g.clear_bytes % 8 != 0)) return false;
+    if (g.owner_flags && (g.group_offsets || stream_shape(g) || g.owner_rows <= 0 || g.owner_rows % BM != 0 ||
+                          g.m % g.owner_rows != 0 || g.m / g.owner_rows > SFB_MAX_PEERS || g.owner_self < 0 ||
+                          g.owner_self >= g.m / g.owner_rows))
+        return false;
     if (g.kv_k_pool && (g.epilogue != SFB_EPI_ROPE_SPLIT || !g.kv_v_pool || !g.kv_table || g.kv_block_tokens <= 0 ||
                         g.kv_max_blocks <= 0 || g.kv_position < 0))
         return false;
@@ -1303,7 +1344,7 @@ bool gemm_bf16_tcgen05_supported(const sfb_gemm_args& g) {
 
 sfb_status gemm_bf16_tcgen05(const sfb_gemm_args& g, cudaStream_t stream) {
     if (g.bt_scales) return launch_w8(g, stream);
-    const bool extra = g.row_ss || g.ss_out || g.scatter_rows > 0 || g.kv_k_pool || g.clear;
+    const bool extra = g.row_ss || g.ss_out || g.scatter_rows > 0 || g.kv_k_pool || g.clear || g.owner_flags;
     if (pick_bn(g) == 256) return extra ? launch<256, false, true>(g, stream) : launch<256, false, false>(g, stream);
     if (stream_shape(g)) return extra ? launch<128, true, true>(g, stream) : launch<128, true, false>(g, stream);
     return extra ? launch<128, false, true>(g, stream) : launch<128, false, false>(g, stream);

@@ -209,7 +209,37 @@ struct DecoderExecutablePlan::Impl {
     // fetches its rows from them with wide peer loads, which use NVLink far better than 64-byte stores out of a
     // GEMM epilogue), three gathered tensors (layer input, attention_residual, output) that every rank's finish
     // kernel fills on every rank, and the gathered sums of squares of the first two.
-    int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot
+    int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot, 3 = two-shot with the all-gather on copy engines
+    // mode 3: after the owner kernel (sum, no gather) the finished rows, their sums of squares and a "rows sent" word
+    // go to every peer with peer-to-peer copies on a side stream, i.e. on copy engines, while the next GEMM already
+    // runs on the rows it has (it waits per owner, sfb_gemm_args.owner_flags); the pass ends with a wait for the
+    // peers' last rows and for this rank's own copies
+    cudaStream_t ce_stream = nullptr;
+    cudaEvent_t ce_ready = nullptr, ce_done = nullptr;
+    bool ce_pending = false;
+    bool ce_gather() const { return two_shot() && peer_mode == 3; }
+    uint32_t* ce_epoch_word(int coll) const { return reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + 8 + coll; }
+    uint32_t* ce_flags(int r, int coll) const {
+        return reinterpret_cast<uint32_t*>(peer_base(r) + flags2_offset()) + (5 + coll) * 2 * SFB_MAX_PEERS;
+    }
+    void ce_push(int coll, bool with_ss, cudaStream_t s) {
+        const std::size_t rows_own = static_cast<std::size_t>(T / size);
+        const std::size_t row_bytes = rows_own * H * 2, first = static_cast<std::size_t>(rank) * row_bytes;
+        cuda_check(cudaEventRecord(ce_ready, s), "event");
+        cuda_check(cudaStreamWaitEvent(ce_stream, ce_ready, 0), "stream wait");
+        for (int step = 1; step < size; ++step) {
+            const int r = (rank - step + size) % size;  // the rank that reaches this owner's rows first is served first
+            cuda_check(cudaMemcpyAsync(peer_remote[r] + gathered_offset(coll) + first, peer_local + gathered_offset(coll) + first,
+                                       row_bytes, cudaMemcpyDeviceToDevice, ce_stream), "peer copy");
+            if (with_ss)
+                cuda_check(cudaMemcpyAsync(peer_remote[r] + ss_offset(coll) + rank * rows_own * 4,
+                                           peer_local + ss_offset(coll) + rank * rows_own * 4, rows_own * 4,
+                                           cudaMemcpyDeviceToDevice, ce_stream), "peer copy");
+            cuda_check(cudaMemcpyAsync(ce_flags(r, coll) + rank, ce_epoch_word(coll), sizeof(uint32_t), cudaMemcpyDeviceToDevice,
+                                       ce_stream), "peer flag copy");
+        }
+        ce_pending = true;
+    }
     bool input_in_peer = false;    // the resident input is the gathered copy (sfb_decoder_execute_rows on a two-shot plan)
     uint32_t gather_epoch[6] = {0, 0, 0, 0, 0, 0};  // collectives 0-2: gathers; 3-5: expert-parallel plan / send / return
     std::size_t th_bytes() const { return (static_cast<std::size_t>(T) * H * 2 + 1023) / 1024 * 1024; }
@@ -244,12 +274,12 @@ struct DecoderExecutablePlan::Impl {
     char* peer_base(int r) const { return r == rank ? peer_local : peer_remote[r]; }
     template <class P = void> P* gathered(int which) const { return reinterpret_cast<P*>(peer_local + gathered_offset(which)); }
     float* gathered_ss(int which) const { return reinterpret_cast<float*>(peer_local + ss_offset(which)); }
-    bool two_shot() const { return size > 1 && peer_local != nullptr && peer_mode == 2; }
+    bool two_shot() const { return size > 1 && peer_local != nullptr && peer_mode >= 2; }
     void* partial(int set) const { return peer_local + partial_offset(set); }
     // Owner side of collective `coll` (0 = all-gather of the input rows, 1 = after O, 2 = after Down): sums the slots of
     // set coll - 1 (+ residual rows), writes gathered tensor `coll` and optionally its sums of squares on every rank.
     sfb_status reduce_gather(int coll, const void* source, const float* source_ss, const void* residual, bool with_ss, cudaStream_t s,
-                             int gather = 1) {
+                             int gather = 1, uint32_t* epoch_out = nullptr) {
         sfb_peer_gather_args a{};
         const int rows_own = T / size;
         if (coll > 0 && !source) {  // this owner's rows inside every rank's partial tensor of set coll - 1
@@ -267,7 +297,7 @@ struct DecoderExecutablePlan::Impl {
         a.local_flags = reinterpret_cast<uint32_t*>(peer_local + flags2_offset()) + coll * 2 * SFB_MAX_PEERS;
         a.done_counter = reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + coll;
         a.rank = rank; a.size = size; a.epoch = ++gather_epoch[coll];
-        a.rows_own = rows_own; a.width = H; a.gather = gather;
+        a.rows_own = rows_own; a.width = H; a.gather = gather; a.epoch_out = epoch_out;
         return sfb_k_peer_reduce_gather(&a, s);
     }
     // completes the all-reduce whose data the preceding GEMM pushed: `count` elements starting `offset` elements in
@@ -317,6 +347,9 @@ DecoderExecutablePlan::~DecoderExecutablePlan() {
         if (impl_->copy_out) cudaStreamDestroy(impl_->copy_out);
         if (impl_->status_host) cudaFreeHost(impl_->status_host);
         if (impl_->len_pinned) cudaFreeHost(impl_->len_pinned);
+        if (impl_->ce_stream) cudaStreamDestroy(impl_->ce_stream);
+        if (impl_->ce_ready) cudaEventDestroy(impl_->ce_ready);
+        if (impl_->ce_done) cudaEventDestroy(impl_->ce_done);
     }
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -828,11 +861,19 @@ void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* pe
         m.peer_mode = 0;
         return;
     }
-    if (mode < 0 || mode > 2) throw std::invalid_argument("peer all-reduce: unknown mode");
+    if (mode < 0 || mode > 3) throw std::invalid_argument("peer all-reduce: unknown mode");
     const bool can_two_shot = m.T % std::max(1, m.size) == 0 && m.H % 8 == 0;
-    if (mode == 2 && !can_two_shot) throw std::invalid_argument("two-shot peer all-reduce needs rows divisible by the rank count");
+    if (mode >= 2 && !can_two_shot) throw std::invalid_argument("two-shot peer all-reduce needs rows divisible by the rank count");
+    // the copy-engine all-gather needs whole 128-row tiles per owner (the GEMM that consumes the rows waits per owner)
+    const bool can_overlap = can_two_shot && config.ffn == DecoderFFNKind::Dense && (m.T / std::max(1, m.size)) % 128 == 0;
+    if (mode == 3 && !can_overlap) throw std::invalid_argument("the overlapped all-gather needs a dense plan with 128-row multiples per rank");
     // one-shot pushes (size - 1) x the tensor per rank: right for two ranks and for the small outputs of decode plans
-    if (mode == 0) mode = (can_two_shot && m.size > 2 && m.T > 128) ? 2 : 1;
+    if (mode == 0) mode = (can_two_shot && m.size > 2 && m.T > 128) ? (can_overlap ? 3 : 2) : 1;
+    if (mode == 3 && !m.ce_stream) {
+        cuda_check(cudaStreamCreateWithFlags(&m.ce_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_check(cudaEventCreateWithFlags(&m.ce_ready, cudaEventDisableTiming), "cudaEventCreate");
+        cuda_check(cudaEventCreateWithFlags(&m.ce_done, cudaEventDisableTiming), "cudaEventCreate");
+    }
     if (m.size < 2 || m.size > SFB_MAX_PEERS) throw std::invalid_argument("peer all-reduce needs a sharded plan of 2..8 ranks");
     if (m.dtype != SFB_BF16 || !policy.fuse_epilogues || policy.gemm_backend == SFB_GEMM_SIMT || m.H % 8 != 0 ||
         m.hidden_l % 8 != 0 || m.I_l % 8 != 0)
@@ -1009,6 +1050,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
         if (im.fold2) {
             g.row_ss = im.cur_ss2; g.row_ss_fixed = im.cur_ss2_fixed ? 1 : 0; g.rms_epsilon = im.rms_eps;
         }
+        if (im.ce_gather()) {  // rows of the other owners may still be on their way: wait per owner, own rows first
+            g.owner_flags = im.ce_flags(im.rank, 1); g.owner_epoch = im.gather_epoch[1];
+            g.owner_rows = rows / im.size; g.owner_self = im.rank;
+        }
     };
     if (fused) {
         if (two) {
@@ -1017,7 +1062,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             // rows to everybody
             gemm(m.ws("attention"), m.wo, m.partial(0), T, H, m.hidden_l, SFB_EPI_STORE);
             // (an expert-parallel MoE layer keeps the reduced rows with their owner: its FFN half is token sharded)
-            throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s, moe ? 0 : 1));
+            const bool ce = m.ce_gather();
+            throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s,
+                                     moe || ce ? 0 : 1, ce ? m.ce_epoch_word(1) : nullptr));
+            if (ce) m.ce_push(1, m.fold2, s);  // the other ranks' rows arrive while the gate/up GEMM runs
         } else if (peer) {
             gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
                  nullptr, 0, false, 0);
@@ -1052,7 +1100,13 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
                 gemm(m.ws("activation"), m.wd, m.ws("output_f32"), T, H, I, SFB_EPI_RESIDUAL, r1, 0, nullptr, 0, true);
             } else if (two) {
                 gemm(m.ws("activation"), m.wd, m.partial(1), T, H, I, SFB_EPI_STORE);
-                throw_on(m.reduce_gather(2, nullptr, nullptr, static_cast<const char*>(r1) + own_rows_offset, false, s));
+                const bool ce = m.ce_gather();
+                throw_on(m.reduce_gather(2, nullptr, nullptr, static_cast<const char*>(r1) + own_rows_offset, false, s, ce ? 0 : 1,
+                                         ce ? m.ce_epoch_word(2) : nullptr));
+                if (ce) {  // nothing in this layer reads the gathered output: send it and wait for the peers' rows
+                    m.ce_push(2, false, s);
+                    throw_on(sfb_k_peer_wait(m.ce_flags(m.rank, 2), m.rank, m.size, m.gather_epoch[2], s));
+                }
             } else if (peer) {
                 gemm(m.ws("activation"), m.wd, out, T, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0,
                      nullptr, 0, false, 1);
@@ -1190,6 +1244,11 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     // The layer's product on the device is the bf16 output (what a next layer would read).  A single shard also
     // leaves the fp32 copy the host calls hand out; a sharded plan converts only the rows a host call asks for,
     // instead of every rank converting the whole replicated tensor on every pass.
+    if (m.ce_pending) {  // the pass is over when this rank's outgoing copies are, too
+        cuda_check(cudaEventRecord(m.ce_done, m.ce_stream), "event");
+        cuda_check(cudaStreamWaitEvent(s, m.ce_done, 0), "stream wait");
+        m.ce_pending = false;
+    }
     m.output_bf16 = out;
     m.output_f32_valid = !bf || m.direct_f32_output || m.size == 1;
     if (bf && !m.direct_f32_output && m.size == 1)
@@ -1594,7 +1653,9 @@ std::string DecoderExecutablePlan::dump() const {
     for (const auto& constant : constants) out << "  " << constant.dump() << '\n';
     const char* gemm_kind = bf ? "gemm.bf16.tcgen05_tma" : "gemm.f32.fma_chain";
     out << "}\ndecoder.memory naive=" << naive_bytes << " workspace=" << workspace_bytes << " weights=" << weight_bytes
-        << "\ndecoder.shard rank=" << m.rank << " size=" << m.size << " dtype=" << (bf ? "bf16" : "f32")
+        << "\ndecoder.shard rank=" << m.rank << " size=" << m.size << " dtype=" << (bf ? "bf16" : "f32") << " collective="
+        << (m.size == 1 ? "none" : !m.peer_local ? "hook" : m.peer_mode == 1 ? "peer_one_shot" : m.peer_mode == 2
+                ? "peer_two_shot" : "peer_two_shot_copy_engine_gather")
         << "\nkernels {\n"
         << "  qkv {\n    " << gemm_kind << " m=" << m.T << " n=" << m.qkv_l << " k=" << m.H
         << " epilogue=" << (policy.fuse_epilogues ? "rope_split" : "store") << (m.fold1 ? " prologue=rms_norm_folded" : "")

@@ -133,6 +133,7 @@ struct GatherParams {
     int rank, size;
     uint32_t epoch;
     int rows_own, width, gather;
+    uint32_t* epoch_out;  // optional: receives the epoch (the word a copy engine then hands to the peers as "rows sent")
     uint32_t* status;
 };
 
@@ -229,7 +230,10 @@ peer_reduce_gather_kernel(const GatherParams p) {
             }
         }
     }
-    if (!p.gather) return;
+    if (!p.gather) {
+        if (p.epoch_out && blockIdx.x == 0 && threadIdx.x == 0) *p.epoch_out = p.epoch;
+        return;
+    }
     // (B) the last block to finish announces this rank's rows and waits for the peers' rows
     __threadfence_system();
     __syncthreads();
@@ -245,6 +249,12 @@ peer_reduce_gather_kernel(const GatherParams p) {
         store_release_sys(p.peer_flags_b[threadIdx.x], p.epoch);
     }
     if (threadIdx.x == 0) wait_peers(p.local_flags_b, p.rank, p.size, p.epoch, p.status);
+}
+
+// Bounded wait until every peer's flag has reached `epoch` (one thread): the end of an all-gather whose rows were
+// moved by copy engines, placed in the stream before the first kernel that needs all rows.
+__global__ void peer_wait_kernel(const uint32_t* flags, int rank, int size, uint32_t epoch, uint32_t* status) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) wait_peers(flags, rank, size, epoch, status);
 }
 
 }  // namespace
@@ -320,10 +330,17 @@ sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* a, sfb_stream st
     p.rows_own = a->rows_own;
     p.width = a->width;
     p.gather = a->gather;
+    p.epoch_out = a->epoch_out;
     p.status = device_status_word();
     const int blocks = std::min((a->rows_own + 7) / 8, sm_count() * 4);
     peer_reduce_gather_kernel<<<blocks, 256, 0, as_stream(stream)>>>(p);
     return check_launch("peer_reduce_gather");
+}
+
+sfb_status sfb_k_peer_wait(const uint32_t* local_flags, int rank, int size, uint32_t epoch, sfb_stream stream) {
+    SFB_REQUIRE(local_flags && size >= 2 && size <= SFB_MAX_PEERS && rank >= 0 && rank < size, "peer wait: invalid group");
+    peer_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(local_flags, rank, size, epoch, device_status_word());
+    return check_launch("peer_wait");
 }
 
 // ---- peer-visible device memory (CUDA IPC) -----------------------------------------------------

@@ -70,6 +70,12 @@ __device__ __forceinline__ bool named_barrier_all(uint32_t id, uint32_t threads,
         : "memory");
     return result != 0;
 }
+// System-scope acquire load (a flag another GPU or a copy engine writes).
+__device__ __forceinline__ uint32_t load_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 // fp32 x4 reduction into global memory (performed at L2, no return value).
 __device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d)

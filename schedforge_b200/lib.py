@@ -32,6 +32,7 @@ class GemmArgs(C.Structure):
                 ("rope_row_offset", C.c_int), ("bt_scales", vp),
                 ("row_ss", vp), ("row_ss_fixed", C.c_int), ("rms_epsilon", C.c_float),
                 ("ss_out", vp), ("clear", vp), ("clear_bytes", C.c_size_t),
+                ("owner_flags", vp), ("owner_epoch", C.c_uint32), ("owner_rows", C.c_int), ("owner_self", C.c_int),
                 ("kv_k_pool", vp), ("kv_v_pool", vp), ("kv_table", vp),
                 ("kv_position", C.c_int), ("kv_block_tokens", C.c_int), ("kv_max_blocks", C.c_int),
                 ("kv_num_blocks", C.c_int)]
@@ -156,7 +157,7 @@ EXPORTS = (
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
     "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_execute_rows sfb_decoder_upload_input "
     "sfb_decoder_step sfb_decoder_kv_info sfb_decoder_kv_truncate sfb_decoder_kv_release "
-    "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_k_peer_reduce_gather sfb_k_moe_ep_plan sfb_moe_ep_tables sfb_k_moe_ep_send sfb_k_moe_ep_return sfb_decoder_set_peer_collective sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
+    "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_k_peer_reduce_gather sfb_k_peer_wait sfb_k_moe_ep_plan sfb_moe_ep_tables sfb_k_moe_ep_send sfb_k_moe_ep_return sfb_decoder_set_peer_collective sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
     "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
     "sfb_attention_execute sfb_attention_decode "
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "

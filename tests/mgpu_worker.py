@@ -42,6 +42,8 @@ def main():
     cases = [("dense", dict(batch=2, sequence=128, hidden=1024, intermediate=1024, query_heads=16, kv_heads=8, head_dim=64), False),
              ("dense_decode", dict(batch=3, sequence=1, hidden=2048, intermediate=1024, query_heads=16, kv_heads=8,
                                    head_dim=128, context_sequence=200), False),
+             # 1024 rows: 128-row multiples per rank up to eight ranks (the all-gather that runs on copy engines under the GEMM)
+             ("dense_1k", dict(batch=2, sequence=512, hidden=1024, intermediate=2048, query_heads=16, kv_heads=8, head_dim=64), False),
              ("moe", dict(batch=1, sequence=256, hidden=512, intermediate=256, query_heads=8, kv_heads=8, head_dim=64,
                           experts=8, top_k=2), True)]
     for name, kw, moe in cases:
@@ -94,11 +96,13 @@ def main():
             return handles
         nccl_trace = trace
         modes = [("one-shot", 1)] + ([("two-shot", 2)] if t_rows % world == 0 and t_rows // world >= 1 else [])
+        if not moe and t_rows > 128 and t_rows % world == 0 and (t_rows // world) % 128 == 0:
+            modes.append(("two-shot, gather on copy engines under the GEMM", 3))
         for mode_name, mode in modes:
             plan.enable_peer_allreduce(rank, world, exchange, mode)
             dist.barrier()
             for _ in range(3):
-                if mode == 2:  # the whole-tensor pass (the host-buffer call of a dense plan runs row chunks, one-shot)
+                if mode >= 2:  # the whole-tensor pass (the host-buffer call of a dense plan runs row chunks, one-shot)
                     plan.upload_input(data["input"])
                     plan.execute_resident()
                     fused = plan.download_output()
@@ -186,7 +190,7 @@ def main():
                         failures.append(f"{name}:{mode_name} differs from the oracle")
                 if not err < 2e-2:  # both are sums of the same bf16 partial sums, rounded in a different order (8 ranks: 1.04e-2 seen)
                     failures.append(f"{name}:{mode_name} differs")
-                if mode == 2:  # every rank brings its rows: the input is gathered with peer stores too
+                if mode >= 2:  # every rank brings its rows: the input is gathered with peer stores too
                     rows = t_rows // world
                     x2d = data["input"].reshape(t_rows, oc.hidden)
                     mine_rows, _ = plan.execute_rows(x2d[rank * rows:(rank + 1) * rows], rank * rows)

@@ -78,7 +78,7 @@ class GatherArgs(C.Structure):
                 ("source_ss", C.c_void_p), ("residual", C.c_void_p), ("gathered", C.c_void_p * 8), ("ss", C.c_void_p * 8),
                 ("local_flags", C.c_void_p), ("peer_flags", C.c_void_p * 8), ("done_counter", C.c_void_p),
                 ("rank", C.c_int), ("size", C.c_int), ("epoch", C.c_uint32), ("rows_own", C.c_int), ("width", C.c_int),
-                ("gather", C.c_int)]
+                ("gather", C.c_int), ("epoch_out", C.c_void_p)]
 
 
 def _run_gather(dev, port, size, rank, rows_own, width, flag_a, flag_b, epoch, slots=None, with_residual=True, pull=False):
