@@ -184,6 +184,7 @@ __device__ __forceinline__ Walk make_walk(const TcParams& p, int m_tiles, int k_
     return w;
 }
 
+template <bool ROTATE = false>
 __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile, int m_tiles) {
     const int band_tiles = GROUP_M * p.n_tiles;
     const int band = tile / band_tiles;
@@ -191,7 +192,9 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile, int
     const int band_m = min(GROUP_M, m_tiles - first_m);
     const int local = tile - band * band_tiles;
     int m_index = first_m + local % band_m;
-    if (p.m_rotate > 0) m_index = (m_index + p.m_rotate) % m_tiles;
+    if constexpr (ROTATE) {
+        if (p.m_rotate > 0) m_index = (m_index + p.m_rotate) % m_tiles;
+    }
     TileCoord c;
     c.n_index = local / band_m;
     if (p.tile_table) {
@@ -647,7 +650,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                     Walk ahead = walk;
                     Segment first;
                     if (ahead.next(first)) {
-                        const TileCoord c = tile_coord(p, first.tile, m_tiles);
+                        const TileCoord c = tile_coord<EXTRA>(p, first.tile, m_tiles);
                         for (int kb = first.kb0; kb < first.kb1 && early < static_cast<uint32_t>(SB); ++kb, ++early) {
                             const uint32_t full = ptx::smem_u32(&full_b[early]);
                             ptx::mbar_expect_tx(full, T::kStageBytes);
@@ -658,7 +661,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 }
                 uint32_t arrived = 0;  // owners whose rows this CTA has seen complete
                 while (ok && walk.next(sg)) {
-                    const TileCoord c = tile_coord(p, sg.tile, m_tiles);
+                    const TileCoord c = tile_coord<EXTRA>(p, sg.tile, m_tiles);
                     if constexpr (EXTRA) {
                         if (p.owner_flags) {
                             const int owner = c.row_start / p.owner_rows;
@@ -705,7 +708,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 auto open = [&](Cursor& cu) {
                     cu.live = cu.walk.next(cu.sg);
                     if (cu.live) {
-                        cu.c = tile_coord(p, cu.sg.tile, m_tiles);
+                        cu.c = tile_coord<EXTRA>(p, cu.sg.tile, m_tiles);
                         cu.kb = cu.sg.kb0;
                     }
                 };
@@ -816,7 +819,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         uint32_t count = 0;
         Segment sg;
         for (; walk.next(sg); ++count) {
-            const TileCoord c = tile_coord(p, sg.tile, m_tiles);
+            const TileCoord c = tile_coord<EXTRA>(p, sg.tile, m_tiles);
             const uint32_t buf = count & 1, tph = (count >> 1) & 1;
             // read while the tile's main loop is still running
             float row_inv = EXTRA && !p.owner_flags
