@@ -747,18 +747,45 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     const std::size_t TH = static_cast<std::size_t>(T) * H;
     // The layer input stays resident for the whole pass so that the plan can be re-run.
     m.pipeline_chunks = 1;
-    if (bf && fused && !moe && !m.decode && c.batch >= 2 && opt.no_pipeline == 0) {
+    // Causal attention of rows [r0, r1) of a sequence needs its keys [0, r1), which the chunks before have
+    // produced, so a chunk may be any row range; only the tensor-core attention kernel takes such slices.
+    const bool row_chunks = c.causal && D == 128 && c.sequence % 128 == 0 && plan->policy.attention_backend != 1;
+    if (bf && fused && !moe && !m.decode && opt.no_pipeline == 0 && G == 1 && row_chunks && H % 256 == 0 &&
+        sm_count() / (H / 256) >= 2 && T / 128 >= 8 + sm_count() / (H / 256)) {
+        // Chunks sized for the GEMMs whose output is H wide (O and Down: 128 x 256 tiles, H / 256 per row block):
+        // a multiple of `unit` row blocks fills whole rounds of the SMs (9 row blocks x 16 = 144 tiles on 148 SMs
+        // at H = 4096), where 1536 rows were 192 tiles = two rounds of which the second is a third full.  Nothing
+        // overlaps the first upload and the last download, so the first and the last chunk are short; the chunks
+        // between them grow and shrink again (the copies run a little faster than the kernels).
+        const int unit = sm_count() / (H / 256), blocks = T / 128;
+        const int first = 4, last = 4 + (blocks - 8) % unit;
+        int units = (blocks - first - last) / unit;
+        std::vector<int> sizes{first};
+        if (units <= 2) {
+            for (int i = 0; i < units; ++i) sizes.push_back(unit);
+        } else {
+            sizes.push_back(unit);
+            int left = units - 2;
+            const int group = std::max(2, (left + 5) / 6);
+            for (; left > 0; left -= std::min(group, left)) sizes.push_back(std::min(group, left) * unit);
+            sizes.push_back(unit);
+        }
+        sizes.push_back(last);
+        int row = 0;
+        for (int size : sizes) {
+            m.pipeline_ranges.push_back({row, size * 128});
+            row += size * 128;
+        }
+        m.pipeline_chunks = static_cast<int>(m.pipeline_ranges.size());
+    } else if (bf && fused && !moe && !m.decode && c.batch >= 2 && opt.no_pipeline == 0) {
         m.pipeline_chunks = c.batch;
         while (m.pipeline_chunks > 8 || c.batch % m.pipeline_chunks != 0) --m.pipeline_chunks;
         const int per_chunk = c.batch / m.pipeline_chunks * c.sequence;
         for (int i = 0; i < m.pipeline_chunks; ++i) m.pipeline_ranges.push_back({i * per_chunk, per_chunk});
-        // Nothing overlaps the first upload and the last download, so the first and the last chunk
-        // are cut short: 512 rows at the head of the first sequence and at the tail of the last one.
-        // Causal attention of rows [r0, r1) of a sequence needs its keys [0, r1), which the chunks
-        // before have produced; only the tensor-core attention kernel takes such slices.
+        // the first and the last chunk cut short: 512 rows at the head of the first sequence and at the tail
+        // of the last one
         const int edge = 512;
-        if (c.causal && D == 128 && per_chunk == c.sequence && c.sequence >= 2 * edge && c.sequence % 256 == 0 &&
-            plan->policy.attention_backend != 1) {
+        if (row_chunks && per_chunk == c.sequence && c.sequence >= 2 * edge && c.sequence % 256 == 0) {
             std::vector<std::pair<int, int>> ranges;
             ranges.push_back({0, edge});
             ranges.push_back({edge, c.sequence - edge});
@@ -782,7 +809,8 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     wp.add("query", static_cast<std::size_t>(T) * m.hidden_l * e, 2, 4);
     // chunks that are part of a sequence attend to the keys and values of the chunks before them
     bool sliced = false;
-    for (const auto& range : m.pipeline_ranges) sliced = sliced || range.second < c.sequence;
+    for (const auto& range : m.pipeline_ranges)
+        sliced = sliced || range.first % c.sequence != 0 || range.second % c.sequence != 0;
     wp.add("key", static_cast<std::size_t>(T) * m.kvw_l * e, 2, sliced ? 13 : 4);
     wp.add("value", static_cast<std::size_t>(T) * m.kvw_l * e, 2, sliced ? 13 : 4);
     if (m.paged)
@@ -1423,10 +1451,10 @@ void DecoderExecutablePlan::execute_rows(const float* input_rows, float* output_
     result->kernel_launches = sfb_launch_count() - launches_before;
 }
 
-// Dense bf16 prefill with fused epilogues, one chunk of whole sequences at a time: the host->device
-// copy of chunk c+1 and the device->host copy of chunk c-1 run on their own streams while chunk c
-// computes.  Sequences are independent in every stage (row-wise GEMMs and norms, per-sequence
-// attention), so the result equals the unchunked pass.
+// Dense bf16 prefill with fused epilogues, one chunk of rows at a time: the host->device copy of
+// chunk c+1 and the device->host copy of chunk c-1 run on their own streams while chunk c computes.
+// Every stage but attention is row-wise, and causal attention of a row needs only the rows of its
+// sequence before it, which earlier chunks hold: the result equals the unchunked pass.
 void DecoderExecutablePlan::execute_pipelined(const float* input, float* output, sfb_decoder_result* result) {
     auto& m = *impl_;
     if (!input || !output) throw std::invalid_argument("decoder input or output is null");
@@ -1478,6 +1506,9 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         else if (m.size > 1 && allreduce_) allreduce_(allreduce_user_, buffer, static_cast<int64_t>(rows) * H, m.dtype, s);
     };
     cudaEvent_t t0 = m.events[12], t1 = m.events[15];
+    // Stage marks between the kernels of a chunk cost about 10 us each and keep a kernel from starting under the
+    // tail of the one before: they are recorded only for a caller that asks for the stage times.
+    const bool stage_marks = result != nullptr;
     cuda_check(cudaEventRecord(t0, s), "event");
     cuda_check(cudaStreamWaitEvent(m.copy_in, t0, 0), "stream wait");
     const bool add_residual_here = m.rank == 0;
@@ -1485,9 +1516,6 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         cudaEvent_t* ev = &m.chunk_events[static_cast<std::size_t>(ch) * 7];
         const int g0 = m.pipeline_ranges[ch].first;      // first row of the chunk in the [T, H] input
         rows = m.pipeline_ranges[ch].second;
-        const bool slices = rows < S;                    // the chunk is part of one sequence
-        const int nb = slices ? 1 : rows / S;
-        const int b0 = g0 / S, t0_in_sequence = g0 % S;  // its sequence and position inside it
         const std::size_t r0 = static_cast<std::size_t>(g0);
         cuda_check(cudaMemcpyAsync(at(m.ws("input_f32"), r0 * row_f32), input + r0 * H, rows * row_f32,
                                    cudaMemcpyHostToDevice, m.copy_in), "input upload");
@@ -1501,7 +1529,7 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         void* act = at(m.ws("activation"), r0 * static_cast<std::size_t>(I) * 2);
         void* out = at(m.ws("output"), r0 * row_bf);
         void* out32 = at(m.ws("output_f32"), r0 * row_f32);
-        cuda_check(cudaEventRecord(ev[2], s), "event");
+        if (stage_marks) cuda_check(cudaEventRecord(ev[2], s), "event");
         if (m.fold1) {
             throw_on(sfb_k_convert_rows_sumsq(static_cast<const float*>(at(m.ws("input_f32"), r0 * row_f32)), x,
                                               m.ws<float>("ss1") + g0, rows, H, s));
@@ -1510,33 +1538,42 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
             throw_on(sfb_k_rms_norm(x, m.rms1, n1, rows, H, c.rms_epsilon, SFB_BF16, s));
         }
         gemm(n1, m.wqkv, nullptr, m.qkv_l, H, SFB_EPI_ROPE_SPLIT, nullptr, 0, g0, false, -1, 1);
-        cuda_check(cudaEventRecord(ev[3], s), "event");
-        sfb_attention_args a{};
-        a.q = at(m.ws("query"), (static_cast<std::size_t>(b0) * m.hq * S + t0_in_sequence) * D * 2);
-        a.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * S * D * 2);
-        a.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * S * D * 2);
-        a.out = attn;
-        a.batch = nb; a.q_heads = m.hq; a.kv_heads = m.hkv;
-        a.seq_q = slices ? rows : S;
-        a.seq_kv = slices ? t0_in_sequence + rows : S;  // rows [r0, r1) of a sequence attend to its keys [0, r1)
-        if (slices) { a.q_head_rows = S; a.kv_head_rows = S; }
-        a.head_dim = D; a.head_dim_value = D; a.causal = c.causal; a.scale = 0.0F; a.token_major = 1;
-        a.dtype = SFB_BF16; a.backend = policy.attention_backend;
-        throw_on(sfb_k_attention_prefill(&a, s));
-        cuda_check(cudaEventRecord(ev[4], s), "event");
+        if (stage_marks) cuda_check(cudaEventRecord(ev[3], s), "event");
+        // one attention launch per run of whole sequences and per part of a sequence that the chunk holds
+        for (int r = g0; r < g0 + rows;) {
+            const int b0 = r / S, begin = r % S;                       // sequence and position of row r
+            const int left = g0 + rows - r;
+            const bool part = begin != 0 || left < S;                  // rows [begin, end) of sequence b0
+            const int end = part ? std::min(S, begin + left) : S;
+            const int nb = part ? 1 : left / S;
+            sfb_attention_args a{};
+            a.q = at(m.ws("query"), (static_cast<std::size_t>(b0) * m.hq * S + begin) * D * 2);
+            a.key = at(m.ws("key"), static_cast<std::size_t>(b0) * m.hkv * S * D * 2);
+            a.value = at(m.ws("value"), static_cast<std::size_t>(b0) * m.hkv * S * D * 2);
+            a.out = at(m.ws("attention"), static_cast<std::size_t>(r) * m.hidden_l * 2);
+            a.batch = nb; a.q_heads = m.hq; a.kv_heads = m.hkv;
+            a.seq_q = end - begin;
+            a.seq_kv = end;  // rows [begin, end) of a sequence attend to its keys [0, end)
+            if (part) { a.q_head_rows = S; a.kv_head_rows = S; }
+            a.head_dim = D; a.head_dim_value = D; a.causal = c.causal; a.scale = 0.0F; a.token_major = 1;
+            a.dtype = SFB_BF16; a.backend = policy.attention_backend;
+            throw_on(sfb_k_attention_prefill(&a, s));
+            r += part ? end - begin : nb * S;
+        }
+        if (stage_marks) cuda_check(cudaEventRecord(ev[4], s), "event");
         gemm(attn, m.wo, r1, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0, g0, false, peer ? 0 : -1, 2);
         reduce(0, r1, g0);
         if (!m.fold2) throw_on(sfb_k_rms_norm(r1, m.rms2, n2, rows, H, c.rms_epsilon, SFB_BF16, s));
         else if (m.size > 1) throw_on(sfb_k_row_sumsq(r1, m.ws<float>("ss2") + g0, rows, H, s));
-        cuda_check(cudaEventRecord(ev[5], s), "event");
+        if (stage_marks) cuda_check(cudaEventRecord(ev[5], s), "event");
         gemm(n2, m.wgu, act, 2 * I, H, SFB_EPI_SWIGLU, nullptr, m.swiglu_block, g0, false, -1, 3);
         if (m.direct_f32_output) {
             gemm(act, m.wd, out32, H, I, SFB_EPI_RESIDUAL, r1, 0, g0, true);
-            cuda_check(cudaEventRecord(ev[6], s), "event");
+            if (stage_marks) cuda_check(cudaEventRecord(ev[6], s), "event");
         } else {
             gemm(act, m.wd, out, H, I, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, r1, 0, g0, false, peer ? 1 : -1);
             reduce(1, out, g0);
-            cuda_check(cudaEventRecord(ev[6], s), "event");
+            if (stage_marks) cuda_check(cudaEventRecord(ev[6], s), "event");
             throw_on(sfb_k_convert(out, SFB_BF16, out32, SFB_F32, static_cast<int64_t>(rows) * H, s));
         }
         cuda_check(cudaEventRecord(ev[1], s), "event");

@@ -62,6 +62,20 @@ def test_llama_layer_prefill_pipelined_row_chunks(llama_prefill_b2_s1024, llama_
     plan.close()
 
 
+def test_llama_layer_prefill_pipelined_chunks_across_sequences(port, llama_weights):
+    """Two sequences of 2048 tokens (half the headline batch): sfb_decoder_execute runs chunks of 4, 9, 9 and 10
+    row blocks (9 x 128 rows = 144 output tiles of the O and Down GEMMs on 148 SMs); the third chunk holds the
+    end of the first sequence and the start of the second."""
+    kw = dict(LLAMA, batch=2, sequence=2048)
+    data = dict(llama_weights, input=_normal((4096, 4096), 1.0, 3))
+    want = port.decoder_layer(ob.decoder_config(**kw), data, native=True)
+    plan = api.DecoderCompiler.compile(api.decoder_config(**kw), llama_weights)
+    out, result = plan.execute(data["input"])
+    assert rel_err(out, want) < BF16_TOL
+    assert result.kernel_launches >= 4 * 6 + 1   # four chunks went through the layer, one of them with two attention launches
+    plan.close()
+
+
 @pytest.mark.parametrize("norm_fusion", [False, True])
 def test_llama_layer_prefill_one_shot(port, llama_weights, norm_fusion):
     """One sequence of 384 tokens through the unchunked path (the sample the CPU baseline of bench.py times), with

@@ -308,6 +308,26 @@ def test_pipelined_execute_in_row_chunks_equals_the_one_shot_plan(port):
     one_shot.close()
 
 
+def test_pipelined_execute_in_chunks_that_span_sequences_equals_the_one_shot_plan(port):
+    """Three sequences of 1280 tokens at hidden 1792: the chunks are sized in row blocks that fill whole rounds of
+    the SMs (4, 21 and 5 blocks of 128 rows on 148 SMs), so the middle chunk holds the tail of the first sequence,
+    the whole second one and the head of the third: three attention launches.  Same numbers as the one-shot form
+    (below 2048 columns the RMSNorm kernel is the same one for every row count)."""
+    kw = dict(batch=3, sequence=1280, hidden=1792, intermediate=1024, query_heads=14, kv_heads=2, head_dim=128,
+              rope_theta=500000.0)
+    oc, c, data = bf16_case(port, 43, **kw)
+    piped = api.DecoderCompiler.compile(c, weights_of(data))
+    one_shot = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(no_pipeline=True))
+    out_piped, result = piped.execute(data["input"])
+    out_one, one_result = one_shot.execute(data["input"])
+    assert result.kernel_launches > one_result.kernel_launches + 8    # it did run in several chunks
+    assert np.array_equal(out_piped, out_one)
+    assert rel_err(out_piped, port.decoder_layer(oc, data, native=True)) < BF16_TOL
+    assert np.array_equal(piped.execute(data["input"])[0], out_piped)  # and again on the used workspace
+    piped.close()
+    one_shot.close()
+
+
 @pytest.mark.parametrize("kw", [
     dict(batch=5, sequence=1, hidden=1024, intermediate=512, query_heads=8, kv_heads=2, head_dim=128, context_sequence=300),
     dict(batch=1, sequence=96, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64),   # few rows: int8 kept
