@@ -673,6 +673,11 @@ sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* args, sfb_stream
 /* Bounded wait (one thread) until local_flags[s] has reached epoch for every peer s: closes an all-gather whose rows
  * travel by copy engine while other kernels run.  Bit 0x100 of sfb_device_status when it gives up. */
 sfb_status sfb_k_peer_wait(const uint32_t* local_flags, int rank, int size, uint32_t epoch, sfb_stream stream);
+/* Bounded wait (one thread) until the device word *flag has reached epoch (wrap-around compare).  The word is
+ * written by a copy that a copy engine runs behind the data it announces (sfb_decoder_execute: the upload of a row
+ * chunk, then a 4-byte copy of the epoch), so the stream of kernels needs no event from the copy stream.  Bit 0x100 of
+ * sfb_device_status when it gives up. */
+sfb_status sfb_k_flag_wait(const uint32_t* flag, uint32_t epoch, sfb_stream stream);
 
 /* ---- token-sharded expert parallelism: all-to-all dispatch and combine over peer stores --------------------
  * No counterpart in the reference (a single-process library); what must be preserved is the order of its

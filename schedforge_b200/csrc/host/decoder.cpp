@@ -151,6 +151,12 @@ struct DecoderExecutablePlan::Impl {
     int pipeline_chunks = 1;      // host copies overlap compute in this many row chunks (1 = off)
     std::vector<std::pair<int, int>> pipeline_ranges;  // (first row, rows) of every chunk: whole sequences or part of one
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    // "chunk landed" words: the copy stream copies upload_epoch_host (pinned) into chunk_flags[c] behind the rows of
+    // chunk c and the kernel stream waits for the word with a kernel.  An event from the copy stream would do, but
+    // beside saturated PCIe traffic every cross-stream event wait held the kernels up by tens of microseconds.
+    uint32_t* chunk_flags = nullptr;
+    uint32_t* upload_epoch_host = nullptr;
+    uint32_t upload_epoch = 0;
     std::vector<cudaEvent_t> chunk_events;   // per chunk: input landed, compute done, + 4 stage marks
     bool has_input = false;
     void* output_bf16 = nullptr;    // where the last pass left the bf16 output
@@ -344,6 +350,8 @@ DecoderExecutablePlan::~DecoderExecutablePlan() {
         for (auto& e : impl_->chunk_events)
             if (e) cudaEventDestroy(e);
         if (impl_->copy_in) cudaStreamDestroy(impl_->copy_in);
+        if (impl_->chunk_flags) cudaFree(impl_->chunk_flags);
+        if (impl_->upload_epoch_host) cudaFreeHost(impl_->upload_epoch_host);
         if (impl_->copy_out) cudaStreamDestroy(impl_->copy_out);
         if (impl_->status_host) cudaFreeHost(impl_->status_host);
         if (impl_->len_pinned) cudaFreeHost(impl_->len_pinned);
@@ -867,6 +875,9 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     *m.status_host = 0;
     if (piped) {
         cuda_check(cudaStreamCreateWithFlags(&m.copy_in, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_check(cudaMalloc(reinterpret_cast<void**>(&m.chunk_flags), sizeof(uint32_t) * m.pipeline_chunks), "chunk flags");
+        cuda_check(cudaMemset(m.chunk_flags, 0, sizeof(uint32_t) * m.pipeline_chunks), "chunk flags");
+        cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&m.upload_epoch_host), sizeof(uint32_t), cudaHostAllocDefault), "epoch word");
         cuda_check(cudaStreamCreateWithFlags(&m.copy_out, cudaStreamNonBlocking), "cudaStreamCreate");
         m.chunk_events.resize(static_cast<std::size_t>(m.pipeline_chunks) * 7);
         for (auto& ev : m.chunk_events) cuda_check(cudaEventCreate(&ev), "cudaEventCreate");
@@ -1511,6 +1522,7 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
     const bool stage_marks = result != nullptr;
     cuda_check(cudaEventRecord(t0, s), "event");
     cuda_check(cudaStreamWaitEvent(m.copy_in, t0, 0), "stream wait");
+    *m.upload_epoch_host = ++m.upload_epoch;  // (the call before has ended: it waits for its last event)
     const bool add_residual_here = m.rank == 0;
     for (int ch = 0; ch < chunks; ++ch) {
         cudaEvent_t* ev = &m.chunk_events[static_cast<std::size_t>(ch) * 7];
@@ -1519,8 +1531,10 @@ void DecoderExecutablePlan::execute_pipelined(const float* input, float* output,
         const std::size_t r0 = static_cast<std::size_t>(g0);
         cuda_check(cudaMemcpyAsync(at(m.ws("input_f32"), r0 * row_f32), input + r0 * H, rows * row_f32,
                                    cudaMemcpyHostToDevice, m.copy_in), "input upload");
-        cuda_check(cudaEventRecord(ev[0], m.copy_in), "event");
-        cuda_check(cudaStreamWaitEvent(s, ev[0], 0), "stream wait");
+        cuda_check(cudaMemcpyAsync(m.chunk_flags + ch, m.upload_epoch_host, sizeof(uint32_t), cudaMemcpyHostToDevice, m.copy_in),
+                   "chunk flag");
+        if (ch == 0) cuda_check(cudaEventRecord(ev[0], m.copy_in), "event");  // end of the exposed upload, for the result
+        throw_on(sfb_k_flag_wait(m.chunk_flags + ch, m.upload_epoch, s));
         void* x = at(m.ws("input"), r0 * row_bf);
         void* n1 = m.fold1 ? x : at(m.ws("normalized1"), r0 * row_bf);
         void* attn = at(m.ws("attention"), r0 * static_cast<std::size_t>(m.hidden_l) * 2);

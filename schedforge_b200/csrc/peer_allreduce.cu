@@ -337,6 +337,12 @@ sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* a, sfb_stream st
     return check_launch("peer_reduce_gather");
 }
 
+sfb_status sfb_k_flag_wait(const uint32_t* flag, uint32_t epoch, sfb_stream stream) {
+    SFB_REQUIRE(flag, "flag wait: null flag");
+    peer_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(flag, -1, 1, epoch, device_status_word());
+    return check_launch("flag_wait");
+}
+
 sfb_status sfb_k_peer_wait(const uint32_t* local_flags, int rank, int size, uint32_t epoch, sfb_stream stream) {
     SFB_REQUIRE(local_flags && size >= 2 && size <= SFB_MAX_PEERS && rank >= 0 && rank < size, "peer wait: invalid group");
     peer_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(local_flags, rank, size, epoch, device_status_word());

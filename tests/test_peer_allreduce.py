@@ -158,3 +158,24 @@ def test_two_shot_wait_that_runs_out_reports_and_leaves_the_rows_alone(dev, port
     assert status & 0x100 and float(np.abs(copies[0]).sum()) == 0.0
     want, copies, _, _, counter, status = _run_gather(dev, port, 2, 0, 16, 256, 1, 0, 1)
     assert status & 0x100 and np.array_equal(copies[1][:16], want) and counter == 0
+
+
+def test_flag_wait_returns_for_a_word_a_copy_wrote_and_reports_one_that_nothing_writes(dev):
+    """sfb_k_flag_wait: the kernel stream of sfb_decoder_execute waits with it for "chunk landed" words that the
+    copy stream writes behind each upload.  A word at or past the epoch (wrap-around compare) lets it through; a
+    word that nothing writes ends the bounded wait with status bit 0x100 and the device stays usable."""
+    torch = dev.torch
+    lib = L.load()
+    flags = torch.tensor([7, 0, 0xFFFFFFF0 - (1 << 32)], dtype=torch.int32, device="cuda")
+    word = C.c_uint32(0)
+    L.check(lib.sfb_device_status(C.byref(word)))
+    for index, epoch in ((0, 7), (0, 5), (2, 0xFFFFFFF0), (0, 0xFFFFFFF8)):   # the last one: 7 is past a wrapped epoch
+        L.check(lib.sfb_k_flag_wait(C.c_void_p(flags.data_ptr() + 4 * index), C.c_uint32(epoch), C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    L.check(lib.sfb_device_status(C.byref(word)))
+    assert word.value == 0
+    L.check(lib.sfb_k_flag_wait(C.c_void_p(flags.data_ptr() + 4), C.c_uint32(1), C.c_void_p(dev.stream())))
+    torch.cuda.synchronize()
+    L.check(lib.sfb_device_status(C.byref(word)))
+    assert word.value & 0x100
+    assert lib.sfb_k_flag_wait(None, C.c_uint32(1), C.c_void_p(dev.stream())) != 0
