@@ -451,6 +451,10 @@ typedef struct sfb_compile_options {
                              only this rank's experts/tp_size experts (expert tp_rank * experts/tp_size first), so
                              that a rank never has to materialise the other ranks' expert weights on its host;
                              0 = the full [experts, ...] arrays, of which the rank takes its slice. */
+    int fixed_order;      /* != 0: the weight-streaming GEMMs of plans of at most 128 rows never cut an output tile
+                             between CTAs, so no fp32 partial sums meet at L2 in arrival order: the plan's output is
+                             bitwise the same from run to run.  Slower: the tiles left over after the last full
+                             round of the SMs are then computed by one CTA each.  0: left-over tiles are shared. */
 } sfb_compile_options;
 
 /* DecoderBenchmarkResult, include/schedforge/decoder_compiler.h:119-130 (device-event times). */

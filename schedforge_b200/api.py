@@ -38,11 +38,12 @@ def decoder_config(batch=1, sequence=16, hidden=64, intermediate=128, query_head
 def compile_options(dtype=L.BF16, token_major_attention=True, fuse_epilogues=True, gemm_backend=L.GEMM_AUTO,
                     attention_backend=0, page_tokens=16, tp_rank=0, tp_size=1, seed_block_table=0,
                     no_workspace_reuse=False, no_pipeline=False, append_new_token=False, weight_int8=False,
-                    kv_capacity=0, norm_fusion=None, local_expert_weights=False):
+                    kv_capacity=0, norm_fusion=None, local_expert_weights=False, fixed_order=False):
     return L.CompileOptions(dtype, int(token_major_attention), int(fuse_epilogues), gemm_backend,
                             attention_backend, page_tokens, tp_rank, tp_size, seed_block_table,
                             int(no_workspace_reuse), int(no_pipeline), int(append_new_token), int(weight_int8),
-                            int(kv_capacity), 0 if norm_fusion is None else (1 if norm_fusion else -1), int(local_expert_weights))
+                            int(kv_capacity), 0 if norm_fusion is None else (1 if norm_fusion else -1), int(local_expert_weights),
+                            int(fixed_order))
 
 
 class StableHLOImporter:

@@ -858,7 +858,7 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
         }
         wp.add("expert_output", A * H * e, 10, 11);
     }
-    if (bf && T <= 128)  // partial tile sums of the weight-streaming GEMMs; zero between kernels
+    if (bf && T <= 128 && opt.fixed_order == 0)  // partial tile sums of the weight-streaming GEMMs; zero between kernels
         wp.add("gemm_partials", sfb_gemm_stream_workspace_bytes(std::max({m.qkv_l, H, 2 * I})), 0, 13);
     wp.add("output", TH * e, 11, 13);
     if (bf) wp.add("output_f32", TH * 4, piped ? 0 : (m.direct_f32_output ? 10 : 12), 13);  // written by the last GEMM when direct
@@ -906,8 +906,11 @@ void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* pe
     // the copy-engine all-gather needs whole 128-row tiles per owner (the GEMM that consumes the rows waits per owner)
     const bool can_overlap = can_two_shot && config.ffn == DecoderFFNKind::Dense && (m.T / std::max(1, m.size)) % 128 == 0;
     if (mode == 3 && !can_overlap) throw std::invalid_argument("the overlapped all-gather needs a dense plan with 128-row multiples per rank");
-    // one-shot pushes (size - 1) x the tensor per rank: right for two ranks and for the small outputs of decode plans
-    if (mode == 0) mode = (can_two_shot && m.size > 2 && m.T > 128) ? (can_overlap ? 3 : 2) : 1;
+    // one-shot pushes (size - 1) x the tensor per rank: right for the small outputs of decode plans and for two ranks
+    // of a dense layer; an MoE layer wants the row ownership of the two-shot form at any rank count (its experts then
+    // see only the tokens routed to them instead of every rank's replica of all tokens)
+    const bool moe_rows = config.ffn != DecoderFFNKind::Dense;
+    if (mode == 0) mode = (can_two_shot && m.T > 128 && (m.size > 2 || moe_rows)) ? (can_overlap ? 3 : 2) : 1;
     if (mode == 3 && !m.ce_stream) {
         cuda_check(cudaStreamCreateWithFlags(&m.ce_stream, cudaStreamNonBlocking), "cudaStreamCreate");
         cuda_check(cudaEventCreateWithFlags(&m.ce_ready, cudaEventDisableTiming), "cudaEventCreate");

@@ -84,7 +84,7 @@ class CompileOptions(C.Structure):
                                        "gemm_backend", "attention_backend", "page_tokens", "tp_rank",
                                        "tp_size", "seed_block_table", "no_workspace_reuse", "no_pipeline",
                                        "append_new_token", "weight_int8", "kv_capacity", "norm_fusion",
-                                       "local_expert_weights")]
+                                       "local_expert_weights", "fixed_order")]
 
 
 class PlanCost(C.Structure):

@@ -48,7 +48,7 @@ def test_struct_layouts_match_header(sfb):
     """ctypes mirrors: field counts and sizes follow the C structs (natural alignment)."""
     assert C.sizeof(sfb.DecoderConfig) == 14 * 4
     assert C.sizeof(sfb.DecoderData) == 16 * 8
-    assert C.sizeof(sfb.CompileOptions) == 16 * 4
+    assert C.sizeof(sfb.CompileOptions) == 17 * 4
     assert C.sizeof(sfb.AttentionConfig) == 9 * 4
     assert C.sizeof(sfb.MoeConfig) == 5 * 4
     assert C.sizeof(sfb.GraphSummary) == 7 * 4

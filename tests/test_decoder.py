@@ -328,6 +328,24 @@ def test_pipelined_execute_in_chunks_that_span_sequences_equals_the_one_shot_pla
     one_shot.close()
 
 
+def test_fixed_order_decode_plan_is_bitwise_reproducible(port):
+    """fixed_order: the few-row GEMMs of a decode plan compute every output tile in one CTA (no fp32 partial sums
+    meeting at L2 in arrival order), so repeated runs give the same bits; the default plan of the same layer only
+    promises the bf16 tolerance."""
+    kw = dict(batch=5, sequence=1, hidden=1024, intermediate=1536, query_heads=8, kv_heads=2, head_dim=128,
+              context_sequence=300)
+    oc, c, data = bf16_case(port, 53, **kw)
+    want = port.decoder_layer(oc, data, native=True)
+    plan = api.DecoderCompiler.compile(c, weights_of(data), "", api.compile_options(fixed_order=True))
+    outs = [plan.execute(data["input"])[0] for _ in range(8)]
+    assert all(np.array_equal(o, outs[0]) for o in outs[1:])
+    assert rel_err(outs[0], want) < BF16_TOL
+    plan.close()
+    shared = api.DecoderCompiler.compile(c, weights_of(data))
+    assert rel_err(shared.execute(data["input"])[0], outs[0]) < BF16_TOL / 4
+    shared.close()
+
+
 @pytest.mark.parametrize("kw", [
     dict(batch=5, sequence=1, hidden=1024, intermediate=512, query_heads=8, kv_heads=2, head_dim=128, context_sequence=300),
     dict(batch=1, sequence=96, hidden=512, intermediate=1024, query_heads=8, kv_heads=2, head_dim=64),   # few rows: int8 kept
