@@ -1299,14 +1299,14 @@ int pick_bn(const sfb_gemm_args& g) {
     if (g.epilogue == SFB_EPI_SWIGLU) return 2 * g.swiglu_block;
     if (g.bt_tiled || stream_shape(g)) return 128;
     if (g.n < 256) return 128;
-    // Wave quantisation: the tiles run in rounds of one per SM, so the time is about rounds x tile cost.  A 128-column
-    // tile costs a little more than half a 256-column one (the A tile is re-read for half the work), but a narrow or
-    // short output can need fewer, better filled rounds with it (a sharded QKV projection: 192 wide tiles = 2 rounds,
-    // 384 narrow ones = 3 rounds of half the length).
+    // Wave quantisation: the tiles run in rounds of one per SM, so the time is about rounds x tile cost.  A round of
+    // 128-column tiles measured 0.8 of a round of 256-column tiles (8192 rows; N 768..6144, K 2048..4096: the A tile
+    // is re-read for half the work and the epilogue does not shrink), so the narrow tile only pays where it does not
+    // add rounds: a short or narrow output whose wide tiles leave most SMs idle.
     const long long m_tiles = ceil_div(g.m, BM);
     const long long rounds_wide = ceil_div64(m_tiles * ceil_div(g.n, 256), sm_count());
     const long long rounds_narrow = ceil_div64(m_tiles * ceil_div(g.n, 128), sm_count());
-    return rounds_narrow * 115 < rounds_wide * 200 ? 128 : 256;
+    return rounds_narrow * 160 < rounds_wide * 200 ? 128 : 256;
 }
 
 }  // namespace
