@@ -214,6 +214,8 @@ def time_kernel(kernel, small, head_dim, steps, warmup):
 
     gemm       the fused gate/up projection (tcgen05, SwiGLU epilogue), Llama-3-8B shape
                (small: M=4096, N=16384, K=4096, 224 MB of operands, larger than L2)
+    gemm_shard the O projection of one shard of an 8-way tensor-parallel plan: M=8192, N=4096, K=512, plain store of
+               the partial sums (three rotated outputs of 67 MB; the short K loop leaves the epilogue in charge)
     gemm_decode  the same projection for the 128 rows of a decode step: blocked weights, streamed
                once (small: N=8192; three weight copies are rotated so that L2 does not help)
     attention  headline attention case: causal GQA prefill B4 Hq32 Hkv8 S4096 D128 (small: B1; head_dim 64)
@@ -240,6 +242,27 @@ def time_kernel(kernel, small, head_dim, steps, warmup):
         work, unit, peak, bound = 2.0 * m * n * k, "TFLOP/s", peaks["bf16_tflops"], "tensor"
         name, shape = "gemm_tcgen05_kernel<256>", {"m": m, "n": n, "k": k, "epilogue": "swiglu"}
         l2 = "operands (0.3 GB) exceed the 126 MB L2"
+    elif kernel == "gemm_shard":
+        m, n, k = 8192, 4096, 512
+        a = (torch.randn((m, k), generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+        bt = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+        outs = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+        gs = []
+        for o in outs:
+            g = L.GemmArgs()
+            g.a, g.bt, g.out, g.m, g.n, g.k = a.data_ptr(), bt.data_ptr(), o.data_ptr(), m, n, k
+            g.epilogue, g.backend = L.EPI_STORE, L.GEMM_TCGEN05
+            gs.append(g)
+        keep += outs
+        turn = [0]
+
+        def launch():
+            turn[0] += 1
+            L.check(lib.sfb_k_gemm_bf16(C.byref(gs[turn[0] % 3]), sp))
+        # memory-bound by its output: A and B once, the bf16 result once
+        work, unit, peak, bound = (m * k + n * k + m * n) * 2, "GB/s", peaks["hbm_gbs"], "hbm"
+        name, shape = "gemm_tcgen05_kernel<256>", {"m": m, "n": n, "k": k, "epilogue": "store"}
+        l2 = "three outputs of 67 MB are rotated (201 MB, larger than L2)"
     elif kernel == "gemm_decode":
         # gate/up projection of the decode step: 128 rows, every weight byte read once (HBM-bound)
         m, n, k = 128, (8192 if small else 28672), 4096
@@ -628,7 +651,7 @@ def main():
     ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer", "two-shot", "two-shot-sm", "two-shot-ce"],
                     help="N > 1: all-reduce after the O and Down projections through NCCL, or fused into the GEMM "
                          "epilogues over NVLink peer memory")
-    ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_decode", "attention", "decode"],
+    ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_shard", "gemm_decode", "attention", "decode"],
                     help="time ONE kernel through the kernel ABI instead of the layer (also the ncu target)")
     ap.add_argument("--head-dim", type=int, default=128, choices=[128, 64], help="--kernel attention: head dimension")
     ap.add_argument("--small", action="store_true", help="--kernel: a case small enough for an ncu --set full capture")
