@@ -423,8 +423,9 @@ typedef struct sfb_compile_options {
     int no_workspace_reuse; /* != 0: every intermediate keeps its own bytes (DecoderPlanPolicy::
                                reuse_workspace = false), so tests can read any of them back */
     int no_pipeline;      /* != 0: sfb_decoder_execute copies the whole input, runs, copies the whole output;
-                             0: dense bf16 prefill plans overlap the host copies of one group of sequences
-                             with the computation of another */
+                             0: dense bf16 prefill plans overlap the host copies of one row chunk with the
+                             computation of another (chunks of whole sequences, or, for causal head_dim-128
+                             plans of one shard, row ranges sized to whole rounds of GEMM tiles) */
     int append_new_token; /* decode plans (sequence == 1, context_sequence > 0).  0 = the reference's
                              semantics (src/decoder_compiler.cpp:238-241): RoPE position 0, the new token's
                              K/V are dropped, attention sees the cached context only.  != 0 = a real
@@ -497,7 +498,10 @@ void sfb_decoder_destroy(sfb_decoder_plan* plan);
 /* execute_decoder_layer, src/decoder_compiler.cpp:675-692, one repetition: copies
  * input [T,H] float32 from host, runs the layer, copies output [T,H] float32 back.
  * routing trace (optional, MoE): expert_ids/expert_weights [T*k] and counts [E] replace the
- * router, like DecoderData::routing_trace (include/schedforge/decoder_compiler.h:48). */
+ * router, like DecoderData::routing_trace (include/schedforge/decoder_compiler.h:48).
+ * Dense bf16 prefill plans run the pass in row chunks whose host copies overlap the kernels of other chunks (see
+ * no_pipeline of sfb_compile_options); the numbers equal the one-shot pass.  result == NULL skips the stage marks
+ * between the kernels, which cost the chunked pass a few per cent beside saturated PCIe traffic. */
 sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float* output,
                                const int* trace_expert_ids, const float* trace_expert_weights,
                                const int* trace_counts, sfb_decoder_result* result);
