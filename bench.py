@@ -410,12 +410,12 @@ class Layer:
                     collective = "peer"
                 else:
                     collective = "two-shot"
-            if collective in ("peer", "two-shot", "two-shot-sm", "two-shot-ce", "two-shot-ce2"):
+            if collective in ("peer", "two-shot", "two-shot-sm", "two-shot-ce"):
                 def exchange(handle):
                     handles = [None] * world
                     dist.all_gather_object(handles, handle)
                     return handles
-                self.plan.enable_peer_allreduce(rank, world, exchange, {"peer": 1, "two-shot": 0, "two-shot-sm": 2, "two-shot-ce": 3, "two-shot-ce2": 4}[collective])
+                self.plan.enable_peer_allreduce(rank, world, exchange, {"peer": 1, "two-shot": 0, "two-shot-sm": 2, "two-shot-ce": 3}[collective])
                 dist.barrier()
             self.collective = collective
             for line in self.plan.dump().splitlines():
@@ -429,9 +429,7 @@ class Layer:
                             "sum; dense layers all-gather the rows with copy engines under the next GEMM, MoE layers run "
                             "token-sharded expert parallelism (all-to-all over peer stores)",
                 "two-shot-sm": "row owners pull, sum and all-gather with peer stores from one kernel",
-                "two-shot-ce": "row owners pull and sum; all-gather on copy engines under the next GEMM",
-                "two-shot-ce2": "partial sums travel to the row owners on copy engines under the second half of the GEMM; "
-                                "owners sum local slots; all-gather on copy engines under the next GEMM"}[self.collective]
+                "two-shot-ce": "row owners pull and sum; all-gather on copy engines under the next GEMM"}[self.collective]
 
     def close(self):
         import torch
@@ -439,7 +437,7 @@ class Layer:
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier()
-            if self.collective in ("peer", "two-shot", "two-shot-sm", "two-shot-ce", "two-shot-ce2"):
+            if self.collective in ("peer", "two-shot", "two-shot-sm", "two-shot-ce"):
                 self.plan.disable_peer_allreduce()
         self.plan.close()
 
@@ -488,7 +486,7 @@ def time_layer(layer, args, sampler):
     # e2e: host buffers through the plan call.  With several ranks every rank brings and takes its own rows
     # (sfb_decoder_execute_rows): the whole job still moves the full input and output between host and device
     # each step, 1/N of it per PCIe link.
-    sharded_io = world > 1 and tokens % world == 0 and (layer.workload != "moe" or layer.collective in ("two-shot", "two-shot-sm", "two-shot-ce", "two-shot-ce2"))
+    sharded_io = world > 1 and tokens % world == 0 and (layer.workload != "moe" or layer.collective in ("two-shot", "two-shot-sm", "two-shot-ce"))
     if sharded_io:
         rows = tokens // world
         row0 = rank * rows
@@ -522,7 +520,7 @@ def time_layer(layer, args, sampler):
               "ms_per_step": ms, "tokens_per_s": tokens * 1000.0 / ms,
               "e2e": {"value": tokens * 1000.0 / e2e_ms, "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": args.steps,
                       "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
-                      "io": ("each rank copies its 1/N of the rows; " + ("peer stores gather the input" if layer.collective in ("two-shot", "two-shot-sm", "two-shot-ce", "two-shot-ce2")
+                      "io": ("each rank copies its 1/N of the rows; " + ("peer stores gather the input" if layer.collective in ("two-shot", "two-shot-sm", "two-shot-ce")
                                                                             else "the all-reduce hook gathers the input")) if sharded_io
                       else "whole input and output on every rank"},
               "gpu_launches": int(launches), "collective": layer.collective_text(), "collective_form": layer.form,
@@ -650,7 +648,7 @@ def main():
                     help="fold the RMSNorms into the QKV and gate/up GEMMs instead of stand-alone norm kernels (for A/B runs)")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "int8"],
                     help="int8: per-output-channel weight-only INT8 (the reference's quantized layer); not the default")
-    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer", "two-shot", "two-shot-sm", "two-shot-ce", "two-shot-ce2"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "peer", "two-shot", "two-shot-sm", "two-shot-ce"],
                     help="N > 1: all-reduce after the O and Down projections through NCCL, or fused into the GEMM "
                          "epilogues over NVLink peer memory")
     ap.add_argument("--kernel", default="", choices=["", "gemm", "gemm_shard", "gemm_decode", "attention", "decode"],
@@ -730,7 +728,7 @@ def main():
             record["roofline"] = layer_roofline(name, sub_layer.cfg, world, sub_result, record["ms_per_step"])
             record["parallelism"] = (f"tp{world}" if name == "decode" else
                                      f"attention tp{world}; FFN token-sharded expert parallel ep{world}: local route + dispatch, "
-                                     f"all-to-all dispatch and combine over NVLink peer stores" if sub_layer.collective in ("two-shot", "two-shot-sm", "two-shot-ce", "two-shot-ce2")
+                                     f"all-to-all dispatch and combine over NVLink peer stores" if sub_layer.collective in ("two-shot", "two-shot-sm", "two-shot-ce")
                                      else f"attention tp{world}, experts sharded {world} ways on replicated tokens")
             subs[name] = record
         if world == 1:

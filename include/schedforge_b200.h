@@ -686,10 +686,6 @@ sfb_status sfb_k_peer_wait(const uint32_t* local_flags, int rank, int size, uint
  * chunk, then a 4-byte copy of the epoch), so the stream of kernels needs no event from the copy stream.  Bit 0x100 of
  * sfb_device_status when it gives up. */
 sfb_status sfb_k_flag_wait(const uint32_t* flag, uint32_t epoch, sfb_stream stream);
-/* Stores `value` into count (1..8) flag words, usually in peers' memory, with release semantics at system scope.
- * Enqueued behind peer-to-peer copies on the same stream it announces "the rows have landed" to the kernels that wait
- * for the words (sfb_k_peer_reduce_gather, sfb_k_peer_wait, sfb_k_flag_wait). */
-sfb_status sfb_k_peer_signal(uint32_t* const* flags, int count, uint32_t value, sfb_stream stream);
 
 /* ---- token-sharded expert parallelism: all-to-all dispatch and combine over peer stores --------------------
  * No counterpart in the reference (a single-process library); what must be preserved is the order of its
@@ -773,12 +769,8 @@ sfb_status sfb_decoder_set_peer_allreduce(sfb_decoder_plan* plan, void* local_ba
  * RMSNorm and all-gather the finished rows with peer stores; needs rows % tp_size == 0), mode 3 = the two-shot form
  * with the all-gather moved to copy engines (peer-to-peer copies on a side stream of the plan) so that it runs UNDER
  * the next GEMM, which waits per owner for the rows it has not got yet (sfb_gemm_args.owner_flags; dense plans with
- * 128-row multiples per rank), mode 4 = mode 3 with the reduce-scatter on copy engines too: the O / Down GEMM runs
- * as two launches over row ranges, the finished range of the partial tensor is copied peer to peer into this rank's
- * slot at the row owners while the second range is multiplied, sfb_k_peer_signal announces the delivery and the
- * owners sum local slots.  mode 0 = one-shot for two ranks of a dense layer and for plans of at most 128 rows, else
- * the most overlapped two-shot form the plan admits.  With the two-shot form sfb_decoder_execute_rows gathers the input rows with peer
- * stores as well instead of going through the hook. */
+ * 128-row multiples per rank), mode 0 = mode 3 or 2 for more than two ranks and more than 128 rows, else one-shot.  With the two-shot form sfb_decoder_execute_rows gathers
+ * the input rows with peer stores as well instead of going through the hook. */
 sfb_status sfb_decoder_set_peer_collective(sfb_decoder_plan* plan, void* local_base, void* const* peer_bases, int mode);
 
 /* Tensor-parallel hook: called on the plan's stream after the O projection and after the

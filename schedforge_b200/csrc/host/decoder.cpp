@@ -215,8 +215,7 @@ struct DecoderExecutablePlan::Impl {
     // fetches its rows from them with wide peer loads, which use NVLink far better than 64-byte stores out of a
     // GEMM epilogue), three gathered tensors (layer input, attention_residual, output) that every rank's finish
     // kernel fills on every rank, and the gathered sums of squares of the first two.
-    int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot, 3 = two-shot with the all-gather on copy engines,
-                                   // 4 = 3 with the reduce-scatter on copy engines as well
+    int peer_mode = 0;             // 0 = hook, 1 = one-shot fused all-reduce, 2 = two-shot, 3 = two-shot with the all-gather on copy engines
     // mode 3: after the owner kernel (sum, no gather) the finished rows, their sums of squares and a "rows sent" word
     // go to every peer with peer-to-peer copies on a side stream, i.e. on copy engines, while the next GEMM already
     // runs on the rows it has (it waits per owner, sfb_gemm_args.owner_flags); the pass ends with a wait for the
@@ -224,53 +223,7 @@ struct DecoderExecutablePlan::Impl {
     cudaStream_t ce_stream = nullptr;
     cudaEvent_t ce_ready = nullptr, ce_done = nullptr;
     bool ce_pending = false;
-    bool ce_gather() const { return two_shot() && peer_mode >= 3; }
-    // mode 4: the O / Down GEMM runs as two launches over row ranges; as soon as a range of the partial tensor is
-    // complete, copy engines carry each owner's rows of it into this rank's slot of the owner's receive buffer (the
-    // slots of the one-shot form, unused here) while the second range is still being multiplied; a one-thread kernel
-    // behind the last copy publishes "partial sums delivered" to the owners, whose kernel then sums local slots
-    // instead of pulling rows over NVLink with SM loads.
-    bool ce_scatter() const { return two_shot() && peer_mode == 4; }
-    char* scatter_slot(int r_base, int set, int from) const {  // rows of rank `from` in the receive buffer of rank r_base
-        return peer_base(r_base) + (static_cast<std::size_t>(set) * size + from) * peer_slot_bytes();
-    }
-    // first rows of the two launches: both ranges should fill whole rounds of the SMs with 128 x 256 tiles
-    int scatter_split() const {
-        const int m_tiles = T / 128, per_row = (H + 255) / 256, sms = std::max(1, sm_count());
-        auto rounds = [&](int tiles_m) { return (tiles_m * per_row + sms - 1) / sms; };
-        int best = m_tiles / 2, best_rounds = rounds(best) + rounds(m_tiles - best);
-        for (int first = m_tiles / 2; first <= m_tiles * 3 / 4; ++first) {
-            const int r = rounds(first) + rounds(m_tiles - first);
-            if (r <= best_rounds) { best = first; best_rounds = r; }   // ties: the longer first range (less to send at the end)
-        }
-        return best * 128;
-    }
-    // rows [row0, row1) of partial tensor `set` are complete on stream s: send every other owner its part of them
-    void ce_scatter_push(int set, int row0, int row1, cudaStream_t s) {
-        const int rows_own = T / size;
-        cuda_check(cudaEventRecord(ce_ready, s), "event");
-        cuda_check(cudaStreamWaitEvent(ce_stream, ce_ready, 0), "stream wait");
-        for (int step = 1; step < size; ++step) {
-            const int owner = (rank + step) % size;
-            const int lo = std::max(row0, owner * rows_own), hi = std::min(row1, (owner + 1) * rows_own);
-            if (lo >= hi) continue;
-            const std::size_t row_bytes = static_cast<std::size_t>(H) * 2;
-            cuda_check(cudaMemcpyAsync(scatter_slot(owner, set, rank) + static_cast<std::size_t>(lo - owner * rows_own) * row_bytes,
-                                       peer_local + partial_offset(set) + static_cast<std::size_t>(lo) * row_bytes,
-                                       static_cast<std::size_t>(hi - lo) * row_bytes, cudaMemcpyDeviceToDevice, ce_stream),
-                       "peer copy");
-        }
-        ce_pending = true;
-    }
-    // behind the copies: "partial sums of collective coll delivered" with the epoch the owners' kernels will wait for
-    void ce_scatter_signal(int coll) {
-        uint32_t* flags[SFB_MAX_PEERS];
-        int count = 0;
-        for (int r = 0; r < size; ++r)
-            if (r != rank)
-                flags[count++] = reinterpret_cast<uint32_t*>(peer_remote[r] + flags2_offset()) + coll * 2 * SFB_MAX_PEERS + rank;
-        throw_on(sfb_k_peer_signal(flags, count, gather_epoch[coll] + 1, ce_stream));
-    }
+    bool ce_gather() const { return two_shot() && peer_mode == 3; }
     uint32_t* ce_epoch_word(int coll) const { return reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + 8 + coll; }
     uint32_t* ce_flags(int r, int coll) const {
         return reinterpret_cast<uint32_t*>(peer_base(r) + flags2_offset()) + (5 + coll) * 2 * SFB_MAX_PEERS;
@@ -332,16 +285,13 @@ struct DecoderExecutablePlan::Impl {
     // Owner side of collective `coll` (0 = all-gather of the input rows, 1 = after O, 2 = after Down): sums the slots of
     // set coll - 1 (+ residual rows), writes gathered tensor `coll` and optionally its sums of squares on every rank.
     sfb_status reduce_gather(int coll, const void* source, const float* source_ss, const void* residual, bool with_ss, cudaStream_t s,
-                             int gather = 1, uint32_t* epoch_out = nullptr, bool from_slots = false) {
+                             int gather = 1, uint32_t* epoch_out = nullptr) {
         sfb_peer_gather_args a{};
         const int rows_own = T / size;
         if (coll > 0 && !source) {  // this owner's rows inside every rank's partial tensor of set coll - 1
             a.slots = size;
-            for (int r = 0; r < size; ++r) {
+            for (int r = 0; r < size; ++r)
                 a.pull[r] = peer_base(r) + partial_offset(coll - 1) + static_cast<std::size_t>(rank) * rows_own * H * 2;
-                // ... or where copy engines have put them: the local receive slot of rank r (own rows: the partial tensor)
-                if (from_slots && r != rank) a.pull[r] = scatter_slot(rank, coll - 1, r);
-            }
         }
         a.source = source; a.source_ss = source_ss; a.residual = residual;
         for (int r = 0; r < size; ++r) {
@@ -349,8 +299,6 @@ struct DecoderExecutablePlan::Impl {
             a.ss[r] = with_ss ? reinterpret_cast<float*>(peer_base(r) + ss_offset(coll)) : nullptr;
             if (r != rank)
                 a.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_remote[r] + flags2_offset()) + coll * 2 * SFB_MAX_PEERS + rank;
-            // the copy stream has already announced the delivery: the kernel's own announcement goes to a local sink
-            if (from_slots && r != rank) a.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + 16 + r;
         }
         a.local_flags = reinterpret_cast<uint32_t*>(peer_local + flags2_offset()) + coll * 2 * SFB_MAX_PEERS;
         a.done_counter = reinterpret_cast<uint32_t*>(peer_local + counters_offset()) + coll;
@@ -952,18 +900,18 @@ void DecoderExecutablePlan::set_peer_allreduce(void* local_base, void* const* pe
         m.peer_mode = 0;
         return;
     }
-    if (mode < 0 || mode > 4) throw std::invalid_argument("peer all-reduce: unknown mode");
+    if (mode < 0 || mode > 3) throw std::invalid_argument("peer all-reduce: unknown mode");
     const bool can_two_shot = m.T % std::max(1, m.size) == 0 && m.H % 8 == 0;
     if (mode >= 2 && !can_two_shot) throw std::invalid_argument("two-shot peer all-reduce needs rows divisible by the rank count");
     // the copy-engine all-gather needs whole 128-row tiles per owner (the GEMM that consumes the rows waits per owner)
     const bool can_overlap = can_two_shot && config.ffn == DecoderFFNKind::Dense && (m.T / std::max(1, m.size)) % 128 == 0;
-    if (mode >= 3 && !can_overlap) throw std::invalid_argument("the overlapped all-gather needs a dense plan with 128-row multiples per rank");
+    if (mode == 3 && !can_overlap) throw std::invalid_argument("the overlapped all-gather needs a dense plan with 128-row multiples per rank");
     // one-shot pushes (size - 1) x the tensor per rank: right for the small outputs of decode plans and for two ranks
     // of a dense layer; an MoE layer wants the row ownership of the two-shot form at any rank count (its experts then
     // see only the tokens routed to them instead of every rank's replica of all tokens)
     const bool moe_rows = config.ffn != DecoderFFNKind::Dense;
     if (mode == 0) mode = (can_two_shot && m.T > 128 && (m.size > 2 || moe_rows)) ? (can_overlap ? 3 : 2) : 1;
-    if (mode >= 3 && !m.ce_stream) {
+    if (mode == 3 && !m.ce_stream) {
         cuda_check(cudaStreamCreateWithFlags(&m.ce_stream, cudaStreamNonBlocking), "cudaStreamCreate");
         cuda_check(cudaEventCreateWithFlags(&m.ce_ready, cudaEventDisableTiming), "cudaEventCreate");
         cuda_check(cudaEventCreateWithFlags(&m.ce_done, cudaEventDisableTiming), "cudaEventCreate");
@@ -1059,22 +1007,6 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
     };
     const bool peer = m.size > 1 && m.peer_local != nullptr;
     auto peer_finish = [&](int peer_set, void* buffer, int64_t count) { throw_on(m.peer_finish(peer_set, buffer, 0, count, s)); };
-    // O / Down projection of a two-shot plan: partial sums [T, H] into partial tensor `set` (K = k columns of a); with
-    // the reduce-scatter on copy engines, in two row ranges whose rows leave for their owners as soon as they exist
-    auto scattered_gemm = [&](const void* a, const void* w, int set, int k) {
-        if (!m.ce_scatter()) {
-            gemm(a, w, m.partial(set), T, H, k, SFB_EPI_STORE);
-            return;
-        }
-        const int first = m.scatter_split();
-        const std::size_t e2 = 2;
-        gemm(a, w, m.partial(set), first, H, k, SFB_EPI_STORE);
-        m.ce_scatter_push(set, 0, first, s);
-        gemm(static_cast<const char*>(a) + static_cast<std::size_t>(first) * k * e2, w,
-             static_cast<char*>(m.partial(set)) + static_cast<std::size_t>(first) * H * e2, T - first, H, k, SFB_EPI_STORE);
-        m.ce_scatter_push(set, first, T, s);
-        m.ce_scatter_signal(set + 1);
-    };
 
     // QKV GEMM with the first RMSNorm folded in (1/rms from the sums of squares the input conversion left) and, in an
     // appending decode plan, the new token's K/V written into the paged cache by the same epilogue
@@ -1170,11 +1102,11 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             // the partial tensor stays in this rank's peer-visible memory; every owner fetches its rows from all ranks,
             // adds them up with its rows of the residual stream, takes the sums of squares and hands the finished
             // rows to everybody
-            scattered_gemm(m.ws("attention"), m.wo, 0, m.hidden_l);
+            gemm(m.ws("attention"), m.wo, m.partial(0), T, H, m.hidden_l, SFB_EPI_STORE);
             // (an expert-parallel MoE layer keeps the reduced rows with their owner: its FFN half is token sharded)
             const bool ce = m.ce_gather();
             throw_on(m.reduce_gather(1, nullptr, nullptr, static_cast<const char*>(x) + own_rows_offset, m.fold2, s,
-                                     moe || ce ? 0 : 1, ce ? m.ce_epoch_word(1) : nullptr, m.ce_scatter()));
+                                     moe || ce ? 0 : 1, ce ? m.ce_epoch_word(1) : nullptr));
             if (ce) m.ce_push(1, m.fold2, s);  // the other ranks' rows arrive while the gate/up GEMM runs
         } else if (peer) {
             gemm(m.ws("attention"), m.wo, r1, T, H, m.hidden_l, add_residual_here ? SFB_EPI_RESIDUAL : SFB_EPI_STORE, x, 0,
@@ -1209,10 +1141,10 @@ void DecoderExecutablePlan::run(cudaStream_t s, RoutingTraceView trace, bool sta
             if (m.direct_f32_output) {
                 gemm(m.ws("activation"), m.wd, m.ws("output_f32"), T, H, I, SFB_EPI_RESIDUAL, r1, 0, nullptr, 0, true);
             } else if (two) {
-                scattered_gemm(m.ws("activation"), m.wd, 1, I);
+                gemm(m.ws("activation"), m.wd, m.partial(1), T, H, I, SFB_EPI_STORE);
                 const bool ce = m.ce_gather();
                 throw_on(m.reduce_gather(2, nullptr, nullptr, static_cast<const char*>(r1) + own_rows_offset, false, s, ce ? 0 : 1,
-                                         ce ? m.ce_epoch_word(2) : nullptr, m.ce_scatter()));
+                                         ce ? m.ce_epoch_word(2) : nullptr));
                 if (ce) {  // nothing in this layer reads the gathered output: send it and wait for the peers' rows
                     m.ce_push(2, false, s);
                     throw_on(sfb_k_peer_wait(m.ce_flags(m.rank, 2), m.rank, m.size, m.gather_epoch[2], s));
@@ -1777,7 +1709,7 @@ std::string DecoderExecutablePlan::dump() const {
     out << "}\ndecoder.memory naive=" << naive_bytes << " workspace=" << workspace_bytes << " weights=" << weight_bytes
         << "\ndecoder.shard rank=" << m.rank << " size=" << m.size << " dtype=" << (bf ? "bf16" : "f32") << " collective="
         << (m.size == 1 ? "none" : !m.peer_local ? "hook" : m.peer_mode == 1 ? "peer_one_shot" : m.peer_mode == 2
-                ? "peer_two_shot" : m.peer_mode == 3 ? "peer_two_shot_copy_engine_gather" : "peer_two_shot_copy_engine_scatter_gather")
+                ? "peer_two_shot" : "peer_two_shot_copy_engine_gather")
         << "\nkernels {\n"
         << "  qkv {\n    " << gemm_kind << " m=" << m.T << " n=" << m.qkv_l << " k=" << m.H
         << " epilogue=" << (policy.fuse_epilogues ? "rope_split" : "store") << (m.fold1 ? " prologue=rms_norm_folded" : "")

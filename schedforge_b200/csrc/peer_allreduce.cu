@@ -257,20 +257,6 @@ __global__ void peer_wait_kernel(const uint32_t* flags, int rank, int size, uint
     if (threadIdx.x == 0 && blockIdx.x == 0) wait_peers(flags, rank, size, epoch, status);
 }
 
-// Publishes `value` in up to SFB_MAX_PEERS flag words (peers' memory) with release semantics: placed in a stream
-// behind copy-engine copies, it tells the peers that the copied rows have landed.
-struct SignalParams {
-    uint32_t* flag[SFB_MAX_PEERS];
-    int count;
-    uint32_t value;
-};
-__global__ void peer_signal_kernel(const SignalParams p) {
-    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < p.count) {
-        __threadfence_system();
-        store_release_sys(p.flag[threadIdx.x], p.value);
-    }
-}
-
 }  // namespace
 }  // namespace sfb
 
@@ -349,19 +335,6 @@ sfb_status sfb_k_peer_reduce_gather(const sfb_peer_gather_args* a, sfb_stream st
     const int blocks = std::min((a->rows_own + 7) / 8, sm_count() * 4);
     peer_reduce_gather_kernel<<<blocks, 256, 0, as_stream(stream)>>>(p);
     return check_launch("peer_reduce_gather");
-}
-
-sfb_status sfb_k_peer_signal(uint32_t* const* flags, int count, uint32_t value, sfb_stream stream) {
-    SFB_REQUIRE(flags && count > 0 && count <= SFB_MAX_PEERS, "peer signal: invalid flag list");
-    SignalParams p{};
-    for (int i = 0; i < count; ++i) {
-        SFB_REQUIRE(flags[i] && (reinterpret_cast<uintptr_t>(flags[i]) & 3) == 0, "peer signal: null or misaligned flag");
-        p.flag[i] = flags[i];
-    }
-    p.count = count;
-    p.value = value;
-    peer_signal_kernel<<<1, 32, 0, as_stream(stream)>>>(p);
-    return check_launch("peer_signal");
 }
 
 sfb_status sfb_k_flag_wait(const uint32_t* flag, uint32_t epoch, sfb_stream stream) {

@@ -101,7 +101,6 @@ def main():
         modes = [("one-shot", 1)] + ([("two-shot", 2)] if t_rows % world == 0 and t_rows // world >= 1 else [])
         if not moe and t_rows > 128 and t_rows % world == 0 and (t_rows // world) % 128 == 0:
             modes.append(("two-shot, gather on copy engines under the GEMM", 3))
-            modes.append(("two-shot, scatter and gather on copy engines", 4))
         for mode_name, mode in modes:
             plan.enable_peer_allreduce(rank, world, exchange, mode)
             dist.barrier()
