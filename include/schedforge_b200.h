@@ -505,6 +505,12 @@ void sfb_decoder_destroy(sfb_decoder_plan* plan);
 sfb_status sfb_decoder_execute(sfb_decoder_plan* plan, const float* input, float* output,
                                const int* trace_expert_ids, const float* trace_expert_weights,
                                const int* trace_counts, sfb_decoder_result* result);
+/* The row chunks of that pipelined pass for a causal head_dim-128 plan of one shard with `rows` tokens and `hidden`
+ * columns on a device of sm_count SMs, in blocks of 128 rows (host arithmetic, no device needed): returns the number
+ * of chunks and fills up to `capacity` of them; 0 = the shape is chunked by whole sequences or not at all.  A chunk
+ * is a multiple of the row blocks that fill one round of the SMs with the 128 x 256 output tiles of the O and Down
+ * GEMMs, 4 blocks at the head and 4 + remainder at the tail (rows 8192, hidden 4096, 148 SMs: 4 9 18 18 9 6). */
+int sfb_decoder_row_chunks(int rows, int hidden, int sm_count, int* blocks, int capacity);
 
 /* execute_decoder_layer for a rank of a sharded plan that owns rows [row_begin, row_begin + row_count) of the
  * [T,H] input: only these rows cross this rank's PCIe link (input_rows in, the same rows of the output out).

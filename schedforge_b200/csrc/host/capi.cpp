@@ -202,6 +202,12 @@ sfb_status sfb_decoder_dump(const sfb_decoder_plan* plan, char* buffer, size_t c
     });
 }
 
+int sfb_decoder_row_chunks(int rows, int hidden, int sm_count, int* blocks, int capacity) {
+    const std::vector<int> sizes = sfb::pipelined_row_blocks(rows, hidden, sm_count);
+    for (std::size_t i = 0; blocks && i < sizes.size() && static_cast<int>(i) < capacity; ++i) blocks[i] = sizes[i];
+    return static_cast<int>(sizes.size());
+}
+
 size_t sfb_decoder_peer_bytes(const sfb_decoder_plan* plan) {
     return plan && plan->plan ? plan->plan->peer_bytes() : 0;
 }

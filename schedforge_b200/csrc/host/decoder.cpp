@@ -380,6 +380,32 @@ const float* need(const float* p, const char* name) {
 
 }  // namespace
 
+// Row chunks of the pipelined host-buffer pass, in blocks of 128 rows (empty: the shape takes no row chunks).
+// Chunks are sized for the GEMMs whose output is `hidden` wide (O and Down: 128 x 256 tiles, hidden / 256 per row
+// block): a multiple of `unit` row blocks fills whole rounds of the SMs (9 row blocks x 16 = 144 tiles on 148 SMs at
+// hidden = 4096, where 1536 rows were 192 tiles = two rounds of which the second is a third full).  Nothing overlaps
+// the first upload and the last download, so the first and the last chunk are short; the chunks between them grow
+// and shrink again (the copies run a little faster than the kernels).
+std::vector<int> pipelined_row_blocks(int rows, int hidden, int sms) {
+    if (rows <= 0 || hidden <= 0 || sms <= 0 || rows % 128 != 0 || hidden % 256 != 0) return {};
+    const int unit = sms / (hidden / 256), blocks = rows / 128;
+    if (unit < 2 || blocks < 8 + unit) return {};
+    const int first = 4, last = 4 + (blocks - 8) % unit;
+    const int units = (blocks - first - last) / unit;
+    std::vector<int> sizes{first};
+    if (units <= 2) {
+        for (int i = 0; i < units; ++i) sizes.push_back(unit);
+    } else {
+        sizes.push_back(unit);
+        int left = units - 2;
+        const int group = std::max(2, (left + 5) / 6);
+        for (; left > 0; left -= std::min(group, left)) sizes.push_back(std::min(group, left) * unit);
+        sizes.push_back(unit);
+    }
+    sizes.push_back(last);
+    return sizes;
+}
+
 std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGraph& imported,
                                                                 const DecoderConfig& c,
                                                                 const sfb_decoder_data& data,
@@ -758,29 +784,10 @@ std::unique_ptr<DecoderExecutablePlan> DecoderCompiler::compile(const TensorGrap
     // Causal attention of rows [r0, r1) of a sequence needs its keys [0, r1), which the chunks before have
     // produced, so a chunk may be any row range; only the tensor-core attention kernel takes such slices.
     const bool row_chunks = c.causal && D == 128 && c.sequence % 128 == 0 && plan->policy.attention_backend != 1;
-    if (bf && fused && !moe && !m.decode && opt.no_pipeline == 0 && G == 1 && row_chunks && H % 256 == 0 &&
-        sm_count() / (H / 256) >= 2 && T / 128 >= 8 + sm_count() / (H / 256)) {
-        // Chunks sized for the GEMMs whose output is H wide (O and Down: 128 x 256 tiles, H / 256 per row block):
-        // a multiple of `unit` row blocks fills whole rounds of the SMs (9 row blocks x 16 = 144 tiles on 148 SMs
-        // at H = 4096), where 1536 rows were 192 tiles = two rounds of which the second is a third full.  Nothing
-        // overlaps the first upload and the last download, so the first and the last chunk are short; the chunks
-        // between them grow and shrink again (the copies run a little faster than the kernels).
-        const int unit = sm_count() / (H / 256), blocks = T / 128;
-        const int first = 4, last = 4 + (blocks - 8) % unit;
-        int units = (blocks - first - last) / unit;
-        std::vector<int> sizes{first};
-        if (units <= 2) {
-            for (int i = 0; i < units; ++i) sizes.push_back(unit);
-        } else {
-            sizes.push_back(unit);
-            int left = units - 2;
-            const int group = std::max(2, (left + 5) / 6);
-            for (; left > 0; left -= std::min(group, left)) sizes.push_back(std::min(group, left) * unit);
-            sizes.push_back(unit);
-        }
-        sizes.push_back(last);
+    const std::vector<int> row_blocks = pipelined_row_blocks(T, H, sm_count());
+    if (bf && fused && !moe && !m.decode && opt.no_pipeline == 0 && G == 1 && row_chunks && !row_blocks.empty()) {
         int row = 0;
-        for (int size : sizes) {
+        for (int size : row_blocks) {
             m.pipeline_ranges.push_back({row, size * 128});
             row += size * 128;
         }

@@ -119,6 +119,10 @@ std::unique_ptr<DecoderExecutablePlan> optimize_decoder_plan(
     const float* input, int measurement_budget, int repetitions, sfb_optimization_result* result,
     sfb_plan_candidate* candidates_out, int capacity);
 
+// Row chunks (in blocks of 128 rows) that sfb_decoder_execute pipelines a dense causal prefill pass in; empty when
+// the shape takes none.  Pure arithmetic (decoder.cpp).
+std::vector<int> pipelined_row_blocks(int rows, int hidden, int sms);
+
 class DecoderCompiler {
 public:
     // Throws std::invalid_argument for an invalid configuration or missing fusion patterns.

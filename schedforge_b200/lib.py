@@ -157,7 +157,7 @@ EXPORTS = (
     "sfb_import_stablehlo sfb_import_stablehlo_dump "
     "sfb_decoder_compile sfb_decoder_destroy sfb_decoder_execute sfb_decoder_execute_rows sfb_decoder_upload_input "
     "sfb_decoder_step sfb_decoder_kv_info sfb_decoder_kv_truncate sfb_decoder_kv_release "
-    "sfb_decoder_optimize sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_k_peer_reduce_gather sfb_k_peer_wait sfb_k_flag_wait sfb_k_moe_ep_plan sfb_moe_ep_tables sfb_k_moe_ep_send sfb_k_moe_ep_return sfb_decoder_set_peer_collective sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
+    "sfb_decoder_optimize sfb_decoder_row_chunks sfb_decoder_execute_resident sfb_decoder_download_output sfb_decoder_set_allreduce sfb_decoder_peer_bytes sfb_decoder_set_peer_allreduce sfb_k_peer_allreduce_finish sfb_k_peer_reduce_gather sfb_k_peer_wait sfb_k_flag_wait sfb_k_moe_ep_plan sfb_moe_ep_tables sfb_k_moe_ep_send sfb_k_moe_ep_return sfb_decoder_set_peer_collective sfb_peer_alloc sfb_peer_open sfb_peer_close sfb_peer_free "
     "sfb_decoder_dump sfb_decoder_workspace_bytes sfb_decoder_read_tensor sfb_decoder_stream "
     "sfb_attention_execute sfb_attention_decode "
     "sfb_paged_create sfb_paged_destroy sfb_paged_set_free_pages sfb_paged_append sfb_paged_truncate "

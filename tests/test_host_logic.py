@@ -225,3 +225,27 @@ def test_make_decoder_data_equals_the_reference_generator(sfb, name):
         assert got.shape == z[key].reshape(-1).shape and np.array_equal(got, z[key].reshape(-1)), key
         compared += 1
     assert compared >= 10
+
+
+def test_row_chunks_of_the_pipelined_execute_fill_whole_rounds_of_tiles(sfb):
+    """sfb_decoder_row_chunks: the chunk plan of the host-buffer prefill pass is host arithmetic.  The headline shape
+    (8192 rows, 4096 columns, 148 SMs) runs as 4 9 18 18 9 6 blocks of 128 rows: 9 blocks x 16 tiles = 144 tiles of
+    the O / Down GEMMs per round of 148 SMs, short chunks where nothing overlaps the copies."""
+    lib = sfb.load()
+
+    def chunks(rows, hidden, sms):
+        out = (C.c_int * 64)()
+        n = lib.sfb_decoder_row_chunks(rows, hidden, sms, out, 64)
+        assert lib.sfb_decoder_row_chunks(rows, hidden, sms, None, 0) == n     # the count alone
+        return list(out[:n])
+
+    assert chunks(8192, 4096, 148) == [4, 9, 18, 18, 9, 6]
+    assert chunks(4096, 4096, 148) == [4, 9, 9, 10]          # two sequences of 2048: the third chunk spans both
+    assert chunks(3840, 1792, 148) == [4, 21, 5]             # tests/test_decoder.py: three sequences of 1280
+    assert chunks(2048, 4096, 148) == []                     # too few rows for a middle chunk: whole sequences instead
+    assert chunks(8192, 4100, 148) == [] and chunks(8200, 4096, 148) == [] and chunks(8192, 4096, 0) == []
+    for rows, hidden, sms in [(8192, 4096, 148), (65536, 4096, 148), (16384, 8192, 132), (12288, 2048, 148), (5120, 5120, 148)]:
+        got = chunks(rows, hidden, sms)
+        unit = sms // (hidden // 256)
+        assert sum(got) == rows // 128 and got[0] == 4 and 4 <= got[-1] < 4 + unit and len(got) <= 12
+        assert all(size % unit == 0 for size in got[1:-1])
